@@ -1,0 +1,603 @@
+// Block-table-indexed dense causal attention for sm_100a: tcgen05 MMA with TMEM accumulators,
+// TMA loads whose page coordinate comes from the per-KV-head block table.
+//
+// One CTA owns one KV-head row (b, hkv) and a pair of 128-row query tiles ("A" and "B"). A query
+// tile stacks the G query heads of the KV head along M: tile row i is (token i / G, head i % G),
+// so one K/V stage feeds G heads. K/V are consumed in 128-token steps = two 64-token sub-blocks,
+// each fetched by its own TMA box at (page, token offset) resolved from the block table and the
+// optional page table. Selected past blocks are fully visible; the chunk's own blocks follow in
+// order and are causally masked (bottom-right aligned), which is what
+// compact_attn/kernels/varlen/indexed_dense_prefill_direct_triton.py:155-241 computes.
+//
+// Warp roles (320 threads): warps 0-3 softmax of tile A, warps 4-7 softmax of tile B (thread =
+// TMEM lane = tile row), warp 8 lane 0 issues every tcgen05.mma, warp 9 lane 0 issues every TMA.
+// TMEM (512 columns): S_A | S_B | O_A | O_B, 128 fp32 columns each; P (16-bit) overwrites the
+// first 64 columns of its S and feeds the P.V MMA straight from TMEM.
+// MMA order S_A0 S_B0 { PV_A(j) S_A(j+1) PV_B(j) S_B(j+1) } so one tile's softmax overlaps the
+// other tile's MMAs. Every wait is bounded; on expiry the CTA raises CA_STATUS_TIMEOUT, drains
+// what it issued, frees TMEM and returns.
+#include "ca_common.cuh"
+
+namespace ca {
+namespace attn {
+
+constexpr int kThreads = 320;
+constexpr int kTileM = 128;
+constexpr int kTileN = 128;
+constexpr int kHeadDim = 128;
+constexpr int kSub = 64;               // tokens per TMA box / sub-block
+constexpr int kHalfBytes = 128 * 128;  // one [128 rows][64 x 16-bit] swizzled half tile
+constexpr int kTileBytes = 2 * kHalfBytes;
+constexpr int kBoxBytes = kSub * 128;  // one [64 tokens][64 x 16-bit] box
+constexpr int kStages = 4;
+constexpr int kTmemCols = 512;
+constexpr int kSmemBytes = 2 * kTileBytes + kStages * kTileBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units; lazy accumulator rescale
+
+struct KernelArgs {
+  int Q, G, Hkv, B;
+  int tpt;          // query tokens per 128-row tile = 128 / G
+  int past_blocks;  // Pb
+  int spb;          // 64-token sub-blocks per block
+  int block_size;
+  int past_tokens;  // P
+  int page_size, pages_per_seq, num_pages;
+  const int32_t* block_idx;
+  int block_idx_stride;
+  const int32_t* counts;
+  const int32_t* page_table;
+  void* out;
+  long long o_stride_b, o_stride_t, o_stride_h;
+  float* lse;
+  float scale_log2;
+  int32_t* status;
+  uint32_t idesc_qk, idesc_pv;
+  unsigned long long wait_limit_ns;
+  // K/V tensor-map dimensions 1..3 are ordered by ascending stride at encode time; these give the
+  // coordinate slot (0..2) of the token, page and head coordinates.
+  int slot_tok, slot_page, slot_head;
+};
+
+struct Barriers {
+  uint64_t q_full[2];
+  uint64_t ring_full[kStages];
+  uint64_t ring_empty[kStages];
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t o_done;
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Number of visible columns (0..64) of 64-token sub-block u for chunk token t.
+__device__ __forceinline__ int visible_cols(int u, int n_sub, int n_past_sub, int t) {
+  if (u >= n_sub) return 0;
+  if (u < n_past_sub) return kSub;
+  int lim = t - (u - n_past_sub) * kSub + 1;
+  return lim < 0 ? 0 : (lim > kSub ? kSub : lim);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+    attn_compact_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                        const __grid_constant__ CUtensorMap v_map, const KernelArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_aligned = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  const uint32_t q_smem = smem_base;                      // Q_A, Q_B
+  const uint32_t ring_smem = smem_base + 2 * kTileBytes;  // kStages slots
+  Barriers* bars = reinterpret_cast<Barriers*>(smem_aligned + 2 * kTileBytes + kStages * kTileBytes);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int row = blockIdx.y;  // b * Hkv + hkv
+  const int b = row / a.Hkv;
+  const int hkv = row % a.Hkv;
+  const int mt0 = blockIdx.x * 2;  // first of the two query tiles
+
+  // ---- per-CTA extent of the KV walk ----
+  int count = a.past_blocks;
+  bool bad_index = false;
+  if (a.block_idx != nullptr) {
+    count = a.counts[row];
+    int cap = a.block_idx_stride < a.past_blocks ? a.block_idx_stride : a.past_blocks;
+    if (count < 0 || count > cap) {
+      bad_index = true;
+      count = count < 0 ? 0 : cap;
+    }
+  }
+  const int n_past_sub = count * a.spb;
+  int t_last = (mt0 + 2) * a.tpt - 1;  // last chunk token of tile B
+  if (t_last > a.Q - 1) t_last = a.Q - 1;
+  const int n_sub = n_past_sub + t_last / kSub + 1;
+  const int n_iter = (n_sub + 1) >> 1;
+  volatile int* abort_flag = &bars->abort_flag;
+  const uint64_t limit = a.wait_limit_ns;
+
+  if (tid == 0) {
+    ptx::mbar_init(ptx::smem_u32(&bars->q_full[0]), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->q_full[1]), 1);
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&bars->ring_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->ring_empty[s]), 1);
+    }
+    ptx::mbar_init(ptx::smem_u32(&bars->s_full[0]), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->s_full[1]), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->p_full[0]), 128);
+    ptx::mbar_init(ptx::smem_u32(&bars->p_full[1]), 128);
+    ptx::mbar_init(ptx::smem_u32(&bars->o_done), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->drain), 1);
+    bars->abort_flag = 0;
+    ptx::mbar_fence_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 8) {
+    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 9) {
+    // =============================== TMA producer ===============================
+    bool ok = true;
+    if (lane == 0) {
+      ptx::tma_prefetch_desc(&q_map);
+      ptx::tma_prefetch_desc(&k_map);
+      ptx::tma_prefetch_desc(&v_map);
+      const uint32_t q_bytes = 2u * 128u * static_cast<uint32_t>(a.G * a.tpt);
+      for (int tile = 0; tile < 2; ++tile) {
+        const uint32_t bar = ptx::smem_u32(&bars->q_full[tile]);
+        ptx::mbar_expect_tx(bar, q_bytes);
+        for (int h = 0; h < 2; ++h) {
+          ptx::tma_load_5d(q_smem + tile * kTileBytes + h * kHalfBytes, &q_map, bar, h * 64, 0, hkv,
+                           (mt0 + tile) * a.tpt, b);
+        }
+      }
+    }
+    int n = 0;  // ring entries issued: K0 V0 K1 V1 ...
+    for (int base = 0; base < n_sub && ok; base += 32) {
+      // every lane resolves one sub-block of this batch of 32
+      const int u = base + lane;
+      int page = 0, off = 0;
+      if (u < n_sub) {
+        int tok;
+        if (u < n_past_sub) {
+          const int bi = u / a.spb;
+          int blk = a.block_idx ? a.block_idx[static_cast<long long>(row) * a.block_idx_stride + bi] : bi;
+          if (blk < 0 || blk >= a.past_blocks) {
+            bad_index = true;
+            blk = blk < 0 ? 0 : a.past_blocks - 1;
+          }
+          tok = blk * a.block_size + (u - bi * a.spb) * kSub;
+        } else {
+          tok = a.past_tokens + (u - n_past_sub) * kSub;
+        }
+        const int lp = tok / a.page_size;
+        off = tok - lp * a.page_size;
+        if (a.page_table) {
+          page = (lp < a.pages_per_seq) ? a.page_table[static_cast<long long>(b) * a.pages_per_seq + lp] : -1;
+          if (page < 0 || page >= a.num_pages) {
+            bad_index = true;
+            page = 0;
+          }
+        } else {
+          page = b * a.pages_per_seq + lp;  // beyond the tensor: TMA zero-fills
+        }
+      }
+      for (int i = 0; i < 16 && ok; ++i) {
+        const int j = (base >> 1) + i;
+        if (j >= n_iter) break;
+        const int p0 = __shfl_sync(0xffffffffu, page, 2 * i);
+        const int o0 = __shfl_sync(0xffffffffu, off, 2 * i);
+        const int p1 = __shfl_sync(0xffffffffu, page, 2 * i + 1);
+        const int o1 = __shfl_sync(0xffffffffu, off, 2 * i + 1);
+        const bool two = (2 * j + 1) < n_sub;
+        if (lane == 0) {
+          for (int kv = 0; kv < 2 && ok; ++kv, ++n) {
+            const int slot = n % kStages;
+            const uint32_t phase = (n / kStages) & 1;
+            ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bars->ring_empty[slot]), phase ^ 1u, abort_flag, limit);
+            if (!ok) break;
+            const uint32_t bar = ptx::smem_u32(&bars->ring_full[slot]);
+            const CUtensorMap* map = kv == 0 ? &k_map : &v_map;
+            const uint32_t dst = ring_smem + slot * kTileBytes;
+            ptx::mbar_expect_tx(bar, two ? 4u * kBoxBytes : 2u * kBoxBytes);
+            int c0[3], c1[3];
+            c0[a.slot_tok] = o0, c0[a.slot_page] = p0, c0[a.slot_head] = hkv;
+            c1[a.slot_tok] = o1, c1[a.slot_page] = p1, c1[a.slot_head] = hkv;
+            for (int h = 0; h < 2; ++h) {
+              ptx::tma_load_4d(dst + h * kHalfBytes, map, bar, h * 64, c0[0], c0[1], c0[2]);
+              if (two) ptx::tma_load_4d(dst + h * kHalfBytes + kBoxBytes, map, bar, h * 64, c1[0], c1[1], c1[2]);
+            }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      }
+    }
+    if (!ok && lane == 0) {
+      // drain: give copies already issued a bounded chance to land before the CTA exits
+      for (int e = (n > kStages ? n - kStages : 0); e < n; ++e) {
+        int dummy = 0;
+        ptx::mbar_wait_bounded(ptx::smem_u32(&bars->ring_full[e % kStages]), (e / kStages) & 1, &dummy,
+                               100000000ull);
+      }
+    }
+    if (bad_index && a.status) atomicOr(a.status, CA_STATUS_BAD_INDEX);
+  } else if (warp == 8) {
+    // =============================== MMA issuer ===============================
+    if (lane == 0) {
+      bool ok = true;
+      const uint32_t tS[2] = {tmem + 0u, tmem + 128u};
+      const uint32_t tO[2] = {tmem + 256u, tmem + 384u};
+      auto issue_s = [&](int tile, int slot) {
+        const uint32_t qa = q_smem + tile * kTileBytes;
+        const uint32_t kb = ring_smem + slot * kTileBytes;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t o = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          ptx::mma_ss(tS[tile], ptx::make_smem_desc_sw128(qa + o, 0, 1024),
+                      ptx::make_smem_desc_sw128(kb + o, 0, 1024), a.idesc_qk, k > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int tile, int slot, int ksteps, bool first) {
+        const uint32_t vb = ring_smem + slot * kTileBytes;
+        for (int k = 0; k < ksteps; ++k) {
+          ptx::mma_ts(tO[tile], tS[tile] + k * 8, ptx::make_smem_desc_sw128(vb + k * 2048, kHalfBytes, 1024),
+                      a.idesc_pv, (first && k == 0) ? 0u : 1u);
+        }
+      };
+      auto wait = [&](uint64_t* bar, uint32_t parity) {
+        if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(bar), parity, abort_flag, limit);
+        return ok;
+      };
+      int n = 0;  // ring entries consumed
+      if (wait(&bars->q_full[0], 0) && wait(&bars->q_full[1], 0) && wait(&bars->ring_full[0], 0)) {
+        ptx::tc_fence_after();
+        issue_s(0, 0);
+        ptx::tc_commit(ptx::smem_u32(&bars->s_full[0]));
+        issue_s(1, 0);
+        ptx::tc_commit(ptx::smem_u32(&bars->s_full[1]));
+        ptx::tc_commit(ptx::smem_u32(&bars->ring_empty[0]));
+        n = 1;
+      }
+      for (int j = 0; j < n_iter && ok; ++j) {
+        const int v_slot = n % kStages;
+        const uint32_t v_phase = (n / kStages) & 1;
+        ++n;
+        const bool more = (j + 1) < n_iter;
+        const int k_slot = n % kStages;
+        const uint32_t k_phase = (n / kStages) & 1;
+        if (more) ++n;
+        const int ksteps = ((2 * j + 1) < n_sub) ? 8 : 4;
+        if (!wait(&bars->ring_full[v_slot], v_phase)) break;
+        if (!wait(&bars->p_full[0], j & 1)) break;
+        ptx::tc_fence_after();
+        issue_pv(0, v_slot, ksteps, j == 0);
+        if (more) {
+          if (!wait(&bars->ring_full[k_slot], k_phase)) break;
+          ptx::tc_fence_after();
+          issue_s(0, k_slot);
+          ptx::tc_commit(ptx::smem_u32(&bars->s_full[0]));
+        }
+        if (!wait(&bars->p_full[1], j & 1)) break;
+        ptx::tc_fence_after();
+        issue_pv(1, v_slot, ksteps, j == 0);
+        ptx::tc_commit(ptx::smem_u32(&bars->ring_empty[v_slot]));
+        if (more) {
+          issue_s(1, k_slot);
+          ptx::tc_commit(ptx::smem_u32(&bars->s_full[1]));
+          ptx::tc_commit(ptx::smem_u32(&bars->ring_empty[k_slot]));
+        }
+      }
+      if (ok) {
+        ptx::tc_commit(ptx::smem_u32(&bars->o_done));
+      } else {
+        // drain the tensor pipe (bounded) before TMEM is released
+        ptx::tc_commit(ptx::smem_u32(&bars->drain));
+        int dummy = 0;
+        ptx::mbar_wait_bounded(ptx::smem_u32(&bars->drain), 0, &dummy, 100000000ull);
+      }
+    }
+  } else {
+    // =============================== softmax + epilogue ===============================
+    const int tile = warp >> 2;          // 0: A, 1: B
+    const int r = tid & 127;             // tile row = TMEM lane
+    const int t = (mt0 + tile) * a.tpt + r / a.G;  // chunk token of this row
+    const int g = r % a.G;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + lane_base + tile * 128u;
+    const uint32_t tO = tmem + lane_base + 256u + tile * 128u;
+    const float sc = a.scale_log2;
+    float m_run = -INFINITY;
+    float l_run = 0.f;
+    bool ok = true;
+    uint32_t v[32];
+
+    for (int j = 0; j < n_iter; ++j) {
+      ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bars->s_full[tile]), j & 1, abort_flag, limit);
+      ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the collective TMEM ops
+      if (!ok) break;
+      ptx::tc_fence_after();
+      const bool masked = (2 * j + 1) >= n_past_sub;  // a chunk or tail sub-block is in this step
+      int lim0 = kSub, lim1 = kSub;
+      if (masked) {
+        lim0 = visible_cols(2 * j, n_sub, n_past_sub, t);
+        lim1 = visible_cols(2 * j + 1, n_sub, n_past_sub, t);
+      }
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        ptx::tmem_ld32(tS + c * 32, v);
+        ptx::tc_wait_ld();
+        if (masked) {
+          const int lim = (c < 2 ? lim0 : lim1) - (c & 1) * 32;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, i < lim ? __uint_as_float(v[i]) : -INFINITY);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
+      }
+      // lazy rescale of the running accumulator
+      const float m_new = fmaxf(m_run, mx);
+      const bool need = (m_new - m_run) * sc > kRescaleThreshold;
+      if (__any_sync(0xffffffffu, need)) {
+        const float alpha = need ? ptx::ex2((m_run - m_new) * sc) : 1.0f;
+        if (j > 0) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            ptx::tmem_ld32(tO + c * 32, v);
+            ptx::tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            ptx::tmem_st32(tO + c * 32, v);
+          }
+          ptx::tc_wait_st();
+        }
+        l_run *= alpha;
+        if (need) m_run = m_new;
+      }
+      // pass 2: P = exp2(S*sc - m*sc) -> 16-bit, written over S
+      const float neg_m = -m_run * sc;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        ptx::tmem_ld32(tS + c * 32, v);
+        ptx::tc_wait_ld();
+        uint32_t pk[16];
+        const int lim = masked ? ((c < 2 ? lim0 : lim1) - (c & 1) * 32) : 32;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = ptx::ex2(fmaf(__uint_as_float(v[i]), sc, neg_m));
+          float p1 = ptx::ex2(fmaf(__uint_as_float(v[i + 1]), sc, neg_m));
+          if (masked) {
+            p0 = i < lim ? p0 : 0.f;
+            p1 = (i + 1) < lim ? p1 : 0.f;
+          }
+          l_run += p0 + p1;
+          pk[i >> 1] = pack2<T>(p0, p1);
+        }
+        ptx::tmem_st16(tS + c * 16, pk);
+      }
+      ptx::tc_wait_st();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(ptx::smem_u32(&bars->p_full[tile]));
+    }
+
+    if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bars->o_done), 0, abort_flag, limit);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      ptx::tc_fence_after();
+      const bool live = (r < a.tpt * a.G) && (t < a.Q);
+      const float inv_l = 1.0f / l_run;
+      T* orow = reinterpret_cast<T*>(a.out) + b * a.o_stride_b + static_cast<long long>(t) * a.o_stride_t +
+                static_cast<long long>(hkv * a.G + g) * a.o_stride_h;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        ptx::tmem_ld32(tO + c * 32, v);
+        ptx::tc_wait_ld();
+        if (live) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack2<T>(__uint_as_float(v[i + 0]) * inv_l, __uint_as_float(v[i + 1]) * inv_l);
+            w.y = pack2<T>(__uint_as_float(v[i + 2]) * inv_l, __uint_as_float(v[i + 3]) * inv_l);
+            w.z = pack2<T>(__uint_as_float(v[i + 4]) * inv_l, __uint_as_float(v[i + 5]) * inv_l);
+            w.w = pack2<T>(__uint_as_float(v[i + 6]) * inv_l, __uint_as_float(v[i + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+          }
+        }
+      }
+      if (live && a.lse) {
+        a.lse[(static_cast<long long>(b) * (a.Hkv * a.G) + hkv * a.G + g) * a.Q + t] =
+            0.6931471805599453f * (m_run * sc + log2f(l_run));
+      }
+    }
+  }
+
+  // ---- teardown: every thread arrives here on every path ----
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, kTmemCols);
+  }
+  if (tid == 0 && bars->abort_flag && a.status) atomicOr(a.status, CA_STATUS_TIMEOUT);
+}
+
+static int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const cuuint64_t* dims,
+                      const cuuint64_t* strides_bytes, const cuuint32_t* box, const char* what) {
+  tensor_map_encode_fn enc = get_tensor_map_encoder();
+  if (!enc) return fail(CA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
+  CUresult res = enc(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), dims, strides_bytes, box,
+                     elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) return fail(CA_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)res);
+  return CA_OK;
+}
+
+static int validate(const ca_attn_params* p) {
+  CA_REQUIRE(p != nullptr, "params is null");
+  CA_REQUIRE(p->q && p->out && p->kv.k && p->kv.v, "q, out, kv.k and kv.v must be non-null");
+  CA_REQUIRE(p->D == kHeadDim, "head dim must be 128, got %d", p->D);
+  CA_REQUIRE(p->dtype == CA_DTYPE_BF16 || p->dtype == CA_DTYPE_F16, "dtype must be bf16 or f16");
+  CA_REQUIRE(p->B > 0 && p->Q > 0 && p->Hq > 0 && p->Hkv > 0, "B, Q, Hq, Hkv must be positive");
+  CA_REQUIRE(p->Hq % p->Hkv == 0, "Hq (%d) must be a multiple of Hkv (%d)", p->Hq, p->Hkv);
+  CA_REQUIRE(p->Hq / p->Hkv <= 128, "GQA group larger than 128 is not supported");
+  CA_REQUIRE(p->block_size > 0 && p->block_size % kSub == 0, "block_size must be a positive multiple of 64");
+  CA_REQUIRE(p->kv_len >= p->Q, "kv_len (%d) must be >= Q (%d)", p->kv_len, p->Q);
+  CA_REQUIRE((p->kv_len - p->Q) % p->block_size == 0, "past length must be a multiple of block_size");
+  CA_REQUIRE(p->kv.page_size > 0 && p->kv.page_size % kSub == 0, "page_size must be a positive multiple of 64");
+  CA_REQUIRE(p->kv.num_pages > 0 && p->kv.pages_per_seq > 0, "num_pages and pages_per_seq must be positive");
+  CA_REQUIRE((long long)p->kv.pages_per_seq * p->kv.page_size >= p->kv_len,
+             "pages_per_seq*page_size (%lld) does not cover kv_len (%d)",
+             (long long)p->kv.pages_per_seq * p->kv.page_size, p->kv_len);
+  CA_REQUIRE(p->kv.page_stride % 8 == 0 && p->kv.token_stride % 8 == 0 && p->kv.head_stride % 8 == 0,
+             "kv strides must be multiples of 8 elements (16 bytes)");
+  CA_REQUIRE(p->q_stride_b % 8 == 0 && p->q_stride_t % 8 == 0 && p->q_stride_h % 8 == 0,
+             "q strides must be multiples of 8 elements (16 bytes)");
+  CA_REQUIRE(p->o_stride_b % 8 == 0 && p->o_stride_t % 8 == 0 && p->o_stride_h % 8 == 0,
+             "out strides must be multiples of 8 elements (16 bytes)");
+  CA_REQUIRE((reinterpret_cast<uintptr_t>(p->q) | reinterpret_cast<uintptr_t>(p->out) |
+              reinterpret_cast<uintptr_t>(p->kv.k) | reinterpret_cast<uintptr_t>(p->kv.v)) % 16 == 0,
+             "q, out, k, v must be 16-byte aligned");
+  if (p->block_idx) {
+    CA_REQUIRE(p->counts != nullptr, "counts is required with block_idx");
+    CA_REQUIRE(p->block_idx_stride > 0 || p->kv_len == p->Q, "block_idx_stride must be positive");
+  }
+  return CA_OK;
+}
+
+}  // namespace attn
+}  // namespace ca
+
+extern "C" {
+
+int ca_attn_workspace_bytes(const ca_attn_params* p, size_t* bytes_out) {
+  using namespace ca;
+  CA_REQUIRE(bytes_out != nullptr, "bytes_out is null");
+  int rc = attn::validate(p);
+  if (rc != CA_OK) return rc;
+  *bytes_out = 0;
+  return CA_OK;
+}
+
+int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
+  using namespace ca;
+  using namespace ca::attn;
+  int rc = validate(p);
+  if (rc != CA_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  DeviceInfo dev;
+  rc = get_device_info(&dev);
+  if (rc != CA_OK) return rc;
+  if (dev.cc_major != 10) return fail(CA_ERR_UNSUPPORTED, "this library targets sm_100a; device is sm_%d%d", dev.cc_major, dev.cc_minor);
+
+  const int G = p->Hq / p->Hkv;
+  const int tpt = kTileM / G;
+  const int n_mtiles = ceil_div(p->Q, tpt);
+  const CUtensorMapDataType dt = p->dtype == CA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+
+  CUtensorMap q_map, k_map, v_map;
+  int slot_tok = 0, slot_page = 1, slot_head = 2;
+  {
+    // (d, g, hkv, token, batch): the box walks g fastest, then tokens, so tile row = token*G + g
+    cuuint64_t dims[5] = {(cuuint64_t)kHeadDim, (cuuint64_t)G, (cuuint64_t)p->Hkv, (cuuint64_t)p->Q, (cuuint64_t)p->B};
+    cuuint64_t strides[4] = {(cuuint64_t)p->q_stride_h * 2, (cuuint64_t)p->q_stride_h * G * 2,
+                             (cuuint64_t)p->q_stride_t * 2, (cuuint64_t)p->q_stride_b * 2};
+    cuuint32_t box[5] = {64, (cuuint32_t)G, 1, (cuuint32_t)tpt, 1};
+    rc = encode_map(&q_map, dt, 5, p->q, dims, strides, box, "q");
+    if (rc != CA_OK) return rc;
+  }
+  {
+    // roles: 0 token-in-page, 1 page, 2 head; outer dimensions sorted by ascending stride
+    const cuuint64_t role_dim[3] = {(cuuint64_t)p->kv.page_size, (cuuint64_t)p->kv.num_pages, (cuuint64_t)p->Hkv};
+    const cuuint64_t role_stride[3] = {(cuuint64_t)p->kv.token_stride * 2, (cuuint64_t)p->kv.page_stride * 2,
+                                       (cuuint64_t)p->kv.head_stride * 2};
+    const cuuint32_t role_box[3] = {64, 1, 1};
+    int order[3] = {0, 1, 2};
+    for (int i = 0; i < 3; ++i)
+      for (int j = i + 1; j < 3; ++j)
+        if (role_stride[order[j]] < role_stride[order[i]]) { int t = order[i]; order[i] = order[j]; order[j] = t; }
+    cuuint64_t dims[4] = {(cuuint64_t)kHeadDim, 0, 0, 0};
+    cuuint64_t strides[3];
+    cuuint32_t box[4] = {64, 0, 0, 0};
+    int slot_of_role[3];
+    for (int i = 0; i < 3; ++i) {
+      dims[i + 1] = role_dim[order[i]];
+      strides[i] = role_stride[order[i]];
+      box[i + 1] = role_box[order[i]];
+      slot_of_role[order[i]] = i;
+    }
+    slot_tok = slot_of_role[0], slot_page = slot_of_role[1], slot_head = slot_of_role[2];
+    rc = encode_map(&k_map, dt, 4, p->kv.k, dims, strides, box, "k");
+    if (rc != CA_OK) return rc;
+    rc = encode_map(&v_map, dt, 4, p->kv.v, dims, strides, box, "v");
+    if (rc != CA_OK) return rc;
+  }
+
+  KernelArgs a;
+  a.Q = p->Q;
+  a.G = G;
+  a.Hkv = p->Hkv;
+  a.B = p->B;
+  a.tpt = tpt;
+  a.block_size = p->block_size;
+  a.past_tokens = p->kv_len - p->Q;
+  a.past_blocks = a.past_tokens / p->block_size;
+  a.spb = p->block_size / kSub;
+  a.page_size = p->kv.page_size;
+  a.pages_per_seq = p->kv.pages_per_seq;
+  a.num_pages = p->kv.num_pages;
+  a.block_idx = p->block_idx;
+  a.block_idx_stride = p->block_idx_stride;
+  a.counts = p->counts;
+  a.page_table = p->kv.page_table;
+  a.out = p->out;
+  a.o_stride_b = p->o_stride_b;
+  a.o_stride_t = p->o_stride_t;
+  a.o_stride_h = p->o_stride_h;
+  a.lse = p->lse;
+  a.scale_log2 = p->softmax_scale * 1.4426950408889634f;
+  a.status = p->status;
+  const uint32_t fmt = p->dtype == CA_DTYPE_BF16 ? 1u : 0u;
+  a.idesc_qk = ptx::make_idesc_f16(fmt, kTileM, kTileN, 0, 0);
+  a.idesc_pv = ptx::make_idesc_f16(fmt, kTileM, kHeadDim, 0, 1);
+  a.wait_limit_ns = 2000000000ull;
+  a.slot_tok = slot_tok;
+  a.slot_page = slot_page;
+  a.slot_head = slot_head;
+
+  dim3 grid(ceil_div(n_mtiles, 2), p->B * p->Hkv);
+  // the opt-in shared-memory size is a per-device function attribute; setting it is cheap
+  if (p->dtype == CA_DTYPE_BF16) {
+    CA_CUDA(cudaFuncSetAttribute(attn_compact_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    attn_compact_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(q_map, k_map, v_map, a);
+  } else {
+    CA_CUDA(cudaFuncSetAttribute(attn_compact_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    attn_compact_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(q_map, k_map, v_map, a);
+  }
+  CA_LAUNCH_CHECK("attn_compact_kernel");
+  return CA_OK;
+}
+
+}  // extern "C"

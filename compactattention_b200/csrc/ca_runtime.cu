@@ -1,0 +1,64 @@
+// Host-side runtime shared by every entry point: thread-local error text, launch accounting,
+// driver entry-point resolution and cached device properties.
+#include "ca_common.cuh"
+
+#include <mutex>
+
+namespace ca {
+
+char* last_error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+std::atomic<long long>& launch_counter() {
+  static std::atomic<long long> counter{0};
+  return counter;
+}
+
+tensor_map_encode_fn get_tensor_map_encoder() {
+  static std::once_flag once;
+  static tensor_map_encode_fn fn = nullptr;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres);
+    if (err == cudaSuccess && qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<tensor_map_encode_fn>(sym);
+    }
+  });
+  return fn;
+}
+
+int get_device_info(DeviceInfo* out) {
+  static std::mutex mu;
+  static DeviceInfo cache[64];
+  static bool have[64] = {false};
+  int dev = 0;
+  CA_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(CA_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!have[dev]) {
+    DeviceInfo info;
+    CA_CUDA(cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    CA_CUDA(cudaDeviceGetAttribute(&info.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    CA_CUDA(cudaDeviceGetAttribute(&info.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    CA_CUDA(cudaDeviceGetAttribute(&info.cc_minor, cudaDevAttrComputeCapabilityMinor, dev));
+    cache[dev] = info;
+    have[dev] = true;
+  }
+  *out = cache[dev];
+  return CA_OK;
+}
+
+}  // namespace ca
+
+extern "C" {
+
+const char* ca_last_error(void) { return ca::last_error_buffer(); }
+
+int ca_abi_version(void) { return 1; }
+
+int64_t ca_launch_count(void) { return ca::launch_counter().load(std::memory_order_relaxed); }
+
+}  // extern "C"
