@@ -54,6 +54,123 @@ class AttnParams(C.Structure):
     ]
 
 
+class SelectParams(C.Structure):
+    _fields_ = [
+        ("score", C.c_void_p),
+        ("score_stride_b", C.c_int64), ("score_stride_h", C.c_int64), ("score_stride_q", C.c_int64), ("score_stride_k", C.c_int64),
+        ("score_dtype", C.c_int32),
+        ("rule", C.c_int32),
+        ("valid", C.c_void_p),
+        ("valid_stride_b", C.c_int64), ("valid_stride_h", C.c_int64), ("valid_stride_q", C.c_int64), ("valid_stride_k", C.c_int64),
+        ("bits", C.c_void_p),
+        ("prob_out", C.c_void_p),
+        ("B", C.c_int32), ("H", C.c_int32), ("Qb", C.c_int32), ("Kb", C.c_int32), ("Pb", C.c_int32),
+        ("softmax", C.c_int32),
+        ("threshold", C.c_float),
+        ("alpha", C.c_float),
+        ("topk_k", C.c_int32), ("topk_num", C.c_int32), ("topk_den", C.c_int32),
+        ("min_budget", C.c_int32),
+        ("sink", C.c_int32), ("local", C.c_int32),
+        ("rows_voting", C.c_int32),
+    ]
+
+
+class UnionParams(C.Structure):
+    _fields_ = [
+        ("bits", C.c_void_p),
+        ("mask", C.c_void_p),
+        ("mask_stride_b", C.c_int64), ("mask_stride_h", C.c_int64), ("mask_stride_q", C.c_int64), ("mask_stride_k", C.c_int64),
+        ("B", C.c_int32), ("Hkv", C.c_int32), ("G", C.c_int32), ("Qin", C.c_int32), ("Kb", C.c_int32), ("Pb", C.c_int32),
+        ("keep_recent", C.c_int32),
+        ("block_size", C.c_int32), ("page_size", C.c_int32),
+        ("block_idx", C.c_void_p),
+        ("idx_stride", C.c_int32),
+        ("counts", C.c_void_p),
+        ("cache_seqlens", C.c_void_p),
+        ("pages_per_row", C.c_void_p),
+        ("keep_kv", C.c_void_p),
+    ]
+
+
+class PoolParams(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p),
+        ("x_stride_b", C.c_int64), ("x_stride_t", C.c_int64), ("x_stride_h", C.c_int64),
+        ("x_dtype", C.c_int32),
+        ("out_dtype", C.c_int32),
+        ("out", C.c_void_p),
+        ("out_stride_b", C.c_int64), ("out_stride_blk", C.c_int64), ("out_stride_h", C.c_int64),
+        ("out_block_offset", C.c_int32),
+        ("B", C.c_int32), ("L", C.c_int32), ("H", C.c_int32), ("D", C.c_int32), ("block_size", C.c_int32),
+        ("kinds", C.c_int32),
+    ]
+
+
+class ProjectParams(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p),
+        ("w", C.c_void_p),
+        ("w_dtype", C.c_int32),
+        ("out_dtype", C.c_int32),
+        ("cos", C.c_void_p),
+        ("sin", C.c_void_p),
+        ("rope_batch", C.c_int32),
+        ("out_block_offset", C.c_int32),
+        ("out", C.c_void_p),
+        ("out_stride_b", C.c_int64), ("out_stride_blk", C.c_int64), ("out_stride_h", C.c_int64),
+        ("B", C.c_int32), ("nb", C.c_int32), ("Hin", C.c_int32), ("Hout", C.c_int32), ("Cin", C.c_int32), ("Cout", C.c_int32),
+    ]
+
+
+class GateScoreParams(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p),
+        ("q_stride_b", C.c_int64), ("q_stride_blk", C.c_int64), ("q_stride_h", C.c_int64),
+        ("k", C.c_void_p),
+        ("k_stride_b", C.c_int64), ("k_stride_blk", C.c_int64), ("k_stride_h", C.c_int64),
+        ("q_dtype", C.c_int32), ("k_dtype", C.c_int32),
+        ("out", C.c_void_p),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hk", C.c_int32), ("Qb", C.c_int32), ("Kb", C.c_int32), ("Pb", C.c_int32), ("C", C.c_int32),
+        ("scale", C.c_float),
+        ("masked_value", C.c_float),
+    ]
+
+
+class FlashPrefillScoreParams(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p),
+        ("q_stride_b", C.c_int64), ("q_stride_t", C.c_int64), ("q_stride_h", C.c_int64),
+        ("mean_k", C.c_void_p),
+        ("k_stride_b", C.c_int64), ("k_stride_blk", C.c_int64), ("k_stride_h", C.c_int64),
+        ("q_dtype", C.c_int32), ("k_dtype", C.c_int32),
+        ("score_raw", C.c_void_p),
+        ("max_raw", C.c_void_p),
+        ("score_norm", C.c_void_p),
+        ("B", C.c_int32), ("Q", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("D", C.c_int32), ("Kb", C.c_int32),
+        ("block_size", C.c_int32), ("kv_len", C.c_int32),
+    ]
+
+
+class GatherParams(C.Structure):
+    _fields_ = [
+        ("kv", KvLayout),
+        ("block_idx", C.c_void_p),
+        ("counts", C.c_void_p),
+        ("block_idx_stride", C.c_int32),
+        ("dtype", C.c_int32),
+        ("page_offsets", C.c_void_p),
+        ("dst_row_stride_tokens", C.c_int64),
+        ("k_dst", C.c_void_p),
+        ("v_dst", C.c_void_p),
+        ("dst_page_size", C.c_int32),
+        ("B", C.c_int32), ("Hkv", C.c_int32), ("D", C.c_int32), ("Q", C.c_int32), ("kv_len", C.c_int32), ("block_size", C.c_int32),
+        ("status", C.c_void_p),
+    ]
+
+
+CA_RULE_THRESHOLD, CA_RULE_ALPHA_ROWMAX, CA_RULE_TOPK, CA_RULE_CUMMASS, CA_RULE_MASK = 0, 1, 2, 3, 4
+CA_POOL_MAX, CA_POOL_MIN, CA_POOL_AVG = 1, 2, 4
+
 # name -> (restype, argtypes); filled in below and applied by load().
 _SIGNATURES = {
     "ca_last_error": (C.c_char_p, []),
@@ -61,6 +178,14 @@ _SIGNATURES = {
     "ca_launch_count": (C.c_int64, []),
     "ca_attn_workspace_bytes": (C.c_int, [C.POINTER(AttnParams), C.POINTER(C.c_size_t)]),
     "ca_attn_compact": (C.c_int, [C.POINTER(AttnParams), C.c_void_p]),
+    "ca_select_rows": (C.c_int, [C.POINTER(SelectParams), C.c_void_p]),
+    "ca_union_table": (C.c_int, [C.POINTER(UnionParams), C.c_void_p]),
+    "ca_paged_metadata": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "ca_pool_blocks": (C.c_int, [C.POINTER(PoolParams), C.c_void_p]),
+    "ca_gate_project": (C.c_int, [C.POINTER(ProjectParams), C.c_void_p]),
+    "ca_gate_scores": (C.c_int, [C.POINTER(GateScoreParams), C.c_void_p]),
+    "ca_flashprefill_score": (C.c_int, [C.POINTER(FlashPrefillScoreParams), C.c_void_p]),
+    "ca_gather_kv": (C.c_int, [C.POINTER(GatherParams), C.c_void_p]),
 }
 
 _lib = None

@@ -1,0 +1,486 @@
+// Block scoring for the two selectors.
+//   learned gate (SeerAttention AttnGate): block pooling (max / min / avg) of the chunk's Q and K,
+//     per-head linear projection, block RoPE, append to the gate's K-block cache, then
+//     logits = q_block . k_block * scale for every cached key block;
+//   training-free (FlashPrefill): per-block mean of K, per-token Q x mean-K block score with
+//     per-block max / sum-exp2, and the row normalisation.
+// All of it is small, HBM/launch-bound work on CUDA cores: 128-bit loads, fp32 accumulation,
+// warp-shuffle reductions.
+#include "ca_common.cuh"
+
+namespace ca {
+namespace score {
+
+__device__ __forceinline__ float load_elem(const void* base, long long off, int dtype) {
+  if (dtype == CA_DTYPE_F32) return reinterpret_cast<const float*>(base)[off];
+  if (dtype == CA_DTYPE_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[off]);
+  return __half2float(reinterpret_cast<const __half*>(base)[off]);
+}
+__device__ __forceinline__ void store_elem(void* base, long long off, int dtype, float v) {
+  if (dtype == CA_DTYPE_F32) reinterpret_cast<float*>(base)[off] = v;
+  else if (dtype == CA_DTYPE_BF16) reinterpret_cast<__nv_bfloat16*>(base)[off] = __float2bfloat16_rn(v);
+  else reinterpret_cast<__half*>(base)[off] = __float2half_rn(v);
+}
+// 8 consecutive elements starting at off (16-byte aligned for 16-bit types, 32-byte for f32).
+__device__ __forceinline__ void load8(const void* base, long long off, int dtype, float (&v)[8]) {
+  if (dtype == CA_DTYPE_F32) {
+    const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off);
+    const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off + 4);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+  } else {
+    const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + off);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (dtype == CA_DTYPE_BF16) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      } else {
+        const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+        v[2 * i] = __low2float(h);
+        v[2 * i + 1] = __high2float(h);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Block pooling: x [B,L,H,D] -> out [B, blocks, H, nk*D] at block offset, channel order max|min|avg
+// ------------------------------------------------------------------------------------------
+struct PoolArgs {
+  const void* x;
+  long long x_b, x_t, x_h;
+  int x_dtype;
+  void* out;
+  long long o_b, o_blk, o_h;
+  int o_dtype;
+  int out_block_offset;
+  int B, L, H, D, bs;
+  int kinds;  // bit 0 max, bit 1 min, bit 2 avg
+};
+
+constexpr int kPoolThreads = 128;
+
+__global__ void __launch_bounds__(kPoolThreads) pool_blocks_kernel(const PoolArgs a) {
+  // thread = (token phase, 8-dim group); D/8 groups, kPoolThreads/(D/8) phases
+  extern __shared__ float pool_smem[];  // [3][phases][D]
+  const int groups = a.D / 8;
+  const int phases = kPoolThreads / groups;
+  const int grp = threadIdx.x % groups, ph = threadIdx.x / groups;
+  const int blk = blockIdx.x;
+  const int h = blockIdx.y % a.H, b = blockIdx.y / a.H;
+  const int t0 = blk * a.bs;
+  const int t1 = min(t0 + a.bs, a.L);
+  float mx[8], mn[8], sm[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) mx[i] = -INFINITY, mn[i] = INFINITY, sm[i] = 0.f;
+  if (ph < phases) {
+    for (int t = t0 + ph; t < t1; t += phases) {
+      float v[8];
+      load8(a.x, b * a.x_b + t * a.x_t + h * a.x_h + grp * 8, a.x_dtype, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx[i] = fmaxf(mx[i], v[i]), mn[i] = fminf(mn[i], v[i]), sm[i] += v[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      pool_smem[(0 * phases + ph) * a.D + grp * 8 + i] = mx[i];
+      pool_smem[(1 * phases + ph) * a.D + grp * 8 + i] = mn[i];
+      pool_smem[(2 * phases + ph) * a.D + grp * 8 + i] = sm[i];
+    }
+  }
+  __syncthreads();
+  const float inv_cnt = 1.0f / static_cast<float>(t1 - t0);
+  const long long obase = b * a.o_b + static_cast<long long>(a.out_block_offset + blk) * a.o_blk + h * a.o_h;
+  for (int d = threadIdx.x; d < a.D; d += kPoolThreads) {
+    float rmx = -INFINITY, rmn = INFINITY, rsm = 0.f;
+    for (int p = 0; p < phases; ++p) {
+      rmx = fmaxf(rmx, pool_smem[(0 * phases + p) * a.D + d]);
+      rmn = fminf(rmn, pool_smem[(1 * phases + p) * a.D + d]);
+      rsm += pool_smem[(2 * phases + p) * a.D + d];
+    }
+    int c = 0;
+    if (a.kinds & 1) store_elem(a.out, obase + (c++) * a.D + d, a.o_dtype, rmx);
+    if (a.kinds & 2) store_elem(a.out, obase + (c++) * a.D + d, a.o_dtype, rmn);
+    if (a.kinds & 4) store_elem(a.out, obase + (c++) * a.D + d, a.o_dtype, rsm * inv_cnt);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Per-head linear + block RoPE + append: x [B,nb,Hin,Cin] (f32) * W [Hout,Cin,Cout] -> out
+// ------------------------------------------------------------------------------------------
+struct ProjArgs {
+  const float* x;  // pooled blocks, contiguous [B, nb, Hin, Cin]
+  const void* w;   // [Hout, Cin, Cout] contiguous or NULL (identity, Cin == Cout, Hout == Hin)
+  int w_dtype;
+  const float* cos;  // optional [Bc, nb, Cout] (Bc = 1 or B), half-rotation tables; NULL = no RoPE
+  const float* sin;
+  int rope_batch;    // Bc
+  void* out;
+  long long o_b, o_blk, o_h;
+  int o_dtype;
+  int out_block_offset;
+  int B, nb, Hin, Hout, Cin, Cout;
+};
+
+constexpr int kProjBlocks = 8;  // blocks handled per CTA
+
+__global__ void proj_rope_kernel(const ProjArgs a) {
+  extern __shared__ float proj_smem[];  // x tile [kProjBlocks][Cin] then exchange [kProjBlocks][Cout]
+  float* xs = proj_smem;
+  float* ys = proj_smem + kProjBlocks * a.Cin;
+  const int blk0 = blockIdx.x * kProjBlocks;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hin = h / (a.Hout / a.Hin);  // kv head repeated up to the weight's head count
+  const int nblk = min(kProjBlocks, a.nb - blk0);
+  for (int e = threadIdx.x; e < nblk * a.Cin; e += blockDim.x) {
+    const int r = e / a.Cin, c = e % a.Cin;
+    xs[r * a.Cin + c] = a.x[((static_cast<long long>(b) * a.nb + blk0 + r) * a.Hin + hin) * a.Cin + c];
+  }
+  __syncthreads();
+  for (int o = threadIdx.x; o < a.Cout; o += blockDim.x) {
+    float acc[kProjBlocks];
+#pragma unroll
+    for (int r = 0; r < kProjBlocks; ++r) acc[r] = 0.f;
+    if (a.w) {
+      for (int c = 0; c < a.Cin; ++c) {
+        const float w = load_elem(a.w, (static_cast<long long>(h) * a.Cin + c) * a.Cout + o, a.w_dtype);
+#pragma unroll
+        for (int r = 0; r < kProjBlocks; ++r) acc[r] = fmaf(xs[r * a.Cin + c], w, acc[r]);
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < kProjBlocks; ++r) acc[r] = r < nblk ? xs[r * a.Cin + o] : 0.f;
+    }
+#pragma unroll
+    for (int r = 0; r < kProjBlocks; ++r) ys[r * a.Cout + o] = acc[r];
+  }
+  __syncthreads();
+  const int half = a.Cout / 2;
+  for (int e = threadIdx.x; e < nblk * a.Cout; e += blockDim.x) {
+    const int r = e / a.Cout, o = e % a.Cout;
+    float y = ys[r * a.Cout + o];
+    if (a.cos) {
+      const long long ro = ((a.rope_batch > 1 ? static_cast<long long>(b) : 0) * a.nb + blk0 + r) * a.Cout + o;
+      const float rot = o < half ? -ys[r * a.Cout + o + half] : ys[r * a.Cout + o - half];
+      y = y * a.cos[ro] + rot * a.sin[ro];
+    }
+    store_elem(a.out, b * a.o_b + static_cast<long long>(a.out_block_offset + blk0 + r) * a.o_blk + h * a.o_h + o,
+               a.o_dtype, y);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Gate logits: q_blocks [B,Qb,Hq,C] . k_blocks [B,Kb,Hk,C] * scale -> [B,Hq,Qb,Kb] f32
+// ------------------------------------------------------------------------------------------
+struct GateArgs {
+  const void* q;
+  long long q_b, q_blk, q_h;
+  int q_dtype;
+  const void* k;
+  long long k_b, k_blk, k_h;
+  int k_dtype;
+  float* out;  // [B,Hq,Qb,Kb] contiguous
+  int B, Hq, Hk, Qb, Kb, Pb, C;
+  float scale;
+  float masked_value;  // written where j > Pb + i (the reference fills finfo.min)
+};
+
+constexpr int kGateThreads = 128;
+constexpr int kGateRows = 16;  // q-blocks accumulated per pass
+
+__global__ void __launch_bounds__(kGateThreads) gate_scores_kernel(const GateArgs a) {
+  extern __shared__ float gate_smem[];  // q rows [Qb][C]
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (a.Hq / a.Hk);
+  for (int e = threadIdx.x; e < a.Qb * a.C; e += kGateThreads) {
+    const int i = e / a.C, c = e % a.C;
+    gate_smem[e] = load_elem(a.q, b * a.q_b + i * a.q_blk + h * a.q_h + c, a.q_dtype);
+  }
+  __syncthreads();
+  const int j = blockIdx.x * kGateThreads + threadIdx.x;
+  if (j >= a.Kb) return;
+  const long long kbase = b * a.k_b + static_cast<long long>(j) * a.k_blk + hk * a.k_h;
+  float* orow = a.out + ((static_cast<long long>(b) * a.Hq + h) * a.Qb) * a.Kb + j;
+  for (int i0 = 0; i0 < a.Qb; i0 += kGateRows) {
+    float acc[kGateRows];
+#pragma unroll
+    for (int r = 0; r < kGateRows; ++r) acc[r] = 0.f;
+    for (int c = 0; c < a.C; c += 8) {
+      float kv[8];
+      load8(a.k, kbase + c, a.k_dtype, kv);
+#pragma unroll
+      for (int r = 0; r < kGateRows; ++r) {
+        if (i0 + r < a.Qb) {
+          const float4 q0 = *reinterpret_cast<const float4*>(&gate_smem[(i0 + r) * a.C + c]);
+          const float4 q1 = *reinterpret_cast<const float4*>(&gate_smem[(i0 + r) * a.C + c + 4]);
+          acc[r] += q0.x * kv[0] + q0.y * kv[1] + q0.z * kv[2] + q0.w * kv[3] + q1.x * kv[4] + q1.y * kv[5] +
+                    q1.z * kv[6] + q1.w * kv[7];
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kGateRows; ++r) {
+      const int i = i0 + r;
+      if (i < a.Qb) orow[static_cast<long long>(i) * a.Kb] = (j <= a.Pb + i) ? acc[r] * a.scale : a.masked_value;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// FlashPrefill block score: for q-block i, head h, key block j:
+//   S[t,j] = (q_t . meanK_j) * D^-0.5 * log2e over tokens t of the q-block with P + t >= (j+1)*bs - 1
+//   max[i,j,h] = max_t S, score[i,j,h] = sum_t 2^(S - max); -inf where no token qualifies.
+// ------------------------------------------------------------------------------------------
+struct FpScoreArgs {
+  const void* q;  // [B,Q,Hq,D]
+  long long q_b, q_t, q_h;
+  int q_dtype;
+  const void* mk;  // mean-K [B,Kb,Hkv,D]
+  long long k_b, k_blk, k_h;
+  int k_dtype;
+  float* score;  // [B,Qb,Kb,Hq]
+  float* mx;     // [B,Qb,Kb,Hq]
+  int B, Q, Hq, Hkv, D, Kb, Qb, bs, P;
+  float sm_scale;  // D^-0.5 * log2e
+};
+
+constexpr int kFpThreads = 256;
+constexpr int kFpTile = 64;  // tokens per pass and key blocks per CTA
+
+__global__ void __launch_bounds__(kFpThreads) flashprefill_score_kernel(const FpScoreArgs a) {
+  // shared: key tile [64][D+1], query tile [64][D+1], S tile [64][65]
+  extern __shared__ float fp_smem[];
+  const int ld = a.D + 1;
+  float* ks = fp_smem;
+  float* qs = ks + kFpTile * ld;
+  float* ss = qs + kFpTile * ld;
+  const int jt = blockIdx.x, i = blockIdx.y;
+  const int h = blockIdx.z % a.Hq, b = blockIdx.z / a.Hq;
+  const int hkv = h / (a.Hq / a.Hkv);
+  const int j0 = jt * kFpTile;
+  float* sc_out = a.score + ((static_cast<long long>(b) * a.Qb + i) * a.Kb) * a.Hq + h;
+  float* mx_out = a.mx + ((static_cast<long long>(b) * a.Qb + i) * a.Kb) * a.Hq + h;
+  // key blocks whose last token lies beyond the q-block's last token are never visible
+  const int q_last_abs = a.P + min((i + 1) * a.bs, a.Q) - 1;
+  if (static_cast<long long>(j0 + 1) * a.bs - 1 > q_last_abs) {
+    for (int jj = threadIdx.x; jj < kFpTile && j0 + jj < a.Kb; jj += kFpThreads) {
+      sc_out[static_cast<long long>(j0 + jj) * a.Hq] = -INFINITY;
+      mx_out[static_cast<long long>(j0 + jj) * a.Hq] = -INFINITY;
+    }
+    return;
+  }
+  for (int e = threadIdx.x; e < kFpTile * a.D; e += kFpThreads) {
+    const int r = e / a.D, c = e % a.D;
+    ks[r * ld + c] = (j0 + r < a.Kb) ? load_elem(a.mk, b * a.k_b + static_cast<long long>(j0 + r) * a.k_blk + hkv * a.k_h + c, a.k_dtype) : 0.f;
+  }
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;  // 16x16 threads, 4x4 outputs each
+  float run_m = -INFINITY, run_p = 0.f;  // threads 0..63 own key block j0 + threadIdx.x
+  for (int t0 = i * a.bs; t0 < min((i + 1) * a.bs, a.Q); t0 += kFpTile) {
+    __syncthreads();
+    for (int e = threadIdx.x; e < kFpTile * a.D; e += kFpThreads) {
+      const int r = e / a.D, c = e % a.D;
+      qs[r * ld + c] = (t0 + r < a.Q && t0 + r < (i + 1) * a.bs)
+                           ? load_elem(a.q, b * a.q_b + static_cast<long long>(t0 + r) * a.q_t + h * a.q_h + c, a.q_dtype)
+                           : 0.f;
+    }
+    __syncthreads();
+    float acc[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+    for (int d = 0; d < a.D; ++d) {
+      float qv[4], kv[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) qv[r] = qs[(ty * 4 + r) * ld + d];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) kv[c] = ks[(tx * 4 + c) * ld + d];
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[r][c] = fmaf(qv[r], kv[c], acc[r][c]);
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int t = t0 + ty * 4 + r, j = j0 + tx * 4 + c;
+        const bool vis = t < a.Q && t < (i + 1) * a.bs && j < a.Kb &&
+                         (static_cast<long long>(a.P) + t >= static_cast<long long>(j + 1) * a.bs - 1);
+        ss[(ty * 4 + r) * (kFpTile + 1) + tx * 4 + c] = vis ? acc[r][c] * a.sm_scale : -INFINITY;
+      }
+    __syncthreads();
+    if (threadIdx.x < kFpTile) {
+      float m = run_m;
+      for (int r = 0; r < kFpTile; ++r) m = fmaxf(m, ss[r * (kFpTile + 1) + threadIdx.x]);
+      if (m != -INFINITY) {
+        float p = run_p * exp2f(run_m - m);
+        for (int r = 0; r < kFpTile; ++r) {
+          const float s = ss[r * (kFpTile + 1) + threadIdx.x];
+          p += s == -INFINITY ? 0.f : exp2f(s - m);
+        }
+        run_m = m, run_p = p;
+      }
+    }
+  }
+  if (threadIdx.x < kFpTile && j0 + threadIdx.x < a.Kb) {
+    const long long o = static_cast<long long>(j0 + threadIdx.x) * a.Hq;
+    sc_out[o] = run_m == -INFINITY ? -INFINITY : run_p;
+    mx_out[o] = run_m;
+  }
+}
+
+// normalize_scores: per (b, i, h) over key blocks j:
+//   w_j = 2^(max_j - max_j' max), out_j = score_j * w_j / (sum_j score_j * w_j + 1e-9); 0 where max = -inf.
+__global__ void __launch_bounds__(256) flashprefill_normalize_kernel(const float* score, const float* mx, float* out,
+                                                                     int Kb, int Hq) {
+  // one CTA per (b, i); thread -> head tid % Hq, key phase tid / Hq
+  extern __shared__ float nz_smem[];  // [phases][Hq]
+  const long long base = static_cast<long long>(blockIdx.x) * Kb * Hq;
+  const int h = threadIdx.x % Hq, ph = threadIdx.x / Hq;
+  const int phases = blockDim.x / Hq;
+  float m = -INFINITY;
+  if (ph < phases)
+    for (int j = ph; j < Kb; j += phases) m = fmaxf(m, mx[base + static_cast<long long>(j) * Hq + h]);
+  if (ph < phases) nz_smem[ph * Hq + h] = m;
+  __syncthreads();
+  m = -INFINITY;
+  for (int p = 0; p < phases; ++p) m = fmaxf(m, nz_smem[p * Hq + h]);
+  __syncthreads();
+  float sum = 0.f;
+  if (ph < phases)
+    for (int j = ph; j < Kb; j += phases) {
+      const long long o = base + static_cast<long long>(j) * Hq + h;
+      const float mj = mx[o];
+      sum += mj == -INFINITY ? 0.f : score[o] * exp2f(mj - m);
+    }
+  if (ph < phases) nz_smem[ph * Hq + h] = sum;
+  __syncthreads();
+  sum = 0.f;
+  for (int p = 0; p < phases; ++p) sum += nz_smem[p * Hq + h];
+  const float inv = 1.0f / (sum + 1e-9f);
+  if (ph < phases)
+    for (int j = ph; j < Kb; j += phases) {
+      const long long o = base + static_cast<long long>(j) * Hq + h;
+      const float mj = mx[o];
+      out[o] = mj == -INFINITY ? 0.f : score[o] * exp2f(mj - m) * inv;
+    }
+}
+
+static bool dtype_ok(int dt) { return dt == CA_DTYPE_F32 || dt == CA_DTYPE_BF16 || dt == CA_DTYPE_F16; }
+
+}  // namespace score
+}  // namespace ca
+
+extern "C" {
+
+int ca_pool_blocks(const ca_pool_params* p, ca_stream_t stream_) {
+  using namespace ca;
+  using namespace ca::score;
+  CA_REQUIRE(p != nullptr && p->x && p->out, "params, x and out must be non-null");
+  CA_REQUIRE(dtype_ok(p->x_dtype) && dtype_ok(p->out_dtype), "unsupported dtype");
+  CA_REQUIRE(p->B > 0 && p->L > 0 && p->H > 0 && p->block_size > 0, "B, L, H, block_size must be positive");
+  CA_REQUIRE(p->D > 0 && p->D % 8 == 0 && p->D <= 1024 && kPoolThreads % (p->D / 8) == 0,
+             "D must be a multiple of 8 with D/8 dividing %d", kPoolThreads);
+  CA_REQUIRE(p->kinds > 0 && p->kinds < 8, "kinds must be a non-empty subset of max|min|avg");
+  CA_REQUIRE(p->x_stride_b % 8 == 0 && p->x_stride_t % 8 == 0 && p->x_stride_h % 8 == 0,
+             "x strides must be multiples of 8 elements");
+  CA_REQUIRE(reinterpret_cast<uintptr_t>(p->x) % 32 == 0 || (p->x_dtype != CA_DTYPE_F32 && reinterpret_cast<uintptr_t>(p->x) % 16 == 0),
+             "x must be 16-byte aligned (32-byte for f32)");
+  PoolArgs a;
+  a.x = p->x, a.x_b = p->x_stride_b, a.x_t = p->x_stride_t, a.x_h = p->x_stride_h, a.x_dtype = p->x_dtype;
+  a.out = p->out, a.o_b = p->out_stride_b, a.o_blk = p->out_stride_blk, a.o_h = p->out_stride_h, a.o_dtype = p->out_dtype;
+  a.out_block_offset = p->out_block_offset;
+  a.B = p->B, a.L = p->L, a.H = p->H, a.D = p->D, a.bs = p->block_size, a.kinds = p->kinds;
+  const int nb = ceil_div(p->L, p->block_size);
+  const int phases = kPoolThreads / (p->D / 8);
+  const size_t smem = static_cast<size_t>(3) * phases * p->D * sizeof(float);
+  pool_blocks_kernel<<<dim3(nb, p->B * p->H), kPoolThreads, smem, static_cast<cudaStream_t>(stream_)>>>(a);
+  CA_LAUNCH_CHECK("pool_blocks_kernel");
+  return CA_OK;
+}
+
+int ca_gate_project(const ca_project_params* p, ca_stream_t stream_) {
+  using namespace ca;
+  using namespace ca::score;
+  CA_REQUIRE(p != nullptr && p->x && p->out, "params, x and out must be non-null");
+  CA_REQUIRE(p->B > 0 && p->nb > 0 && p->Hin > 0 && p->Hout > 0 && p->Cin > 0 && p->Cout > 0, "sizes must be positive");
+  CA_REQUIRE(p->Hout % p->Hin == 0, "Hout (%d) must be a multiple of Hin (%d)", p->Hout, p->Hin);
+  CA_REQUIRE(p->w != nullptr || (p->Cin == p->Cout), "identity projection needs Cin == Cout");
+  CA_REQUIRE(p->w == nullptr || dtype_ok(p->w_dtype), "unsupported weight dtype");
+  CA_REQUIRE(dtype_ok(p->out_dtype), "unsupported out dtype");
+  CA_REQUIRE((p->cos == nullptr) == (p->sin == nullptr), "cos and sin must be given together");
+  CA_REQUIRE(p->cos == nullptr || (p->Cout % 2 == 0 && (p->rope_batch == 1 || p->rope_batch == p->B)),
+             "RoPE needs an even Cout and rope_batch in {1, B}");
+  ProjArgs a;
+  a.x = p->x, a.w = p->w, a.w_dtype = p->w_dtype, a.cos = p->cos, a.sin = p->sin, a.rope_batch = p->rope_batch;
+  a.out = p->out, a.o_b = p->out_stride_b, a.o_blk = p->out_stride_blk, a.o_h = p->out_stride_h, a.o_dtype = p->out_dtype;
+  a.out_block_offset = p->out_block_offset;
+  a.B = p->B, a.nb = p->nb, a.Hin = p->Hin, a.Hout = p->Hout, a.Cin = p->Cin, a.Cout = p->Cout;
+  const size_t smem = static_cast<size_t>(kProjBlocks) * (p->Cin + p->Cout) * sizeof(float);
+  CA_REQUIRE(smem <= 48 * 1024, "Cin + Cout too large");
+  const int threads = p->Cout >= 128 ? 128 : 64;
+  proj_rope_kernel<<<dim3(ceil_div(p->nb, kProjBlocks), p->Hout, p->B), threads, smem, static_cast<cudaStream_t>(stream_)>>>(a);
+  CA_LAUNCH_CHECK("proj_rope_kernel");
+  return CA_OK;
+}
+
+int ca_gate_scores(const ca_gate_score_params* p, ca_stream_t stream_) {
+  using namespace ca;
+  using namespace ca::score;
+  CA_REQUIRE(p != nullptr && p->q && p->k && p->out, "params, q, k and out must be non-null");
+  CA_REQUIRE(dtype_ok(p->q_dtype) && dtype_ok(p->k_dtype), "unsupported dtype");
+  CA_REQUIRE(p->B > 0 && p->Hq > 0 && p->Hk > 0 && p->Qb > 0 && p->Kb > 0, "sizes must be positive");
+  CA_REQUIRE(p->Hq % p->Hk == 0, "Hq must be a multiple of Hk");
+  CA_REQUIRE(p->C > 0 && p->C % 8 == 0, "channel count must be a multiple of 8");
+  CA_REQUIRE(p->k_stride_b % 8 == 0 && p->k_stride_blk % 8 == 0 && p->k_stride_h % 8 == 0,
+             "k strides must be multiples of 8 elements");
+  CA_REQUIRE(p->Pb >= 0 && p->Pb + p->Qb >= 1, "Pb out of range");
+  GateArgs a;
+  a.q = p->q, a.q_b = p->q_stride_b, a.q_blk = p->q_stride_blk, a.q_h = p->q_stride_h, a.q_dtype = p->q_dtype;
+  a.k = p->k, a.k_b = p->k_stride_b, a.k_blk = p->k_stride_blk, a.k_h = p->k_stride_h, a.k_dtype = p->k_dtype;
+  a.out = p->out;
+  a.B = p->B, a.Hq = p->Hq, a.Hk = p->Hk, a.Qb = p->Qb, a.Kb = p->Kb, a.Pb = p->Pb, a.C = p->C;
+  a.scale = p->scale;
+  a.masked_value = p->masked_value;
+  const size_t smem = static_cast<size_t>(p->Qb) * p->C * sizeof(float);
+  CA_REQUIRE(smem <= 160 * 1024, "Qb * C too large for the gate score kernel");
+  if (smem > 48 * 1024) CA_CUDA(cudaFuncSetAttribute(gate_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  gate_scores_kernel<<<dim3(ceil_div(p->Kb, kGateThreads), p->Hq, p->B), kGateThreads, smem, static_cast<cudaStream_t>(stream_)>>>(a);
+  CA_LAUNCH_CHECK("gate_scores_kernel");
+  return CA_OK;
+}
+
+int ca_flashprefill_score(const ca_flashprefill_score_params* p, ca_stream_t stream_) {
+  using namespace ca;
+  using namespace ca::score;
+  CA_REQUIRE(p != nullptr && p->q && p->mean_k && p->score_raw && p->max_raw, "params, q, mean_k, score_raw, max_raw must be non-null");
+  CA_REQUIRE(dtype_ok(p->q_dtype) && dtype_ok(p->k_dtype), "unsupported dtype");
+  CA_REQUIRE(p->B > 0 && p->Q > 0 && p->Hq > 0 && p->Hkv > 0 && p->Kb > 0 && p->block_size > 0, "sizes must be positive");
+  CA_REQUIRE(p->Hq % p->Hkv == 0, "Hq must be a multiple of Hkv");
+  CA_REQUIRE(p->D == 128 || p->D == 64, "head dim must be 64 or 128");
+  CA_REQUIRE(p->kv_len >= p->Q, "kv_len must be >= Q");
+  CA_REQUIRE(p->Hq <= 256, "Hq larger than 256 is not supported");
+  FpScoreArgs a;
+  a.q = p->q, a.q_b = p->q_stride_b, a.q_t = p->q_stride_t, a.q_h = p->q_stride_h, a.q_dtype = p->q_dtype;
+  a.mk = p->mean_k, a.k_b = p->k_stride_b, a.k_blk = p->k_stride_blk, a.k_h = p->k_stride_h, a.k_dtype = p->k_dtype;
+  a.score = p->score_raw, a.mx = p->max_raw;
+  a.B = p->B, a.Q = p->Q, a.Hq = p->Hq, a.Hkv = p->Hkv, a.D = p->D, a.Kb = p->Kb, a.bs = p->block_size;
+  a.Qb = ceil_div(p->Q, p->block_size);
+  a.P = p->kv_len - p->Q;
+  a.sm_scale = (1.0f / sqrtf(static_cast<float>(p->D))) * 1.4426950408889634f;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const size_t smem = (static_cast<size_t>(2) * kFpTile * (p->D + 1) + kFpTile * (kFpTile + 1)) * sizeof(float);
+  CA_CUDA(cudaFuncSetAttribute(flashprefill_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  flashprefill_score_kernel<<<dim3(ceil_div(p->Kb, kFpTile), a.Qb, p->B * p->Hq), kFpThreads, smem, stream>>>(a);
+  CA_LAUNCH_CHECK("flashprefill_score_kernel");
+  if (p->score_norm) {
+    const int threads = 256;
+    const size_t nsmem = static_cast<size_t>(threads / p->Hq) * p->Hq * sizeof(float);
+    flashprefill_normalize_kernel<<<p->B * a.Qb, threads, nsmem, stream>>>(p->score_raw, p->max_raw, p->score_norm, p->Kb, p->Hq);
+    CA_LAUNCH_CHECK("flashprefill_normalize_kernel");
+  }
+  return CA_OK;
+}
+
+}  // extern "C"

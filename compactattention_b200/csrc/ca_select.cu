@@ -1,0 +1,507 @@
+// Block selection: per-row rules on a score tensor -> packed keep bits, then Block-Union KV
+// selection (OR over the chunk's Q-blocks, OR over the GQA group) and compaction into the
+// per-KV-head block table.  Integer/byte work, HBM- and launch-bound: coalesced loads, warp
+// ballots for bit packing, popcount prefix scans for compaction; no host synchronisation, every
+// output is sized by capacity.
+#include "ca_common.cuh"
+
+namespace ca {
+namespace select {
+
+constexpr int kRowThreads = 256;
+constexpr int kMaxKb = 8192;  // key blocks per row supported by the row kernels (512K tokens at bs 64)
+
+__device__ __forceinline__ float load_score(const void* base, long long off, int dtype) {
+  if (dtype == CA_DTYPE_F32) return reinterpret_cast<const float*>(base)[off];
+  if (dtype == CA_DTYPE_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[off]);
+  return __half2float(reinterpret_cast<const __half*>(base)[off]);
+}
+
+// Monotone map float -> uint32 (larger float -> larger key); -0 and +0 differ but compare adjacent.
+__device__ __forceinline__ uint32_t order_key(float f) {
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+struct RowArgs {
+  const void* score;  // [B,H,Qb,Kb] by strides; dtype f32/bf16/f16, or uint8 when rule == MASK
+  long long s_b, s_h, s_q, s_k;
+  int score_dtype;
+  const uint8_t* valid;  // optional bool [B,1|H,Qb,Kb] by strides; NULL = block-causal j <= Pb + i
+  long long v_b, v_h, v_q, v_k;
+  uint32_t* bits;  // [B,H,Qb,W]
+  float* prob_out; // optional fp32 [B,H,Qb,Kb] contiguous: the row after softmax / masking
+  int B, H, Qb, Kb, Pb, W;
+  int rule;
+  int softmax;     // apply a masked softmax to the row before the rule
+  float threshold; // THRESHOLD: keep s > threshold.  CUMMASS: tau
+  float alpha;     // ALPHA_ROWMAX: keep s >= alpha * rowmax
+  int topk_k;      // TOPK: absolute k when > 0 ...
+  int topk_num, topk_den;  // ... else k = max(1, (num * n_valid + den/2) / den)
+  int min_budget;  // ALPHA_ROWMAX: also keep the top min_budget entries
+  int sink, local; // forced blocks: j < sink, and 0 <= (Pb+i) - j < local
+  int rows_voting; // rows i >= rows_voting produce no bits (FlashPrefill last_n_block)
+};
+
+// Exclusive block-wide prefix sum of one int per thread (kRowThreads threads).
+__device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    int n = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += n;
+  }
+  if (lane == 31) warp_sums[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int w = lane < (kRowThreads / 32) ? warp_sums[lane] : 0;
+    int winc = w;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int n = __shfl_up_sync(0xffffffffu, winc, d);
+      if (lane >= d) winc += n;
+    }
+    if (lane < (kRowThreads / 32)) warp_sums[lane] = winc - w;
+    if (lane == 31) *total = winc;
+  }
+  __syncthreads();
+  int r = warp_sums[warp] + inc - v;
+  __syncthreads();
+  return r;
+}
+
+__device__ __forceinline__ float block_reduce_max(float v, float* scratch) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = scratch[0];
+  for (int w = 1; w < kRowThreads / 32; ++w) r = fmaxf(r, scratch[w]);
+  __syncthreads();
+  return r;
+}
+
+// Deterministic block sum: fixed tree inside the warp, then warps added in order.
+__device__ __forceinline__ float block_reduce_sum(float v, float* scratch) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = 0.f;
+  for (int w = 0; w < kRowThreads / 32; ++w) r += scratch[w];
+  __syncthreads();
+  return r;
+}
+
+// Marks the k largest entries of s[0..n) (ties -> lower index) in keep[] (1 byte per entry).
+// Radix select over the monotone keys, 8 bits per pass, then an ordered pass for the ties.
+__device__ void topk_mark(const float* s, int n, int k, uint8_t* keep, int* hist, int* warp_sums) {
+  __shared__ uint32_t sh_prefix;
+  __shared__ int sh_remaining, sh_total;
+  if (k >= n) {
+    for (int j = threadIdx.x; j < n; j += kRowThreads) keep[j] = 1;
+    __syncthreads();
+    return;
+  }
+  if (threadIdx.x == 0) {
+    sh_prefix = 0;
+    sh_remaining = k;
+  }
+  __syncthreads();
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += kRowThreads) hist[i] = 0;
+    __syncthreads();
+    const uint32_t prefix = sh_prefix;
+    const uint32_t mask_hi = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+    for (int j = threadIdx.x; j < n; j += kRowThreads) {
+      const uint32_t key = order_key(s[j]);
+      if ((key & mask_hi) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int rem = sh_remaining;
+      int bin = 255;
+      for (; bin > 0; --bin) {
+        if (hist[bin] >= rem) break;
+        rem -= hist[bin];
+      }
+      sh_prefix = prefix | (static_cast<uint32_t>(bin) << shift);
+      sh_remaining = rem;  // how many entries equal to the final key are still wanted
+    }
+    __syncthreads();
+  }
+  const uint32_t kth = sh_prefix;
+  const int want_equal = sh_remaining;
+  // ordered pass: keys above kth are kept, keys equal to kth are kept in index order
+  int taken = 0;
+  for (int base = 0; base < n; base += kRowThreads) {
+    const int j = base + threadIdx.x;
+    const uint32_t key = j < n ? order_key(s[j]) : 0u;
+    const int eq = (j < n && key == kth) ? 1 : 0;
+    const int pos = block_exclusive_scan(eq, warp_sums, &sh_total);
+    if (j < n) keep[j] = (key > kth) || (eq && (taken + pos) < want_equal);
+    taken += sh_total;
+    __syncthreads();
+  }
+}
+
+// Sorts comp[0..n2) ascending (n2 a power of two), bitonic network in shared memory.
+__device__ void bitonic_sort(unsigned long long* comp, int n2) {
+  for (int size = 2; size <= n2; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = threadIdx.x; t < (n2 >> 1); t += kRowThreads) {
+        const int lo = 2 * t - (t & (stride - 1));
+        const int hi = lo + stride;
+        const bool asc = (lo & size) == 0;
+        const unsigned long long x = comp[lo], y = comp[hi];
+        if ((x > y) == asc) {
+          comp[lo] = y;
+          comp[hi] = x;
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs a) {
+  extern __shared__ unsigned char dyn_smem[];
+  float* s = reinterpret_cast<float*>(dyn_smem);                    // [Kb]
+  uint8_t* keep = reinterpret_cast<uint8_t*>(s + a.Kb);              // [Kb]
+  uint8_t* flag = keep + a.Kb;                                       // [Kb] scratch flags
+  unsigned long long* comp =
+      reinterpret_cast<unsigned long long*>(dyn_smem + ((a.Kb * 6 + 15) / 16) * 16);  // cummass only
+  __shared__ float red[kRowThreads / 32];
+  __shared__ int hist[256];
+  __shared__ int warp_sums[kRowThreads / 32];
+  __shared__ int sh_cut;
+
+  const int i = blockIdx.x % a.Qb;
+  const int h = (blockIdx.x / a.Qb) % a.H;
+  const int b = blockIdx.x / (a.Qb * a.H);
+  const int diag = a.Pb + i;  // last causally valid key block of this row
+  uint32_t* bits_row = a.bits + ((static_cast<long long>(b) * a.H + h) * a.Qb + i) * a.W;
+
+  if (i >= a.rows_voting) {
+    for (int w = threadIdx.x; w < a.W; w += kRowThreads) bits_row[w] = 0u;
+    return;
+  }
+  const long long s_off = b * a.s_b + h * a.s_h + i * a.s_q;
+  const long long v_off = a.valid ? (b * a.v_b + h * a.v_h + i * a.v_q) : 0;
+
+  // ---- load the row; invalid entries become -inf ----
+  for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) {
+    const bool ok = a.valid ? (a.valid[v_off + j * a.v_k] != 0) : (j <= diag);
+    float x;
+    if (a.rule == CA_RULE_MASK) {
+      x = reinterpret_cast<const uint8_t*>(a.score)[s_off + j * a.s_k] ? 1.f : 0.f;
+    } else {
+      x = load_score(a.score, s_off + j * a.s_k, a.score_dtype);
+    }
+    s[j] = ok ? x : -INFINITY;
+    keep[j] = 0;
+  }
+  __syncthreads();
+
+  if (a.softmax) {
+    float m = -INFINITY;
+    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) m = fmaxf(m, s[j]);
+    m = block_reduce_max(m, red);
+    float sum = 0.f;
+    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) {
+      const float e = s[j] == -INFINITY ? 0.f : expf(s[j] - m);
+      s[j] = e;
+      sum += e;
+    }
+    sum = block_reduce_sum(sum, red);
+    const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) {
+      const bool ok = a.valid ? (a.valid[v_off + j * a.v_k] != 0) : (j <= diag);
+      s[j] = ok ? s[j] * inv : -INFINITY;
+    }
+    __syncthreads();
+  }
+  if (a.prob_out) {
+    float* prow = a.prob_out + ((static_cast<long long>(b) * a.H + h) * a.Qb + i) * a.Kb;
+    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) prow[j] = s[j] == -INFINITY ? 0.f : s[j];
+  }
+
+  // ---- the rule ----
+  if (a.rule == CA_RULE_THRESHOLD) {
+    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) keep[j] = s[j] > a.threshold;  // -inf never passes
+  } else if (a.rule == CA_RULE_MASK) {
+    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) keep[j] = s[j] > 0.5f;
+  } else if (a.rule == CA_RULE_ALPHA_ROWMAX) {
+    // non-finite or acausal entries count as 0 for the maximum and are never selected by score
+    // (the reference zero-fills them before taking the maximum and the top-k)
+    float m = 0.f;
+    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) {
+      const float x = s[j];
+      const bool fin = (x == x) && fabsf(x) != INFINITY && j <= diag;
+      flag[j] = fin;
+      s[j] = fin ? x : 0.f;
+      m = fmaxf(m, s[j]);
+    }
+    m = block_reduce_max(m, red);
+    if (a.min_budget > 0) {
+      topk_mark(s, a.Kb, a.min_budget < a.Kb ? a.min_budget : a.Kb, keep, hist, warp_sums);
+      __syncthreads();
+    }
+    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) keep[j] = keep[j] || (flag[j] && s[j] >= m * a.alpha);
+  } else if (a.rule == CA_RULE_TOPK) {
+    // valid entries are a prefix for the block-causal case; in general count them
+    int cnt = 0;
+    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) cnt += a.valid ? (a.valid[v_off + j * a.v_k] != 0) : (j <= diag);
+    __shared__ int sh_nvalid;
+    block_exclusive_scan(cnt, warp_sums, &sh_nvalid);
+    const int n_valid = sh_nvalid;
+    int k = a.topk_k > 0 ? a.topk_k
+                         : static_cast<int>((static_cast<long long>(a.topk_num) * n_valid + a.topk_den / 2) / a.topk_den);
+    if (k < 1) k = 1;
+    if (k > n_valid) k = n_valid;
+    // invalid entries are -inf and sort last, so taking k <= n_valid never reaches them
+    if (k > 0) topk_mark(s, a.Kb, k, keep, hist, warp_sums);
+  } else if (a.rule == CA_RULE_CUMMASS) {
+    int n2 = 1;
+    while (n2 < a.Kb) n2 <<= 1;
+    for (int j = threadIdx.x; j < n2; j += kRowThreads) {
+      // descending by value, ascending by index; invalid (-inf) and padding sort last
+      const uint32_t key = j < a.Kb ? order_key(s[j] == -INFINITY ? -1.0f : s[j]) : 0u;
+      comp[j] = (static_cast<unsigned long long>(~key) << 32) | static_cast<uint32_t>(j);
+    }
+    __syncthreads();
+    bitonic_sort(comp, n2);
+    if (threadIdx.x == 0) {
+      // sequential fp32 prefix sum in sorted order; keep the shortest prefix with mass >= tau
+      float acc = 0.f;
+      int cut = a.Kb;
+      for (int r = 0; r < a.Kb; ++r) {
+        const int j = static_cast<int>(comp[r] & 0xffffffffu);
+        const float p = s[j] == -INFINITY ? 0.f : s[j];
+        acc = __fadd_rn(acc, p);
+        if (acc >= a.threshold) {
+          cut = r + 1;
+          break;
+        }
+      }
+      sh_cut = cut;
+    }
+    __syncthreads();
+    const int cut = sh_cut;
+    for (int r = threadIdx.x; r < cut; r += kRowThreads) {
+      const int j = static_cast<int>(comp[r] & 0xffffffffu);
+      keep[j] = s[j] != -INFINITY;
+    }
+  }
+  __syncthreads();
+
+  // ---- forced blocks, validity, bit packing ----
+  for (int base = 0; base < a.W * 32; base += kRowThreads) {
+    const int j = base + threadIdx.x;
+    bool k = false;
+    if (j < a.Kb) {
+      const bool ok = a.valid ? (a.valid[v_off + j * a.v_k] != 0) : (j <= diag);
+      const int d = diag - j;
+      const bool forced = d >= 0 && (j < a.sink || d < a.local);
+      k = (keep[j] || forced) && ok;
+    }
+    const uint32_t word = __ballot_sync(0xffffffffu, k);
+    if ((threadIdx.x & 31) == 0 && (j >> 5) < a.W) bits_row[j >> 5] = word;
+  }
+}
+
+struct UnionArgs {
+  const uint32_t* bits;   // [B,Hin,Qin,W] packed keep bits, or NULL
+  const uint8_t* mask;    // [B,Hin,Qin,Kb] bool by strides, used when bits == NULL
+  long long m_b, m_h, m_q, m_k;
+  int B, Hin, Qin, Hkv, G;  // Hin = Hkv*G (G = 1 when the input is already per KV head)
+  int Kb, Pb, Qb, W;
+  int keep_recent;          // past columns j >= Kb - keep_recent are forced on (Seer keep_recent_blocks)
+  int block_size, page_size;
+  int32_t* block_idx;       // [R, idx_stride] ascending past ids, -1 padded
+  int idx_stride;
+  int32_t* counts;          // [R]
+  int32_t* cache_seqlens;   // optional [R] = (count + Qb) * bs
+  int32_t* pages_per_row;   // optional [R] = ceil(cache_seqlens / page_size)
+  uint8_t* keep_kv;         // optional bool [B,Hkv,Kb]: union with every chunk column on
+};
+
+__global__ void __launch_bounds__(kRowThreads) union_table_kernel(const UnionArgs a) {
+  __shared__ int warp_sums[kRowThreads / 32];
+  __shared__ int sh_total;
+  const int row = blockIdx.x;
+  const int b = row / a.Hkv, hkv = row % a.Hkv;
+  int32_t* idx_row = a.block_idx + static_cast<long long>(row) * a.idx_stride;
+  int running = 0;
+  for (int wbase = 0; wbase < a.W; wbase += kRowThreads) {
+    const int w = wbase + threadIdx.x;
+    uint32_t word = 0;
+    if (w < a.W) {
+      for (int g = 0; g < a.G; ++g) {
+        const int h = hkv * a.G + g;
+        for (int i = 0; i < a.Qin; ++i) {
+          if (a.bits) {
+            word |= a.bits[((static_cast<long long>(b) * a.Hin + h) * a.Qin + i) * a.W + w];
+          } else {
+            const uint8_t* m = a.mask + b * a.m_b + h * a.m_h + i * a.m_q;
+            const int j0 = w * 32;
+            const int n = a.Kb - j0 < 32 ? a.Kb - j0 : 32;
+            for (int t = 0; t < n; ++t) word |= (m[(j0 + t) * a.m_k] ? 1u : 0u) << t;
+          }
+        }
+      }
+      // forced recent columns, then split into past (table) and chunk (always on) parts
+      const int j0 = w * 32;
+      for (int t = 0; t < 32; ++t) {
+        const int j = j0 + t;
+        if (j < a.Kb && j >= a.Kb - a.keep_recent) word |= 1u << t;
+        if (j >= a.Kb) word &= ~(1u << t);
+      }
+      if (a.keep_kv) {
+        uint8_t* out = a.keep_kv + (static_cast<long long>(row)) * a.Kb;
+        for (int t = 0; t < 32 && j0 + t < a.Kb; ++t) out[j0 + t] = ((word >> t) & 1u) || (j0 + t >= a.Pb);
+      }
+      // keep past columns only
+      if (j0 + 32 > a.Pb) word = j0 >= a.Pb ? 0u : (word & ((1u << (a.Pb - j0)) - 1u));
+    }
+    const int pc = __popc(word);
+    const int off = running + block_exclusive_scan(pc, warp_sums, &sh_total);
+    int o = off;
+    while (word) {
+      const int t = __ffs(word) - 1;
+      word &= word - 1;
+      if (o < a.idx_stride) idx_row[o] = w * 32 + t;
+      ++o;
+    }
+    running += sh_total;
+    __syncthreads();
+  }
+  const int count = running < a.idx_stride ? running : a.idx_stride;
+  for (int o = count + threadIdx.x; o < a.idx_stride; o += kRowThreads) idx_row[o] = -1;
+  if (threadIdx.x == 0) {
+    a.counts[row] = count;
+    const int seqlen = (count + a.Qb) * a.block_size;
+    if (a.cache_seqlens) a.cache_seqlens[row] = seqlen;
+    if (a.pages_per_row) a.pages_per_row[row] = (seqlen + a.page_size - 1) / a.page_size;
+  }
+}
+
+// Exclusive prefix over rows of pages_per_row -> page_offsets[R+1]; block_table[row,slot] =
+// page_offsets[row] + slot for slot < pages_per_row[row] (else 0).  One CTA; R is small.
+__global__ void __launch_bounds__(kRowThreads) paged_metadata_kernel(const int32_t* pages_per_row, int R,
+                                                                     int32_t* page_offsets, int32_t* block_table,
+                                                                     int max_pages) {
+  __shared__ int warp_sums[kRowThreads / 32];
+  __shared__ int sh_total;
+  int running = 0;
+  for (int base = 0; base < R; base += kRowThreads) {
+    const int r = base + threadIdx.x;
+    const int v = r < R ? pages_per_row[r] : 0;
+    const int off = running + block_exclusive_scan(v, warp_sums, &sh_total);
+    if (r < R) page_offsets[r] = off;
+    running += sh_total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) page_offsets[R] = running;
+  __syncthreads();
+  if (block_table) {
+    for (long long e = threadIdx.x; e < static_cast<long long>(R) * max_pages; e += kRowThreads) {
+      const int r = static_cast<int>(e / max_pages), slot = static_cast<int>(e % max_pages);
+      block_table[e] = slot < pages_per_row[r] ? page_offsets[r] + slot : 0;
+    }
+  }
+}
+
+}  // namespace select
+}  // namespace ca
+
+extern "C" {
+
+int ca_select_rows(const ca_select_params* p, ca_stream_t stream_) {
+  using namespace ca;
+  using namespace ca::select;
+  CA_REQUIRE(p != nullptr, "params is null");
+  CA_REQUIRE(p->score && p->bits, "score and bits must be non-null");
+  CA_REQUIRE(p->B > 0 && p->H > 0 && p->Qb > 0 && p->Kb > 0, "B, H, Qb, Kb must be positive");
+  CA_REQUIRE(p->Kb <= kMaxKb, "Kb %d exceeds the supported maximum %d", p->Kb, kMaxKb);
+  CA_REQUIRE(p->Pb >= 0 && p->Pb + p->Qb <= p->Kb + p->Qb, "Pb out of range");
+  CA_REQUIRE(p->rule >= CA_RULE_THRESHOLD && p->rule <= CA_RULE_MASK, "unknown rule %d", p->rule);
+  CA_REQUIRE(p->rule == CA_RULE_MASK || p->score_dtype == CA_DTYPE_F32 || p->score_dtype == CA_DTYPE_BF16 ||
+                 p->score_dtype == CA_DTYPE_F16,
+             "score dtype must be f32, bf16 or f16");
+  if (p->rule == CA_RULE_TOPK) CA_REQUIRE(p->topk_k > 0 || (p->topk_num >= 0 && p->topk_den > 0), "top-k needs k or num/den");
+  RowArgs a;
+  a.score = p->score;
+  a.s_b = p->score_stride_b, a.s_h = p->score_stride_h, a.s_q = p->score_stride_q, a.s_k = p->score_stride_k;
+  a.score_dtype = p->score_dtype;
+  a.valid = static_cast<const uint8_t*>(p->valid);
+  a.v_b = p->valid_stride_b, a.v_h = p->valid_stride_h, a.v_q = p->valid_stride_q, a.v_k = p->valid_stride_k;
+  a.bits = static_cast<uint32_t*>(p->bits);
+  a.prob_out = p->prob_out;
+  a.B = p->B, a.H = p->H, a.Qb = p->Qb, a.Kb = p->Kb, a.Pb = p->Pb;
+  a.W = (p->Kb + 31) / 32;
+  a.rule = p->rule;
+  a.softmax = p->softmax;
+  a.threshold = p->threshold;
+  a.alpha = p->alpha;
+  a.topk_k = p->topk_k, a.topk_num = p->topk_num, a.topk_den = p->topk_den;
+  a.min_budget = p->min_budget;
+  a.sink = p->sink, a.local = p->local;
+  a.rows_voting = p->rows_voting > 0 ? p->rows_voting : p->Qb;
+  size_t smem = ((static_cast<size_t>(p->Kb) * 6 + 15) / 16) * 16;
+  if (p->rule == CA_RULE_CUMMASS) {
+    size_t n2 = 1;
+    while (n2 < static_cast<size_t>(p->Kb)) n2 <<= 1;
+    smem += n2 * 8;
+  }
+  if (smem > 48 * 1024) {
+    CA_CUDA(cudaFuncSetAttribute(select_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  }
+  select_rows_kernel<<<p->B * p->H * p->Qb, kRowThreads, smem, static_cast<cudaStream_t>(stream_)>>>(a);
+  CA_LAUNCH_CHECK("select_rows_kernel");
+  return CA_OK;
+}
+
+int ca_union_table(const ca_union_params* p, ca_stream_t stream_) {
+  using namespace ca;
+  using namespace ca::select;
+  CA_REQUIRE(p != nullptr, "params is null");
+  CA_REQUIRE((p->bits != nullptr) != (p->mask != nullptr), "exactly one of bits and mask must be given");
+  CA_REQUIRE(p->block_idx && p->counts, "block_idx and counts must be non-null");
+  CA_REQUIRE(p->B > 0 && p->Hkv > 0 && p->G > 0 && p->Qin > 0 && p->Kb > 0, "B, Hkv, G, Qin, Kb must be positive");
+  CA_REQUIRE(p->Pb >= 0 && p->Pb <= p->Kb, "Pb (%d) must lie in [0, Kb=%d]", p->Pb, p->Kb);
+  CA_REQUIRE(p->idx_stride >= (p->Pb > 0 ? p->Pb : 1), "block_idx capacity %d is smaller than the past block count %d",
+             p->idx_stride, p->Pb);
+  CA_REQUIRE(p->block_size > 0 && p->page_size > 0, "block_size and page_size must be positive");
+  UnionArgs a;
+  a.bits = static_cast<const uint32_t*>(p->bits);
+  a.mask = static_cast<const uint8_t*>(p->mask);
+  a.m_b = p->mask_stride_b, a.m_h = p->mask_stride_h, a.m_q = p->mask_stride_q, a.m_k = p->mask_stride_k;
+  a.B = p->B, a.Hkv = p->Hkv, a.G = p->G, a.Hin = p->Hkv * p->G, a.Qin = p->Qin;
+  a.Kb = p->Kb, a.Pb = p->Pb, a.Qb = p->Kb - p->Pb;
+  a.W = (p->Kb + 31) / 32;
+  a.keep_recent = p->keep_recent;
+  a.block_size = p->block_size, a.page_size = p->page_size;
+  a.block_idx = p->block_idx, a.idx_stride = p->idx_stride, a.counts = p->counts;
+  a.cache_seqlens = p->cache_seqlens, a.pages_per_row = p->pages_per_row;
+  a.keep_kv = static_cast<uint8_t*>(p->keep_kv);
+  union_table_kernel<<<p->B * p->Hkv, kRowThreads, 0, static_cast<cudaStream_t>(stream_)>>>(a);
+  CA_LAUNCH_CHECK("union_table_kernel");
+  return CA_OK;
+}
+
+int ca_paged_metadata(const int32_t* pages_per_row, int rows, int32_t* page_offsets, int32_t* block_table,
+                      int max_pages, ca_stream_t stream_) {
+  using namespace ca;
+  using namespace ca::select;
+  CA_REQUIRE(pages_per_row && page_offsets, "pages_per_row and page_offsets must be non-null");
+  CA_REQUIRE(rows > 0, "rows must be positive");
+  CA_REQUIRE(block_table == nullptr || max_pages > 0, "max_pages must be positive with a block_table");
+  paged_metadata_kernel<<<1, kRowThreads, 0, static_cast<cudaStream_t>(stream_)>>>(pages_per_row, rows, page_offsets,
+                                                                                    block_table, max_pages);
+  CA_LAUNCH_CHECK("paged_metadata_kernel");
+  return CA_OK;
+}
+
+}  // extern "C"

@@ -140,3 +140,340 @@ def attn_compact(
     lib = _lib.load()
     _lib.check(lib.ca_attn_compact(C.byref(p), _stream()), "ca_attn_compact")
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# Block selection
+# ---------------------------------------------------------------------------------------------
+RULES = {
+    "threshold": _lib.CA_RULE_THRESHOLD,
+    "alpha_rowmax": _lib.CA_RULE_ALPHA_ROWMAX,
+    "topk": _lib.CA_RULE_TOPK,
+    "cummass": _lib.CA_RULE_CUMMASS,
+    "mask": _lib.CA_RULE_MASK,
+}
+
+
+def words_for(kv_blocks: int) -> int:
+    return (kv_blocks + 31) // 32
+
+
+def select_rows(
+    score: torch.Tensor,  # [B, H, Qb, Kb] (any strides); bool/uint8 for rule "mask"
+    past_blocks: int,
+    rule: str,
+    *,
+    valid: Optional[torch.Tensor] = None,  # bool [B, 1|H, Qb, Kb]; None = block-causal
+    softmax: bool = False,
+    threshold: float = 0.0,
+    alpha: float = 0.0,
+    topk_k: int = 0,
+    topk_ratio: Optional[tuple[int, int]] = None,  # (num, den): k = max(1, round_half_up(num*n_valid/den))
+    min_budget: int = 0,
+    sink: int = 0,
+    local: int = 0,
+    rows_voting: int = 0,
+    bits: Optional[torch.Tensor] = None,
+    prob_out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Per-row selection rule -> packed keep bits int32 [B, H, Qb, ceil(Kb/32)]."""
+    _require_cuda(score, valid, bits, prob_out)
+    B, H, Qb, Kb = score.shape
+    p = _lib.SelectParams()
+    if rule == "mask":
+        if score.dtype not in (torch.bool, torch.uint8):
+            raise ValueError("rule 'mask' needs a bool/uint8 tensor")
+        p.score_dtype = 0
+    else:
+        if score.dtype not in _DTYPES:
+            raise ValueError(f"unsupported score dtype {score.dtype}")
+        p.score_dtype = _DTYPES[score.dtype]
+    if bits is None:
+        bits = torch.empty((B, H, Qb, words_for(Kb)), dtype=torch.int32, device=score.device)
+    if bits.dtype != torch.int32 or not bits.is_contiguous() or bits.shape != (B, H, Qb, words_for(Kb)):
+        raise ValueError("bits must be a contiguous int32 [B,H,Qb,ceil(Kb/32)] tensor")
+    if prob_out is not None and (prob_out.dtype != torch.float32 or not prob_out.is_contiguous() or prob_out.shape != (B, H, Qb, Kb)):
+        raise ValueError("prob_out must be a contiguous float32 [B,H,Qb,Kb] tensor")
+    p.score = score.data_ptr()
+    p.score_stride_b, p.score_stride_h, p.score_stride_q, p.score_stride_k = score.stride()
+    p.rule = RULES[rule]
+    if valid is not None:
+        if valid.dtype not in (torch.bool, torch.uint8) or valid.dim() != 4:
+            raise ValueError("valid must be a bool [B,1|H,Qb,Kb] tensor")
+        valid = valid.expand(B, valid.shape[1], Qb, Kb)
+        p.valid = valid.data_ptr()
+        sb, sh, sq, sk = valid.stride()
+        p.valid_stride_b, p.valid_stride_h, p.valid_stride_q, p.valid_stride_k = sb, (sh if valid.shape[1] > 1 else 0), sq, sk
+    p.bits = bits.data_ptr()
+    p.prob_out = _ptr(prob_out)
+    p.B, p.H, p.Qb, p.Kb, p.Pb = B, H, Qb, Kb, past_blocks
+    p.softmax = int(softmax)
+    p.threshold, p.alpha = float(threshold), float(alpha)
+    p.topk_k = int(topk_k)
+    p.topk_num, p.topk_den = (topk_ratio if topk_ratio is not None else (0, 1))
+    p.min_budget, p.sink, p.local, p.rows_voting = int(min_budget), int(sink), int(local), int(rows_voting)
+    _lib.check(_lib.load().ca_select_rows(C.byref(p), _stream()), "ca_select_rows")
+    return bits
+
+
+@dataclass
+class BlockTable:
+    """Per-KV-head block table: ascending selected past block ids (-1 padded) and their counts."""
+
+    block_idx: torch.Tensor  # int32 [B, Hkv, cap]
+    counts: torch.Tensor  # int32 [B, Hkv]
+    cache_seqlens: torch.Tensor  # int32 [B, Hkv] = (count + Qb) * bs
+    pages_per_row: torch.Tensor  # int32 [B, Hkv]
+    keep_kv: Optional[torch.Tensor] = None  # bool [B, Hkv, Kb]
+
+
+def union_table(
+    *,
+    bits: Optional[torch.Tensor] = None,  # int32 [B, Hkv*G, Qin, W]
+    mask: Optional[torch.Tensor] = None,  # bool [B, Hkv*G, Qin, Kb] or [B, Hkv*G, Kb]
+    num_kv_heads: int,
+    kv_blocks: int,
+    past_blocks: int,
+    block_size: int = 64,
+    page_size: int = 256,
+    keep_recent: int = 0,
+    want_keep_kv: bool = False,
+    out: Optional[BlockTable] = None,
+) -> BlockTable:
+    """Block-Union KV selection (Q-block union, GQA union) and compaction into the block table."""
+    src = bits if bits is not None else mask
+    if src is None or (bits is not None and mask is not None):
+        raise ValueError("give exactly one of bits and mask")
+    _require_cuda(src)
+    p = _lib.UnionParams()
+    if mask is not None:
+        if mask.dtype not in (torch.bool, torch.uint8):
+            raise ValueError("mask must be bool/uint8")
+        if mask.dim() == 3:
+            mask = mask.unsqueeze(2)
+        B, Hin, Qin, Kb = mask.shape
+        if Kb != kv_blocks:
+            raise ValueError(f"mask has {Kb} key blocks, expected {kv_blocks}")
+        p.mask = mask.data_ptr()
+        p.mask_stride_b, p.mask_stride_h, p.mask_stride_q, p.mask_stride_k = mask.stride()
+    else:
+        if bits.dtype != torch.int32 or not bits.is_contiguous() or bits.shape[-1] != words_for(kv_blocks):
+            raise ValueError("bits must be a contiguous int32 [B,H,Qin,ceil(Kb/32)] tensor")
+        B, Hin, Qin, _ = bits.shape
+        p.bits = bits.data_ptr()
+    if Hin % num_kv_heads != 0:
+        raise ValueError(f"{Hin} input heads is not a multiple of {num_kv_heads} kv heads")
+    dev = src.device
+    cap = max(past_blocks, 1)
+    if out is None:
+        out = BlockTable(
+            torch.empty((B, num_kv_heads, cap), dtype=torch.int32, device=dev),
+            torch.empty((B, num_kv_heads), dtype=torch.int32, device=dev),
+            torch.empty((B, num_kv_heads), dtype=torch.int32, device=dev),
+            torch.empty((B, num_kv_heads), dtype=torch.int32, device=dev),
+            torch.empty((B, num_kv_heads, kv_blocks), dtype=torch.bool, device=dev) if want_keep_kv else None,
+        )
+    p.B, p.Hkv, p.G, p.Qin, p.Kb, p.Pb = B, num_kv_heads, Hin // num_kv_heads, Qin, kv_blocks, past_blocks
+    p.keep_recent = int(keep_recent)
+    p.block_size, p.page_size = block_size, page_size
+    p.block_idx, p.idx_stride = out.block_idx.data_ptr(), out.block_idx.shape[-1]
+    p.counts = out.counts.data_ptr()
+    p.cache_seqlens = out.cache_seqlens.data_ptr()
+    p.pages_per_row = out.pages_per_row.data_ptr()
+    p.keep_kv = _ptr(out.keep_kv)
+    _lib.check(_lib.load().ca_union_table(C.byref(p), _stream()), "ca_union_table")
+    return out
+
+
+def paged_metadata(pages_per_row: torch.Tensor, max_pages: int = 0):
+    """Exclusive prefix of pages_per_row -> page_offsets [R+1]; optional block_table [R, max_pages]."""
+    _require_cuda(pages_per_row)
+    flat = pages_per_row.reshape(-1)
+    R = flat.numel()
+    offsets = torch.empty(R + 1, dtype=torch.int32, device=flat.device)
+    table = torch.empty((R, max_pages), dtype=torch.int32, device=flat.device) if max_pages > 0 else None
+    _lib.check(_lib.load().ca_paged_metadata(flat.data_ptr(), R, offsets.data_ptr(), _ptr(table), max_pages, _stream()),
+               "ca_paged_metadata")
+    return offsets, table
+
+
+# ---------------------------------------------------------------------------------------------
+# Block scoring
+# ---------------------------------------------------------------------------------------------
+_POOL_BITS = {"max": _lib.CA_POOL_MAX, "min": _lib.CA_POOL_MIN, "avg": _lib.CA_POOL_AVG}
+
+
+def pool_blocks(
+    x: torch.Tensor,  # [B, L, H, D]
+    block_size: int,
+    kinds: tuple[str, ...] = ("avg",),
+    out: Optional[torch.Tensor] = None,  # [B, >= off + nb, H, nk*D] (any batch/block/head strides)
+    out_block_offset: int = 0,
+    out_dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """max/min/avg pooling of token blocks, channels ordered max|min|avg; can append into a cache."""
+    _require_cuda(x, out)
+    B, L, H, D = x.shape
+    if x.stride(3) != 1:
+        raise ValueError("x must have a contiguous last dim")
+    nb = (L + block_size - 1) // block_size
+    bitsel = 0
+    for k in kinds:
+        bitsel |= _POOL_BITS[k]
+    nk = bin(bitsel).count("1")
+    if out is None:
+        out = torch.empty((B, nb, H, nk * D), dtype=out_dtype or torch.float32, device=x.device)
+    if out.stride(3) != 1 or out.shape[3] != nk * D or out.shape[1] < out_block_offset + nb:
+        raise ValueError("out has the wrong shape for this pooling")
+    p = _lib.PoolParams()
+    p.x, p.x_stride_b, p.x_stride_t, p.x_stride_h = x.data_ptr(), x.stride(0), x.stride(1), x.stride(2)
+    p.x_dtype, p.out_dtype = _DTYPES[x.dtype], _DTYPES[out.dtype]
+    p.out, p.out_stride_b, p.out_stride_blk, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
+    p.out_block_offset = out_block_offset
+    p.B, p.L, p.H, p.D, p.block_size, p.kinds = B, L, H, D, block_size, bitsel
+    _lib.check(_lib.load().ca_pool_blocks(C.byref(p), _stream()), "ca_pool_blocks")
+    return out
+
+
+def gate_project(
+    x: torch.Tensor,  # f32 contiguous [B, nb, Hin, Cin]
+    weight: Optional[torch.Tensor],  # [Hout, Cin, Cout] or None (identity)
+    cos: Optional[torch.Tensor] = None,  # f32 [1|B, nb, Cout]
+    sin: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,  # [B, >= off + nb, Hout, Cout]
+    out_block_offset: int = 0,
+    out_dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """Per-head linear + block RoPE, written at a block offset of ``out`` (cache append)."""
+    _require_cuda(x, weight, cos, sin, out)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise ValueError("x must be contiguous float32")
+    B, nb, Hin, Cin = x.shape
+    if weight is not None:
+        if not weight.is_contiguous() or weight.shape[1] != Cin:
+            raise ValueError("weight must be contiguous [Hout, Cin, Cout]")
+        Hout, _, Cout = weight.shape
+    else:
+        Hout, Cout = Hin, Cin
+    if cos is not None:
+        cos, sin = cos.to(torch.float32).contiguous(), sin.to(torch.float32).contiguous()
+        if cos.shape[-2:] != (nb, Cout) or sin.shape != cos.shape:
+            raise ValueError("cos/sin must be [1|B, nb, Cout]")
+    if out is None:
+        out = torch.empty((B, nb, Hout, Cout), dtype=out_dtype or torch.float32, device=x.device)
+    if out.stride(3) != 1 or out.shape[2] != Hout or out.shape[3] != Cout or out.shape[1] < out_block_offset + nb:
+        raise ValueError("out has the wrong shape for this projection")
+    p = _lib.ProjectParams()
+    p.x, p.w = x.data_ptr(), _ptr(weight)
+    p.w_dtype = _DTYPES[weight.dtype] if weight is not None else 0
+    p.out_dtype = _DTYPES[out.dtype]
+    p.cos, p.sin = _ptr(cos), _ptr(sin)
+    p.rope_batch = cos.shape[0] if cos is not None else 1
+    p.out_block_offset = out_block_offset
+    p.out, p.out_stride_b, p.out_stride_blk, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
+    p.B, p.nb, p.Hin, p.Hout, p.Cin, p.Cout = B, nb, Hin, Hout, Cin, Cout
+    _lib.check(_lib.load().ca_gate_project(C.byref(p), _stream()), "ca_gate_project")
+    return out
+
+
+def gate_scores(
+    q_blocks: torch.Tensor,  # [B, Qb, Hq, C]
+    k_blocks: torch.Tensor,  # [B, Kb, Hk, C] (a view of the K-block cache)
+    past_blocks: int,
+    scale: Optional[float] = None,
+    masked_value: float = float(torch.finfo(torch.float32).min),
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Gate logits [B, Hq, Qb, Kb] float32; entries above the block diagonal get masked_value."""
+    _require_cuda(q_blocks, k_blocks, out)
+    B, Qb, Hq, Cc = q_blocks.shape
+    Kb, Hk = k_blocks.shape[1], k_blocks.shape[2]
+    if q_blocks.stride(3) != 1 or k_blocks.stride(3) != 1:
+        raise ValueError("block tensors must have a contiguous channel dim")
+    if out is None:
+        out = torch.empty((B, Hq, Qb, Kb), dtype=torch.float32, device=q_blocks.device)
+    if out.dtype != torch.float32 or not out.is_contiguous() or out.shape != (B, Hq, Qb, Kb):
+        raise ValueError("out must be a contiguous float32 [B,Hq,Qb,Kb] tensor")
+    p = _lib.GateScoreParams()
+    p.q, p.q_stride_b, p.q_stride_blk, p.q_stride_h = q_blocks.data_ptr(), q_blocks.stride(0), q_blocks.stride(1), q_blocks.stride(2)
+    p.k, p.k_stride_b, p.k_stride_blk, p.k_stride_h = k_blocks.data_ptr(), k_blocks.stride(0), k_blocks.stride(1), k_blocks.stride(2)
+    p.q_dtype, p.k_dtype = _DTYPES[q_blocks.dtype], _DTYPES[k_blocks.dtype]
+    p.out = out.data_ptr()
+    p.B, p.Hq, p.Hk, p.Qb, p.Kb, p.Pb, p.C = B, Hq, Hk, Qb, Kb, past_blocks, Cc
+    p.scale = float(scale) if scale is not None else Cc ** -0.5
+    p.masked_value = masked_value
+    _lib.check(_lib.load().ca_gate_scores(C.byref(p), _stream()), "ca_gate_scores")
+    return out
+
+
+def flashprefill_score(
+    q: torch.Tensor,  # [B, Q, Hq, D]
+    mean_k: torch.Tensor,  # [B, Kb, Hkv, D]
+    kv_len: int,
+    block_size: int,
+    normalize: bool = True,
+):
+    """Training-free block score -> (score_raw, max_raw, score_norm|None), each [B, Qb, Kb, Hq] f32."""
+    _require_cuda(q, mean_k)
+    B, Q, Hq, D = q.shape
+    Kb, Hkv = mean_k.shape[1], mean_k.shape[2]
+    Qb = (Q + block_size - 1) // block_size
+    if q.stride(3) != 1 or mean_k.stride(3) != 1:
+        raise ValueError("q and mean_k must have a contiguous head dim")
+    raw = torch.empty((B, Qb, Kb, Hq), dtype=torch.float32, device=q.device)
+    mx = torch.empty_like(raw)
+    norm = torch.empty_like(raw) if normalize else None
+    p = _lib.FlashPrefillScoreParams()
+    p.q, p.q_stride_b, p.q_stride_t, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1), q.stride(2)
+    p.mean_k, p.k_stride_b, p.k_stride_blk, p.k_stride_h = mean_k.data_ptr(), mean_k.stride(0), mean_k.stride(1), mean_k.stride(2)
+    p.q_dtype, p.k_dtype = _DTYPES[q.dtype], _DTYPES[mean_k.dtype]
+    p.score_raw, p.max_raw, p.score_norm = raw.data_ptr(), mx.data_ptr(), _ptr(norm)
+    p.B, p.Q, p.Hq, p.Hkv, p.D, p.Kb, p.block_size, p.kv_len = B, Q, Hq, Hkv, D, Kb, block_size, kv_len
+    _lib.check(_lib.load().ca_flashprefill_score(C.byref(p), _stream()), "ca_flashprefill_score")
+    return raw, mx, norm
+
+
+# ---------------------------------------------------------------------------------------------
+# Compact KV gather
+# ---------------------------------------------------------------------------------------------
+def gather_kv(
+    kv: KvCacheView,
+    num_kv_heads: int,
+    batch: int,
+    q_len: int,
+    kv_len: int,
+    block_idx: torch.Tensor,
+    counts: torch.Tensor,
+    k_dst: torch.Tensor,  # contiguous [tokens, D] (or [pages, page, 1, D])
+    v_dst: torch.Tensor,
+    *,
+    block_size: int = 64,
+    page_offsets: Optional[torch.Tensor] = None,
+    dst_page_size: int = 256,
+    dst_row_stride_tokens: int = 0,
+    status: Optional[torch.Tensor] = None,
+) -> None:
+    """Copies the selected past blocks and the chunk of every (b, kv head) row into the compact cache."""
+    _require_cuda(kv.k, kv.v, block_idx, counts, k_dst, v_dst, page_offsets, status)
+    if not (k_dst.is_contiguous() and v_dst.is_contiguous()) or k_dst.dtype != kv.k.dtype:
+        raise ValueError("destination caches must be contiguous and match the source dtype")
+    if block_idx.dtype != torch.int32 or counts.dtype != torch.int32 or not block_idx.is_contiguous():
+        raise ValueError("block_idx/counts must be contiguous int32")
+    p = _lib.GatherParams()
+    p.kv = kv.to_c()
+    p.block_idx, p.counts, p.block_idx_stride = block_idx.data_ptr(), counts.data_ptr(), block_idx.shape[-1]
+    p.dtype = _DTYPES[kv.k.dtype]
+    p.page_offsets = _ptr(page_offsets)
+    p.dst_row_stride_tokens = dst_row_stride_tokens
+    p.k_dst, p.v_dst = k_dst.data_ptr(), v_dst.data_ptr()
+    p.dst_page_size = dst_page_size
+    p.B, p.Hkv, p.D, p.Q, p.kv_len, p.block_size = batch, num_kv_heads, kv.k.shape[-1], q_len, kv_len, block_size
+    p.status = _ptr(status)
+    _lib.check(_lib.load().ca_gather_kv(C.byref(p), _stream()), "ca_gather_kv")
+
+
+def unpack_bits(bits: torch.Tensor, kv_blocks: int) -> torch.Tensor:
+    """Packed keep bits [..., W] -> bool [..., Kb] (host-side helper for tests and statistics)."""
+    shifts = torch.arange(32, device=bits.device, dtype=torch.int64)
+    expanded = ((bits.to(torch.int64).unsqueeze(-1) & 0xFFFFFFFF) >> shifts) & 1
+    return expanded.reshape(*bits.shape[:-1], -1)[..., :kv_blocks].to(torch.bool)

@@ -107,6 +107,231 @@ typedef struct ca_attn_params {
 int ca_attn_workspace_bytes(const ca_attn_params* p, size_t* bytes_out);
 int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Block selection
+ * ---------------------------------------------------------------------------------------- */
+#define CA_RULE_THRESHOLD 0    /* keep s > threshold (strict, fp32 compare) */
+#define CA_RULE_ALPHA_ROWMAX 1 /* keep s >= alpha * rowmax, optional top-min_budget */
+#define CA_RULE_TOPK 2         /* keep the k largest, ties to the lower block index */
+#define CA_RULE_CUMMASS 3      /* keep the shortest descending prefix whose mass reaches threshold */
+#define CA_RULE_MASK 4         /* score is a bool mask (uint8): keep where non-zero */
+
+/*
+ * Per-row selection rule on a score tensor [B,H,Qb,Kb] (any strides; f32/bf16/f16, or uint8 for
+ * CA_RULE_MASK) -> packed keep bits [B,H,Qb,W], W = ceil(Kb/32), bit j%32 of word j/32 = block j.
+ * Row (b,h,i) sees key block j iff valid[b,*,i,j] (bool, broadcast over h when valid_stride_h==0)
+ * or, with valid==NULL, iff j <= Pb + i.  Optional masked softmax over the row first.
+ * Blocks j < sink and blocks with 0 <= (Pb+i)-j < local are forced on.  Rows i >= rows_voting
+ * (0 = all rows vote) produce empty bits.
+ * Replaces, one rule each:
+ *  THRESHOLD    _build_keep_block_mask / _build_keep_block_mask_chunked_fast_path
+ *               (compact_attn/modules/attention_forward_chunked_dense.py:352-403, 559-638) and kernels
+ *               build_keep_past_fast_kernel / build_keep_curr_fast_kernel
+ *               (compact_attn/csrc/compactattn/cache_fill_kernel.cu:275-326): OR over rows of
+ *               (s > thr) equals (max over rows > thr);
+ *  ALPHA_ROWMAX _flashprefill_keep_block_from_scores_rowwise
+ *               (compact_attn/modules/flashprefill_prefill.py:596-666) and the fused Triton
+ *               _flashprefill_kv_union_from_scores_kernel (:307-376);
+ *  TOPK         torch.topk + scatter in sparse_flash_attention_forward
+ *               (compact_attn/modules/attention_forward.py:43-50), with the tie order fixed;
+ *  CUMMASS      no counterpart in the reference (defined by this library: stable descending sort,
+ *               sequential fp32 prefix sum, shortest prefix with mass >= threshold);
+ *  MASK         a caller-made block mask.
+ * Top-k size: topk_k when > 0, else max(1, (topk_num*n_valid + topk_den/2) / topk_den) with
+ * n_valid the number of visible blocks of the row; clamped to n_valid.
+ */
+typedef struct ca_select_params {
+  const void* score;
+  int64_t score_stride_b, score_stride_h, score_stride_q, score_stride_k;
+  int32_t score_dtype;
+  int32_t rule;
+  const void* valid; /* optional bool (uint8) mask, strides below; NULL = block-causal */
+  int64_t valid_stride_b, valid_stride_h, valid_stride_q, valid_stride_k;
+  void* bits;      /* uint32 [B,H,Qb,W] */
+  float* prob_out; /* optional f32 [B,H,Qb,Kb]: the row the rule saw (after softmax), 0 where masked */
+  int32_t B, H, Qb, Kb, Pb;
+  int32_t softmax;
+  float threshold;
+  float alpha;
+  int32_t topk_k, topk_num, topk_den;
+  int32_t min_budget;
+  int32_t sink, local;
+  int32_t rows_voting;
+} ca_select_params;
+
+int ca_select_rows(const ca_select_params* p, ca_stream_t stream);
+
+/*
+ * Block-Union KV selection and the per-KV-head block table.
+ * Input: packed bits [B,Hkv*G,Qin,W] from ca_select_rows, or a bool mask [B,Hkv*G,Qin,Kb] by
+ * strides (Qin = 1 for a [B,H,Kb] keep_block; G = 1 for a mask that is already per KV head).
+ * keep_kv[b,hkv,j] = OR over the G heads and Qin rows, OR (j >= Kb - keep_recent), OR (j >= Pb).
+ * block_idx[row, 0:count] = ascending kept past block ids (j < Pb), rest -1; counts[row];
+ * cache_seqlens[row] = (count + Kb - Pb) * block_size; pages_per_row = ceil(cache_seqlens / page_size).
+ * Replaces _build_kv_head_union_keep_block_mask, _build_kv_head_union_past_block_indices and
+ * _build_kv_head_past_block_indices_from_kv_keep_block
+ * (compact_attn/modules/attention_forward_chunked_dense.py:641-683, 737-782, 785-819) and kernel
+ * build_past_indices_and_metadata_from_keep_block_kernel
+ * (compact_attn/csrc/compactattn/cache_fill_kernel.cu:328-385).
+ */
+typedef struct ca_union_params {
+  const void* bits; /* uint32 [B,Hkv*G,Qin,W] or NULL */
+  const void* mask; /* uint8 bool by strides or NULL */
+  int64_t mask_stride_b, mask_stride_h, mask_stride_q, mask_stride_k;
+  int32_t B, Hkv, G, Qin, Kb, Pb;
+  int32_t keep_recent;
+  int32_t block_size, page_size;
+  int32_t* block_idx; /* [B*Hkv, idx_stride] */
+  int32_t idx_stride; /* >= max(Pb, 1) */
+  int32_t* counts;        /* [B*Hkv] */
+  int32_t* cache_seqlens; /* optional [B*Hkv] */
+  int32_t* pages_per_row; /* optional [B*Hkv] */
+  void* keep_kv;          /* optional bool (uint8) [B,Hkv,Kb] */
+} ca_union_params;
+
+int ca_union_table(const ca_union_params* p, ca_stream_t stream);
+
+/*
+ * Paged metadata of the compact cache: page_offsets[r] = exclusive prefix of pages_per_row
+ * (page_offsets[rows] = total) and block_table[r, slot] = page_offsets[r] + slot for
+ * slot < pages_per_row[r], else 0.  Replaces build_block_table_kernel
+ * (compact_attn/csrc/compactattn/cache_fill_kernel.cu:163-190).
+ */
+int ca_paged_metadata(const int32_t* pages_per_row, int rows, int32_t* page_offsets, int32_t* block_table,
+                      int max_pages, ca_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Block scoring
+ * ---------------------------------------------------------------------------------------- */
+#define CA_POOL_MAX 1
+#define CA_POOL_MIN 2
+#define CA_POOL_AVG 4
+
+/*
+ * Block pooling over tokens: x [B,L,H,D] (strides, f32/bf16/f16) -> out[b, out_block_offset + blk,
+ * h, :] = [max | min | avg] (the kinds present, in that order) of tokens blk*bs .. min((blk+1)*bs, L),
+ * fp32 accumulation, avg divides by the tokens present.  Writing at a block offset appends to a
+ * selector cache in place.
+ * Replaces AttnGate.compress_query_blocks / compress_key_blocks pooling
+ * (compact_attn/prefill_sparse/attn_gate.py:113-130), the Triton compute_mean_vector
+ * (compact_attn/flashprefill_vendor/flashprefill_native_forward.py:44-95) and the mean-K cache
+ * update (compact_attn/prefill_sparse/llama/modeling_llama_flashprefill_compactattn.py:121-150).
+ */
+typedef struct ca_pool_params {
+  const void* x;
+  int64_t x_stride_b, x_stride_t, x_stride_h;
+  int32_t x_dtype;
+  int32_t out_dtype;
+  void* out; /* [B, >= out_block_offset + ceil(L/bs), H, nk*D] by strides */
+  int64_t out_stride_b, out_stride_blk, out_stride_h;
+  int32_t out_block_offset;
+  int32_t B, L, H, D, block_size;
+  int32_t kinds; /* CA_POOL_* bits */
+} ca_pool_params;
+
+int ca_pool_blocks(const ca_pool_params* p, ca_stream_t stream);
+
+/*
+ * Per-head linear projection of pooled blocks, block RoPE (half-rotation form) and write at a
+ * block offset of the destination (the gate's K-block cache, or the chunk's Q blocks):
+ *   y[b,blk,h,:] = x[b,blk,h / (Hout/Hin),:] @ w[h]   (w == NULL: identity)
+ *   out = y*cos + rotate_half(y)*sin                  (cos == NULL: no RoPE)
+ * x is contiguous f32 [B,nb,Hin,Cin]; w contiguous [Hout,Cin,Cout]; cos/sin f32 [rope_batch,nb,Cout].
+ * Replaces MultiHeadLinear.forward (compact_attn/prefill_sparse/attn_gate.py:29-33),
+ * AttnGate.apply_block_position_embeddings (:132-171) and _compactattn_append_cached_k_blocks
+ * (compact_attn/prefill_sparse/llama/modeling_llama_seerattn_chunked_dense.py:426-478).
+ */
+typedef struct ca_project_params {
+  const float* x;
+  const void* w;
+  int32_t w_dtype;
+  int32_t out_dtype;
+  const float* cos;
+  const float* sin;
+  int32_t rope_batch;
+  int32_t out_block_offset;
+  void* out;
+  int64_t out_stride_b, out_stride_blk, out_stride_h;
+  int32_t B, nb, Hin, Hout, Cin, Cout;
+} ca_project_params;
+
+int ca_gate_project(const ca_project_params* p, ca_stream_t stream);
+
+/*
+ * Gate logits: out[b,h,i,j] = (q[b,i,h,:] . k[b,j,h / (Hq/Hk),:]) * scale for j <= Pb + i, else
+ * masked_value; out is contiguous f32 [B,Hq,Qb,Kb].  The softmax of
+ * AttnGate.score_compressed_blocks (compact_attn/prefill_sparse/attn_gate.py:173-204) is applied
+ * by ca_select_rows (softmax = 1), fused with the selection rule.
+ */
+typedef struct ca_gate_score_params {
+  const void* q; /* [B,Qb,Hq,C] by strides */
+  int64_t q_stride_b, q_stride_blk, q_stride_h;
+  const void* k; /* [B,Kb,Hk,C] by strides */
+  int64_t k_stride_b, k_stride_blk, k_stride_h;
+  int32_t q_dtype, k_dtype;
+  float* out;
+  int32_t B, Hq, Hk, Qb, Kb, Pb, C;
+  float scale;
+  float masked_value;
+} ca_gate_score_params;
+
+int ca_gate_scores(const ca_gate_score_params* p, ca_stream_t stream);
+
+/*
+ * Training-free block score.  For q-block i, head h, key block j over the tokens t of the q-block
+ * with P + t >= (j+1)*bs - 1:  S = (q_t . mean_k_j) * D^-0.5 * log2(e),  max_raw = max_t S,
+ * score_raw = sum_t 2^(S - max_raw)  (-inf where no token qualifies); all [B,Qb,Kb,Hq] f32.
+ * score_norm (optional) = score_raw * 2^(max_raw - max_j max_raw) / (sum_j ... + 1e-9), 0 where
+ * max_raw = -inf.
+ * Replaces the Triton compute_block_score_chunked and normalize_scores
+ * (compact_attn/flashprefill_vendor/flashprefill_native_forward.py:98-207, 365-374) as driven by
+ * flash_prefill_score_chunked_from_mean_k (:541-586).
+ */
+typedef struct ca_flashprefill_score_params {
+  const void* q; /* [B,Q,Hq,D] by strides */
+  int64_t q_stride_b, q_stride_t, q_stride_h;
+  const void* mean_k; /* [B,Kb,Hkv,D] by strides */
+  int64_t k_stride_b, k_stride_blk, k_stride_h;
+  int32_t q_dtype, k_dtype;
+  float* score_raw;
+  float* max_raw;
+  float* score_norm; /* optional */
+  int32_t B, Q, Hq, Hkv, D, Kb, block_size, kv_len;
+} ca_flashprefill_score_params;
+
+int ca_flashprefill_score(const ca_flashprefill_score_params* p, ca_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Compact KV gather (cache fill)
+ * ---------------------------------------------------------------------------------------- */
+/*
+ * For each row r = (b,hkv): copies blocks block_idx[r, 0:counts[r]] (block_size tokens x D each)
+ * and then the chunk's Q tokens of K and V from the source cache into the compact cache at token
+ * position  base(r) + rank*block_size,  base(r) = page_offsets[r]*dst_page_size  (page_offsets
+ * from ca_paged_metadata) or r*dst_row_stride_tokens when page_offsets is NULL.  Destination
+ * caches are contiguous [tokens, D] (viewed by the caller as [pages, dst_page_size, 1, D]).
+ * Replaces build_paged_kv_cache_from_keep_block_fast / build_paged_kv_cache_from_token_mask
+ * (compact_attn/kernels/varlen/indexed_dense_prefill_varlen.py:466-766, 1414-1470) and kernels
+ * cache_fill_from_past_indices_compact_kernel + cache_fill_current_tail_kernel
+ * (compact_attn/csrc/compactattn/cache_fill_kernel.cu:596-720).
+ */
+typedef struct ca_gather_params {
+  ca_kv_layout kv;
+  const int32_t* block_idx;
+  const int32_t* counts;
+  int32_t block_idx_stride;
+  int32_t dtype; /* CA_DTYPE_BF16 or CA_DTYPE_F16 (a byte copy of 16-bit elements) */
+  const int32_t* page_offsets; /* optional [B*Hkv + 1] */
+  int64_t dst_row_stride_tokens;
+  void* k_dst;
+  void* v_dst;
+  int32_t dst_page_size;
+  int32_t B, Hkv, D, Q, kv_len, block_size;
+  int32_t* status; /* optional */
+} ca_gather_params;
+
+int ca_gather_kv(const ca_gather_params* p, ca_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

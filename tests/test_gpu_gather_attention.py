@@ -1,0 +1,204 @@
+"""GPU parity of the compact KV gather (byte-exact) and of the block-table attention kernel
+(bf16/f16: max-abs 2e-2, mean-abs 2e-3 against the fp32 oracle, the tolerance the path's
+specification states)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import compact_oracle as co
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, MEAN_ABS = 2e-2, 2e-3
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from compactattention_b200 import ops as o
+
+    return o
+
+
+def T(a):
+    return torch.from_numpy(np.asarray(a))
+
+
+def random_table(B, Hkv, Pb, density, g):
+    keep = torch.rand((B, Hkv, max(Pb, 1)), generator=g) < density
+    if Pb == 0:
+        keep[:] = False
+    kv = torch.cat([keep[..., :Pb], torch.ones((B, Hkv, 0), dtype=torch.bool)], dim=-1)
+    idx = torch.full((B, Hkv, max(Pb, 1)), -1, dtype=torch.int32)
+    counts = torch.zeros((B, Hkv), dtype=torch.int32)
+    for b in range(B):
+        for h in range(Hkv):
+            sel = torch.nonzero(kv[b, h]).flatten().to(torch.int32)
+            idx[b, h, : sel.numel()] = sel
+            counts[b, h] = sel.numel()
+    return idx, counts
+
+
+def paged_copy(k, v, g):
+    """Scatter a contiguous [B,K,Hkv,D] cache into randomly permuted 64-token pages."""
+    B, K, Hkv, D = k.shape
+    n = B * K // 64
+    perm = torch.randperm(n, generator=g)
+    kp, vp = torch.empty((n, 64, Hkv, D), dtype=k.dtype), torch.empty((n, 64, Hkv, D), dtype=v.dtype)
+    kp[perm], vp[perm] = k.reshape(n, 64, Hkv, D), v.reshape(n, 64, Hkv, D)
+    return kp, vp, perm.to(torch.int32).view(B, K // 64).contiguous()
+
+
+def check_attention(out, want):
+    err = (out.float().cpu() - want).abs()
+    assert not torch.isnan(out.float()).any()
+    assert err.max().item() < MAX_ABS and err.mean().item() < MEAN_ABS, (err.max().item(), err.mean().item())
+
+
+def run_attention(ops, q, k, v, idx, counts, bs, layout="seq", g=None, lse=False):
+    B, Q, Hq, D = q.shape
+    K, Hkv = k.shape[1], k.shape[2]
+    if layout == "seq":
+        kv = ops.KvCacheView.from_seq_first(k.cuda(), v.cuda())
+    elif layout == "heads":
+        kv = ops.KvCacheView.from_heads_first(k.transpose(1, 2).contiguous().cuda(), v.transpose(1, 2).contiguous().cuda())
+    else:
+        kp, vp, table = paged_copy(k, v, g)
+        kv = ops.KvCacheView.from_paged(kp.cuda(), vp.cuda(), table.cuda())
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lse_t = torch.empty((B, Hq, Q), dtype=torch.float32, device="cuda") if lse else None
+    out = ops.attn_compact(q.cuda(), kv, K, Hkv, None if idx is None else idx.cuda(), None if counts is None else counts.cuda(),
+                           block_size=bs, status=status, lse=lse_t)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    return (out, lse_t) if lse else out
+
+
+def test_attention_golden(ops, golden):
+    g = golden("gather_attention")
+    B, Q, K, Hq, Hkv, D, bs = [int(x) for x in g["meta"]]
+    q, k, v = T(g["q"]), T(g["k"]), T(g["v"])  # fp16-representable values
+    idx, counts = T(g["idx"]), T(g["counts"])
+    out = run_attention(ops, q, k, v, idx, counts, bs)
+    check_attention(out, T(g["out_compact"]))
+    dense = run_attention(ops, q, k, v, None, None, bs)
+    check_attention(dense, T(g["out_dense"]))
+
+
+@pytest.mark.parametrize("B,Q,K,Hq,Hkv,bs,density,dtype,layout", [
+    (1, 256, 8192, 32, 8, 64, 0.2, torch.bfloat16, "seq"),     # the CPU configuration's shape
+    (1, 1024, 32768, 32, 8, 64, 0.1, torch.bfloat16, "paged"),  # 32K paged cache, permuted pages
+    (2, 256, 2048, 8, 2, 64, 0.3, torch.bfloat16, "seq"),
+    (1, 256, 4096, 28, 4, 64, 0.25, torch.bfloat16, "seq"),     # G = 7
+    (1, 256, 4096, 32, 8, 128, 0.25, torch.bfloat16, "seq"),    # block 128
+    (1, 256, 4096, 32, 8, 64, 0.25, torch.float16, "heads"),    # heads-first source, f16
+    (1, 64, 64, 4, 4, 64, None, torch.bfloat16, "seq"),         # first chunk: no past, one block
+    (1, 128, 1152, 2, 2, 64, 0.0, torch.bfloat16, "seq"),       # nothing selected: chunk only
+    (1, 192, 1216, 16, 2, 64, 1.0, torch.bfloat16, "paged"),    # everything selected, G = 8
+    (1, 2048, 6144, 8, 8, 64, 0.5, torch.bfloat16, "seq"),      # long chunk, G = 1
+])
+def test_attention_random(ops, B, Q, K, Hq, Hkv, bs, density, dtype, layout):
+    g = torch.Generator().manual_seed(Q * 7 + K)
+    q = torch.randn((B, Q, Hq, 128), generator=g).to(dtype)
+    k = torch.randn((B, K, Hkv, 128), generator=g).to(dtype)
+    v = torch.randn((B, K, Hkv, 128), generator=g).to(dtype)
+    if density is None:
+        idx = counts = None
+    else:
+        idx, counts = random_table(B, Hkv, (K - Q) // bs, density, g)
+    out, lse = run_attention(ops, q, k, v, idx, counts, bs, layout, g, lse=True)
+    want, want_lse = co.compact_attention(q, k, v, idx, counts, bs, return_lse=True)
+    check_attention(out, want)
+    assert torch.allclose(lse.cpu(), want_lse, rtol=1e-3, atol=2e-2)
+
+
+def test_attention_peaked_scores(ops):
+    """Large-magnitude logits (sharp softmax, frequent running-max updates)."""
+    g = torch.Generator().manual_seed(5)
+    q = (torch.randn((1, 128, 8, 128), generator=g) * 4).to(torch.bfloat16)
+    k = (torch.randn((1, 2048, 2, 128), generator=g) * 4).to(torch.bfloat16)
+    v = torch.randn((1, 2048, 2, 128), generator=g).to(torch.bfloat16)
+    idx, counts = random_table(1, 2, 30, 0.5, g)
+    out = run_attention(ops, q, k, v, idx, counts, 64)
+    check_attention(out, co.compact_attention(q, k, v, idx, counts, 64))
+
+
+def test_attention_strided_out_and_scale(ops):
+    g = torch.Generator().manual_seed(6)
+    q = torch.randn((1, 128, 8, 128), generator=g).to(torch.bfloat16)
+    k = torch.randn((1, 1024, 2, 128), generator=g).to(torch.bfloat16)
+    v = torch.randn((1, 1024, 2, 128), generator=g).to(torch.bfloat16)
+    idx, counts = random_table(1, 2, 14, 0.4, g)
+    buf = torch.zeros((1, 128, 8, 256), dtype=torch.bfloat16, device="cuda")
+    kv = ops.KvCacheView.from_seq_first(k.cuda(), v.cuda())
+    ops.attn_compact(q.cuda(), kv, 1024, 2, idx.cuda(), counts.cuda(), softmax_scale=0.05, out=buf[..., :128])
+    check_attention(buf[..., :128], co.compact_attention(q, k, v, idx, counts, 64, softmax_scale=0.05))
+    assert float(buf[..., 128:].abs().max()) == 0.0
+
+
+def test_attention_bad_table_is_reported_not_fatal(ops):
+    """Out-of-range table entries are clamped and flagged in the status word; nothing faults."""
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn((1, 64, 2, 128), generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn((1, 512, 1, 128), generator=g).to(torch.bfloat16).cuda()
+    kv = ops.KvCacheView.from_seq_first(k, k.clone())
+    idx = torch.tensor([[0, 99, -5, 3, -1, -1, -1]], dtype=torch.int32, device="cuda")
+    counts = torch.tensor([4], dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.attn_compact(q, kv, 512, 1, idx, counts, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) & 2
+    assert not torch.isnan(out.float()).any()
+
+
+def test_attention_contract_errors(ops):
+    q = torch.zeros((1, 64, 2, 64), dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros((1, 128, 1, 64), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="head dim"):
+        ops.attn_compact(q, ops.KvCacheView.from_seq_first(k, k), 128, 1, None, None)
+    q = torch.zeros((1, 64, 2, 128), dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros((1, 160 + 64, 1, 128), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError, match="multiple of 64"):
+        ops.KvCacheView.from_seq_first(k, k)
+
+
+@pytest.mark.parametrize("B,Q,K,Hkv,bs,density,layout,page", [(1, 128, 640, 2, 64, 0.2, "seq", 256), (2, 256, 4096, 4, 64, 0.3, "paged", 256),
+                                                              (1, 256, 4096, 2, 128, 0.5, "seq", 128), (1, 64, 64, 1, 64, 0.0, "seq", 256)])
+def test_gather_byte_exact(ops, B, Q, K, Hkv, bs, density, layout, page):
+    g = torch.Generator().manual_seed(K + Q)
+    k = torch.randn((B, K, Hkv, 128), generator=g).to(torch.bfloat16)
+    v = torch.randn((B, K, Hkv, 128), generator=g).to(torch.bfloat16)
+    idx, counts = random_table(B, Hkv, (K - Q) // bs, density, g)
+    kc, vc, table, seqlens = co.gather_compact_kv(k, v, idx, counts, Q, bs, page_size=page)
+    if layout == "seq":
+        kv = ops.KvCacheView.from_seq_first(k.cuda(), v.cuda())
+    else:
+        kp, vp, pt = paged_copy(k, v, g)
+        kv = ops.KvCacheView.from_paged(kp.cuda(), vp.cuda(), pt.cuda())
+    pages = ((counts + Q // bs) * bs + page - 1) // page
+    offs, got_table = ops.paged_metadata(pages.to(torch.int32).cuda(), max_pages=int(pages.max()))
+    kd = torch.zeros(kc.shape, dtype=torch.bfloat16, device="cuda")
+    vd = torch.zeros(vc.shape, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.gather_kv(kv, Hkv, B, Q, K, idx.cuda(), counts.cuda(), kd, vd, block_size=bs, page_offsets=offs, dst_page_size=page, status=status)
+    assert torch.equal(kd.cpu(), kc) and torch.equal(vd.cpu(), vc)
+    assert torch.equal(got_table.cpu(), table) and int(status.item()) == 0
+
+
+def test_gather_golden(ops, golden):
+    g = golden("gather_attention")
+    B, Q, K, Hq, Hkv, D, bs = [int(x) for x in g["meta"]]
+    k, v = T(g["k"]).to(torch.float16), T(g["v"]).to(torch.float16)
+    idx, counts = T(g["idx"]), T(g["counts"])
+    pages = T(g["block_table"]).shape[1]
+    kv = ops.KvCacheView.from_seq_first(k.cuda(), v.cuda())
+    ppr = ((counts + Q // bs) * bs + 255) // 256
+    offs, table = ops.paged_metadata(ppr.to(torch.int32).cuda(), max_pages=pages)
+    kd = torch.zeros(T(g["k_cache"]).shape, dtype=torch.float16, device="cuda")
+    vd = torch.zeros_like(kd)
+    ops.gather_kv(kv, Hkv, B, Q, K, idx.cuda(), counts.cuda(), kd, vd, block_size=bs, page_offsets=offs, dst_page_size=256)
+    assert torch.equal(kd.cpu(), T(g["k_cache"])) and torch.equal(vd.cpu(), T(g["v_cache"]))
+    assert torch.equal(table.cpu(), T(g["block_table"]))

@@ -1,0 +1,145 @@
+"""GPU parity of block scoring: pooling, gate projection + RoPE + cache append, gate logits and
+softmax, FlashPrefill block score and normalisation.  Floating point: scores must agree with the
+fp32 oracle within 1e-3 relative (the tolerance the path's specification states); pooling of
+fp32 inputs within 1e-6."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import compact_oracle as co
+
+pytestmark = pytest.mark.gpu
+
+REL = 1e-3
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from compactattention_b200 import ops as o
+
+    return o
+
+
+def T(a):
+    return torch.from_numpy(np.asarray(a))
+
+
+def rel_err(got, want):
+    scale = want.abs().amax(dim=-1, keepdim=True).clamp_min(1e-30)
+    return ((got - want).abs() / scale).max().item()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("L,bs", [(1024, 64), (674, 64), (256, 128), (64, 64)])
+def test_pool_blocks(ops, dtype, L, bs):
+    g = torch.Generator().manual_seed(L + bs)
+    x = torch.randn((2, L, 4, 128), generator=g).to(dtype)
+    for kinds in (("avg",), ("max", "min", "avg"), ("max",), ("min", "avg")):
+        got = ops.pool_blocks(x.cuda(), bs, kinds).cpu()
+        want = co.pool_blocks(x.float(), bs, kinds)
+        assert torch.allclose(got, want, rtol=1e-5, atol=1e-6), kinds
+    # mean-K as the training-free selector stores it: in the input dtype
+    got = ops.pool_blocks(x.cuda(), bs, ("avg",), out_dtype=dtype).cpu()
+    assert got.dtype == dtype
+    assert torch.equal(got, co.mean_pool_blocks(x, bs)) or torch.allclose(got.float(), co.mean_pool_blocks(x, bs).float(), rtol=1e-2, atol=1e-3)
+
+
+def test_pool_append_into_cache(ops):
+    g = torch.Generator().manual_seed(3)
+    cache = torch.zeros((1, 40, 2, 128), dtype=torch.float32, device="cuda")
+    full = torch.randn((1, 40 * 64, 2, 128), generator=g)
+    for c in range(5):  # five chunks of 8 blocks
+        ops.pool_blocks(full[:, c * 512:(c + 1) * 512].cuda(), 64, ("avg",), out=cache, out_block_offset=c * 8)
+    assert torch.allclose(cache.cpu(), co.pool_blocks(full, 64, ("avg",)), rtol=1e-5, atol=1e-6)
+
+
+def test_mean_k_golden(ops, golden):
+    g = golden("flashprefill")
+    k = T(g["k"]).float()
+    got = ops.pool_blocks(k.cuda(), 64, ("avg",)).cpu()
+    assert torch.allclose(got, T(g["mean_k"]), rtol=1e-5, atol=1e-6)
+    got_r = ops.pool_blocks(k[:, :674].contiguous().cuda(), 64, ("avg",)).cpu()
+    assert torch.allclose(got_r, T(g["mean_k_ragged"]), rtol=1e-5, atol=1e-6)
+
+
+def test_attn_gate_golden(ops, golden):
+    """Whole learned-gate chain against the reference AttnGate's outputs."""
+    g = golden("attn_gate")
+    B, Q, K, Hq, Hkv, D, bs = [int(x) for x in g["meta"]]
+    Qb, Kb = Q // bs, K // bs
+    q, k = T(g["q"]).float().cuda(), T(g["k"]).float().cuda()
+    cos, sin = T(g["cos"]).cuda(), T(g["sin"]).cuda()
+    for name, kk in (("Qavg_Kmaxminavg", ("max", "min", "avg")), ("Qavg_Kavg", ("avg",))):
+        wq = T(g[f"{name}_wq"]).float().cuda() if f"{name}_wq" in g.files else None
+        wk = T(g[f"{name}_wk"]).float().cuda()
+        q_pooled = ops.pool_blocks(q, bs, ("avg",))
+        k_pooled = ops.pool_blocks(k, bs, kk)
+        qb = ops.gate_project(q_pooled, wq)
+        kb = ops.gate_project(k_pooled, wk)
+        assert torch.allclose(qb.cpu(), T(g[f"{name}_qb"]), rtol=1e-4, atol=1e-5)
+        assert torch.allclose(kb.cpu(), T(g[f"{name}_kb"]), rtol=1e-4, atol=1e-5)
+        qb_r = ops.gate_project(q_pooled, wq, cos[:, Kb - Qb:], sin[:, Kb - Qb:])
+        # K blocks are projected, roped and appended into a heads-first cache with spare capacity
+        cache = torch.zeros((B, Hq, 16, 128), dtype=torch.float32, device="cuda")
+        ops.gate_project(k_pooled[:, :3].contiguous(), wk, cos[:, :3], sin[:, :3], out=cache.transpose(1, 2))
+        ops.gate_project(k_pooled[:, 3:].contiguous(), wk, cos[:, 3:], sin[:, 3:], out=cache.transpose(1, 2), out_block_offset=3)
+        kb_r = cache.transpose(1, 2)[:, :Kb]
+        assert torch.allclose(qb_r.cpu(), T(g[f"{name}_qb_rope"]), rtol=1e-4, atol=1e-5)
+        assert torch.allclose(kb_r.cpu(), T(g[f"{name}_kb_rope"]), rtol=1e-4, atol=1e-5)
+        logits = ops.gate_scores(qb_r, kb_r, Kb - Qb)
+        want_raw = T(g[f"{name}_score_raw"])
+        vis = T(g["mask"]).expand_as(want_raw)
+        assert rel_err(logits.cpu()[vis], want_raw[vis]) < REL
+        assert torch.equal(logits.cpu()[~vis], want_raw[~vis])  # finfo.min fill
+        prob = torch.empty_like(logits)
+        ops.select_rows(logits, Kb - Qb, "threshold", softmax=True, threshold=5e-4, prob_out=prob)
+        assert rel_err(prob.cpu(), T(g[f"{name}_score_softmax"])) < REL
+
+
+@pytest.mark.parametrize("B,Qb,Kb,Hq,Hk,dtype", [(1, 16, 512, 32, 32, torch.bfloat16), (1, 16, 2048, 8, 2, torch.float32),
+                                                 (2, 4, 130, 28, 4, torch.bfloat16), (1, 128, 256, 4, 4, torch.float16)])
+def test_gate_scores_random(ops, B, Qb, Kb, Hq, Hk, dtype):
+    g = torch.Generator().manual_seed(Kb)
+    qb = torch.randn((B, Qb, Hq, 128), generator=g).to(dtype)
+    kb = torch.randn((B, Kb, Hk, 128), generator=g).to(dtype)
+    Pb = Kb - Qb
+    mask = co.gate_block_causal_mask(Qb * 64, Kb * 64, 64, B)
+    want = co.gate_score(qb, kb, mask, use_softmax=False)
+    got = ops.gate_scores(qb.cuda(), kb.cuda(), Pb).cpu()
+    vis = mask.expand_as(want)
+    assert rel_err(got.masked_fill(~vis, 0), want.masked_fill(~vis, 0)) < REL
+    prob = torch.empty_like(got, device="cuda")
+    ops.select_rows(got.cuda(), Pb, "threshold", softmax=True, threshold=5e-4, prob_out=prob)
+    assert rel_err(prob.cpu(), co.gate_score(qb, kb, mask, use_softmax=True)) < REL
+
+
+def test_flashprefill_score_golden(ops, golden):
+    g = golden("flashprefill")
+    B, Q, K, Hq, Hkv, D, bs = [int(x) for x in g["meta"]]
+    q = T(g["q"]).float().cuda()
+    mean_k = T(g["mean_k"]).cuda()
+    raw, mx, norm = ops.flashprefill_score(q, mean_k, K, bs)
+    ref_mx, ref_sc, ref_norm = T(g["max_raw"]), T(g["score_raw"]), T(g["score_norm"])
+    fin = torch.isfinite(ref_mx)
+    assert torch.equal(torch.isfinite(mx.cpu()), fin)
+    assert torch.allclose(mx.cpu()[fin], ref_mx[fin], rtol=1e-4, atol=1e-4)
+    assert torch.allclose(raw.cpu()[fin], ref_sc[fin], rtol=1e-3, atol=1e-5)
+    assert ((norm.cpu() - ref_norm).abs().max() / ref_norm.max()).item() < REL
+
+
+@pytest.mark.parametrize("Q,K,Hq,Hkv,bs,dtype", [(1024, 8192, 8, 2, 64, torch.bfloat16), (512, 4096, 4, 4, 128, torch.bfloat16),
+                                                 (192, 704, 28, 4, 64, torch.float16), (100, 1060, 4, 1, 64, torch.float32)])
+def test_flashprefill_score_random(ops, Q, K, Hq, Hkv, bs, dtype):
+    g = torch.Generator().manual_seed(Q + K)
+    q = torch.randn((1, Q, Hq, 128), generator=g).to(dtype)
+    k = torch.randn((1, K, Hkv, 128), generator=g).to(dtype)
+    mean_k = co.mean_pool_blocks(k, bs)
+    raw, mx, norm = ops.flashprefill_score(q.cuda(), mean_k.cuda(), K, bs)
+    o_raw, o_mx = co.flashprefill_block_score_raw(q, mean_k, K, bs)
+    o_norm = co.flashprefill_normalize_scores(o_raw, o_mx)
+    fin = torch.isfinite(o_mx)
+    assert torch.equal(torch.isfinite(mx.cpu()), fin)
+    assert torch.allclose(mx.cpu()[fin], o_mx[fin], rtol=1e-4, atol=1e-4)
+    assert ((norm.cpu() - o_norm).abs().max() / o_norm.max()).item() < REL

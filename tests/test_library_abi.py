@@ -1,0 +1,90 @@
+"""CPU checks of the C-ABI boundary: the library builds/loads without a GPU driver and exports
+every function that include/compactattn_b200.h declares (no compute calls here)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "compactattn_b200.h"
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from compactattention_b200 import _lib, build
+
+    build.build()
+    return _lib.load()
+
+
+def declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(ca_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_functions_are_exported(lib):
+    names = declared_functions()
+    assert "ca_attn_compact" in names and "ca_union_table" in names and len(names) >= 13
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+
+
+def test_binding_table_matches_header(lib):
+    from compactattention_b200 import _lib
+
+    assert set(_lib.exported_names()) == set(declared_functions())
+
+
+def test_abi_version_and_error_string(lib):
+    assert lib.ca_abi_version() == 1
+    assert isinstance(lib.ca_last_error(), bytes)
+    assert lib.ca_launch_count() >= 0
+
+
+def test_contract_violations_return_codes_without_gpu(lib):
+    from compactattention_b200 import _lib
+
+    p = _lib.AttnParams()  # all zero: null pointers
+    rc = lib.ca_attn_compact(ctypes.byref(p), None)
+    assert rc == -1 and b"non-null" in lib.ca_last_error()
+    u = _lib.UnionParams()
+    assert lib.ca_union_table(ctypes.byref(u), None) == -1
+    s = _lib.SelectParams()
+    assert lib.ca_select_rows(ctypes.byref(s), None) == -1
+    g = _lib.GatherParams()
+    assert lib.ca_gather_kv(ctypes.byref(g), None) == -1
+
+
+def test_struct_sizes_match_c_layout():
+    """ctypes mirrors must have the size the C compiler gives the header's structs."""
+    import subprocess, tempfile, textwrap
+    from compactattention_b200 import _lib
+
+    src = textwrap.dedent("""
+        #include <stdio.h>
+        #include "compactattn_b200.h"
+        int main(void) {
+          printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(ca_kv_layout), sizeof(ca_attn_params),
+                 sizeof(ca_select_params), sizeof(ca_union_params), sizeof(ca_pool_params),
+                 sizeof(ca_project_params), sizeof(ca_gate_score_params), sizeof(ca_flashprefill_score_params),
+                 sizeof(ca_gather_params));
+          return 0;
+        }""")
+    with tempfile.TemporaryDirectory() as d:
+        c = Path(d) / "sz.c"
+        c.write_text(src)
+        exe = Path(d) / "sz"
+        subprocess.run(["gcc", "-I", str(ROOT / "include"), str(c), "-o", str(exe)], check=True)
+        sizes = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
+    mirrors = [_lib.KvLayout, _lib.AttnParams, _lib.SelectParams, _lib.UnionParams, _lib.PoolParams,
+               _lib.ProjectParams, _lib.GateScoreParams, _lib.FlashPrefillScoreParams, _lib.GatherParams]
+    assert sizes == [ctypes.sizeof(m) for m in mirrors]
+
+
+def test_ops_refuse_cpu_tensors():
+    import torch
+    from compactattention_b200 import ops
+
+    with pytest.raises(ValueError, match="CUDA tensors only"):
+        ops.union_table(mask=torch.zeros((1, 4, 8), dtype=torch.bool), num_kv_heads=1, kv_blocks=8, past_blocks=4)
