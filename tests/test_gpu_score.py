@@ -82,7 +82,7 @@ def test_attn_gate_golden(ops, golden):
         assert torch.allclose(kb.cpu(), T(g[f"{name}_kb"]), rtol=1e-4, atol=1e-5)
         qb_r = ops.gate_project(q_pooled, wq, cos[:, Kb - Qb:], sin[:, Kb - Qb:])
         # K blocks are projected, roped and appended into a heads-first cache with spare capacity
-        cache = torch.zeros((B, Hq, 16, 128), dtype=torch.float32, device="cuda")
+        cache = torch.zeros((B, wk.shape[0], 16, 128), dtype=torch.float32, device="cuda")
         ops.gate_project(k_pooled[:, :3].contiguous(), wk, cos[:, :3], sin[:, :3], out=cache.transpose(1, 2))
         ops.gate_project(k_pooled[:, 3:].contiguous(), wk, cos[:, 3:], sin[:, 3:], out=cache.transpose(1, 2), out_block_offset=3)
         kb_r = cache.transpose(1, 2)[:, :Kb]
