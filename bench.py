@@ -1,0 +1,434 @@
+#!/usr/bin/env python
+"""Benchmark of the CompactAttention chunked-prefill hot path on B200.
+
+Workload (N = 1): one Llama-3.1-8B-shaped attention layer (32 q heads / 8 KV heads, d = 128, bf16),
+a 1024-token chunk appended at the end of a 128K-token paged KV cache (64-token pages, randomly
+permuted page ids), block size 64.  Selection = learned-gate-style selector with random-init weights
+(pooled Q and pooled K, 128 -> 128 projections per head, block RoPE) and per-row block top-k at 20 %
+density plus sink and local blocks.  A step is one pass of the path for one chunk:
+pool Q/K blocks, project + RoPE + append to the gate's K-block cache, gate logits, top-k rows,
+Block-Union table, block-table attention.  Data is synthetic (seeded N(0,1)); steps rotate over
+several independent layer states so consecutive steps read different HBM (total > L2).
+
+At N > 1 the KV heads are sharded over the ranks (tensor parallel): every rank selects and attends
+its own heads, then the layer output partial sums are all-reduced over NCCL; total work is fixed
+("strong" scaling) and the value is the max-over-ranks latency.
+
+`--impl reference` times the CPU restatement of the reference's path (oracle port, torch on all host
+cores) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HQ, HKV, D, BS = 32, 8, 128, 64
+METRIC = "per-chunk attn latency @128K ctx, chunk 1024"
+# DRAM bytes (read + write) of one attention launch of this workload from the ncu capture summarised
+# in profiles/attn_compact_kernel_c3_128k.md (captured on a 32K-context case and scaled by selected
+# blocks, traffic is proportional to them); None until a capture exists.
+NCU_ATTN_TRAFFIC_BYTES = None
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["native", "reference"], default="native")
+    ap.add_argument("--kv-len", type=int, default=131072)
+    ap.add_argument("--chunk", type=int, default=1024)
+    ap.add_argument("--density", type=float, default=0.2)
+    ap.add_argument("--layers", type=int, default=4, help="independent layer states the steps rotate over")
+    ap.add_argument("--seed", type=int, default=1234 + 3)
+    ap.add_argument("--no-dense", action="store_true", help="skip the dense comparator")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def load_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        p = json.loads(path.read_text())
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons during the timed region."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.rows, self.proc = [], None
+        self.device_index = device_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.device_index)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, idx in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7), ("sw_power_cap", 8)):
+                if len(r) > idx and r[idx].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_layer_inputs(seed, kv_len, chunk, hq, hkv, device):
+    """Seeded synthetic tensors of one layer: logical K/V [1,K,hkv,D], the chunk's Q, gate weights."""
+    device = torch.device(device)
+    g = torch.Generator(device=device).manual_seed(seed)
+    past = kv_len - chunk
+    k = torch.randn((1, kv_len, hkv, D), generator=g, dtype=torch.float32, device=device).to(torch.bfloat16)
+    v = torch.randn((1, kv_len, hkv, D), generator=g, dtype=torch.float32, device=device).to(torch.bfloat16)
+    q = torch.randn((1, chunk, hq, D), generator=g, dtype=torch.float32, device=device).to(torch.bfloat16)
+    wq = (torch.randn((hq, D, 128), generator=g, device=device) * 0.02).to(torch.bfloat16)
+    wk = (torch.randn((hkv, D, 128), generator=g, device=device) * 0.02).to(torch.bfloat16)
+    perm = torch.randperm(kv_len // 64, generator=g, device=device).to(torch.int32).view(1, -1)
+    return {"k": k, "v": v, "q": q, "wq": wq, "wk": wk, "perm": perm, "past": past}
+
+
+def block_rope_tables(n_blocks, block_size, device):
+    inv = 1.0 / (500000.0 ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))
+    pos = torch.arange(0, n_blocks * block_size, block_size, dtype=torch.float32)
+    ang = torch.cat([pos.view(-1, 1) * inv.view(1, -1)] * 2, dim=-1)
+    return ang.cos().unsqueeze(0).to(device), ang.sin().unsqueeze(0).to(device)
+
+
+def run_native(args):
+    from compactattention_b200 import _lib, ops
+    from compactattention_b200.chunk_driver import GateSelectorState, SelectionRule, select_and_attend
+    from compactattention_b200.paged_cache import PagedKVCache
+    from compactattention_b200.prefill_sparse.attn_gate import ATTNGATE_CLASSES
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU path); use --impl reference for the CPU baseline")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group(backend="nccl", device_id=dev)
+    if HKV % world:
+        raise SystemExit(f"{world} ranks do not divide {HKV} KV heads")
+    hkv, hq = HKV // world, HQ // world
+    K, Q = args.kv_len, args.chunk
+    Kb, Qb = K // BS, Q // BS
+    Pb = Kb - Qb
+    num, den = int(round(args.density * 1000)), 1000
+    rule = SelectionRule(rule="topk", softmax=False, topk_ratio=(num, den), sink=1, local=2)
+    cos, sin = block_rope_tables(Kb, BS, dev)
+
+    # ---- resident state of `layers` independent layers (each rank: its own heads) ----
+    layers = []
+    for li in range(args.layers):
+        t = make_layer_inputs(args.seed + 1000 * li + 17 * rank, K, Q, hq, hkv, dev)
+        cache = PagedKVCache(1, K, hkv, D, dev, page_table=t["perm"].to(dev))
+        cache.append(t["k"].to(dev), t["v"].to(dev), position=0)
+        gate = ATTNGATE_CLASSES["Qavg_Kavg"](BS, D, 128, hkv, hq, force_double=True).to(dev).to(torch.bfloat16)
+        with torch.no_grad():
+            gate.mask_linear_q.weight.copy_(t["wq"].to(dev))
+            gate.mask_linear_k.weight.copy_(t["wk"].to(dev))
+        sel = GateSelectorState(gate, 1, dev)
+        sel.cache.reserve(Kb)
+        k_dev = t["k"].to(dev)
+        gate.append_key_blocks(sel.cache, k_dev[:, : K - Q], (cos[:, :Pb], sin[:, :Pb]))  # past blocks
+        layers.append({
+            "cache": cache, "kv": cache.view(), "sel": sel, "gate": gate,
+            "q": t["q"].to(dev), "k_chunk": k_dev[:, K - Q:].contiguous(), "v_chunk": t["v"][:, K - Q:].to(dev),
+            "host": {n: (t[n][:, K - Q:] if n != "q" else t["q"]).contiguous().cpu().pin_memory() for n in ("q", "k", "v")},
+            "out": torch.empty((1, Q, hq, D), dtype=torch.bfloat16, device=dev),
+            "table": ops.BlockTable(torch.empty((1, hkv, Pb), dtype=torch.int32, device=dev),
+                                    torch.empty((1, hkv), dtype=torch.int32, device=dev),
+                                    torch.empty((1, hkv), dtype=torch.int32, device=dev),
+                                    torch.empty((1, hkv), dtype=torch.int32, device=dev)),
+            "bits": torch.empty((1, hq, Qb, ops.words_for(Kb)), dtype=torch.int32, device=dev),
+            "status": torch.zeros(1, dtype=torch.int32, device=dev),
+        })
+        del k_dev
+    reduce_buf = torch.zeros((1, Q, HQ * D), dtype=torch.bfloat16, device=dev) if world > 1 else None
+    attn_events = []
+
+    def step(L, record=False):
+        sel = L["sel"]
+        sel.cache.length = Pb  # the chunk's blocks are (re)appended at the end of the past blocks
+        logits = sel.append_and_score(L["q"], L["k_chunk"], (cos[:, Pb:], sin[:, Pb:]), (cos[:, Pb:], sin[:, Pb:]))
+        Qb_, Kb_ = logits.shape[2], logits.shape[3]
+        bits = ops.select_rows(logits, Kb_ - Qb_, rule.rule, softmax=rule.softmax, topk_ratio=rule.topk_ratio,
+                               sink=rule.sink, local=rule.local, bits=L["bits"])
+        table = ops.union_table(bits=bits, num_kv_heads=hkv, kv_blocks=Kb_, past_blocks=Pb, block_size=BS, out=L["table"])
+        if record:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        ops.attn_compact(L["q"], L["kv"], K, hkv, table.block_idx, table.counts, block_size=BS, out=L["out"], status=L["status"])
+        if record:
+            e1.record()
+            attn_events.append((e0, e1))
+        if world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(reduce_buf)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(layers[i % len(layers)])
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for i in range(args.steps):
+        step(layers[i % len(layers)], record=True)
+    t1.record()
+    barrier()
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = t0.elapsed_time(t1)
+    attn_ms = statistics.mean(a.elapsed_time(b) for a, b in attn_events)
+    if world > 1:
+        import torch.distributed as dist
+        tt = torch.tensor([ms_total, attn_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms_total, attn_ms = float(tt[0]), float(tt[1])
+    ms_per_step = ms_total / args.steps
+    status = max(int(L["status"].item()) for L in layers)
+
+    # ---- algorithmic work of one attention launch (this rank) ----
+    G = hq // hkv
+    counts = torch.stack([L["table"].counts.reshape(-1) for L in layers]).float().mean(0).cpu()
+    sel_blocks = float(counts.sum())
+    flops = 4.0 * D * G * (Q * sel_blocks * BS + hkv * Q * (Q + 1) / 2.0)
+    kv_bytes = 2.0 * D * 2 * (sel_blocks * BS + hkv * Q) + 2.0 * Q * hq * D * 2
+    peaks = load_peaks()
+    achieved = flops / (attn_ms * 1e-3) / 1e12
+    # the slower of tensor time and HBM time bounds the launch; here it is the tensor pipe
+    t_tensor = flops / (peaks["bf16_tflops"] * 1e12)
+    t_hbm = kv_bytes / (peaks["hbm_gbs"] * 1e9)
+    roofline = {
+        "bound": "tensor" if t_tensor >= t_hbm else "hbm",
+        "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+        "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{peaks['source']} (cuBLAS bf16 burst)",
+        "traffic": NCU_ATTN_TRAFFIC_BYTES, "kernel": "attn_compact_kernel", "kernel_us": round(attn_ms * 1e3, 1),
+        "algorithmic_flops": flops, "algorithmic_bytes": kv_bytes,
+        "roofline_us": round(max(t_tensor, t_hbm) * 1e6, 1),
+        "path_frac_of_roofline": round(max(t_tensor, t_hbm) * 1e3 / ms_per_step, 4),
+    }
+
+    # ---- dense comparator: same shape, same kernel, every past block ----
+    dense_us = None
+    if not args.no_dense:
+        L = layers[0]
+        for _ in range(2):
+            ops.attn_compact(L["q"], L["kv"], K, hkv, None, None, block_size=BS, out=L["out"])
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        d0.record()
+        for i in range(5):
+            LL = layers[i % len(layers)]
+            ops.attn_compact(LL["q"], LL["kv"], K, hkv, None, None, block_size=BS, out=LL["out"])
+        d1.record()
+        barrier()
+        dense_us = d0.elapsed_time(d1) / 5 * 1e3
+        if world > 1:
+            import torch.distributed as dist
+            tt = torch.tensor([dense_us], dtype=torch.float64, device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            dense_us = float(tt[0])
+
+    # ---- end to end through the public operator with host buffers ----
+    from compactattention_b200.modules import chunked_prefill_column_dense_attention_from_keep_block  # noqa: F401
+    host_out = torch.empty((1, Q, hq, D), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(L):
+        q = L["q"].copy_(L["host"]["q"], non_blocking=True)
+        kc = L["k_chunk"].copy_(L["host"]["k"], non_blocking=True)
+        vc = L["v_chunk"].copy_(L["host"]["v"], non_blocking=True)
+        L["cache"].append(kc, vc, position=K - Q)
+        step(L)
+        host_out.copy_(L["out"], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(3):
+        e2e_step(layers[i % len(layers)])
+    barrier()
+    w0 = time.perf_counter()
+    n_e2e = max(5, min(args.steps, 20))
+    for i in range(n_e2e):
+        e2e_step(layers[i % len(layers)])
+    barrier()
+    e2e_us = (time.perf_counter() - w0) / n_e2e * 1e6
+    if world > 1:
+        import torch.distributed as dist
+        tt = torch.tensor([e2e_us], dtype=torch.float64, device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_us = float(tt[0])
+    h2d = (Q * hq * D + 2 * Q * hkv * D) * 2
+    d2h = Q * hq * D * 2
+
+    if rank != 0:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+        return
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(args, sample_heads=1)
+    value_us = ms_per_step * 1e3
+    line = {
+        "metric": METRIC, "value": round(value_us, 1), "unit": "us", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {
+            "workload": f"config 3: 1 layer, {HQ}q/{HKV}kv heads d{D}, chunk {Q} at the end of a {K}-token paged KV cache "
+                        f"(page 64, permuted), block {BS}, learned-gate selector (128->128, random init) + per-row top-k "
+                        f"{args.density:.0%} + sink 1 + local 2",
+            "kv_len": K, "chunk": Q, "density_target": args.density,
+            "selected_past_blocks_per_kv_head": round(sel_blocks / hkv, 1), "past_blocks": Pb,
+            "parallelism": f"tp{world} (KV-head sharded)" if world > 1 else "single GPU",
+            "l2": f"steps rotate over {len(layers)} layer states ({len(layers) * 2 * K * hkv * D * 2 / 2**30:.1f} GiB of KV), more than L2",
+            "launches_per_step": launches / args.steps,
+            "dense_same_shape_us": None if dense_us is None else round(dense_us, 1),
+            "speedup_vs_dense": None if dense_us is None else round(dense_us / value_us, 2),
+            "attention_effective_tflops": round(achieved, 1),
+            "status_word": status,
+        },
+        "roofline": roofline,
+        "cpu_baseline": cpu,
+        "e2e": {"value": round(e2e_us, 1), "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def cpu_path_once(q, k, v, wq, wk, cos, sin, num, den, G):
+    """The reference's CPU path (oracle port) for the given heads: gate scores, top-k rows, union,
+    block table, gather, attention over the gathered KV."""
+    from oracle import compact_oracle as co
+    Q, K = q.shape[1], k.shape[1]
+    Qb, Kb = Q // BS, K // BS
+    Pb = Kb - Qb
+    qb = co.apply_block_rope(co.multi_head_linear(co.pool_blocks(q.float(), BS, ("avg",)), wq.float()), cos[:, Pb:], sin[:, Pb:])
+    kb = co.apply_block_rope(co.multi_head_linear(co.pool_blocks(k.float(), BS, ("avg",)), wk.float()), cos, sin)
+    mask = co.gate_block_causal_mask(Q, K, BS)
+    logits = co.gate_score(qb, kb, mask, use_softmax=False)
+    valid = mask.expand_as(logits)
+    n_valid = Pb + torch.arange(Qb) + 1
+    kk = torch.minimum(torch.clamp((num * n_valid + den // 2) // den, min=1), n_valid)
+    keep = co.topk_rows(logits, valid, kk) | (co.forced_mask(Qb, Kb, Pb, 1, 2) & valid)
+    keep_block = keep.any(dim=2)
+    idx, counts = co.block_union_table(keep_block, Q, K, BS, G)
+    co.gather_compact_kv(k, v, idx, counts, Q, BS)
+    return co.compact_attention(q, k, v, idx, counts, BS)
+
+
+def cpu_baseline(args, sample_heads=1, runs=1):
+    """Times the CPU path on `sample_heads` of the 8 KV heads (with their query heads) at the full
+    context, all host threads, and scales to the full layer (heads are independent)."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    K, Q = args.kv_len, args.chunk
+    G = HQ // HKV
+    t = make_layer_inputs(args.seed, K, Q, G * sample_heads, sample_heads, "cpu")
+    cos, sin = block_rope_tables(K // BS, BS, "cpu")
+    num, den = int(round(args.density * 1000)), 1000
+    best = None
+    for _ in range(runs):
+        w0 = time.perf_counter()
+        cpu_path_once(t["q"], t["k"], t["v"], t["wq"], t["wk"], cos, sin, num, den, G)
+        dt = time.perf_counter() - w0
+        best = dt if best is None else min(best, dt)
+    return {"value": round(best * (HKV / sample_heads) * 1e6, 1), "unit": "us", "cores": cores, "kind": "port",
+            "sample": f"{sample_heads} of {HKV} KV heads (with their {G} query heads each) at the full {K}-token context, "
+                      f"measured {best:.2f} s, scaled x{HKV // sample_heads} (heads are independent)"}
+
+
+def run_reference(args):
+    """Reference arm: the CPU restatement of the reference's path on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 3))
+    vals = []
+    cpu = None
+    for _ in range(min(args.warmup, 1)):
+        cpu_baseline(args, sample_heads=1)
+    for _ in range(steps):
+        cpu = cpu_baseline(args, sample_heads=1)
+        vals.append(cpu["value"])
+    value = statistics.mean(vals)
+    cpu["value"] = round(value, 1)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 1), "unit": "us",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps, "warmup": min(args.warmup, 1),
+        "ms_per_step": round(value / 1e3, 3), "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"config 3 on the host CPU: chunk {args.chunk} at the end of a {args.kv_len}-token cache, "
+                               f"top-k {args.density:.0%}; {cpu['sample']}"},
+        "cpu_baseline": cpu,
+        "e2e": {"value": round(value, 1), "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()

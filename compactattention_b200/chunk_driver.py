@@ -1,0 +1,102 @@
+"""One attention layer's chunked-prefill step on one GPU: selector -> Block-Union table -> compact
+attention, with every buffer pre-allocated so a step is a fixed sequence of kernel launches with no
+host synchronisation.  It is what the benchmark times and what the attention modules call.
+
+Selectors (reference anchors in ``compact_attn``):
+* ``gate``   learned AttnGate over a growing K-block cache, then a per-row rule
+             (prefill_sparse/attn_gate.py:37-222, llama/modeling_llama_seerattn.py:437-481);
+* ``flashprefill``  mean-K cache + per-token block score + alpha * row-max rule
+             (modules/flashprefill_prefill.py:880-1189).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from . import ops
+from .paged_cache import PagedKVCache
+from .prefill_sparse.attn_gate import AttnGate, GateKeyBlockCache
+
+
+@dataclass
+class SelectionRule:
+    """Per-row rule applied to the selector's scores (see ``ca_select_rows``)."""
+
+    rule: str = "threshold"  # threshold | topk | cummass | alpha_rowmax
+    softmax: bool = True
+    threshold: float = 5e-4
+    alpha: float = 0.06
+    topk_ratio: Optional[Tuple[int, int]] = None
+    topk_k: int = 0
+    min_budget: int = 0
+    sink: int = 0
+    local: int = 0
+    keep_recent: int = 0
+    last_n_block: int = 0
+
+
+class GateSelectorState:
+    """Learned-gate selector state of one layer: the gate, its K-block cache and scratch buffers."""
+
+    def __init__(self, gate: AttnGate, batch: int, device, cache_dtype=torch.bfloat16):
+        self.gate = gate
+        heads = gate.mask_linear_k.weight.shape[0]
+        self.cache = GateKeyBlockCache(batch, heads, gate.hidden_size, device, dtype=cache_dtype)
+
+    def append_and_score(self, q_nope: torch.Tensor, k_nope: torch.Tensor, block_rope_q=None, block_rope_k=None) -> torch.Tensor:
+        """Appends the chunk's K blocks, then scores the chunk's Q blocks against every cached block.
+        Returns logits ``[B, Hq, Qb, Kb]`` (float32, acausal entries filled with finfo.min)."""
+        self.gate.append_key_blocks(self.cache, k_nope, block_rope_k)
+        pooled_q = ops.pool_blocks(q_nope, self.gate.block_size, self.gate.q_pooling_funcs)
+        wq = None if self.gate.mask_linear_q is None else self.gate.mask_linear_q.weight.detach()
+        cos, sin = block_rope_q if block_rope_q is not None else (None, None)
+        qb = ops.gate_project(pooled_q, wq, cos, sin)
+        kb = self.cache.blocks()
+        return ops.gate_scores(qb, kb, kb.shape[1] - qb.shape[1], scale=self.gate.scale)
+
+
+class MeanKSelectorState:
+    """Training-free selector state of one layer: the mean-K cache ``[B, capacity, Hkv, D]``."""
+
+    def __init__(self, batch: int, max_blocks: int, num_kv_heads: int, head_dim: int, block_size: int, device, dtype):
+        self.block_size = block_size
+        self.mean_k = torch.empty((batch, max_blocks, num_kv_heads, head_dim), dtype=dtype, device=device)
+        self.length = 0
+
+    def append_and_score(self, q: torch.Tensor, k_chunk: torch.Tensor, kv_len: int) -> torch.Tensor:
+        nb = k_chunk.shape[1] // self.block_size
+        ops.pool_blocks(k_chunk, self.block_size, ("avg",), out=self.mean_k, out_block_offset=self.length)
+        self.length += nb
+        _, _, norm = ops.flashprefill_score(q, self.mean_k[:, : self.length], kv_len, self.block_size)
+        return norm.permute(0, 3, 1, 2)  # [B, Hq, Qb, Kb] view
+
+
+def select_and_attend(
+    q: torch.Tensor,  # [B, Q, Hq, D] post-RoPE queries of the chunk
+    kv: ops.KvCacheView,
+    kv_len: int,
+    num_kv_heads: int,
+    score: torch.Tensor,  # [B, Hq, Qb, Kb] selector scores / logits (any strides)
+    rule: SelectionRule,
+    block_size: int,
+    softmax_scale: Optional[float] = None,
+    out: Optional[torch.Tensor] = None,
+    table: Optional[ops.BlockTable] = None,
+    bits: Optional[torch.Tensor] = None,
+    status: Optional[torch.Tensor] = None,
+):
+    """Row rule -> Block-Union table -> compact attention (three launches).  Returns (out, table)."""
+    Qb, Kb = score.shape[2], score.shape[3]
+    rows_voting = 0
+    if rule.last_n_block > 0 and Qb > 1:
+        rows_voting = max(Qb - min(rule.last_n_block, Qb - 1), 1)
+    bits = ops.select_rows(score, Kb - Qb, rule.rule, softmax=rule.softmax, threshold=rule.threshold, alpha=rule.alpha,
+                           topk_k=rule.topk_k, topk_ratio=rule.topk_ratio, min_budget=rule.min_budget, sink=rule.sink,
+                           local=rule.local, rows_voting=rows_voting, bits=bits)
+    table = ops.union_table(bits=bits, num_kv_heads=num_kv_heads, kv_blocks=Kb, past_blocks=Kb - Qb, block_size=block_size,
+                            keep_recent=rule.keep_recent, out=table)
+    out = ops.attn_compact(q, kv, kv_len, num_kv_heads, table.block_idx, table.counts, block_size=block_size,
+                           softmax_scale=softmax_scale, out=out, status=status)
+    return out, table

@@ -1,0 +1,284 @@
+"""Chunked-prefill CompactAttention operators with the reference's signatures.
+
+Mirrors ``compact_attn/modules/attention_forward_chunked_dense.py`` of the reference:
+``chunked_prefill_column_dense_attention_forward`` (:2732-2912) and
+``chunked_prefill_column_dense_attention_from_keep_block`` (:2147-2729) keep their names,
+argument meaning, return contract ``(out, stats | None)`` and ``ValueError`` behaviour, but every
+stage runs in ``libcompactattn_b200.so``: selection rule -> packed bits, Block-Union + block table,
+and the block-table-indexed tcgen05 attention kernel that reads the selected KV blocks in place
+(there is no materialised compact cache on this route and no host synchronisation).
+
+Differences a caller can observe, all deliberate:
+* ``pack_impl`` / ``indexed_impl`` / ``cache_fill_backend`` are accepted (every value the
+  reference accepts, plus ``"b200_native"``) but select nothing: there is one implementation.
+* Padded batches (an ``attention_mask`` containing zeros), lengths that are not multiples of the
+  block size and head dims other than 128 raise ``NotImplementedError`` instead of falling down the
+  reference's ladder of slower paths; the reference only takes its indexed path under the same
+  preconditions (:993-999, :2267-2277).
+* ``attention_mask`` is assumed all-ones when given (checking would need a device-to-host sync,
+  which the reference performs once and caches, :529-543); pass ``None`` for the common case.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, Optional, Tuple, Union
+
+import torch
+
+from .. import ops
+
+COMPACTATTN_VERSION = "CompactAttn-B200-v0.1"
+
+_INDEXED_IMPLS = {
+    "fa2_paged", "triton_direct", "fa2_indexed", "fi_paged", "fi_zero_copy", "fi_zero_copy_per_query",
+    "fi_zero_copy_subgroup", "cudnn_one_shot", "b200_native",
+}
+
+
+def _timed(fn, enabled: bool):
+    """CUDA-event timing of one stage on the current stream (the reference's ``_cuda_elapsed_ms``, :52-61)."""
+    if not enabled:
+        return fn(), 0.0
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    out = fn()
+    end.record()
+    end.synchronize()
+    return out, float(start.elapsed_time(end))
+
+
+def _effective_threshold(threshold):
+    """``SEERATTN_DEBUG_COMPACTATTN_THRESHOLD_OVERRIDE`` is honoured like the reference (:139-160)."""
+    raw = os.environ.get("SEERATTN_DEBUG_COMPACTATTN_THRESHOLD_OVERRIDE", "")
+    if raw:
+        try:
+            return float(raw)
+        except ValueError:
+            pass
+    return threshold
+
+
+def _check_common(query_states, key_states, value_states, query_length, block_size, indexed_impl):
+    if query_length <= 1:
+        raise ValueError("chunked compact attention expects query_length > 1.")
+    if block_size <= 0:
+        raise ValueError("block_size must be positive.")
+    if indexed_impl not in _INDEXED_IMPLS:
+        raise ValueError(f"Unsupported indexed_impl: {indexed_impl}")
+    if not (query_states.is_cuda and key_states.is_cuda and value_states.is_cuda):
+        raise RuntimeError("compactattention_b200 has no CPU path: tensors must live on a CUDA device")
+    if query_states.dtype not in (torch.float16, torch.bfloat16) or key_states.dtype != query_states.dtype \
+            or value_states.dtype != query_states.dtype:
+        raise NotImplementedError("the B200 path computes in bf16/f16; q, k, v must share one of these dtypes")
+    if query_states.shape[-1] != 128:
+        raise NotImplementedError("the B200 path supports head_dim 128 only")
+    q_len, kv_len = query_states.shape[1], key_states.shape[1]
+    if block_size % 64 or q_len % block_size or kv_len % block_size:
+        raise NotImplementedError(
+            f"q_len ({q_len}) and kv_len ({kv_len}) must be multiples of block_size ({block_size}), itself a multiple of 64")
+
+
+def _kv_view(key_states, value_states, k_hf, v_hf) -> ops.KvCacheView:
+    """Source KV addressing: a caller-made ``KvCacheView`` (paged cache) passes through; tensors are
+    viewed in place, seq-first ``[B,K,Hkv,D]`` or, for B == 1, heads-first ``k_hf [B,Hkv,K,D]``."""
+    if isinstance(key_states, ops.KvCacheView):
+        return key_states
+    if key_states.stride(3) == 1 and (key_states.shape[0] == 1 or key_states.stride(0) == key_states.shape[1] * key_states.stride(1)):
+        return ops.KvCacheView.from_seq_first(key_states, value_states)
+    if k_hf is not None and v_hf is not None and k_hf.shape[0] == 1:
+        return ops.KvCacheView.from_heads_first(k_hf, v_hf)
+    return ops.KvCacheView.from_seq_first(key_states.contiguous(), value_states.contiguous())
+
+
+def chunked_prefill_column_dense_attention_from_keep_block(
+    query_states: torch.Tensor,  # [B, Q, Hq, D]
+    key_states: torch.Tensor,  # [B, K, Hkv, D]
+    value_states: torch.Tensor,  # [B, K, Hkv, D]
+    keep_block: Optional[torch.Tensor],  # [B, Hq, Kb]
+    attention_mask: Optional[torch.Tensor],  # [B, K]
+    query_length: int,
+    softmax_scale: float,
+    block_size: int = 64,
+    num_key_value_groups: int = 1,
+    pack_impl: str = "torch",
+    indexed_impl: str = "fa2_paged",
+    cache_fill_backend: str = "auto",
+    return_stats: bool = False,
+    valid_block: Optional[torch.Tensor] = None,  # [B, Hq, Kb]
+    allow_indexed_dense: bool = False,
+    keep_block_kv_preprojected: Optional[torch.Tensor] = None,  # [B, Hkv, Kb]
+    attn_module=None,
+    k_hf: Optional[torch.Tensor] = None,
+    v_hf: Optional[torch.Tensor] = None,
+    _row_bits: Optional[torch.Tensor] = None,  # packed bits [B, H, Qin, W] from ops.select_rows (internal)
+    _keep_recent: int = 0,
+) -> Tuple[torch.Tensor, Optional[Dict[str, float]]]:
+    """Block-Union KV selection from a keep mask, then dense causal attention over the kept blocks.
+
+    Same contract as the reference function of this name (:2147-2167): ``keep_block`` is the
+    per-query-head column mask, ``keep_block_kv_preprojected`` the per-KV-head one (wins when both
+    are given); the chunk's own blocks are always attended.
+    """
+    _check_common(query_states, key_states, value_states, query_length, block_size, indexed_impl)
+    bsz, q_len, num_q_heads, _ = query_states.shape
+    kv_len = key_states.shape[1]
+    kv_blocks = (kv_len + block_size - 1) // block_size
+    num_kv_heads = key_states.shape[2]
+    if keep_block is None and keep_block_kv_preprojected is None and _row_bits is None:
+        raise ValueError("Either keep_block or keep_block_kv_preprojected must be provided.")
+    if keep_block is not None and keep_block.shape != (bsz, num_q_heads, kv_blocks):
+        raise ValueError(f"keep_block shape mismatch: expected {(bsz, num_q_heads, kv_blocks)}, got {tuple(keep_block.shape)}")
+    if keep_block_kv_preprojected is not None and keep_block_kv_preprojected.shape != (bsz, num_kv_heads, kv_blocks):
+        raise ValueError("keep_block_kv_preprojected shape mismatch: "
+                         f"expected {(bsz, num_kv_heads, kv_blocks)}, got {tuple(keep_block_kv_preprojected.shape)}")
+    if valid_block is not None:
+        if keep_block is None:
+            raise ValueError("valid_block requires keep_block to be provided.")
+        if valid_block.shape != keep_block.shape:
+            raise ValueError(f"valid_block shape mismatch: expected {tuple(keep_block.shape)}, got {tuple(valid_block.shape)}")
+    if num_q_heads != num_kv_heads * num_key_value_groups:
+        raise ValueError("num_key_value_groups does not match the head counts")
+    past_blocks = (kv_len - q_len) // block_size
+    timing = bool(return_stats)
+
+    def _build():
+        if _row_bits is not None:
+            return ops.union_table(bits=_row_bits, num_kv_heads=num_kv_heads, kv_blocks=kv_blocks, past_blocks=past_blocks,
+                                   block_size=block_size, keep_recent=_keep_recent, want_keep_kv=timing)
+        src = keep_block_kv_preprojected if keep_block_kv_preprojected is not None else keep_block
+        if valid_block is not None and keep_block_kv_preprojected is None:
+            src = src & valid_block.to(torch.bool)
+        src = src if src.dtype in (torch.bool, torch.uint8) else src.to(torch.bool)
+        return ops.union_table(mask=src, num_kv_heads=num_kv_heads, kv_blocks=kv_blocks, past_blocks=past_blocks,
+                               block_size=block_size, keep_recent=_keep_recent, want_keep_kv=timing)
+
+    table, index_ms = _timed(_build, timing)
+    kv = _kv_view(key_states, value_states, k_hf, v_hf)
+    out, attn_ms = _timed(
+        lambda: ops.attn_compact(query_states, kv, kv_len, num_kv_heads, table.block_idx, table.counts,
+                                 block_size=block_size, softmax_scale=softmax_scale),
+        timing,
+    )
+    if not return_stats:
+        return out, None
+    selected = float(table.keep_kv.sum().item())
+    valid = float(table.keep_kv.numel())
+    stats = {
+        "col_index_build_ms": index_ms,
+        "col_indexed_dense_kernel_ms": attn_ms,
+        "dense_kernel_ms": attn_ms,
+        "col_selected_kv_materialize_ms": 0.0,  # blocks are read in place: nothing is materialised
+        "gather_pack_ms": 0.0,
+        "fallback_used": 0.0,
+        "selected_blocks": selected,
+        "valid_blocks": valid,
+        "select_ratio": selected / valid if valid else 1.0,
+        "selected_tokens": selected * block_size,
+        "valid_tokens": valid * block_size,
+        "col_indexed_dense_calls": 1.0,
+        "path": "chunked_selected",
+        "compactattn_version": COMPACTATTN_VERSION,
+    }
+    return out, stats
+
+
+def chunked_prefill_column_dense_attention_forward(
+    query_states: torch.Tensor,  # [B, Q, Hq, D]
+    key_states: torch.Tensor,  # [B, K, Hkv, D]
+    value_states: torch.Tensor,  # [B, K, Hkv, D]
+    attention_mask: Optional[torch.Tensor],  # [B, K]
+    query_length: int,
+    softmax_scale: Optional[float] = None,
+    attn_gate_score: Optional[torch.Tensor] = None,  # [B, Hq|Hkv, Qb, Kb]
+    block_attention_mask: Optional[torch.Tensor] = None,  # [B, 1, Qb, Kb]
+    threshold: Union[float, torch.Tensor] = 0.0,
+    keep_recent_blocks: int = 2,
+    block_size: int = 64,
+    num_key_value_groups: int = 1,
+    attn_gate_is_kv_group_aware: bool = False,
+    pack_impl: str = "torch",
+    indexed_impl: str = "fa2_paged",
+    cache_fill_backend: str = "auto",
+    return_stats: bool = False,
+    attn_module=None,
+    k_hf: Optional[torch.Tensor] = None,
+    v_hf: Optional[torch.Tensor] = None,
+) -> Tuple[torch.Tensor, Optional[Dict[str, float]]]:
+    """Threshold selection on gate scores, Block-Union, then compact attention.
+
+    Same contract as the reference function of this name (:2732-2753).  A key block is kept for a
+    query head when any valid Q-block row scores above ``threshold`` (strict, fp32 compare, :352-403
+    / kernels ``build_keep_*_fast_kernel``); the last ``keep_recent_blocks`` columns are forced on;
+    the G heads of a KV head are OR-ed; the chunk's own blocks are always attended.
+    """
+    if attn_gate_score is None:
+        raise ValueError("attn_gate_score is required for chunked column-dense attention.")
+    _check_common(query_states, key_states, value_states, query_length, block_size, indexed_impl)
+    threshold = _effective_threshold(threshold)
+    if isinstance(threshold, torch.Tensor):
+        if threshold.numel() != 1:
+            raise NotImplementedError("per-batch threshold tensors are not supported by the B200 path")
+        threshold = float(threshold.item())
+    bsz, q_len, num_q_heads, head_dim = query_states.shape
+    kv_len = key_states.shape[1]
+    num_kv_heads = key_states.shape[2]
+    kv_blocks = kv_len // block_size
+    q_blocks = q_len // block_size
+    if attn_gate_score.dim() != 4 or attn_gate_score.shape[0] != bsz or attn_gate_score.shape[2] != q_blocks:
+        raise ValueError(f"attn_gate_score must be [B, H, {q_blocks}, Kb], got {tuple(attn_gate_score.shape)}")
+    gate_heads = attn_gate_score.shape[1]
+    expect_heads = num_kv_heads if attn_gate_is_kv_group_aware else num_q_heads
+    if gate_heads != expect_heads:
+        raise ValueError(f"attn_gate_score has {gate_heads} heads, expected {expect_heads}")
+    score_blocks = attn_gate_score.shape[3]
+    if score_blocks > kv_blocks:
+        raise ValueError(f"short keep_block width {score_blocks} exceeds expected KV blocks {kv_blocks}")
+    if softmax_scale is None:
+        softmax_scale = head_dim ** -0.5
+    timing = bool(return_stats)
+    past_blocks = kv_blocks - q_blocks
+    # a score tensor narrower than the cache covers its last `score_blocks` key blocks (:708-734)
+    missing = kv_blocks - score_blocks
+    if missing > past_blocks:
+        raise NotImplementedError("gate scores must at least cover the chunk's own key blocks")
+    valid = None
+    if block_attention_mask is not None:
+        valid = block_attention_mask[..., -q_blocks:, -score_blocks:].to(torch.bool)
+
+    def _select():
+        return ops.select_rows(attn_gate_score, past_blocks - missing, "threshold", threshold=float(threshold), valid=valid)
+
+    bits, select_ms = _timed(_select, timing)
+    if missing:
+        # left-pad the packed columns with `missing` never-selected blocks
+        full = ops.unpack_bits(bits, score_blocks)
+        mask = torch.zeros((*full.shape[:-1], kv_blocks), dtype=torch.bool, device=full.device)
+        mask[..., missing:] = full
+        keep = mask.any(dim=2)
+        if keep_recent_blocks > 0:
+            keep[..., kv_blocks - min(int(keep_recent_blocks), kv_blocks):] = True
+        out, stats = chunked_prefill_column_dense_attention_from_keep_block(
+            query_states, key_states, value_states,
+            keep_block=None if attn_gate_is_kv_group_aware else keep,
+            attention_mask=attention_mask, query_length=query_length, softmax_scale=softmax_scale, block_size=block_size,
+            num_key_value_groups=num_key_value_groups, pack_impl=pack_impl, indexed_impl=indexed_impl,
+            cache_fill_backend=cache_fill_backend, return_stats=return_stats, allow_indexed_dense=True,
+            keep_block_kv_preprojected=keep if attn_gate_is_kv_group_aware else None, attn_module=attn_module, k_hf=k_hf, v_hf=v_hf)
+    else:
+        out, stats = chunked_prefill_column_dense_attention_from_keep_block(
+            query_states, key_states, value_states, keep_block=None, attention_mask=attention_mask,
+            query_length=query_length, softmax_scale=softmax_scale, block_size=block_size,
+            num_key_value_groups=num_key_value_groups, pack_impl=pack_impl, indexed_impl=indexed_impl,
+            cache_fill_backend=cache_fill_backend, return_stats=return_stats, allow_indexed_dense=True,
+            attn_module=attn_module, k_hf=k_hf, v_hf=v_hf, _row_bits=bits, _keep_recent=max(int(keep_recent_blocks), 0))
+    if not return_stats:
+        return out, None
+    stats.update({
+        "col_select_mask_ms": select_ms,
+        "col_select_mask_past_ms": select_ms,
+        "col_select_mask_curr_ms": 0.0,
+        "col_select_mask_fastpath_calls": 1.0,
+        "col_select_mask_generic_calls": 0.0,
+        "compactattn_version": COMPACTATTN_VERSION,
+    })
+    return out, stats
