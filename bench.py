@@ -123,6 +123,30 @@ def make_layer_inputs(seed, kv_len, chunk, hq, hkv, device):
     wq = (torch.randn((hq, D, 128), generator=g, device=device) * 0.02).to(torch.bfloat16)
     wk = (torch.randn((hkv, D, 128), generator=g, device=device) * 0.02).to(torch.bfloat16)
     perm = torch.randperm(kv_len // 64, generator=g, device=device).to(torch.int32).view(1, -1)
+    # Per-head rank-1 bias so that the query heads of a group and the Q-blocks of a chunk agree on
+    # which key blocks matter (the premise of Block-Union selection).  For each KV-head group a unit
+    # direction g is chosen in the gate's slowly rotating RoPE channels (so it survives the block
+    # RoPE for every Q-block of the chunk) such that the inputs that the random projections map onto
+    # g are as small as possible; key block j carries importance a_j along that input direction and
+    # every query token leans the same way.  Without it, independent per-row top-k selections of
+    # random data union to ~100 % of the blocks.
+    G = hq // hkv
+    slow = torch.cat([torch.arange(45, 64), torch.arange(109, 128)]).to(device)
+    inv_k = torch.linalg.inv(wk.double())  # input = g @ inv(W)
+    inv_q = torch.linalg.inv(wq.double())
+    x = torch.empty((hkv, 128), dtype=torch.float64, device=device)
+    y = torch.empty((hq, 128), dtype=torch.float64, device=device)
+    for h in range(hkv):
+        mats = [inv_k[h]] + [inv_q[h * G + gi] for gi in range(G)]
+        m = sum(a_[slow] @ a_[slow].T for a_ in mats)
+        g_dir = torch.zeros(128, dtype=torch.float64, device=device)
+        g_dir[slow] = torch.linalg.eigh(m).eigenvectors[:, 0]
+        x[h] = g_dir @ inv_k[h]
+        for gi in range(G):
+            y[h * G + gi] = g_dir @ inv_q[h * G + gi]
+    a = torch.rand((kv_len // BS, hkv), generator=g, device=device) ** 3
+    k = (k.float() + a.repeat_interleave(BS, dim=0).view(1, kv_len, hkv, 1) * x.float().view(1, 1, hkv, 128)).to(torch.bfloat16)
+    q = (q.float() + 1.5 * y.float().view(1, 1, hq, 128)).to(torch.bfloat16)
     return {"k": k, "v": v, "q": q, "wq": wq, "wk": wk, "perm": perm, "past": past}
 
 
