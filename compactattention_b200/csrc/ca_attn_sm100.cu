@@ -1,27 +1,36 @@
 // Block-table-indexed dense causal attention for sm_100a: tcgen05 MMA with TMEM accumulators,
 // TMA loads whose page coordinate comes from the per-KV-head block table.
 //
-// One CTA owns one KV-head row (b, hkv) and a pair of 128-row query tiles ("A" and "B"). A query
+// Work unit = one KV-head row (b, hkv) and a pair of 128-row query tiles ("A" and "B").  A query
 // tile stacks the G query heads of the KV head along M: tile row i is (token i / G, head i % G),
-// so one K/V stage feeds G heads. K/V are consumed in 128-token steps = two 64-token sub-blocks,
+// so one K/V stage feeds G heads.  K/V are consumed in 128-token steps = two 64-token sub-blocks,
 // each fetched by its own TMA box at (page, token offset) resolved from the block table and the
-// optional page table. Selected past blocks are fully visible; the chunk's own blocks follow in
+// optional page table.  Selected past blocks are fully visible; the chunk's own blocks follow in
 // order and are causally masked (bottom-right aligned), which is what
 // compact_attn/kernels/varlen/indexed_dense_prefill_direct_triton.py:155-241 computes.
 //
-// Warp roles (320 threads): warps 0-3 softmax of tile A, warps 4-7 softmax of tile B (thread =
-// TMEM lane = tile row), warp 8 lane 0 issues every tcgen05.mma, warp 9 lane 0 issues every TMA.
+// Scheduling: a persistent grid of one CTA per SM.  The KV steps of all units are laid end to end
+// and cut into equal spans, one per CTA ("stream-K"), so the SMs stay balanced whatever the
+// per-row block counts are and however few rows a tensor-parallel rank owns.  A unit that falls
+// entirely inside one span is written straight to the output; a unit cut by a span boundary
+// leaves per-segment partials (unnormalised O, running max, running sum) in the workspace and a
+// small combine kernel merges them.  Without a workspace the spans snap to unit boundaries.
+//
+// Warp roles (384 threads): warps 0-3 softmax of tile A, warps 4-7 softmax of tile B (thread =
+// TMEM lane = tile row), warp 8 lane 0 issues every tcgen05.mma, warp 9 issues every TMA, warps
+// 10-11 idle.  The third warpgroup gives its registers to the softmax warpgroups (setmaxnreg),
+// which hold a whole 128-column S row per thread.
 // TMEM (512 columns): S_A | S_B | O_A | O_B, 128 fp32 columns each; P (16-bit) overwrites the
 // first 64 columns of its S and feeds the P.V MMA straight from TMEM.
 // MMA order S_A0 S_B0 { PV_A(j) S_A(j+1) PV_B(j) S_B(j+1) } so one tile's softmax overlaps the
-// other tile's MMAs. Every wait is bounded; on expiry the CTA raises CA_STATUS_TIMEOUT, drains
+// other tile's MMAs.  Every wait is bounded; on expiry the CTA raises CA_STATUS_TIMEOUT, drains
 // what it issued, frees TMEM and returns.
 #include "ca_common.cuh"
 
 namespace ca {
 namespace attn {
 
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;  // three warpgroups: softmax A, softmax B, {MMA, TMA, 2 idle warps}
 constexpr int kTileM = 128;
 constexpr int kTileN = 128;
 constexpr int kHeadDim = 128;
@@ -31,12 +40,32 @@ constexpr int kTileBytes = 2 * kHalfBytes;
 constexpr int kBoxBytes = kSub * 128;  // one [64 tokens][64 x 16-bit] box
 constexpr int kStages = 4;
 constexpr int kTmemCols = 512;
-constexpr int kSmemBytes = 2 * kTileBytes + kStages * kTileBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kMaxRows = 1024;  // (batch x kv heads) rows per launch
+constexpr int kMaxSegs = 64;    // segments planned per batch
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; lazy accumulator rescale
+
+// Partial results of one segment of a split unit.
+constexpr int kPartialOFloats = 2 * kTileM * kHeadDim;  // [tile][col/4][row][4]
+constexpr int kPartialMLFloats = 2 * kTileM * 2;        // [tile][row][m, l]
+
+struct SegDesc {  // one per workspace slot
+  int unit;       // row * n_pairs + pair, or -1 when the slot is unused
+  int j0, j1;     // KV-step range of the segment inside the unit
+  int n_iter;     // KV steps of the whole unit
+};
+
+struct Segment {
+  int row, pair;
+  int j0, j1;
+  int n_sub, n_past_sub;
+  int slot;  // workspace slot of a partial segment, -1: whole unit, written to the output
+  int pad;
+};
 
 struct KernelArgs {
   int Q, G, Hkv, B;
   int tpt;          // query tokens per 128-row tile = 128 / G
+  int n_pairs;      // tile pairs per row
   int past_blocks;  // Pb
   int spb;          // 64-token sub-blocks per block
   int block_size;
@@ -56,19 +85,32 @@ struct KernelArgs {
   // K/V tensor-map dimensions 1..3 are ordered by ascending stride at encode time; these give the
   // coordinate slot (0..2) of the token, page and head coordinates.
   int slot_tok, slot_page, slot_head;
+  int split;           // 1: spans may cut units (needs the workspace)
+  SegDesc* descs;      // [2 * gridDim.x]
+  float* part_ml;      // [2 * gridDim.x][kPartialMLFloats]
+  float* part_o;       // [2 * gridDim.x][kPartialOFloats]
 };
 
-struct Barriers {
+struct Shared {
   uint64_t q_full[2];
   uint64_t ring_full[kStages];
   uint64_t ring_empty[kStages];
   uint64_t s_full[2];
   uint64_t p_full[2];
   uint64_t o_done;
+  uint64_t o_free[2];
   uint64_t drain;
   uint32_t tmem_base;
   int abort_flag;
+  int n_segs;
+  int more;            // another batch of segments follows
+  long long next_x;    // linear KV-step index where the next batch starts
+  int row_count[kMaxRows];
+  long long row_prefix[kMaxRows + 1];
+  Segment segs[kMaxSegs];
 };
+
+constexpr int kSmemBytes = 2 * kTileBytes + kStages * kTileBytes + 1024 /*align*/ + static_cast<int>(sizeof(Shared));
 
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi);
@@ -91,6 +133,60 @@ __device__ __forceinline__ int visible_cols(int u, int n_sub, int n_past_sub, in
   return lim < 0 ? 0 : (lim > kSub ? kSub : lim);
 }
 
+// 64-token sub-blocks of the chunk that tile pair `pair` can see.
+__device__ __forceinline__ int chunk_subs(const KernelArgs& a, int pair) {
+  int t_last = (2 * pair + 2) * a.tpt - 1;
+  if (t_last > a.Q - 1) t_last = a.Q - 1;
+  return t_last / kSub + 1;
+}
+__device__ __forceinline__ int unit_iters(const KernelArgs& a, int count, int pair) {
+  return (count * a.spb + chunk_subs(a, pair) + 1) >> 1;
+}
+
+// Plans up to kMaxSegs segments of this CTA's span starting at linear step x (thread 0 only).
+__device__ void plan_segments(const KernelArgs& a, Shared* sh, long long x, long long span_begin, long long span_end,
+                              int R) {
+  int n = 0;
+  // row containing x: largest r with row_prefix[r] <= x
+  int lo = 0, hi = R;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (sh->row_prefix[mid] <= x) lo = mid; else hi = mid;
+  }
+  int row = lo;
+  long long acc = sh->row_prefix[row];
+  int pair = 0;
+  while (x < span_end && n < kMaxSegs && row < R) {
+    const int count = sh->row_count[row];
+    const int ni = unit_iters(a, count, pair);
+    if (x >= acc + ni) {  // unit lies before x: walk on
+      acc += ni;
+      if (++pair == a.n_pairs) pair = 0, ++row;
+      continue;
+    }
+    Segment s;
+    s.row = row, s.pair = pair;
+    s.j0 = static_cast<int>(x - acc);
+    const long long rem = span_end - acc;
+    s.j1 = rem < ni ? static_cast<int>(rem) : ni;
+    s.n_past_sub = count * a.spb;
+    s.n_sub = s.n_past_sub + chunk_subs(a, pair);
+    const bool partial = !(s.j0 == 0 && s.j1 == ni);
+    s.slot = partial ? static_cast<int>(2 * blockIdx.x + (x == span_begin ? 0 : 1)) : -1;
+    s.pad = 0;
+    if (partial) {
+      SegDesc d;
+      d.unit = row * a.n_pairs + pair, d.j0 = s.j0, d.j1 = s.j1, d.n_iter = ni;
+      a.descs[s.slot] = d;
+    }
+    sh->segs[n++] = s;
+    x = acc + s.j1;
+  }
+  sh->n_segs = n;
+  sh->next_x = x;
+  sh->more = (x < span_end && row < R) ? 1 : 0;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
     attn_compact_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
@@ -100,347 +196,522 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* smem_aligned = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   const uint32_t q_smem = smem_base;                      // Q_A, Q_B
   const uint32_t ring_smem = smem_base + 2 * kTileBytes;  // kStages slots
-  Barriers* bars = reinterpret_cast<Barriers*>(smem_aligned + 2 * kTileBytes + kStages * kTileBytes);
+  Shared* sh = reinterpret_cast<Shared*>(smem_aligned + 2 * kTileBytes + kStages * kTileBytes);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int row = blockIdx.y;  // b * Hkv + hkv
-  const int b = row / a.Hkv;
-  const int hkv = row % a.Hkv;
-  const int mt0 = blockIdx.x * 2;  // first of the two query tiles
-
-  // ---- per-CTA extent of the KV walk ----
-  int count = a.past_blocks;
-  bool bad_index = false;
-  if (a.block_idx != nullptr) {
-    count = a.counts[row];
-    int cap = a.block_idx_stride < a.past_blocks ? a.block_idx_stride : a.past_blocks;
-    if (count < 0 || count > cap) {
-      bad_index = true;
-      count = count < 0 ? 0 : cap;
-    }
-  }
-  const int n_past_sub = count * a.spb;
-  int t_last = (mt0 + 2) * a.tpt - 1;  // last chunk token of tile B
-  if (t_last > a.Q - 1) t_last = a.Q - 1;
-  const int n_sub = n_past_sub + t_last / kSub + 1;
-  const int n_iter = (n_sub + 1) >> 1;
-  volatile int* abort_flag = &bars->abort_flag;
+  const int R = a.B * a.Hkv;
+  volatile int* abort_flag = &sh->abort_flag;
   const uint64_t limit = a.wait_limit_ns;
+  bool bad_index = false;
 
-  if (tid == 0) {
-    ptx::mbar_init(ptx::smem_u32(&bars->q_full[0]), 1);
-    ptx::mbar_init(ptx::smem_u32(&bars->q_full[1]), 1);
-    for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(ptx::smem_u32(&bars->ring_full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->ring_empty[s]), 1);
+  // ---- per-row KV-step totals and their prefix (every CTA; a few thousand integer operations) ----
+  for (int r = tid; r < R; r += kThreads) {
+    int count = a.past_blocks;
+    if (a.block_idx != nullptr) {
+      count = a.counts[r];
+      const int cap = a.block_idx_stride < a.past_blocks ? a.block_idx_stride : a.past_blocks;
+      if (count < 0 || count > cap) {
+        bad_index = true;
+        count = count < 0 ? 0 : cap;
+      }
     }
-    ptx::mbar_init(ptx::smem_u32(&bars->s_full[0]), 1);
-    ptx::mbar_init(ptx::smem_u32(&bars->s_full[1]), 1);
-    ptx::mbar_init(ptx::smem_u32(&bars->p_full[0]), 128);
-    ptx::mbar_init(ptx::smem_u32(&bars->p_full[1]), 128);
-    ptx::mbar_init(ptx::smem_u32(&bars->o_done), 1);
-    ptx::mbar_init(ptx::smem_u32(&bars->drain), 1);
-    bars->abort_flag = 0;
+    sh->row_count[r] = count;
+    long long tot = 0;
+    for (int p = 0; p < a.n_pairs; ++p) tot += unit_iters(a, count, p);
+    sh->row_prefix[r + 1] = tot;  // turned into a prefix below
+  }
+  if (tid == 0) {
+    sh->row_prefix[0] = 0;
+    sh->abort_flag = 0;
+    ptx::mbar_init(ptx::smem_u32(&sh->q_full[0]), 1);
+    ptx::mbar_init(ptx::smem_u32(&sh->q_full[1]), 1);
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&sh->ring_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&sh->ring_empty[s]), 1);
+    }
+    ptx::mbar_init(ptx::smem_u32(&sh->s_full[0]), 1);
+    ptx::mbar_init(ptx::smem_u32(&sh->s_full[1]), 1);
+    ptx::mbar_init(ptx::smem_u32(&sh->p_full[0]), 128);
+    ptx::mbar_init(ptx::smem_u32(&sh->p_full[1]), 128);
+    ptx::mbar_init(ptx::smem_u32(&sh->o_done), 1);
+    ptx::mbar_init(ptx::smem_u32(&sh->o_free[0]), 128);
+    ptx::mbar_init(ptx::smem_u32(&sh->o_free[1]), 128);
+    ptx::mbar_init(ptx::smem_u32(&sh->drain), 1);
     ptx::mbar_fence_init();
     ptx::fence_proxy_async_smem();
+    if (a.descs) {
+      SegDesc none;
+      none.unit = -1, none.j0 = 0, none.j1 = 0, none.n_iter = 0;
+      a.descs[2 * blockIdx.x] = none;
+      a.descs[2 * blockIdx.x + 1] = none;
+    }
   }
   if (warp == 8) {
-    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), kTmemCols);
+    ptx::tmem_alloc(ptx::smem_u32(&sh->tmem_base), kTmemCols);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
-  const uint32_t tmem = bars->tmem_base;
+  const uint32_t tmem = sh->tmem_base;
 
-  if (warp == 9) {
-    // =============================== TMA producer ===============================
-    bool ok = true;
-    if (lane == 0) {
-      ptx::tma_prefetch_desc(&q_map);
-      ptx::tma_prefetch_desc(&k_map);
-      ptx::tma_prefetch_desc(&v_map);
-      const uint32_t q_bytes = 2u * 128u * static_cast<uint32_t>(a.G * a.tpt);
-      for (int tile = 0; tile < 2; ++tile) {
-        const uint32_t bar = ptx::smem_u32(&bars->q_full[tile]);
-        ptx::mbar_expect_tx(bar, q_bytes);
-        for (int h = 0; h < 2; ++h) {
-          ptx::tma_load_5d(q_smem + tile * kTileBytes + h * kHalfBytes, &q_map, bar, h * 64, 0, hkv,
-                           (mt0 + tile) * a.tpt, b);
-        }
-      }
+  long long span_begin = 0, span_end = 0;
+  if (tid == 0) {
+    for (int r = 0; r < R; ++r) sh->row_prefix[r + 1] += sh->row_prefix[r];
+    const long long total = sh->row_prefix[R];
+    const long long nc = gridDim.x, c = blockIdx.x;
+    if (a.split) {
+      span_begin = total * c / nc;
+      span_end = total * (c + 1) / nc;
+    } else {
+      // whole units only: equal unit counts per CTA
+      const long long nu = static_cast<long long>(R) * a.n_pairs;
+      auto unit_start = [&](long long u) -> long long {
+        if (u >= nu) return total;
+        const int r = static_cast<int>(u / a.n_pairs), p = static_cast<int>(u % a.n_pairs);
+        long long s = sh->row_prefix[r];
+        for (int q = 0; q < p; ++q) s += unit_iters(a, sh->row_count[r], q);
+        return s;
+      };
+      span_begin = unit_start(nu * c / nc);
+      span_end = unit_start(nu * (c + 1) / nc);
     }
-    int n = 0;  // ring entries issued: K0 V0 K1 V1 ...
-    for (int base = 0; base < n_sub && ok; base += 32) {
-      // every lane resolves one sub-block of this batch of 32
-      const int u = base + lane;
-      int page = 0, off = 0;
-      if (u < n_sub) {
-        int tok;
-        if (u < n_past_sub) {
-          const int bi = u / a.spb;
-          int blk = a.block_idx ? a.block_idx[static_cast<long long>(row) * a.block_idx_stride + bi] : bi;
-          if (blk < 0 || blk >= a.past_blocks) {
-            bad_index = true;
-            blk = blk < 0 ? 0 : a.past_blocks - 1;
-          }
-          tok = blk * a.block_size + (u - bi * a.spb) * kSub;
-        } else {
-          tok = a.past_tokens + (u - n_past_sub) * kSub;
-        }
-        const int lp = tok / a.page_size;
-        off = tok - lp * a.page_size;
-        if (a.page_table) {
-          page = (lp < a.pages_per_seq) ? a.page_table[static_cast<long long>(b) * a.pages_per_seq + lp] : -1;
-          if (page < 0 || page >= a.num_pages) {
-            bad_index = true;
-            page = 0;
-          }
-        } else {
-          page = b * a.pages_per_seq + lp;  // beyond the tensor: TMA zero-fills
-        }
-      }
-      for (int i = 0; i < 16 && ok; ++i) {
-        const int j = (base >> 1) + i;
-        if (j >= n_iter) break;
-        const int p0 = __shfl_sync(0xffffffffu, page, 2 * i);
-        const int o0 = __shfl_sync(0xffffffffu, off, 2 * i);
-        const int p1 = __shfl_sync(0xffffffffu, page, 2 * i + 1);
-        const int o1 = __shfl_sync(0xffffffffu, off, 2 * i + 1);
-        const bool two = (2 * j + 1) < n_sub;
-        if (lane == 0) {
-          for (int kv = 0; kv < 2 && ok; ++kv, ++n) {
-            const int slot = n % kStages;
-            const uint32_t phase = (n / kStages) & 1;
-            ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bars->ring_empty[slot]), phase ^ 1u, abort_flag, limit);
-            if (!ok) break;
-            const uint32_t bar = ptx::smem_u32(&bars->ring_full[slot]);
-            const CUtensorMap* map = kv == 0 ? &k_map : &v_map;
-            const uint32_t dst = ring_smem + slot * kTileBytes;
-            ptx::mbar_expect_tx(bar, two ? 4u * kBoxBytes : 2u * kBoxBytes);
-            int c0[3], c1[3];
-            c0[a.slot_tok] = o0, c0[a.slot_page] = p0, c0[a.slot_head] = hkv;
-            c1[a.slot_tok] = o1, c1[a.slot_page] = p1, c1[a.slot_head] = hkv;
-            for (int h = 0; h < 2; ++h) {
-              ptx::tma_load_4d(dst + h * kHalfBytes, map, bar, h * 64, c0[0], c0[1], c0[2]);
-              if (two) ptx::tma_load_4d(dst + h * kHalfBytes + kBoxBytes, map, bar, h * 64, c1[0], c1[1], c1[2]);
+    sh->next_x = span_begin;
+    sh->more = span_end > span_begin ? 1 : 0;
+    sh->n_segs = 0;
+  }
+  __syncthreads();
+
+  // role state that lives across segments
+  int ring_n = 0;        // ring entries issued (loader) / consumed (MMA)
+  uint32_t it = 0;       // KV steps processed so far: parity of s_full / p_full
+  uint32_t seg_seq = 0;  // segments processed so far: parity of q_full / o_done / o_free
+  bool ok = true;
+
+  // The producer warpgroup hands registers to the softmax warpgroups (2 x 128 x 208 + 128 x 96 =
+  // 65536).  Each side keeps its own copy of the batch loop so the raised budget applies to the
+  // softmax code; both sides execute the same sequence of CTA-wide barriers.
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+    while (true) {
+      __syncthreads();  // thread 0 (softmax side) has planned the next batch
+      const int n_segs = sh->n_segs;
+      if (n_segs == 0) break;
+      if (warp == 9) {
+        // =============================== TMA producer ===============================
+        for (int si = 0; si < n_segs && ok; ++si) {
+          const Segment sg = sh->segs[si];
+          const int b = sg.row / a.Hkv, hkv = sg.row % a.Hkv;
+          if (lane == 0) {
+            // Q smem is free once every MMA of the previous segment has completed
+            if (seg_seq > 0) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&sh->o_done), (seg_seq - 1) & 1, abort_flag, limit);
+            if (ok) {
+              const uint32_t q_bytes = 2u * 128u * static_cast<uint32_t>(a.G * a.tpt);
+              for (int tile = 0; tile < 2; ++tile) {
+                const uint32_t bar = ptx::smem_u32(&sh->q_full[tile]);
+                ptx::mbar_expect_tx(bar, q_bytes);
+                for (int h = 0; h < 2; ++h) {
+                  ptx::tma_load_5d(q_smem + tile * kTileBytes + h * kHalfBytes, &q_map, bar, h * 64, 0, hkv,
+                                   (2 * sg.pair + tile) * a.tpt, b);
+                }
+              }
             }
           }
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          for (int base = 2 * sg.j0; base < 2 * sg.j1 && ok; base += 32) {
+            // every lane resolves one sub-block of this batch of 32
+            const int u = base + lane;
+            int page = 0, off = 0;
+            if (u < sg.n_sub) {
+              int tok;
+              if (u < sg.n_past_sub) {
+                const int bi = u / a.spb;
+                int blk = a.block_idx ? a.block_idx[static_cast<long long>(sg.row) * a.block_idx_stride + bi] : bi;
+                if (blk < 0 || blk >= a.past_blocks) {
+                  bad_index = true;
+                  blk = blk < 0 ? 0 : a.past_blocks - 1;
+                }
+                tok = blk * a.block_size + (u - bi * a.spb) * kSub;
+              } else {
+                tok = a.past_tokens + (u - sg.n_past_sub) * kSub;
+              }
+              const int lp = tok / a.page_size;
+              off = tok - lp * a.page_size;
+              if (a.page_table) {
+                page = (lp < a.pages_per_seq) ? a.page_table[static_cast<long long>(b) * a.pages_per_seq + lp] : -1;
+                if (page < 0 || page >= a.num_pages) {
+                  bad_index = true;
+                  page = 0;
+                }
+              } else {
+                page = b * a.pages_per_seq + lp;  // beyond the tensor: TMA zero-fills
+              }
+            }
+            for (int i = 0; i < 16 && ok; ++i) {
+              const int j = (base >> 1) + i;
+              if (j >= sg.j1) break;
+              const int p0 = __shfl_sync(0xffffffffu, page, 2 * i);
+              const int o0 = __shfl_sync(0xffffffffu, off, 2 * i);
+              const int p1 = __shfl_sync(0xffffffffu, page, 2 * i + 1);
+              const int o1 = __shfl_sync(0xffffffffu, off, 2 * i + 1);
+              const bool two = (2 * j + 1) < sg.n_sub;
+              if (lane == 0) {
+                for (int kv = 0; kv < 2 && ok; ++kv, ++ring_n) {
+                  const int slot = ring_n % kStages;
+                  const uint32_t phase = (ring_n / kStages) & 1;
+                  ok = ptx::mbar_wait_bounded(ptx::smem_u32(&sh->ring_empty[slot]), phase ^ 1u, abort_flag, limit);
+                  if (!ok) break;
+                  const uint32_t bar = ptx::smem_u32(&sh->ring_full[slot]);
+                  const CUtensorMap* map = kv == 0 ? &k_map : &v_map;
+                  const uint32_t dst = ring_smem + slot * kTileBytes;
+                  ptx::mbar_expect_tx(bar, two ? 4u * kBoxBytes : 2u * kBoxBytes);
+                  int c0[3], c1[3];
+                  c0[a.slot_tok] = o0, c0[a.slot_page] = p0, c0[a.slot_head] = hkv;
+                  c1[a.slot_tok] = o1, c1[a.slot_page] = p1, c1[a.slot_head] = hkv;
+                  for (int h = 0; h < 2; ++h) {
+                    ptx::tma_load_4d(dst + h * kHalfBytes, map, bar, h * 64, c0[0], c0[1], c0[2]);
+                    if (two) ptx::tma_load_4d(dst + h * kHalfBytes + kBoxBytes, map, bar, h * 64, c1[0], c1[1], c1[2]);
+                  }
+                }
+              }
+              ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            }
+          }
+          ++seg_seq;
         }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      }
-    }
-    if (!ok && lane == 0) {
-      // drain: give copies already issued a bounded chance to land before the CTA exits
-      for (int e = (n > kStages ? n - kStages : 0); e < n; ++e) {
-        int dummy = 0;
-        ptx::mbar_wait_bounded(ptx::smem_u32(&bars->ring_full[e % kStages]), (e / kStages) & 1, &dummy,
-                               100000000ull);
-      }
-    }
-    if (bad_index && a.status) atomicOr(a.status, CA_STATUS_BAD_INDEX);
-  } else if (warp == 8) {
-    // =============================== MMA issuer ===============================
-    if (lane == 0) {
-      bool ok = true;
-      const uint32_t tS[2] = {tmem + 0u, tmem + 128u};
-      const uint32_t tO[2] = {tmem + 256u, tmem + 384u};
-      auto issue_s = [&](int tile, int slot) {
-        const uint32_t qa = q_smem + tile * kTileBytes;
-        const uint32_t kb = ring_smem + slot * kTileBytes;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t o = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          ptx::mma_ss(tS[tile], ptx::make_smem_desc_sw128(qa + o, 0, 1024),
-                      ptx::make_smem_desc_sw128(kb + o, 0, 1024), a.idesc_qk, k > 0 ? 1u : 0u);
+      } else if (warp == 8) {
+        // =============================== MMA issuer ===============================
+        if (lane == 0) {
+          const uint32_t tS[2] = {tmem + 0u, tmem + 128u};
+          const uint32_t tO[2] = {tmem + 256u, tmem + 384u};
+          auto issue_s = [&](int tile, int slot) {
+            const uint32_t qa = q_smem + tile * kTileBytes;
+            const uint32_t kb = ring_smem + slot * kTileBytes;
+  #pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t o = (k >> 2) * kHalfBytes + (k & 3) * 32;
+              ptx::mma_ss(tS[tile], ptx::make_smem_desc_sw128(qa + o, 0, 1024),
+                          ptx::make_smem_desc_sw128(kb + o, 0, 1024), a.idesc_qk, k > 0 ? 1u : 0u);
+            }
+          };
+          auto issue_pv = [&](int tile, int slot, int ksteps, bool first) {
+            const uint32_t vb = ring_smem + slot * kTileBytes;
+            for (int k = 0; k < ksteps; ++k) {
+              ptx::mma_ts(tO[tile], tS[tile] + k * 8, ptx::make_smem_desc_sw128(vb + k * 2048, kHalfBytes, 1024),
+                          a.idesc_pv, (first && k == 0) ? 0u : 1u);
+            }
+          };
+          auto wait = [&](uint64_t* bar, uint32_t parity) {
+            if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(bar), parity, abort_flag, limit);
+            return ok;
+          };
+          for (int si = 0; si < n_segs && ok; ++si) {
+            const Segment sg = sh->segs[si];
+            const uint32_t qpar = seg_seq & 1;
+            {
+              const int slot = ring_n % kStages;
+              const uint32_t phase = (ring_n / kStages) & 1;
+              if (!(wait(&sh->q_full[0], qpar) && wait(&sh->q_full[1], qpar) && wait(&sh->ring_full[slot], phase))) break;
+              ptx::tc_fence_after();
+              issue_s(0, slot);
+              ptx::tc_commit(ptx::smem_u32(&sh->s_full[0]));
+              issue_s(1, slot);
+              ptx::tc_commit(ptx::smem_u32(&sh->s_full[1]));
+              ptx::tc_commit(ptx::smem_u32(&sh->ring_empty[slot]));
+              ++ring_n;
+            }
+            for (int j = sg.j0; j < sg.j1 && ok; ++j, ++it) {
+              const int v_slot = ring_n % kStages;
+              const uint32_t v_phase = (ring_n / kStages) & 1;
+              ++ring_n;
+              const bool more = (j + 1) < sg.j1;
+              const int k_slot = ring_n % kStages;
+              const uint32_t k_phase = (ring_n / kStages) & 1;
+              if (more) ++ring_n;
+              const int ksteps = ((2 * j + 1) < sg.n_sub) ? 8 : 4;
+              const bool first = j == sg.j0;
+              if (!wait(&sh->ring_full[v_slot], v_phase)) break;
+              if (!wait(&sh->p_full[0], it & 1)) break;
+              // the accumulator is free once the previous segment's epilogue has read it
+              if (first && seg_seq > 0 && !wait(&sh->o_free[0], (seg_seq - 1) & 1)) break;
+              ptx::tc_fence_after();
+              issue_pv(0, v_slot, ksteps, first);
+              if (more) {
+                if (!wait(&sh->ring_full[k_slot], k_phase)) break;
+                ptx::tc_fence_after();
+                issue_s(0, k_slot);
+                ptx::tc_commit(ptx::smem_u32(&sh->s_full[0]));
+              }
+              if (!wait(&sh->p_full[1], it & 1)) break;
+              if (first && seg_seq > 0 && !wait(&sh->o_free[1], (seg_seq - 1) & 1)) break;
+              ptx::tc_fence_after();
+              issue_pv(1, v_slot, ksteps, first);
+              ptx::tc_commit(ptx::smem_u32(&sh->ring_empty[v_slot]));
+              if (more) {
+                issue_s(1, k_slot);
+                ptx::tc_commit(ptx::smem_u32(&sh->s_full[1]));
+                ptx::tc_commit(ptx::smem_u32(&sh->ring_empty[k_slot]));
+              }
+            }
+            if (ok) ptx::tc_commit(ptx::smem_u32(&sh->o_done));
+            ++seg_seq;
+          }
         }
-      };
-      auto issue_pv = [&](int tile, int slot, int ksteps, bool first) {
-        const uint32_t vb = ring_smem + slot * kTileBytes;
-        for (int k = 0; k < ksteps; ++k) {
-          ptx::mma_ts(tO[tile], tS[tile] + k * 8, ptx::make_smem_desc_sw128(vb + k * 2048, kHalfBytes, 1024),
-                      a.idesc_pv, (first && k == 0) ? 0u : 1u);
-        }
-      };
-      auto wait = [&](uint64_t* bar, uint32_t parity) {
-        if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(bar), parity, abort_flag, limit);
-        return ok;
-      };
-      int n = 0;  // ring entries consumed
-      if (wait(&bars->q_full[0], 0) && wait(&bars->q_full[1], 0) && wait(&bars->ring_full[0], 0)) {
-        ptx::tc_fence_after();
-        issue_s(0, 0);
-        ptx::tc_commit(ptx::smem_u32(&bars->s_full[0]));
-        issue_s(1, 0);
-        ptx::tc_commit(ptx::smem_u32(&bars->s_full[1]));
-        ptx::tc_commit(ptx::smem_u32(&bars->ring_empty[0]));
-        n = 1;
       }
-      for (int j = 0; j < n_iter && ok; ++j) {
-        const int v_slot = n % kStages;
-        const uint32_t v_phase = (n / kStages) & 1;
-        ++n;
-        const bool more = (j + 1) < n_iter;
-        const int k_slot = n % kStages;
-        const uint32_t k_phase = (n / kStages) & 1;
-        if (more) ++n;
-        const int ksteps = ((2 * j + 1) < n_sub) ? 8 : 4;
-        if (!wait(&bars->ring_full[v_slot], v_phase)) break;
-        if (!wait(&bars->p_full[0], j & 1)) break;
-        ptx::tc_fence_after();
-        issue_pv(0, v_slot, ksteps, j == 0);
-        if (more) {
-          if (!wait(&bars->ring_full[k_slot], k_phase)) break;
-          ptx::tc_fence_after();
-          issue_s(0, k_slot);
-          ptx::tc_commit(ptx::smem_u32(&bars->s_full[0]));
-        }
-        if (!wait(&bars->p_full[1], j & 1)) break;
-        ptx::tc_fence_after();
-        issue_pv(1, v_slot, ksteps, j == 0);
-        ptx::tc_commit(ptx::smem_u32(&bars->ring_empty[v_slot]));
-        if (more) {
-          issue_s(1, k_slot);
-          ptx::tc_commit(ptx::smem_u32(&bars->s_full[1]));
-          ptx::tc_commit(ptx::smem_u32(&bars->ring_empty[k_slot]));
-        }
-      }
-      if (ok) {
-        ptx::tc_commit(ptx::smem_u32(&bars->o_done));
-      } else {
-        // drain the tensor pipe (bounded) before TMEM is released
-        ptx::tc_commit(ptx::smem_u32(&bars->drain));
-        int dummy = 0;
-        ptx::mbar_wait_bounded(ptx::smem_u32(&bars->drain), 0, &dummy, 100000000ull);
-      }
+      ok = __syncthreads_and(ok ? 1 : 0) != 0;  // all roles finished this batch (or aborted)
+      if (!ok) break;
     }
   } else {
-    // =============================== softmax + epilogue ===============================
-    const int tile = warp >> 2;          // 0: A, 1: B
-    const int r = tid & 127;             // tile row = TMEM lane
-    const int t = (mt0 + tile) * a.tpt + r / a.G;  // chunk token of this row
-    const int g = r % a.G;
-    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem + lane_base + tile * 128u;
-    const uint32_t tO = tmem + lane_base + 256u + tile * 128u;
-    const float sc = a.scale_log2;
-    float m_run = -INFINITY;
-    float l_run = 0.f;
-    bool ok = true;
-    uint32_t v[32];
-
-    for (int j = 0; j < n_iter; ++j) {
-      ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bars->s_full[tile]), j & 1, abort_flag, limit);
-      ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the collective TMEM ops
-      if (!ok) break;
-      ptx::tc_fence_after();
-      const bool masked = (2 * j + 1) >= n_past_sub;  // a chunk or tail sub-block is in this step
-      int lim0 = kSub, lim1 = kSub;
-      if (masked) {
-        lim0 = visible_cols(2 * j, n_sub, n_past_sub, t);
-        lim1 = visible_cols(2 * j + 1, n_sub, n_past_sub, t);
-      }
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        ptx::tmem_ld32(tS + c * 32, v);
-        ptx::tc_wait_ld();
-        if (masked) {
-          const int lim = (c < 2 ? lim0 : lim1) - (c & 1) * 32;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, i < lim ? __uint_as_float(v[i]) : -INFINITY);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-        }
-      }
-      // lazy rescale of the running accumulator
-      const float m_new = fmaxf(m_run, mx);
-      const bool need = (m_new - m_run) * sc > kRescaleThreshold;
-      if (__any_sync(0xffffffffu, need)) {
-        const float alpha = need ? ptx::ex2((m_run - m_new) * sc) : 1.0f;
-        if (j > 0) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            ptx::tmem_ld32(tO + c * 32, v);
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    while (true) {
+      if (tid == 0 && sh->more) plan_segments(a, sh, sh->next_x, span_begin, span_end, R);
+      else if (tid == 0) sh->n_segs = 0;
+      __syncthreads();
+      const int n_segs = sh->n_segs;
+      if (n_segs == 0) break;
+      {
+        // =============================== softmax + epilogue ===============================
+        const int tile = warp >> 2;  // 0: A, 1: B
+        const int r = tid & 127;     // tile row = TMEM lane
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t tS = tmem + lane_base + tile * 128u;
+        const uint32_t tO = tmem + lane_base + 256u + tile * 128u;
+        const float sc = a.scale_log2;
+        uint32_t v[32];
+        for (int si = 0; si < n_segs && ok; ++si) {
+          const Segment sg = sh->segs[si];
+          const int b = sg.row / a.Hkv, hkv = sg.row % a.Hkv;
+          const int t = (2 * sg.pair + tile) * a.tpt + r / a.G;  // chunk token of this row
+          const int g = r % a.G;
+          float m_run = -INFINITY;
+          float l_run = 0.f;
+          for (int j = sg.j0; j < sg.j1; ++j, ++it) {
+            ok = ptx::mbar_wait_bounded(ptx::smem_u32(&sh->s_full[tile]), it & 1, abort_flag, limit);
+            ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the collective TMEM ops
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const bool masked = (2 * j + 1) >= sg.n_past_sub;  // a chunk or tail sub-block is in this step
+            int lim0 = kSub, lim1 = kSub;
+            if (masked) {
+              lim0 = visible_cols(2 * j, sg.n_sub, sg.n_past_sub, t);
+              lim1 = visible_cols(2 * j + 1, sg.n_sub, sg.n_past_sub, t);
+            }
+            // the whole S row (128 fp32) comes into registers with one wait
+            uint32_t sv[128];
+            ptx::tmem_ld32_row<0>(tS + 0, sv);
+            ptx::tmem_ld32_row<32>(tS + 32, sv);
+            ptx::tmem_ld32_row<64>(tS + 64, sv);
+            ptx::tmem_ld32_row<96>(tS + 96, sv);
             ptx::tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            ptx::tmem_st32(tO + c * 32, v);
+            if (masked) {
+  #pragma unroll
+              for (int i = 0; i < 128; ++i) {
+                const int lim = i < 64 ? lim0 : lim1;
+                if ((i & 63) >= lim) sv[i] = 0xff800000u;  // -inf
+              }
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+  #pragma unroll
+            for (int i = 0; i < 128; i += 4) {
+              mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
+              mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
+              mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2]));
+              mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            // lazy rescale of the running accumulator
+            const float m_new = fmaxf(m_run, mx);
+            const bool need = m_new > m_run && (m_run == -INFINITY || (m_new - m_run) * sc > kRescaleThreshold);
+            if (__any_sync(0xffffffffu, need)) {
+              const float alpha = need ? (m_run == -INFINITY ? 0.f : ptx::ex2((m_run - m_new) * sc)) : 1.0f;
+              if (j > sg.j0) {
+  #pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  ptx::tmem_ld32(tO + c * 32, v);
+                  ptx::tc_wait_ld();
+  #pragma unroll
+                  for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                  ptx::tmem_st32(tO + c * 32, v);
+                }
+                ptx::tc_wait_st();
+              }
+              l_run *= alpha;
+              if (need) m_run = m_new;
+            }
+            // P = exp2(S*sc - m*sc) -> 16-bit, written over S.  Masked entries are -inf -> 0; a row
+            // that has seen nothing yet (m = -inf) produces zeros.
+            const float neg_m = m_run == -INFINITY ? 0.f : -m_run * sc;
+            float l0 = 0.f, l1 = 0.f;
+  #pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t pk[16];
+  #pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float p0 = ptx::ex2(fmaf(__uint_as_float(sv[c * 32 + i]), sc, neg_m));
+                const float p1 = ptx::ex2(fmaf(__uint_as_float(sv[c * 32 + i + 1]), sc, neg_m));
+                l0 += p0;
+                l1 += p1;
+                pk[i >> 1] = pack2<T>(p0, p1);
+              }
+              ptx::tmem_st16(tS + c * 16, pk);
+            }
+            l_run += l0 + l1;
+            ptx::tc_wait_st();
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(ptx::smem_u32(&sh->p_full[tile]));
           }
-          ptx::tc_wait_st();
-        }
-        l_run *= alpha;
-        if (need) m_run = m_new;
-      }
-      // pass 2: P = exp2(S*sc - m*sc) -> 16-bit, written over S
-      const float neg_m = -m_run * sc;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        ptx::tmem_ld32(tS + c * 32, v);
-        ptx::tc_wait_ld();
-        uint32_t pk[16];
-        const int lim = masked ? ((c < 2 ? lim0 : lim1) - (c & 1) * 32) : 32;
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = ptx::ex2(fmaf(__uint_as_float(v[i]), sc, neg_m));
-          float p1 = ptx::ex2(fmaf(__uint_as_float(v[i + 1]), sc, neg_m));
-          if (masked) {
-            p0 = i < lim ? p0 : 0.f;
-            p1 = (i + 1) < lim ? p1 : 0.f;
+          if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&sh->o_done), seg_seq & 1, abort_flag, limit);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          const bool live = (r < a.tpt * a.G) && (t < a.Q);
+          if (sg.slot < 0) {
+            // whole unit: normalise and write the output rows
+            const float inv_l = 1.0f / l_run;
+            T* orow = reinterpret_cast<T*>(a.out) + b * a.o_stride_b + static_cast<long long>(t) * a.o_stride_t +
+                      static_cast<long long>(hkv * a.G + g) * a.o_stride_h;
+  #pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              ptx::tmem_ld32(tO + c * 32, v);
+              ptx::tc_wait_ld();
+              if (live) {
+  #pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                  uint4 w;
+                  w.x = pack2<T>(__uint_as_float(v[i + 0]) * inv_l, __uint_as_float(v[i + 1]) * inv_l);
+                  w.y = pack2<T>(__uint_as_float(v[i + 2]) * inv_l, __uint_as_float(v[i + 3]) * inv_l);
+                  w.z = pack2<T>(__uint_as_float(v[i + 4]) * inv_l, __uint_as_float(v[i + 5]) * inv_l);
+                  w.w = pack2<T>(__uint_as_float(v[i + 6]) * inv_l, __uint_as_float(v[i + 7]) * inv_l);
+                  *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+                }
+              }
+            }
+            if (live && a.lse) {
+              a.lse[(static_cast<long long>(b) * (a.Hkv * a.G) + hkv * a.G + g) * a.Q + t] =
+                  0.6931471805599453f * (m_run * sc + log2f(l_run));
+            }
+          } else {
+            // segment of a split unit: unnormalised accumulator, running max and sum to the workspace
+            float* po = a.part_o + static_cast<long long>(sg.slot) * kPartialOFloats + tile * (kTileM * kHeadDim);
+            float* pml = a.part_ml + static_cast<long long>(sg.slot) * kPartialMLFloats + (tile * kTileM + r) * 2;
+  #pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              ptx::tmem_ld32(tO + c * 32, v);
+              ptx::tc_wait_ld();
+  #pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                const int c4 = (c * 32 + i) >> 2;
+                *reinterpret_cast<uint4*>(po + (static_cast<long long>(c4) * kTileM + r) * 4) =
+                    make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+              }
+            }
+            pml[0] = m_run;
+            pml[1] = l_run;
           }
-          l_run += p0 + p1;
-          pk[i >> 1] = pack2<T>(p0, p1);
-        }
-        ptx::tmem_st16(tS + c * 16, pk);
-      }
-      ptx::tc_wait_st();
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(ptx::smem_u32(&bars->p_full[tile]));
-    }
-
-    if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bars->o_done), 0, abort_flag, limit);
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
-      ptx::tc_fence_after();
-      const bool live = (r < a.tpt * a.G) && (t < a.Q);
-      const float inv_l = 1.0f / l_run;
-      T* orow = reinterpret_cast<T*>(a.out) + b * a.o_stride_b + static_cast<long long>(t) * a.o_stride_t +
-                static_cast<long long>(hkv * a.G + g) * a.o_stride_h;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        ptx::tmem_ld32(tO + c * 32, v);
-        ptx::tc_wait_ld();
-        if (live) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 w;
-            w.x = pack2<T>(__uint_as_float(v[i + 0]) * inv_l, __uint_as_float(v[i + 1]) * inv_l);
-            w.y = pack2<T>(__uint_as_float(v[i + 2]) * inv_l, __uint_as_float(v[i + 3]) * inv_l);
-            w.z = pack2<T>(__uint_as_float(v[i + 4]) * inv_l, __uint_as_float(v[i + 5]) * inv_l);
-            w.w = pack2<T>(__uint_as_float(v[i + 6]) * inv_l, __uint_as_float(v[i + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
-          }
+          // the accumulator may be overwritten by the next segment
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(ptx::smem_u32(&sh->o_free[tile]));
+          ++seg_seq;
         }
       }
-      if (live && a.lse) {
-        a.lse[(static_cast<long long>(b) * (a.Hkv * a.G) + hkv * a.G + g) * a.Q + t] =
-            0.6931471805599453f * (m_run * sc + log2f(l_run));
-      }
+      ok = __syncthreads_and(ok ? 1 : 0) != 0;  // all roles finished this batch (or aborted)
+      if (!ok) break;
     }
   }
 
   // ---- teardown: every thread arrives here on every path ----
+  if (sh->abort_flag) {
+    if (warp == 9 && lane == 0) {
+      // drain: give copies already issued a bounded chance to land before the CTA exits
+      for (int e = (ring_n > kStages ? ring_n - kStages : 0); e < ring_n; ++e) {
+        int dummy = 0;
+        ptx::mbar_wait_bounded(ptx::smem_u32(&sh->ring_full[e % kStages]), (e / kStages) & 1, &dummy, 100000000ull);
+      }
+    }
+    if (warp == 8 && lane == 0) {
+      // drain the tensor pipe (bounded) before TMEM is released
+      ptx::tc_commit(ptx::smem_u32(&sh->drain));
+      int dummy = 0;
+      ptx::mbar_wait_bounded(ptx::smem_u32(&sh->drain), 0, &dummy, 100000000ull);
+    }
+  }
+  if (bad_index && a.status) atomicOr(a.status, CA_STATUS_BAD_INDEX);
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 8) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, kTmemCols);
   }
-  if (tid == 0 && bars->abort_flag && a.status) atomicOr(a.status, CA_STATUS_TIMEOUT);
+  if (tid == 0 && sh->abort_flag && a.status) atomicOr(a.status, CA_STATUS_TIMEOUT);
+}
+
+// Merges the segments of every split unit.  One CTA per (workspace slot, tile); the CTA whose slot
+// holds the first segment of a unit (j0 == 0) walks the following CTAs' head slots until the unit
+// is complete.  Thread = tile row.
+template <typename T>
+__global__ void __launch_bounds__(kTileM) attn_combine_kernel(const KernelArgs a, int n_slots) {
+  const int slot = blockIdx.x, tile = blockIdx.y, r = threadIdx.x;
+  const SegDesc first = a.descs[slot];
+  if (first.unit < 0 || first.j0 != 0) return;
+  // chain of slots: this one, then the head slots (even) of the following CTAs
+  // (CTAs whose span is empty leave their slots unused and are skipped)
+  int chain[256];
+  int n = 0;
+  chain[n++] = slot;
+  int reached = first.j1;
+  for (int s = (slot / 2 + 1) * 2; s < n_slots && reached < first.n_iter && n < 256; s += 2) {
+    const SegDesc d = a.descs[s];
+    if (d.unit < 0) continue;
+    if (d.unit != first.unit || d.j0 != reached) break;
+    chain[n++] = s;
+    reached = d.j1;
+  }
+  if (reached != first.n_iter) {
+    if (r == 0 && a.status) atomicOr(a.status, CA_STATUS_BAD_INDEX);
+    return;
+  }
+  const int row = first.unit / a.n_pairs, pair = first.unit % a.n_pairs;
+  const int b = row / a.Hkv, hkv = row % a.Hkv;
+  const int t = (2 * pair + tile) * a.tpt + r / a.G;
+  const int g = r % a.G;
+  const bool live = (r < a.tpt * a.G) && (t < a.Q);
+  const float sc = a.scale_log2;
+  float m = -INFINITY;
+  for (int i = 0; i < n; ++i)
+    m = fmaxf(m, a.part_ml[static_cast<long long>(chain[i]) * kPartialMLFloats + (tile * kTileM + r) * 2]);
+  float l = 0.f;
+  for (int i = 0; i < n; ++i) {
+    const float* pml = a.part_ml + static_cast<long long>(chain[i]) * kPartialMLFloats + (tile * kTileM + r) * 2;
+    l += pml[0] == -INFINITY ? 0.f : pml[1] * ptx::ex2((pml[0] - m) * sc);
+  }
+  const float inv_l = 1.0f / l;
+  T* orow = reinterpret_cast<T*>(a.out) + b * a.o_stride_b + static_cast<long long>(t) * a.o_stride_t +
+            static_cast<long long>(hkv * a.G + g) * a.o_stride_h;
+  for (int c8 = 0; c8 < kHeadDim / 8; ++c8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < n; ++i) {
+      const float ms = a.part_ml[static_cast<long long>(chain[i]) * kPartialMLFloats + (tile * kTileM + r) * 2];
+      const float w = ms == -INFINITY ? 0.f : ptx::ex2((ms - m) * sc);
+      const float* po = a.part_o + static_cast<long long>(chain[i]) * kPartialOFloats + tile * (kTileM * kHeadDim);
+      const float4 x0 = *reinterpret_cast<const float4*>(po + (static_cast<long long>(2 * c8) * kTileM + r) * 4);
+      const float4 x1 = *reinterpret_cast<const float4*>(po + (static_cast<long long>(2 * c8 + 1) * kTileM + r) * 4);
+      acc[0] += w * x0.x, acc[1] += w * x0.y, acc[2] += w * x0.z, acc[3] += w * x0.w;
+      acc[4] += w * x1.x, acc[5] += w * x1.y, acc[6] += w * x1.z, acc[7] += w * x1.w;
+    }
+    if (live) {
+      uint4 w;
+      w.x = pack2<T>(acc[0] * inv_l, acc[1] * inv_l);
+      w.y = pack2<T>(acc[2] * inv_l, acc[3] * inv_l);
+      w.z = pack2<T>(acc[4] * inv_l, acc[5] * inv_l);
+      w.w = pack2<T>(acc[6] * inv_l, acc[7] * inv_l);
+      *reinterpret_cast<uint4*>(orow + c8 * 8) = w;
+    }
+  }
+  if (live && a.lse) {
+    a.lse[(static_cast<long long>(b) * (a.Hkv * a.G) + hkv * a.G + g) * a.Q + t] = 0.6931471805599453f * (m * sc + log2f(l));
+  }
 }
 
 static int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const cuuint64_t* dims,
@@ -463,6 +734,7 @@ static int validate(const ca_attn_params* p) {
   CA_REQUIRE(p->B > 0 && p->Q > 0 && p->Hq > 0 && p->Hkv > 0, "B, Q, Hq, Hkv must be positive");
   CA_REQUIRE(p->Hq % p->Hkv == 0, "Hq (%d) must be a multiple of Hkv (%d)", p->Hq, p->Hkv);
   CA_REQUIRE(p->Hq / p->Hkv <= 128, "GQA group larger than 128 is not supported");
+  CA_REQUIRE(static_cast<long long>(p->B) * p->Hkv <= kMaxRows, "more than %d (batch x kv head) rows are not supported", kMaxRows);
   CA_REQUIRE(p->block_size > 0 && p->block_size % kSub == 0, "block_size must be a positive multiple of 64");
   CA_REQUIRE(p->kv_len >= p->Q, "kv_len (%d) must be >= Q (%d)", p->kv_len, p->Q);
   CA_REQUIRE((p->kv_len - p->Q) % p->block_size == 0, "past length must be a multiple of block_size");
@@ -484,8 +756,16 @@ static int validate(const ca_attn_params* p) {
     CA_REQUIRE(p->counts != nullptr, "counts is required with block_idx");
     CA_REQUIRE(p->block_idx_stride > 0 || p->kv_len == p->Q, "block_idx_stride must be positive");
   }
+  CA_REQUIRE(p->workspace == nullptr || reinterpret_cast<uintptr_t>(p->workspace) % 256 == 0,
+             "workspace must be 256-byte aligned");
   return CA_OK;
 }
+
+// Workspace layout for a grid of nc CTAs: descriptors, then (max, sum) pairs, then accumulators.
+static size_t desc_bytes(int nc) { return ((static_cast<size_t>(2) * nc * sizeof(SegDesc) + 255) / 256) * 256; }
+static size_t ml_bytes(int nc) { return static_cast<size_t>(2) * nc * kPartialMLFloats * sizeof(float); }
+static size_t o_bytes(int nc) { return static_cast<size_t>(2) * nc * kPartialOFloats * sizeof(float); }
+static size_t workspace_bytes_for(int nc) { return desc_bytes(nc) + ml_bytes(nc) + o_bytes(nc); }
 
 }  // namespace attn
 }  // namespace ca
@@ -497,7 +777,10 @@ int ca_attn_workspace_bytes(const ca_attn_params* p, size_t* bytes_out) {
   CA_REQUIRE(bytes_out != nullptr, "bytes_out is null");
   int rc = attn::validate(p);
   if (rc != CA_OK) return rc;
-  *bytes_out = 0;
+  DeviceInfo dev;
+  rc = get_device_info(&dev);
+  if (rc != CA_OK) return rc;
+  *bytes_out = attn::workspace_bytes_for(dev.sm_count);
   return CA_OK;
 }
 
@@ -515,6 +798,7 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
   const int G = p->Hq / p->Hkv;
   const int tpt = kTileM / G;
   const int n_mtiles = ceil_div(p->Q, tpt);
+  const int n_pairs = ceil_div(n_mtiles, 2);
   const CUtensorMapDataType dt = p->dtype == CA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
 
   CUtensorMap q_map, k_map, v_map;
@@ -561,6 +845,7 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
   a.Hkv = p->Hkv;
   a.B = p->B;
   a.tpt = tpt;
+  a.n_pairs = n_pairs;
   a.block_size = p->block_size;
   a.past_tokens = p->kv_len - p->Q;
   a.past_blocks = a.past_tokens / p->block_size;
@@ -587,7 +872,22 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
   a.slot_page = slot_page;
   a.slot_head = slot_head;
 
-  dim3 grid(ceil_div(n_mtiles, 2), p->B * p->Hkv);
+  // persistent grid: one CTA per SM, never more CTAs than units when units cannot be cut
+  const long long n_units = static_cast<long long>(p->B) * p->Hkv * n_pairs;
+  int grid = dev.sm_count;
+  // cutting units pays when whole units cannot fill the SMs evenly
+  const bool want_split = n_units < 16LL * dev.sm_count;
+  const bool can_split = p->workspace != nullptr && p->workspace_bytes >= workspace_bytes_for(grid);
+  a.split = (want_split && can_split) ? 1 : 0;
+  if (!a.split && n_units < grid) grid = static_cast<int>(n_units);
+  a.descs = nullptr, a.part_ml = nullptr, a.part_o = nullptr;
+  if (a.split) {
+    uint8_t* ws = static_cast<uint8_t*>(p->workspace);
+    a.descs = reinterpret_cast<SegDesc*>(ws);
+    a.part_ml = reinterpret_cast<float*>(ws + desc_bytes(grid));
+    a.part_o = reinterpret_cast<float*>(ws + desc_bytes(grid) + ml_bytes(grid));
+  }
+
   // the opt-in shared-memory size is a per-device function attribute; setting it is cheap
   if (p->dtype == CA_DTYPE_BF16) {
     CA_CUDA(cudaFuncSetAttribute(attn_compact_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
@@ -597,6 +897,14 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
     attn_compact_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(q_map, k_map, v_map, a);
   }
   CA_LAUNCH_CHECK("attn_compact_kernel");
+  if (a.split) {
+    if (p->dtype == CA_DTYPE_BF16) {
+      attn_combine_kernel<__nv_bfloat16><<<dim3(2 * grid, 2), kTileM, 0, stream>>>(a, 2 * grid);
+    } else {
+      attn_combine_kernel<__half><<<dim3(2 * grid, 2), kTileM, 0, stream>>>(a, 2 * grid);
+    }
+    CA_LAUNCH_CHECK("attn_combine_kernel");
+  }
   return CA_OK;
 }
 

@@ -88,6 +88,23 @@ class KvCacheView:
                              _ptr(self.page_table))
 
 
+_ATTN_WORKSPACES: dict = {}
+
+
+def attn_workspace(device: torch.device, params: "_lib.AttnParams") -> torch.Tensor:
+    """Scratch for the attention kernel's split units (partial accumulators of the segments that the
+    combine kernel merges).  One buffer per (device, stream): launches on one stream run in order, so
+    they can share it; launches on different streams must not."""
+    key = (device.index, _stream())
+    ws = _ATTN_WORKSPACES.get(key)
+    if ws is None:
+        need = C.c_size_t(0)
+        _lib.check(_lib.load().ca_attn_workspace_bytes(C.byref(params), C.byref(need)), "ca_attn_workspace_bytes")
+        ws = torch.empty(max(int(need.value), 256), dtype=torch.uint8, device=device)
+        _ATTN_WORKSPACES[key] = ws
+    return ws
+
+
 def attn_compact(
     q: torch.Tensor,  # [B, Q, Hq, D]
     kv: KvCacheView,
@@ -100,8 +117,13 @@ def attn_compact(
     out: Optional[torch.Tensor] = None,
     lse: Optional[torch.Tensor] = None,
     status: Optional[torch.Tensor] = None,
+    workspace: Optional[torch.Tensor] = None,
+    use_workspace: bool = True,
 ) -> torch.Tensor:
-    """Dense causal attention over the selected KV blocks, read in place through the block table."""
+    """Dense causal attention over the selected KV blocks, read in place through the block table.
+
+    With a workspace (default: a cached per-stream buffer) the kernel may cut work units across SMs
+    and merge the pieces; ``use_workspace=False`` keeps every unit on one SM."""
     _require_cuda(q, kv.k, kv.v, block_idx, counts, out, lse, status)
     B, Q, Hq, D = q.shape
     if q.dtype not in (torch.bfloat16, torch.float16) or kv.k.dtype != q.dtype or kv.v.dtype != q.dtype:
@@ -137,6 +159,9 @@ def attn_compact(
     p.workspace = None
     p.workspace_bytes = 0
     p.status = _ptr(status)
+    if use_workspace:
+        ws = attn_workspace(q.device, p) if workspace is None else workspace
+        p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
     lib = _lib.load()
     _lib.check(lib.ca_attn_compact(C.byref(p), _stream()), "ca_attn_compact")
     return out
