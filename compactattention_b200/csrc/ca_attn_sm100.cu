@@ -290,11 +290,13 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint32_t seg_seq = 0;  // segments processed so far: parity of q_full / o_done / o_free
   bool ok = true;
 
-  // The producer warpgroup hands registers to the softmax warpgroups (2 x 128 x 208 + 128 x 96 =
-  // 65536).  Each side keeps its own copy of the batch loop so the raised budget applies to the
-  // softmax code; both sides execute the same sequence of CTA-wide barriers.
+  // The producer warpgroup hands registers to the softmax warpgroups.  The pool is what the CTA got
+  // at launch, 384 threads x 168 registers = 64512, so 2 x 128 x 208 + 128 x 88 = 64512 fits it
+  // exactly; asking for more would block the second setmaxnreg.inc forever.  Each side keeps its
+  // own copy of the batch loop so the raised budget applies to the softmax code; both sides
+  // execute the same sequence of CTA-wide barriers.
   if (warp >= 8) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
     while (true) {
       __syncthreads();  // thread 0 (softmax side) has planned the next batch
       const int n_segs = sh->n_segs;

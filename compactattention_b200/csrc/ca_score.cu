@@ -123,40 +123,62 @@ struct ProjArgs {
 };
 
 constexpr int kProjBlocks = 8;  // blocks handled per CTA
+constexpr int kProjSlices = 4;  // the Cin reduction is split over this many thread slices
 
-__global__ void proj_rope_kernel(const ProjArgs a) {
-  extern __shared__ float proj_smem[];  // x tile [kProjBlocks][Cin] then exchange [kProjBlocks][Cout]
+// blockDim = (min(Cout,128), kProjSlices).  Weight loads are issued eight at a time so their
+// latencies overlap; slice partial sums meet in shared memory.
+__global__ void __launch_bounds__(128 * kProjSlices) proj_rope_kernel(const ProjArgs a) {
+  extern __shared__ float proj_smem[];  // x tile [kProjBlocks][Cin], partials [kProjSlices][kProjBlocks][Cout]
   float* xs = proj_smem;
   float* ys = proj_smem + kProjBlocks * a.Cin;
+  const int tid = threadIdx.y * blockDim.x + threadIdx.x;
+  const int nthreads = blockDim.x * blockDim.y;
   const int blk0 = blockIdx.x * kProjBlocks;
   const int h = blockIdx.y, b = blockIdx.z;
   const int hin = h / (a.Hout / a.Hin);  // kv head repeated up to the weight's head count
   const int nblk = min(kProjBlocks, a.nb - blk0);
-  for (int e = threadIdx.x; e < nblk * a.Cin; e += blockDim.x) {
+  for (int e = tid; e < kProjBlocks * a.Cin; e += nthreads) {
     const int r = e / a.Cin, c = e % a.Cin;
-    xs[r * a.Cin + c] = a.x[((static_cast<long long>(b) * a.nb + blk0 + r) * a.Hin + hin) * a.Cin + c];
+    xs[e] = r < nblk ? a.x[((static_cast<long long>(b) * a.nb + blk0 + r) * a.Hin + hin) * a.Cin + c] : 0.f;
   }
   __syncthreads();
+  const int slice = threadIdx.y;
+  const int c_per = (a.Cin + kProjSlices - 1) / kProjSlices;
+  const int c_lo = slice * c_per, c_hi = min(a.Cin, c_lo + c_per);
   for (int o = threadIdx.x; o < a.Cout; o += blockDim.x) {
     float acc[kProjBlocks];
 #pragma unroll
     for (int r = 0; r < kProjBlocks; ++r) acc[r] = 0.f;
     if (a.w) {
-      for (int c = 0; c < a.Cin; ++c) {
-        const float w = load_elem(a.w, (static_cast<long long>(h) * a.Cin + c) * a.Cout + o, a.w_dtype);
+      const long long wbase = static_cast<long long>(h) * a.Cin * a.Cout + o;
+      for (int c0 = c_lo; c0 < c_hi; c0 += 8) {
+        float w[8];
 #pragma unroll
-        for (int r = 0; r < kProjBlocks; ++r) acc[r] = fmaf(xs[r * a.Cin + c], w, acc[r]);
+        for (int u = 0; u < 8; ++u) w[u] = (c0 + u < c_hi) ? load_elem(a.w, wbase + static_cast<long long>(c0 + u) * a.Cout, a.w_dtype) : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int c = min(c0 + u, a.Cin - 1);
+#pragma unroll
+          for (int r = 0; r < kProjBlocks; ++r) acc[r] = fmaf(xs[r * a.Cin + c], w[u], acc[r]);
+        }
       }
-    } else {
+    } else if (slice == 0) {
 #pragma unroll
-      for (int r = 0; r < kProjBlocks; ++r) acc[r] = r < nblk ? xs[r * a.Cin + o] : 0.f;
+      for (int r = 0; r < kProjBlocks; ++r) acc[r] = xs[r * a.Cin + o];
     }
 #pragma unroll
-    for (int r = 0; r < kProjBlocks; ++r) ys[r * a.Cout + o] = acc[r];
+    for (int r = 0; r < kProjBlocks; ++r) ys[(slice * kProjBlocks + r) * a.Cout + o] = acc[r];
+  }
+  __syncthreads();
+  // fold the slices into slice 0
+  for (int e = tid; e < kProjBlocks * a.Cout; e += nthreads) {
+    float y = ys[e];
+    for (int sidx = 1; sidx < kProjSlices; ++sidx) y += ys[sidx * kProjBlocks * a.Cout + e];
+    ys[e] = y;
   }
   __syncthreads();
   const int half = a.Cout / 2;
-  for (int e = threadIdx.x; e < nblk * a.Cout; e += blockDim.x) {
+  for (int e = tid; e < nblk * a.Cout; e += nthreads) {
     const int r = e / a.Cout, o = e % a.Cout;
     float y = ys[r * a.Cout + o];
     if (a.cos) {
@@ -205,16 +227,26 @@ __global__ void __launch_bounds__(kGateThreads) gate_scores_kernel(const GateArg
     float acc[kGateRows];
 #pragma unroll
     for (int r = 0; r < kGateRows; ++r) acc[r] = 0.f;
-    for (int c = 0; c < a.C; c += 8) {
-      float kv[8];
-      load8(a.k, kbase + c, a.k_dtype, kv);
+    for (int c0 = 0; c0 < a.C; c0 += 32) {
+      // four 16-byte loads of the key block in flight before any arithmetic
+      float kv[4][8];
 #pragma unroll
-      for (int r = 0; r < kGateRows; ++r) {
-        if (i0 + r < a.Qb) {
-          const float4 q0 = *reinterpret_cast<const float4*>(&gate_smem[(i0 + r) * a.C + c]);
-          const float4 q1 = *reinterpret_cast<const float4*>(&gate_smem[(i0 + r) * a.C + c + 4]);
-          acc[r] += q0.x * kv[0] + q0.y * kv[1] + q0.z * kv[2] + q0.w * kv[3] + q1.x * kv[4] + q1.y * kv[5] +
-                    q1.z * kv[6] + q1.w * kv[7];
+      for (int u = 0; u < 4; ++u) {
+        if (c0 + u * 8 < a.C) load8(a.k, kbase + c0 + u * 8, a.k_dtype, kv[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * 8;
+        if (c < a.C) {
+#pragma unroll
+          for (int r = 0; r < kGateRows; ++r) {
+            if (i0 + r < a.Qb) {
+              const float4 q0 = *reinterpret_cast<const float4*>(&gate_smem[(i0 + r) * a.C + c]);
+              const float4 q1 = *reinterpret_cast<const float4*>(&gate_smem[(i0 + r) * a.C + c + 4]);
+              acc[r] += q0.x * kv[u][0] + q0.y * kv[u][1] + q0.z * kv[u][2] + q0.w * kv[u][3] + q1.x * kv[u][4] +
+                        q1.y * kv[u][5] + q1.z * kv[u][6] + q1.w * kv[u][7];
+            }
+          }
         }
       }
     }
@@ -417,9 +449,9 @@ int ca_gate_project(const ca_project_params* p, ca_stream_t stream_) {
   a.out = p->out, a.o_b = p->out_stride_b, a.o_blk = p->out_stride_blk, a.o_h = p->out_stride_h, a.o_dtype = p->out_dtype;
   a.out_block_offset = p->out_block_offset;
   a.B = p->B, a.nb = p->nb, a.Hin = p->Hin, a.Hout = p->Hout, a.Cin = p->Cin, a.Cout = p->Cout;
-  const size_t smem = static_cast<size_t>(kProjBlocks) * (p->Cin + p->Cout) * sizeof(float);
+  const size_t smem = static_cast<size_t>(kProjBlocks) * (p->Cin + kProjSlices * p->Cout) * sizeof(float);
   CA_REQUIRE(smem <= 48 * 1024, "Cin + Cout too large");
-  const int threads = p->Cout >= 128 ? 128 : 64;
+  const dim3 threads(p->Cout >= 128 ? 128 : (p->Cout >= 64 ? 64 : 32), kProjSlices);
   proj_rope_kernel<<<dim3(ceil_div(p->nb, kProjBlocks), p->Hout, p->B), threads, smem, static_cast<cudaStream_t>(stream_)>>>(a);
   CA_LAUNCH_CHECK("proj_rope_kernel");
   return CA_OK;

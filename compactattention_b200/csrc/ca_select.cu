@@ -98,7 +98,7 @@ __device__ __forceinline__ float block_reduce_sum(float v, float* scratch) {
 // Radix select over the monotone keys, 8 bits per pass, then an ordered pass for the ties.
 __device__ void topk_mark(const float* s, int n, int k, uint8_t* keep, int* hist, int* warp_sums) {
   __shared__ uint32_t sh_prefix;
-  __shared__ int sh_remaining, sh_total;
+  __shared__ int sh_remaining, sh_total, sh_last_bin_count;
   if (k >= n) {
     for (int j = threadIdx.x; j < n; j += kRowThreads) keep[j] = 1;
     __syncthreads();
@@ -119,20 +119,44 @@ __device__ void topk_mark(const float* s, int n, int k, uint8_t* keep, int* hist
       if ((key & mask_hi) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int rem = sh_remaining;
-      int bin = 255;
-      for (; bin > 0; --bin) {
-        if (hist[bin] >= rem) break;
-        rem -= hist[bin];
+    if (threadIdx.x < 32) {
+      // warp 0 finds the bin that holds the rem-th largest key: lane l owns bins 255-8l .. 248-8l
+      const int lane = threadIdx.x;
+      const int rem = sh_remaining;
+      int mine = 0;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) mine += hist[255 - 8 * lane - u];
+      int inc = mine;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int nb = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += nb;
       }
-      sh_prefix = prefix | (static_cast<uint32_t>(bin) << shift);
-      sh_remaining = rem;  // how many entries equal to the final key are still wanted
+      const uint32_t hit = __ballot_sync(0xffffffffu, inc >= rem);
+      const int owner = hit ? __ffs(hit) - 1 : 31;
+      if (lane == owner) {
+        int left = rem - (inc - mine);  // still wanted inside this lane's eight bins
+        int bin = 255 - 8 * lane;
+        for (int u = 0; u < 7; ++u) {
+          if (hist[bin] >= left) break;
+          left -= hist[bin];
+          --bin;
+        }
+        sh_prefix = prefix | (static_cast<uint32_t>(bin) << shift);
+        sh_remaining = left;  // entries still wanted among those equal to the chosen digit
+        sh_last_bin_count = hist[bin];
+      }
     }
     __syncthreads();
   }
   const uint32_t kth = sh_prefix;
   const int want_equal = sh_remaining;
+  if (want_equal == sh_last_bin_count) {
+    // every key equal to the k-th is wanted: no tie to break
+    for (int j = threadIdx.x; j < n; j += kRowThreads) keep[j] = order_key(s[j]) >= kth;
+    __syncthreads();
+    return;
+  }
   // ordered pass: keys above kth are kept, keys equal to kth are kept in index order
   int taken = 0;
   for (int base = 0; base < n; base += kRowThreads) {
