@@ -122,6 +122,33 @@ class ProjectParams(C.Structure):
     ]
 
 
+class GateSide(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p),
+        ("x_stride_b", C.c_int64), ("x_stride_t", C.c_int64), ("x_stride_h", C.c_int64),
+        ("x_dtype", C.c_int32),
+        ("H", C.c_int32),
+        ("kinds", C.c_int32),
+        ("w_dtype", C.c_int32),
+        ("w", C.c_void_p),
+        ("Hw", C.c_int32),
+        ("rope_batch", C.c_int32),
+        ("cos", C.c_void_p),
+        ("sin", C.c_void_p),
+        ("out", C.c_void_p),
+        ("out_stride_b", C.c_int64), ("out_stride_blk", C.c_int64), ("out_stride_h", C.c_int64),
+        ("out_dtype", C.c_int32),
+        ("out_block_offset", C.c_int32),
+    ]
+
+
+class GatePrepareParams(C.Structure):
+    _fields_ = [
+        ("q", GateSide), ("k", GateSide),
+        ("B", C.c_int32), ("L", C.c_int32), ("D", C.c_int32), ("C", C.c_int32), ("block_size", C.c_int32),
+    ]
+
+
 class GateScoreParams(C.Structure):
     _fields_ = [
         ("q", C.c_void_p),
@@ -183,6 +210,7 @@ _SIGNATURES = {
     "ca_paged_metadata": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "ca_pool_blocks": (C.c_int, [C.POINTER(PoolParams), C.c_void_p]),
     "ca_gate_project": (C.c_int, [C.POINTER(ProjectParams), C.c_void_p]),
+    "ca_gate_prepare": (C.c_int, [C.POINTER(GatePrepareParams), C.c_void_p]),
     "ca_gate_scores": (C.c_int, [C.POINTER(GateScoreParams), C.c_void_p]),
     "ca_flashprefill_score": (C.c_int, [C.POINTER(FlashPrefillScoreParams), C.c_void_p]),
     "ca_gather_kv": (C.c_int, [C.POINTER(GatherParams), C.c_void_p]),

@@ -44,17 +44,28 @@ class GateSelectorState:
         self.gate = gate
         heads = gate.mask_linear_k.weight.shape[0]
         self.cache = GateKeyBlockCache(batch, heads, gate.hidden_size, device, dtype=cache_dtype)
+        self.q_blocks = None  # [B, Qb, Hq, C] scratch of the current chunk
+        self.logits = None    # [B, Hq, Qb, Kb] scratch of the current chunk
 
     def append_and_score(self, q_nope: torch.Tensor, k_nope: torch.Tensor, block_rope_q=None, block_rope_k=None) -> torch.Tensor:
-        """Appends the chunk's K blocks, then scores the chunk's Q blocks against every cached block.
-        Returns logits ``[B, Hq, Qb, Kb]`` (float32, acausal entries filled with finfo.min)."""
-        self.gate.append_key_blocks(self.cache, k_nope, block_rope_k)
-        pooled_q = ops.pool_blocks(q_nope, self.gate.block_size, self.gate.q_pooling_funcs)
-        wq = None if self.gate.mask_linear_q is None else self.gate.mask_linear_q.weight.detach()
-        cos, sin = block_rope_q if block_rope_q is not None else (None, None)
-        qb = ops.gate_project(pooled_q, wq, cos, sin)
+        """Appends the chunk's K blocks, then scores the chunk's Q blocks against every cached block
+        (two launches).  Returns logits ``[B, Hq, Qb, Kb]`` (float32, acausal entries = finfo.min)."""
+        gate = self.gate
+        nb = (q_nope.shape[1] + gate.block_size - 1) // gate.block_size
+        self.cache.reserve(self.cache.length + nb)
+        if self.q_blocks is None or self.q_blocks.shape[1] != nb:
+            self.q_blocks = torch.empty((q_nope.shape[0], nb, gate.num_q_head, gate.hidden_size), dtype=torch.float32,
+                                        device=q_nope.device)
+        wq = None if gate.mask_linear_q is None else gate.mask_linear_q.weight.detach()
+        ops.gate_prepare(q_nope, k_nope, gate.block_size, gate.q_pooling_funcs, gate.k_pooling_funcs, wq,
+                         gate.mask_linear_k.weight.detach(), block_rope_q, block_rope_k, self.q_blocks,
+                         self.cache.blocks_view(), self.cache.length)
+        self.cache.length += nb
         kb = self.cache.blocks()
-        return ops.gate_scores(qb, kb, kb.shape[1] - qb.shape[1], scale=self.gate.scale)
+        if self.logits is None or self.logits.shape[3] != kb.shape[1] or self.logits.shape[2] != nb:
+            self.logits = torch.empty((q_nope.shape[0], gate.num_q_head, nb, kb.shape[1]), dtype=torch.float32,
+                                      device=q_nope.device)
+        return ops.gate_scores(self.q_blocks, kb, kb.shape[1] - nb, scale=gate.scale, out=self.logits)
 
 
 class MeanKSelectorState:

@@ -877,8 +877,11 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
   // persistent grid: one CTA per SM, never more CTAs than units when units cannot be cut
   const long long n_units = static_cast<long long>(p->B) * p->Hkv * n_pairs;
   int grid = dev.sm_count;
-  // cutting units pays when whole units cannot fill the SMs evenly
-  const bool want_split = n_units < 16LL * dev.sm_count;
+  // Cutting units costs partial traffic and a combine launch, and under the power cap idle SMs buy
+  // clock for the busy ones; it pays only when whole units would leave many SMs idle (few rows per
+  // rank under tensor parallelism, or a nearly empty last wave).
+  const long long waves = (n_units + dev.sm_count - 1) / dev.sm_count;
+  const bool want_split = n_units * 100 < waves * dev.sm_count * 80;
   const bool can_split = p->workspace != nullptr && p->workspace_bytes >= workspace_bytes_for(grid);
   a.split = (want_split && can_split) ? 1 : 0;
   if (!a.split && n_units < grid) grid = static_cast<int>(n_units);

@@ -44,6 +44,30 @@ __device__ __forceinline__ void load8(const void* base, long long off, int dtype
   }
 }
 
+// Compile-time-typed variant: a batch of these unrolls into straight-line loads whose latencies overlap.
+template <int DT>
+__device__ __forceinline__ void load8_t(const void* base, long long off, float (&v)[8]) {
+  if (DT == CA_DTYPE_F32) {
+    const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off);
+    const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off + 4);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+  } else {
+    const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + off);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (DT == CA_DTYPE_BF16) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      } else {
+        const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+        v[2 * i] = __low2float(h);
+        v[2 * i + 1] = __high2float(h);
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // Block pooling: x [B,L,H,D] -> out [B, blocks, H, nk*D] at block offset, channel order max|min|avg
 // ------------------------------------------------------------------------------------------
@@ -210,13 +234,37 @@ struct GateArgs {
 constexpr int kGateThreads = 128;
 constexpr int kGateRows = 16;  // q-blocks accumulated per pass
 
+// Widen 8 packed 16-bit elements (KDT: CA_DTYPE_BF16 / CA_DTYPE_F16) to f32.
+template <int KDT>
+__device__ __forceinline__ void widen8(const uint4& raw, float (&v)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (KDT == CA_DTYPE_BF16) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    } else {
+      const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+      v[2 * i] = __low2float(h);
+      v[2 * i + 1] = __high2float(h);
+    }
+  }
+}
+
+// Thread = key block j; the chunk's q-block rows sit in shared memory (broadcast reads).  The key
+// block's channels are fetched 64 at a time as straight-line 128-bit loads so their latencies
+// overlap, then widened to f32.
+template <int KDT>
 __global__ void __launch_bounds__(kGateThreads) gate_scores_kernel(const GateArgs a) {
   extern __shared__ float gate_smem[];  // q rows [Qb][C]
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (a.Hq / a.Hk);
-  for (int e = threadIdx.x; e < a.Qb * a.C; e += kGateThreads) {
+  for (int e = threadIdx.x * 8; e < a.Qb * a.C; e += kGateThreads * 8) {
     const int i = e / a.C, c = e % a.C;
-    gate_smem[e] = load_elem(a.q, b * a.q_b + i * a.q_blk + h * a.q_h + c, a.q_dtype);
+    float v[8];
+    load8(a.q, b * a.q_b + i * a.q_blk + h * a.q_h + c, a.q_dtype, v);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) gate_smem[e + u] = v[u];
   }
   __syncthreads();
   const int j = blockIdx.x * kGateThreads + threadIdx.x;
@@ -227,26 +275,43 @@ __global__ void __launch_bounds__(kGateThreads) gate_scores_kernel(const GateArg
     float acc[kGateRows];
 #pragma unroll
     for (int r = 0; r < kGateRows; ++r) acc[r] = 0.f;
-    for (int c0 = 0; c0 < a.C; c0 += 32) {
-      // four 16-byte loads of the key block in flight before any arithmetic
-      float kv[4][8];
+    const int rows = min(kGateRows, a.Qb - i0);
+    for (int c0 = 0; c0 < a.C; c0 += 64) {
+      float kv[8][8];
+      if (KDT == CA_DTYPE_F32) {
+        const float* kp = reinterpret_cast<const float*>(a.k) + kbase + c0;
+        float4 raw[16];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (c0 + u * 8 < a.C) load8(a.k, kbase + c0 + u * 8, a.k_dtype, kv[u]);
+        for (int u = 0; u < 16; ++u) raw[u] = (c0 + u * 4 < a.C) ? *reinterpret_cast<const float4*>(kp + u * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          kv[u][0] = raw[2 * u].x, kv[u][1] = raw[2 * u].y, kv[u][2] = raw[2 * u].z, kv[u][3] = raw[2 * u].w;
+          kv[u][4] = raw[2 * u + 1].x, kv[u][5] = raw[2 * u + 1].y, kv[u][6] = raw[2 * u + 1].z, kv[u][7] = raw[2 * u + 1].w;
+        }
+      } else {
+        const uint16_t* kp = reinterpret_cast<const uint16_t*>(a.k) + kbase + c0;
+        uint4 raw[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) raw[u] = (c0 + u * 8 < a.C) ? *reinterpret_cast<const uint4*>(kp + u * 8) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) widen8<KDT>(raw[u], kv[u]);
       }
+      const int cn = min(64, a.C - c0);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c = c0 + u * 8;
-        if (c < a.C) {
+      for (int r = 0; r < kGateRows; ++r) {
+        if (r < rows) {
+          const float* qrow = &gate_smem[(i0 + r) * a.C + c0];
+          float sum = acc[r];
 #pragma unroll
-          for (int r = 0; r < kGateRows; ++r) {
-            if (i0 + r < a.Qb) {
-              const float4 q0 = *reinterpret_cast<const float4*>(&gate_smem[(i0 + r) * a.C + c]);
-              const float4 q1 = *reinterpret_cast<const float4*>(&gate_smem[(i0 + r) * a.C + c + 4]);
-              acc[r] += q0.x * kv[u][0] + q0.y * kv[u][1] + q0.z * kv[u][2] + q0.w * kv[u][3] + q1.x * kv[u][4] +
-                        q1.y * kv[u][5] + q1.z * kv[u][6] + q1.w * kv[u][7];
+          for (int u = 0; u < 8; ++u) {
+            if (u * 8 < cn) {
+              const float4 q0 = *reinterpret_cast<const float4*>(qrow + u * 8);
+              const float4 q1 = *reinterpret_cast<const float4*>(qrow + u * 8 + 4);
+              sum += q0.x * kv[u][0] + q0.y * kv[u][1] + q0.z * kv[u][2] + q0.w * kv[u][3] + q1.x * kv[u][4] +
+                     q1.y * kv[u][5] + q1.z * kv[u][6] + q1.w * kv[u][7];
             }
           }
+          acc[r] = sum;
         }
       }
     }
@@ -254,6 +319,90 @@ __global__ void __launch_bounds__(kGateThreads) gate_scores_kernel(const GateArg
     for (int r = 0; r < kGateRows; ++r) {
       const int i = i0 + r;
       if (i < a.Qb) orow[static_cast<long long>(i) * a.Kb] = (j <= a.Pb + i) ? acc[r] * a.scale : a.masked_value;
+    }
+  }
+}
+
+// Lean variant for C % 32 == 0: a thread owns two key blocks (j and j + 128) so every broadcast
+// read of a q value from shared memory feeds two FMAs; q rows are zero-padded to a multiple of 16
+// so the inner loops carry no predicates.
+template <int KDT>
+__device__ __forceinline__ void load_k32(const void* base, long long off, float (&v)[32]) {
+  if (KDT == CA_DTYPE_F32) {
+    const float* kp = reinterpret_cast<const float*>(base) + off;
+    float4 raw[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) raw[u] = *reinterpret_cast<const float4*>(kp + u * 4);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[4 * u] = raw[u].x, v[4 * u + 1] = raw[u].y, v[4 * u + 2] = raw[u].z, v[4 * u + 3] = raw[u].w;
+  } else {
+    const uint16_t* kp = reinterpret_cast<const uint16_t*>(base) + off;
+    uint4 raw[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) raw[u] = *reinterpret_cast<const uint4*>(kp + u * 8);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float t[8];
+      widen8<KDT>(raw[u], t);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[8 * u + i] = t[i];
+    }
+  }
+}
+
+template <int KDT>
+__global__ void __launch_bounds__(kGateThreads) gate_scores2_kernel(const GateArgs a) {
+  extern __shared__ float gate_smem[];  // q rows [ceil16(Qb)][C], zero padded
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (a.Hq / a.Hk);
+  const int q_pad = ((a.Qb + kGateRows - 1) / kGateRows) * kGateRows;
+  for (int e = threadIdx.x * 8; e < q_pad * a.C; e += kGateThreads * 8) {
+    const int i = e / a.C, c = e % a.C;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (i < a.Qb) load8(a.q, b * a.q_b + i * a.q_blk + h * a.q_h + c, a.q_dtype, v);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) gate_smem[e + u] = v[u];
+  }
+  __syncthreads();
+  const int j0 = blockIdx.x * (2 * kGateThreads) + threadIdx.x;
+  const int j1 = j0 + kGateThreads;
+  if (j0 >= a.Kb) return;
+  const int j1c = j1 < a.Kb ? j1 : a.Kb - 1;  // clamped address; its result is not stored
+  const long long k0 = b * a.k_b + static_cast<long long>(j0) * a.k_blk + hk * a.k_h;
+  const long long k1 = b * a.k_b + static_cast<long long>(j1c) * a.k_blk + hk * a.k_h;
+  float* obase = a.out + ((static_cast<long long>(b) * a.Hq + h) * a.Qb) * a.Kb;
+  for (int i0 = 0; i0 < a.Qb; i0 += kGateRows) {
+    float acc0[kGateRows], acc1[kGateRows];
+#pragma unroll
+    for (int r = 0; r < kGateRows; ++r) acc0[r] = 0.f, acc1[r] = 0.f;
+    for (int c0 = 0; c0 < a.C; c0 += 32) {
+      float kv0[32], kv1[32];
+      load_k32<KDT>(a.k, k0 + c0, kv0);
+      load_k32<KDT>(a.k, k1 + c0, kv1);
+#pragma unroll
+      for (int r = 0; r < kGateRows; ++r) {
+        const float* qrow = &gate_smem[(i0 + r) * a.C + c0];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qrow + u * 4);
+          acc0[r] = fmaf(q4.x, kv0[4 * u], acc0[r]);
+          acc1[r] = fmaf(q4.x, kv1[4 * u], acc1[r]);
+          acc0[r] = fmaf(q4.y, kv0[4 * u + 1], acc0[r]);
+          acc1[r] = fmaf(q4.y, kv1[4 * u + 1], acc1[r]);
+          acc0[r] = fmaf(q4.z, kv0[4 * u + 2], acc0[r]);
+          acc1[r] = fmaf(q4.z, kv1[4 * u + 2], acc1[r]);
+          acc0[r] = fmaf(q4.w, kv0[4 * u + 3], acc0[r]);
+          acc1[r] = fmaf(q4.w, kv1[4 * u + 3], acc1[r]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kGateRows; ++r) {
+      const int i = i0 + r;
+      if (i < a.Qb) {
+        obase[static_cast<long long>(i) * a.Kb + j0] = (j0 <= a.Pb + i) ? acc0[r] * a.scale : a.masked_value;
+        if (j1 < a.Kb) obase[static_cast<long long>(i) * a.Kb + j1] = (j1 <= a.Pb + i) ? acc1[r] * a.scale : a.masked_value;
+      }
     }
   }
 }
@@ -399,6 +548,152 @@ __global__ void __launch_bounds__(256) flashprefill_normalize_kernel(const float
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// Fused gate preparation for one chunk: block pooling of Q and K, per-head projection, block RoPE,
+// Q blocks to their buffer and K blocks appended to the gate cache -- one launch.
+// One CTA per (block, job head): job heads 0..Hq-1 are the query side, the rest the key side
+// (one per head of the key weight, pooling the KV head it belongs to).
+// ------------------------------------------------------------------------------------------
+struct PrepSide {
+  const void* x;  // [B, L, H, D] tokens
+  long long x_b, x_t, x_h;
+  int x_dtype;
+  int H;          // heads of x
+  int kinds;      // pooling kinds
+  const void* w;  // [Hw, nk*D, C] or NULL (identity: nk*D == C, Hw == H)
+  int w_dtype;
+  int Hw;         // heads of the weight (= output heads)
+  const float* cos;  // [Bc, nb, C] or NULL
+  const float* sin;
+  int rope_batch;
+  void* out;      // [B, >= off + nb, Hw, C] by strides
+  long long o_b, o_blk, o_h;
+  int o_dtype;
+  int out_block_offset;
+};
+struct PrepArgs {
+  PrepSide q, k;
+  int B, L, D, C, bs, nb;
+};
+
+constexpr int kPrepThreads = 128;
+
+template <int XDT, int WDT>
+__global__ void __launch_bounds__(kPrepThreads) gate_prepare_kernel(const PrepArgs a) {
+  extern __shared__ float prep_smem[];  // partials [3][phases][D], pooled [3*D], y [C]
+  const bool is_q = static_cast<int>(blockIdx.y) < a.q.Hw;
+  const PrepSide& sd = is_q ? a.q : a.k;
+  const int hw = is_q ? blockIdx.y : blockIdx.y - a.q.Hw;  // output / weight head
+  const int hx = hw / (sd.Hw / sd.H);                      // token head it pools
+  const int blk = blockIdx.x, b = blockIdx.z;
+  const int groups = a.D / 8;
+  const int phases = kPrepThreads / groups;
+  float* part = prep_smem;
+  float* pooled = part + 3 * phases * a.D;
+  float* y = pooled + 3 * a.D;
+  const int grp = threadIdx.x % groups, ph = threadIdx.x / groups;
+  const int t0 = blk * a.bs, t1 = min(t0 + a.bs, a.L);
+  float mx[8], mn[8], sm[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) mx[i] = -INFINITY, mn[i] = INFINITY, sm[i] = 0.f;
+  if (ph < phases) {
+    // eight token rows per round, all loads issued before the arithmetic
+    for (int tb = t0 + ph; tb < t1; tb += phases * 8) {
+      float v[8][8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int t = min(tb + u * phases, t1 - 1);  // clamped rows repeat a token: harmless for max/min, skipped for the sum
+        load8_t<XDT>(sd.x, b * sd.x_b + static_cast<long long>(t) * sd.x_t + hx * sd.x_h + grp * 8, v[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool real = tb + u * phases < t1;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          mx[i] = fmaxf(mx[i], v[u][i]), mn[i] = fminf(mn[i], v[u][i]);
+          sm[i] += real ? v[u][i] : 0.f;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      part[(0 * phases + ph) * a.D + grp * 8 + i] = mx[i];
+      part[(1 * phases + ph) * a.D + grp * 8 + i] = mn[i];
+      part[(2 * phases + ph) * a.D + grp * 8 + i] = sm[i];
+    }
+  }
+  __syncthreads();
+  const float inv_cnt = 1.0f / static_cast<float>(t1 - t0);
+  int n_kinds = 0;
+  for (int d = threadIdx.x; d < a.D; d += kPrepThreads) {
+    float rmx = -INFINITY, rmn = INFINITY, rsm = 0.f;
+    for (int p = 0; p < phases; ++p) {
+      rmx = fmaxf(rmx, part[(0 * phases + p) * a.D + d]);
+      rmn = fminf(rmn, part[(1 * phases + p) * a.D + d]);
+      rsm += part[(2 * phases + p) * a.D + d];
+    }
+    int c = 0;
+    if (sd.kinds & 1) pooled[(c++) * a.D + d] = rmx;
+    if (sd.kinds & 2) pooled[(c++) * a.D + d] = rmn;
+    if (sd.kinds & 4) pooled[(c++) * a.D + d] = rsm * inv_cnt;
+  }
+  n_kinds = ((sd.kinds & 1) ? 1 : 0) + ((sd.kinds & 2) ? 1 : 0) + ((sd.kinds & 4) ? 1 : 0);
+  const int Cin = n_kinds * a.D;
+  __syncthreads();
+  if (sd.w) {
+    // Thread = (8 output channels, input-channel phase): every load is a 128-bit piece of a weight row
+    // and a whole round of loads is issued before any arithmetic, so the round costs one latency.
+    const int ogroups = a.C / 8;                   // 16-byte groups per weight row
+    const int cphases = kPrepThreads / ogroups;    // input channels covered per load round
+    const int og = threadIdx.x % ogroups, cp = threadIdx.x / ogroups;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (cp < cphases) {
+      const long long wbase = static_cast<long long>(hw) * Cin * a.C + og * 8;
+      for (int c0 = cp; c0 < Cin; c0 += cphases * 8) {
+        float w[8][8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int c = c0 + u * cphases;
+          if (c < Cin) {
+            load8_t<WDT>(sd.w, wbase + static_cast<long long>(c) * a.C, w[u]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[u][i] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float xv = pooled[min(c0 + u * cphases, Cin - 1)];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = fmaf(xv, w[u][i], acc[i]);
+        }
+      }
+      // partial sums of the input-channel phases meet in shared memory (reusing the pooling scratch)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) part[cp * a.C + og * 8 + i] = acc[i];
+    }
+    __syncthreads();
+    for (int o = threadIdx.x; o < a.C; o += kPrepThreads) {
+      float sum = 0.f;
+      for (int q = 0; q < cphases; ++q) sum += part[q * a.C + o];
+      y[o] = sum;
+    }
+  } else {
+    for (int o = threadIdx.x; o < a.C; o += kPrepThreads) y[o] = pooled[o];
+  }
+  __syncthreads();
+  const int half = a.C / 2;
+  for (int o = threadIdx.x; o < a.C; o += kPrepThreads) {
+    float v = y[o];
+    if (sd.cos) {
+      const long long ro = ((sd.rope_batch > 1 ? static_cast<long long>(b) : 0) * a.nb + blk) * a.C + o;
+      const float rot = o < half ? -y[o + half] : y[o - half];
+      v = v * sd.cos[ro] + rot * sd.sin[ro];
+    }
+    store_elem(sd.out, b * sd.o_b + static_cast<long long>(sd.out_block_offset + blk) * sd.o_blk + hw * sd.o_h + o, sd.o_dtype, v);
+  }
+}
+
 static bool dtype_ok(int dt) { return dt == CA_DTYPE_F32 || dt == CA_DTYPE_BF16 || dt == CA_DTYPE_F16; }
 
 }  // namespace score
@@ -429,6 +724,66 @@ int ca_pool_blocks(const ca_pool_params* p, ca_stream_t stream_) {
   const size_t smem = static_cast<size_t>(3) * phases * p->D * sizeof(float);
   pool_blocks_kernel<<<dim3(nb, p->B * p->H), kPoolThreads, smem, static_cast<cudaStream_t>(stream_)>>>(a);
   CA_LAUNCH_CHECK("pool_blocks_kernel");
+  return CA_OK;
+}
+
+int ca_gate_prepare(const ca_gate_prepare_params* p, ca_stream_t stream_) {
+  using namespace ca;
+  using namespace ca::score;
+  CA_REQUIRE(p != nullptr, "params is null");
+  CA_REQUIRE(p->B > 0 && p->L > 0 && p->block_size > 0, "B, L, block_size must be positive");
+  CA_REQUIRE(p->D > 0 && p->D % 8 == 0 && p->D <= 1024 && kPrepThreads % (p->D / 8) == 0,
+             "D must be a multiple of 8 with D/8 dividing %d", kPrepThreads);
+  CA_REQUIRE(p->C >= 8 && p->C % 8 == 0 && p->C <= 1024 && kPrepThreads % (p->C / 8) == 0,
+             "C must be a multiple of 8 with C/8 dividing %d", kPrepThreads);
+  const ca_gate_side* sides[2] = {&p->q, &p->k};
+  PrepArgs a;
+  PrepSide* out_sides[2] = {&a.q, &a.k};
+  for (int i = 0; i < 2; ++i) {
+    const ca_gate_side* sd = sides[i];
+    CA_REQUIRE(sd->x && sd->out, "token tensor and output of both sides must be non-null");
+    CA_REQUIRE(dtype_ok(sd->x_dtype) && dtype_ok(sd->out_dtype), "unsupported dtype");
+    CA_REQUIRE(sd->H > 0 && sd->Hw > 0 && sd->Hw % sd->H == 0, "weight heads must be a multiple of token heads");
+    CA_REQUIRE(sd->kinds > 0 && sd->kinds < 8, "kinds must be a non-empty subset of max|min|avg");
+    const int nk = ((sd->kinds & 1) ? 1 : 0) + ((sd->kinds & 2) ? 1 : 0) + ((sd->kinds & 4) ? 1 : 0);
+    CA_REQUIRE(sd->w != nullptr || (nk * p->D == p->C && sd->Hw == sd->H), "identity projection needs nk*D == C and Hw == H");
+    CA_REQUIRE(sd->w == nullptr || dtype_ok(sd->w_dtype), "unsupported weight dtype");
+    CA_REQUIRE((sd->cos == nullptr) == (sd->sin == nullptr), "cos and sin must be given together");
+    CA_REQUIRE(sd->cos == nullptr || sd->rope_batch == 1 || sd->rope_batch == p->B, "rope_batch must be 1 or B");
+    CA_REQUIRE(sd->x_stride_b % 8 == 0 && sd->x_stride_t % 8 == 0 && sd->x_stride_h % 8 == 0, "token strides must be multiples of 8 elements");
+    PrepSide* o = out_sides[i];
+    o->x = sd->x, o->x_b = sd->x_stride_b, o->x_t = sd->x_stride_t, o->x_h = sd->x_stride_h, o->x_dtype = sd->x_dtype;
+    o->H = sd->H, o->kinds = sd->kinds, o->w = sd->w, o->w_dtype = sd->w_dtype, o->Hw = sd->Hw;
+    o->cos = sd->cos, o->sin = sd->sin, o->rope_batch = sd->rope_batch;
+    o->out = sd->out, o->o_b = sd->out_stride_b, o->o_blk = sd->out_stride_blk, o->o_h = sd->out_stride_h;
+    o->o_dtype = sd->out_dtype, o->out_block_offset = sd->out_block_offset;
+  }
+  a.B = p->B, a.L = p->L, a.D = p->D, a.C = p->C, a.bs = p->block_size;
+  a.nb = ceil_div(p->L, p->block_size);
+  const int phases = kPrepThreads / (p->D / 8);
+  const size_t smem = (static_cast<size_t>(3) * phases * p->D + 3 * p->D + p->C) * sizeof(float);
+  CA_REQUIRE(smem <= 48 * 1024, "D and C too large for the gate preparation kernel");
+  CA_REQUIRE(p->q.x_dtype == p->k.x_dtype, "q and k tokens must share a dtype");
+  const int wdt = p->k.w ? p->k.w_dtype : (p->q.w ? p->q.w_dtype : p->q.x_dtype);
+  CA_REQUIRE((p->q.w == nullptr || p->q.w_dtype == wdt) && (p->k.w == nullptr || p->k.w_dtype == wdt), "q and k weights must share a dtype");
+  const dim3 grid(a.nb, p->q.Hw + p->k.Hw, p->B);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+#define CA_PREP_CASE(XD, WD)                                                            \
+  if (p->q.x_dtype == XD && wdt == WD) {                                                \
+    gate_prepare_kernel<XD, WD><<<grid, kPrepThreads, smem, stream>>>(a);               \
+  } else
+  CA_PREP_CASE(CA_DTYPE_BF16, CA_DTYPE_BF16)
+  CA_PREP_CASE(CA_DTYPE_BF16, CA_DTYPE_F32)
+  CA_PREP_CASE(CA_DTYPE_F16, CA_DTYPE_F16)
+  CA_PREP_CASE(CA_DTYPE_F16, CA_DTYPE_F32)
+  CA_PREP_CASE(CA_DTYPE_F32, CA_DTYPE_F32)
+  CA_PREP_CASE(CA_DTYPE_F32, CA_DTYPE_BF16)
+  CA_PREP_CASE(CA_DTYPE_F32, CA_DTYPE_F16)
+  CA_PREP_CASE(CA_DTYPE_BF16, CA_DTYPE_F16)
+  CA_PREP_CASE(CA_DTYPE_F16, CA_DTYPE_BF16)
+  { return fail(CA_ERR_UNSUPPORTED, "unsupported dtype combination"); }
+#undef CA_PREP_CASE
+  CA_LAUNCH_CHECK("gate_prepare_kernel");
   return CA_OK;
 }
 
@@ -467,6 +822,8 @@ int ca_gate_scores(const ca_gate_score_params* p, ca_stream_t stream_) {
   CA_REQUIRE(p->C > 0 && p->C % 8 == 0, "channel count must be a multiple of 8");
   CA_REQUIRE(p->k_stride_b % 8 == 0 && p->k_stride_blk % 8 == 0 && p->k_stride_h % 8 == 0,
              "k strides must be multiples of 8 elements");
+  CA_REQUIRE(p->q_stride_b % 8 == 0 && p->q_stride_blk % 8 == 0 && p->q_stride_h % 8 == 0,
+             "q strides must be multiples of 8 elements");
   CA_REQUIRE(p->Pb >= 0 && p->Pb + p->Qb >= 1, "Pb out of range");
   GateArgs a;
   a.q = p->q, a.q_b = p->q_stride_b, a.q_blk = p->q_stride_blk, a.q_h = p->q_stride_h, a.q_dtype = p->q_dtype;
@@ -477,8 +834,36 @@ int ca_gate_scores(const ca_gate_score_params* p, ca_stream_t stream_) {
   a.masked_value = p->masked_value;
   const size_t smem = static_cast<size_t>(p->Qb) * p->C * sizeof(float);
   CA_REQUIRE(smem <= 160 * 1024, "Qb * C too large for the gate score kernel");
-  if (smem > 48 * 1024) CA_CUDA(cudaFuncSetAttribute(gate_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  gate_scores_kernel<<<dim3(ceil_div(p->Kb, kGateThreads), p->Hq, p->B), kGateThreads, smem, static_cast<cudaStream_t>(stream_)>>>(a);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (p->C % 32 == 0) {
+    const int q_pad = ceil_div(p->Qb, kGateRows) * kGateRows;
+    const size_t smem2 = static_cast<size_t>(q_pad) * p->C * sizeof(float);
+    CA_REQUIRE(smem2 <= 160 * 1024, "Qb * C too large for the gate score kernel");
+    const dim3 grid2(ceil_div(p->Kb, 2 * kGateThreads), p->Hq, p->B);
+    if (p->k_dtype == CA_DTYPE_BF16) {
+      if (smem2 > 48 * 1024) CA_CUDA(cudaFuncSetAttribute(gate_scores2_kernel<CA_DTYPE_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
+      gate_scores2_kernel<CA_DTYPE_BF16><<<grid2, kGateThreads, smem2, stream>>>(a);
+    } else if (p->k_dtype == CA_DTYPE_F16) {
+      if (smem2 > 48 * 1024) CA_CUDA(cudaFuncSetAttribute(gate_scores2_kernel<CA_DTYPE_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
+      gate_scores2_kernel<CA_DTYPE_F16><<<grid2, kGateThreads, smem2, stream>>>(a);
+    } else {
+      if (smem2 > 48 * 1024) CA_CUDA(cudaFuncSetAttribute(gate_scores2_kernel<CA_DTYPE_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
+      gate_scores2_kernel<CA_DTYPE_F32><<<grid2, kGateThreads, smem2, stream>>>(a);
+    }
+    CA_LAUNCH_CHECK("gate_scores2_kernel");
+    return CA_OK;
+  }
+  const dim3 grid(ceil_div(p->Kb, kGateThreads), p->Hq, p->B);
+  if (p->k_dtype == CA_DTYPE_BF16) {
+    if (smem > 48 * 1024) CA_CUDA(cudaFuncSetAttribute(gate_scores_kernel<CA_DTYPE_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    gate_scores_kernel<CA_DTYPE_BF16><<<grid, kGateThreads, smem, stream>>>(a);
+  } else if (p->k_dtype == CA_DTYPE_F16) {
+    if (smem > 48 * 1024) CA_CUDA(cudaFuncSetAttribute(gate_scores_kernel<CA_DTYPE_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    gate_scores_kernel<CA_DTYPE_F16><<<grid, kGateThreads, smem, stream>>>(a);
+  } else {
+    if (smem > 48 * 1024) CA_CUDA(cudaFuncSetAttribute(gate_scores_kernel<CA_DTYPE_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    gate_scores_kernel<CA_DTYPE_F32><<<grid, kGateThreads, smem, stream>>>(a);
+  }
   CA_LAUNCH_CHECK("gate_scores_kernel");
   return CA_OK;
 }

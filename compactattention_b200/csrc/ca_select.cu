@@ -357,24 +357,33 @@ __global__ void __launch_bounds__(kRowThreads) union_table_kernel(const UnionArg
   const int row = blockIdx.x;
   const int b = row / a.Hkv, hkv = row % a.Hkv;
   int32_t* idx_row = a.block_idx + static_cast<long long>(row) * a.idx_stride;
+  // phase 1: OR over the group's heads and the Q rows, all threads sharing the (head, row, word) items
+  __shared__ uint32_t words[kMaxKb / 32];
+  for (int w = threadIdx.x; w < a.W; w += kRowThreads) words[w] = 0u;
+  __syncthreads();
+  const int items = a.G * a.Qin * a.W;
+#pragma unroll 4
+  for (int e = threadIdx.x; e < items; e += kRowThreads) {
+    const int w = e % a.W, gi = e / a.W;
+    const int h = hkv * a.G + gi / a.Qin, i = gi % a.Qin;
+    uint32_t word = 0;
+    if (a.bits) {
+      word = a.bits[((static_cast<long long>(b) * a.Hin + h) * a.Qin + i) * a.W + w];
+    } else {
+      const uint8_t* m = a.mask + b * a.m_b + h * a.m_h + i * a.m_q;
+      const int j0 = w * 32;
+      const int n = a.Kb - j0 < 32 ? a.Kb - j0 : 32;
+      for (int t = 0; t < n; ++t) word |= (m[(j0 + t) * a.m_k] ? 1u : 0u) << t;
+    }
+    if (word) atomicOr(&words[w], word);
+  }
+  __syncthreads();
   int running = 0;
   for (int wbase = 0; wbase < a.W; wbase += kRowThreads) {
     const int w = wbase + threadIdx.x;
     uint32_t word = 0;
     if (w < a.W) {
-      for (int g = 0; g < a.G; ++g) {
-        const int h = hkv * a.G + g;
-        for (int i = 0; i < a.Qin; ++i) {
-          if (a.bits) {
-            word |= a.bits[((static_cast<long long>(b) * a.Hin + h) * a.Qin + i) * a.W + w];
-          } else {
-            const uint8_t* m = a.mask + b * a.m_b + h * a.m_h + i * a.m_q;
-            const int j0 = w * 32;
-            const int n = a.Kb - j0 < 32 ? a.Kb - j0 : 32;
-            for (int t = 0; t < n; ++t) word |= (m[(j0 + t) * a.m_k] ? 1u : 0u) << t;
-          }
-        }
-      }
+      word = words[w];
       // forced recent columns, then split into past (table) and chunk (always on) parts
       const int j0 = w * 32;
       for (int t = 0; t < 32; ++t) {

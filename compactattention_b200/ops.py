@@ -401,6 +401,66 @@ def gate_project(
     return out
 
 
+def _gate_side(x, kinds, weight, rope, out, out_block_offset):
+    sd = _lib.GateSide()
+    if x.stride(3) != 1:
+        raise ValueError("token tensors must have a contiguous last dim")
+    sd.x, sd.x_stride_b, sd.x_stride_t, sd.x_stride_h = x.data_ptr(), x.stride(0), x.stride(1), x.stride(2)
+    sd.x_dtype, sd.H = _DTYPES[x.dtype], x.shape[2]
+    bitsel = 0
+    for k in kinds:
+        bitsel |= _POOL_BITS[k]
+    sd.kinds = bitsel
+    if weight is not None:
+        if not weight.is_contiguous():
+            raise ValueError("gate weights must be contiguous [H, Cin, C]")
+        sd.w, sd.w_dtype, sd.Hw = weight.data_ptr(), _DTYPES[weight.dtype], weight.shape[0]
+    else:
+        sd.Hw = x.shape[2]
+    keep = []
+    if rope is not None:
+        cos, sin = rope
+        cos, sin = cos.to(torch.float32).contiguous(), sin.to(torch.float32).contiguous()
+        keep = [cos, sin]
+        sd.cos, sd.sin, sd.rope_batch = cos.data_ptr(), sin.data_ptr(), cos.shape[0]
+    else:
+        sd.rope_batch = 1
+    if out.stride(3) != 1 or out.shape[2] != sd.Hw:
+        raise ValueError("gate block output has the wrong head count or a strided channel dim")
+    sd.out, sd.out_stride_b, sd.out_stride_blk, sd.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
+    sd.out_dtype, sd.out_block_offset = _DTYPES[out.dtype], out_block_offset
+    return sd, keep
+
+
+def gate_prepare(
+    q: torch.Tensor,  # [B, L, Hq, D] chunk queries (pre-RoPE)
+    k: torch.Tensor,  # [B, L, Hkv, D] chunk keys (pre-RoPE)
+    block_size: int,
+    q_kinds: tuple[str, ...],
+    k_kinds: tuple[str, ...],
+    wq: Optional[torch.Tensor],  # [Hq, nq*D, C] or None
+    wk: torch.Tensor,  # [Hk, nk*D, C]
+    rope_q: Optional[tuple[torch.Tensor, torch.Tensor]],  # f32 [1|B, nb, C] each, the chunk's block positions
+    rope_k: Optional[tuple[torch.Tensor, torch.Tensor]],
+    q_out: torch.Tensor,  # [B, >= nb, Hq, C]
+    k_out: torch.Tensor,  # [B, >= off + nb, Hk, C] (block-major view of the K-block cache)
+    k_out_block_offset: int = 0,
+) -> None:
+    """Pool + project + RoPE the chunk's Q and K blocks and append the K blocks, in one launch."""
+    _require_cuda(q, k, wq, wk, q_out, k_out)
+    B, L, _, D = q.shape
+    if k.shape[0] != B or k.shape[1] != L or k.shape[3] != D:
+        raise ValueError("q and k chunks must share batch, length and head dim")
+    p = _lib.GatePrepareParams()
+    p.q, keep_q = _gate_side(q, q_kinds, wq, rope_q, q_out, 0)
+    p.k, keep_k = _gate_side(k, k_kinds, wk, rope_k, k_out, k_out_block_offset)
+    p.B, p.L, p.D, p.C, p.block_size = B, L, D, q_out.shape[3], block_size
+    if k_out.shape[3] != p.C:
+        raise ValueError("q and k gate blocks must share the channel count")
+    _lib.check(_lib.load().ca_gate_prepare(C.byref(p), _stream()), "ca_gate_prepare")
+    del keep_q, keep_k
+
+
 def gate_scores(
     q_blocks: torch.Tensor,  # [B, Qb, Hq, C]
     k_blocks: torch.Tensor,  # [B, Kb, Hk, C] (a view of the K-block cache)

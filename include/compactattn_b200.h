@@ -258,6 +258,40 @@ typedef struct ca_project_params {
 int ca_gate_project(const ca_project_params* p, ca_stream_t stream);
 
 /*
+ * Fused gate preparation of one chunk (one launch): for the query side and the key side, pool the
+ * chunk's token blocks, project per head, apply block RoPE, and write the result at a block offset
+ * of the side's destination (the chunk's Q blocks; the gate's K-block cache, i.e. an append).
+ * Both sides share B, L (chunk tokens), D, C (gate hidden size) and block_size; cos/sin are
+ * f32 [rope_batch, ceil(L/bs), C] for the chunk's block positions.
+ * Replaces _build_chunked_gate_blocks + _gate_k_append as used by _compute_chunked_gate_from_cache
+ * (compact_attn/prefill_sparse/llama/modeling_llama_seerattn.py:437-481).
+ */
+typedef struct ca_gate_side {
+  const void* x; /* [B,L,H,D] by strides */
+  int64_t x_stride_b, x_stride_t, x_stride_h;
+  int32_t x_dtype;
+  int32_t H;
+  int32_t kinds; /* CA_POOL_* bits */
+  int32_t w_dtype;
+  const void* w; /* [Hw, nk*D, C] contiguous, or NULL for identity */
+  int32_t Hw;
+  int32_t rope_batch;
+  const float* cos;
+  const float* sin;
+  void* out; /* [B, >= out_block_offset + ceil(L/bs), Hw, C] by strides */
+  int64_t out_stride_b, out_stride_blk, out_stride_h;
+  int32_t out_dtype;
+  int32_t out_block_offset;
+} ca_gate_side;
+
+typedef struct ca_gate_prepare_params {
+  ca_gate_side q, k;
+  int32_t B, L, D, C, block_size;
+} ca_gate_prepare_params;
+
+int ca_gate_prepare(const ca_gate_prepare_params* p, ca_stream_t stream);
+
+/*
  * Gate logits: out[b,h,i,j] = (q[b,i,h,:] . k[b,j,h / (Hq/Hk),:]) * scale for j <= Pb + i, else
  * masked_value; out is contiguous f32 [B,Hq,Qb,Kb].  The softmax of
  * AttnGate.score_compressed_blocks (compact_attn/prefill_sparse/attn_gate.py:173-204) is applied

@@ -98,6 +98,38 @@ def test_attn_gate_golden(ops, golden):
         assert rel_err(prob.cpu(), T(g[f"{name}_score_softmax"])) < REL
 
 
+@pytest.mark.parametrize("kk,per_q_head,dtype", [(("max", "min", "avg"), True, torch.bfloat16), (("avg",), False, torch.bfloat16),
+                                                 (("avg",), False, torch.float32)])
+def test_gate_prepare_fused_matches_oracle(ops, kk, per_q_head, dtype):
+    """The one-launch pool + project + RoPE + append against the oracle, chunk by chunk."""
+    g = torch.Generator().manual_seed(21)
+    B, Hq, Hkv, D, bs, chunks, L = 2, 8, 2, 128, 64, 3, 256
+    Hk = Hq if per_q_head else Hkv
+    nb = L // bs
+    q = torch.randn((B, chunks * L, Hq, D), generator=g).to(dtype)
+    k = torch.randn((B, chunks * L, Hkv, D), generator=g).to(dtype)
+    wq = None if per_q_head else (torch.randn((Hq, D, 128), generator=g) * 0.05)
+    wk = torch.randn((Hk, len(kk) * D, 128), generator=g) * 0.05
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))
+    ang = torch.cat([torch.arange(0, chunks * L, bs, dtype=torch.float32).view(-1, 1) * inv.view(1, -1)] * 2, dim=-1)
+    cos, sin = ang.cos().unsqueeze(0), ang.sin().unsqueeze(0)
+    cache = torch.zeros((B, Hk, 16, 128), dtype=torch.float32, device="cuda")
+    for c in range(chunks):
+        sl = slice(c * L, (c + 1) * L)
+        bsl = slice(c * nb, (c + 1) * nb)
+        q_out = torch.empty((B, nb, Hq, 128), dtype=torch.float32, device="cuda")
+        ops.gate_prepare(q[:, sl].cuda(), k[:, sl].cuda(), bs, ("avg",), kk, None if wq is None else wq.cuda(), wk.cuda(),
+                         (cos[:, bsl].cuda(), sin[:, bsl].cuda()), (cos[:, bsl].cuda(), sin[:, bsl].cuda()),
+                         q_out, cache.transpose(1, 2), c * nb)
+        want_q = co.pool_blocks(q[:, sl].float(), bs, ("avg",))
+        if wq is not None:
+            want_q = co.multi_head_linear(want_q, wq)
+        want_q = co.apply_block_rope(want_q, cos[:, bsl], sin[:, bsl])
+        assert torch.allclose(q_out.cpu(), want_q, rtol=1e-4, atol=1e-4)
+    want_k = co.apply_block_rope(co.multi_head_linear(co.pool_blocks(k.float(), bs, kk), wk), cos, sin)
+    assert torch.allclose(cache.transpose(1, 2)[:, : chunks * nb].cpu(), want_k, rtol=1e-4, atol=1e-4)
+
+
 @pytest.mark.parametrize("B,Qb,Kb,Hq,Hk,dtype", [(1, 16, 512, 32, 32, torch.bfloat16), (1, 16, 2048, 8, 2, torch.float32),
                                                  (2, 4, 130, 28, 4, torch.bfloat16), (1, 128, 256, 4, 4, torch.float16)])
 def test_gate_scores_random(ops, B, Qb, Kb, Hq, Hk, dtype):
