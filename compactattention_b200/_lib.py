@@ -228,12 +228,13 @@ def load() -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
+    path = LIB_PATH
+    if not path.exists():
         raise MissingLibraryError(
-            f"{LIB_PATH} is missing. Build it with `python -m compactattention_b200.build` "
+            f"{path} is missing. Build it with `python -m compactattention_b200.build` "
             "(needs nvcc); this package has no fallback implementation."
         )
-    lib = C.CDLL(str(LIB_PATH))
+    lib = C.CDLL(str(path))
     for name, (restype, argtypes) in _SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError here means header and library disagree
         fn.restype = restype

@@ -43,6 +43,19 @@ constexpr int kTmemCols = 512;
 constexpr int kMaxRows = 1024;  // (batch x kv heads) rows per launch
 constexpr int kMaxSegs = 64;    // segments planned per batch
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; lazy accumulator rescale
+// Measured on B200 (sustained 300-launch loop, 128K context, 20 % density): handing P to the MMA warp
+// in two halves 434 us, in one piece 450 us; a polynomial exp2 on the FMA pipe for one exponential
+// in four made it slower (the kernel is limited by issue slots and board power, not by the MUFU
+// pipe), so it stays off.
+#ifndef CA_ATTN_P_PARTS
+#define CA_ATTN_P_PARTS 2
+#endif
+#ifndef CA_ATTN_POLY_EXP
+#define CA_ATTN_POLY_EXP 0
+#endif
+static_assert(CA_ATTN_P_PARTS == 1 || CA_ATTN_P_PARTS == 2, "P is handed over in one or two pieces");
+constexpr int kPParts = CA_ATTN_P_PARTS;  // P is handed to the MMA warp in this many pieces so P.V overlaps the softmax
+constexpr bool kPolyExp = CA_ATTN_POLY_EXP != 0;  // one exponential in four on the FMA pipe
 
 // Partial results of one segment of a split unit.
 constexpr int kPartialOFloats = 2 * kTileM * kHeadDim;  // [tile][col/4][row][4]
@@ -96,7 +109,7 @@ struct Shared {
   uint64_t ring_full[kStages];
   uint64_t ring_empty[kStages];
   uint64_t s_full[2];
-  uint64_t p_full[2];
+  uint64_t p_part[2][4];  // [tile][piece]; the last piece in use completes P
   uint64_t o_done;
   uint64_t o_free[2];
   uint64_t drain;
@@ -187,6 +200,38 @@ __device__ void plan_segments(const KernelArgs& a, Shared* sh, long long x, long
   sh->more = (x < span_end && row < R) ? 1 : 0;
 }
 
+// P = exp2(S*sc + neg_m) for one 128-column row held in registers: packs to 16 bit, stores the four
+// 32-column chunks over S in TMEM, signals the first half after two chunks.  kPoly offloads one
+// exponential in four to the FMA pipe (never used for masked steps, whose -inf entries must give
+// exact zeros).  Returns the row sum of P.
+template <typename T, bool kPoly>
+__device__ __forceinline__ float exp_pack_store(const uint32_t (&sv)[128], float sc, float neg_m, uint32_t tS,
+                                                uint32_t p_part_bar) {
+  float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      const float x0 = fmaf(__uint_as_float(sv[c * 32 + i]), sc, neg_m);
+      const float x1 = fmaf(__uint_as_float(sv[c * 32 + i + 1]), sc, neg_m);
+      const float p0 = ptx::ex2(x0);
+      const float p1 = (kPoly && (i & 3) == 2) ? ptx::ex2_poly(x1) : ptx::ex2(x1);
+      l0 += p0;
+      l1 += p1;
+      pk[i >> 1] = pack2<T>(p0, p1);
+    }
+    ptx::tmem_st16(tS + c * 16, pk);
+    if ((c + 1) % (4 / kPParts) == 0) {
+      // a piece of P is in TMEM: let the MMA warp run P.V on it (the last piece completes P)
+      ptx::tc_wait_st();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(p_part_bar + static_cast<uint32_t>(((c + 1) / (4 / kPParts) - 1) * sizeof(uint64_t)));
+    }
+  }
+  return l0 + l1;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
     attn_compact_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
@@ -233,8 +278,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     ptx::mbar_init(ptx::smem_u32(&sh->s_full[0]), 1);
     ptx::mbar_init(ptx::smem_u32(&sh->s_full[1]), 1);
-    ptx::mbar_init(ptx::smem_u32(&sh->p_full[0]), 128);
-    ptx::mbar_init(ptx::smem_u32(&sh->p_full[1]), 128);
+    for (int q = 0; q < 4; ++q) {
+      ptx::mbar_init(ptx::smem_u32(&sh->p_part[0][q]), 128);
+      ptx::mbar_init(ptx::smem_u32(&sh->p_part[1][q]), 128);
+    }
     ptx::mbar_init(ptx::smem_u32(&sh->o_done), 1);
     ptx::mbar_init(ptx::smem_u32(&sh->o_free[0]), 128);
     ptx::mbar_init(ptx::smem_u32(&sh->o_free[1]), 128);
@@ -286,7 +333,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   // role state that lives across segments
   int ring_n = 0;        // ring entries issued (loader) / consumed (MMA)
-  uint32_t it = 0;       // KV steps processed so far: parity of s_full / p_full
+  uint32_t it = 0;       // KV steps processed so far: parity of s_full / p_part
   uint32_t seg_seq = 0;  // segments processed so far: parity of q_full / o_done / o_free
   bool ok = true;
 
@@ -388,21 +435,32 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (lane == 0) {
           const uint32_t tS[2] = {tmem + 0u, tmem + 128u};
           const uint32_t tO[2] = {tmem + 256u, tmem + 384u};
+          // Descriptors: one base per operand buffer, then a constant added per MMA (the start address
+          // sits in the low 14 bits in 16-byte units and never carries), so the single issuing thread
+          // spends two adds per instruction instead of rebuilding descriptors.
+          const uint64_t q_desc[2] = {ptx::make_smem_desc_sw128(q_smem, 0, 1024),
+                                      ptx::make_smem_desc_sw128(q_smem + kTileBytes, 0, 1024)};
+          const uint64_t k_desc0 = ptx::make_smem_desc_sw128(ring_smem, 0, 1024);
+          const uint64_t v_desc0 = ptx::make_smem_desc_sw128(ring_smem, kHalfBytes, 1024);
+          const uint32_t idesc_qk = a.idesc_qk, idesc_pv = a.idesc_pv;
           auto issue_s = [&](int tile, int slot) {
-            const uint32_t qa = q_smem + tile * kTileBytes;
-            const uint32_t kb = ring_smem + slot * kTileBytes;
+            const uint64_t qd = q_desc[tile];
+            const uint64_t kd = k_desc0 + static_cast<uint64_t>(slot * (kTileBytes >> 4));
   #pragma unroll
             for (int k = 0; k < 8; ++k) {
-              const uint32_t o = (k >> 2) * kHalfBytes + (k & 3) * 32;
-              ptx::mma_ss(tS[tile], ptx::make_smem_desc_sw128(qa + o, 0, 1024),
-                          ptx::make_smem_desc_sw128(kb + o, 0, 1024), a.idesc_qk, k > 0 ? 1u : 0u);
+              const uint64_t o = static_cast<uint64_t>(((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4);
+              ptx::mma_ss(tS[tile], qd + o, kd + o, idesc_qk, k > 0 ? 1u : 0u);
             }
           };
-          auto issue_pv = [&](int tile, int slot, int ksteps, bool first) {
-            const uint32_t vb = ring_smem + slot * kTileBytes;
-            for (int k = 0; k < ksteps; ++k) {
-              ptx::mma_ts(tO[tile], tS[tile] + k * 8, ptx::make_smem_desc_sw128(vb + k * 2048, kHalfBytes, 1024),
-                          a.idesc_pv, (first && k == 0) ? 0u : 1u);
+          // k-steps [k0, k1) of O += P.V; kN compile-time so the loop unrolls
+          auto issue_pv = [&](int tile, int slot, int k0, int k1, bool first) {
+            const uint64_t vd = v_desc0 + static_cast<uint64_t>(slot * (kTileBytes >> 4));
+  #pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              if (k >= k0 && k < k1) {
+                ptx::mma_ts(tO[tile], tS[tile] + k * 8, vd + static_cast<uint64_t>(k * (2048 >> 4)), idesc_pv,
+                            (first && k == 0) ? 0u : 1u);
+              }
             }
           };
           auto wait = [&](uint64_t* bar, uint32_t parity) {
@@ -435,21 +493,31 @@ __global__ void __launch_bounds__(kThreads, 1)
               const int ksteps = ((2 * j + 1) < sg.n_sub) ? 8 : 4;
               const bool first = j == sg.j0;
               if (!wait(&sh->ring_full[v_slot], v_phase)) break;
-              if (!wait(&sh->p_full[0], it & 1)) break;
-              // the accumulator is free once the previous segment's epilogue has read it
-              if (first && seg_seq > 0 && !wait(&sh->o_free[0], (seg_seq - 1) & 1)) break;
-              ptx::tc_fence_after();
-              issue_pv(0, v_slot, ksteps, first);
+              // P arrives in pieces so P.V starts while the softmax still works
+              for (int q = 0; q < kPParts && ok; ++q) {
+                if (!wait(&sh->p_part[0][q], it & 1)) break;
+                // the accumulator is free once the previous segment's epilogue has read it
+                if (q == 0 && first && seg_seq > 0 && !wait(&sh->o_free[0], (seg_seq - 1) & 1)) break;
+                ptx::tc_fence_after();
+                const int k1 = (q + 1) * (8 / kPParts);
+                issue_pv(0, v_slot, q * (8 / kPParts), k1 < ksteps ? k1 : ksteps, first);
+              }
+              if (!ok) break;
               if (more) {
                 if (!wait(&sh->ring_full[k_slot], k_phase)) break;
                 ptx::tc_fence_after();
                 issue_s(0, k_slot);
                 ptx::tc_commit(ptx::smem_u32(&sh->s_full[0]));
               }
-              if (!wait(&sh->p_full[1], it & 1)) break;
-              if (first && seg_seq > 0 && !wait(&sh->o_free[1], (seg_seq - 1) & 1)) break;
-              ptx::tc_fence_after();
-              issue_pv(1, v_slot, ksteps, first);
+              for (int q = 0; q < kPParts && ok; ++q) {
+                if (!wait(&sh->p_part[1][q], it & 1)) break;
+                // the accumulator is free once the previous segment's epilogue has read it
+                if (q == 0 && first && seg_seq > 0 && !wait(&sh->o_free[1], (seg_seq - 1) & 1)) break;
+                ptx::tc_fence_after();
+                const int k1 = (q + 1) * (8 / kPParts);
+                issue_pv(1, v_slot, q * (8 / kPParts), k1 < ksteps ? k1 : ksteps, first);
+              }
+              if (!ok) break;
               ptx::tc_commit(ptx::smem_u32(&sh->ring_empty[v_slot]));
               if (more) {
                 issue_s(1, k_slot);
@@ -545,24 +613,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             // P = exp2(S*sc - m*sc) -> 16-bit, written over S.  Masked entries are -inf -> 0; a row
             // that has seen nothing yet (m = -inf) produces zeros.
             const float neg_m = m_run == -INFINITY ? 0.f : -m_run * sc;
-            float l0 = 0.f, l1 = 0.f;
-  #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              uint32_t pk[16];
-  #pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                const float p0 = ptx::ex2(fmaf(__uint_as_float(sv[c * 32 + i]), sc, neg_m));
-                const float p1 = ptx::ex2(fmaf(__uint_as_float(sv[c * 32 + i + 1]), sc, neg_m));
-                l0 += p0;
-                l1 += p1;
-                pk[i >> 1] = pack2<T>(p0, p1);
-              }
-              ptx::tmem_st16(tS + c * 16, pk);
-            }
-            l_run += l0 + l1;
-            ptx::tc_wait_st();
-            ptx::tc_fence_before();
-            ptx::mbar_arrive(ptx::smem_u32(&sh->p_full[tile]));
+            const uint32_t half_bar = ptx::smem_u32(&sh->p_part[tile][0]);
+            l_run += masked ? exp_pack_store<T, false>(sv, sc, neg_m, tS, half_bar)
+                            : exp_pack_store<T, kPolyExp>(sv, sc, neg_m, tS, half_bar);
+
           }
           if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&sh->o_done), seg_seq & 1, abort_flag, limit);
           ok = __all_sync(0xffffffffu, ok);
