@@ -205,6 +205,7 @@ _SIGNATURES = {
     "ca_launch_count": (C.c_int64, []),
     "ca_attn_workspace_bytes": (C.c_int, [C.POINTER(AttnParams), C.POINTER(C.c_size_t)]),
     "ca_attn_compact": (C.c_int, [C.POINTER(AttnParams), C.c_void_p]),
+    "ca_attn_compact_static_scratch": (C.c_int, [C.POINTER(AttnParams), C.c_void_p]),
     "ca_select_rows": (C.c_int, [C.POINTER(SelectParams), C.c_void_p]),
     "ca_union_table": (C.c_int, [C.POINTER(UnionParams), C.c_void_p]),
     "ca_paged_metadata": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),

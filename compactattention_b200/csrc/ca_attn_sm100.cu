@@ -27,6 +27,8 @@
 // what it issued, frees TMEM and returns.
 #include "ca_common.cuh"
 
+#include <mutex>
+
 namespace ca {
 namespace attn {
 
@@ -823,6 +825,39 @@ static size_t ml_bytes(int nc) { return static_cast<size_t>(2) * nc * kPartialML
 static size_t o_bytes(int nc) { return static_cast<size_t>(2) * nc * kPartialOFloats * sizeof(float); }
 static size_t workspace_bytes_for(int nc) { return desc_bytes(nc) + ml_bytes(nc) + o_bytes(nc); }
 
+
+// ---- scratch for callers that cannot allocate -------------------------------------------------
+// Room for the split-unit partials of a grid of up to kStaticMaxCtas CTAs (a B200 has 148 SMs):
+// 160 * 2 slots * (128 KiB accumulator + 2 KiB max/sum) + descriptors = 41.6 MiB, resident on every
+// GPU that loads the library until the process exits.
+constexpr int kStaticMaxCtas = 160;
+constexpr size_t kStaticScratchBytes =
+    ((2 * kStaticMaxCtas * sizeof(SegDesc) + 255) / 256) * 256 +
+    static_cast<size_t>(2) * kStaticMaxCtas * (kPartialMLFloats + kPartialOFloats) * sizeof(float);
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on the current device.  In host code the array's name is only
+// a stand-in for the symbol, not a pointer a kernel can use, so the address is asked from the
+// runtime once per device (with that device current) and remembered.
+static int static_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  CA_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(CA_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess || ptr == nullptr) {
+      return fail(CA_ERR_CUDA, "cudaGetSymbolAddress(static attention scratch) failed: %s", cudaGetErrorString(err));
+    }
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return CA_OK;
+}
+
 }  // namespace attn
 }  // namespace ca
 
@@ -965,6 +1000,30 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
     CA_LAUNCH_CHECK("attn_combine_kernel");
   }
   return CA_OK;
+}
+
+int ca_attn_compact_static_scratch(const ca_attn_params* p, ca_stream_t stream) {
+  using namespace ca;
+  using namespace ca::attn;
+  int rc = validate(p);
+  if (rc != CA_OK) return rc;
+  DeviceInfo dev;
+  rc = get_device_info(&dev);
+  if (rc != CA_OK) return rc;
+  const size_t need = workspace_bytes_for(dev.sm_count);
+  if (need > kStaticScratchBytes) {
+    return fail(CA_ERR_CAPACITY,
+                "this device has %d SMs and needs %zu bytes of attention scratch; the built-in scratch holds %zu bytes "
+                "(up to %d SMs): use ca_attn_compact with a caller-provided workspace",
+                dev.sm_count, need, kStaticScratchBytes, kStaticMaxCtas);
+  }
+  void* scratch = nullptr;
+  rc = static_scratch_address(&scratch);  // first call on a device looks the address up
+  if (rc != CA_OK) return rc;
+  ca_attn_params q = *p;
+  q.workspace = scratch;
+  q.workspace_bytes = kStaticScratchBytes;
+  return ca_attn_compact(&q, stream);
 }
 
 }  // extern "C"

@@ -167,6 +167,48 @@ def attn_compact(
     return out
 
 
+def attn_compact_static_scratch(
+    q: torch.Tensor,  # [B, Q, Hq, D]
+    kv: KvCacheView,
+    kv_len: int,
+    num_kv_heads: int,
+    block_idx: Optional[torch.Tensor],
+    counts: Optional[torch.Tensor],
+    out: torch.Tensor,  # [B, Q, Hq, D], required: this route allocates nothing, here or in the library
+    block_size: int = 64,
+    softmax_scale: Optional[float] = None,
+    lse: Optional[torch.Tensor] = None,
+    status: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """``attn_compact`` for hosts that may not allocate device memory (an engine that has given all
+    of HBM to its own pool, a loop in which allocation is banned).  The kernel's scratch is a buffer
+    built into the library (41.6 MiB per GPU, devices of up to 160 SMs) instead of a workspace
+    tensor.  Every call on a device shares that buffer, so calls must be ordered on one stream, and
+    the first call on a device (which looks the buffer's address up) belongs outside any stream
+    capture."""
+    _require_cuda(q, kv.k, kv.v, block_idx, counts, out, lse, status)
+    B, Q, Hq, D = q.shape
+    if q.dtype not in (torch.bfloat16, torch.float16) or kv.k.dtype != q.dtype or out.dtype != q.dtype:
+        raise ValueError("q, k, v, out must share dtype bfloat16 or float16")
+    if q.stride(3) != 1 or out.stride(3) != 1:
+        raise ValueError("q and out must have a contiguous head dim")
+    if block_idx is not None and (block_idx.dtype != torch.int32 or counts is None or counts.dtype != torch.int32
+                                  or not block_idx.is_contiguous() or not counts.is_contiguous()):
+        raise ValueError("block_idx and counts must be contiguous int32")
+    p = _lib.AttnParams()
+    p.q, p.q_stride_b, p.q_stride_t, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1), q.stride(2)
+    p.out, p.o_stride_b, p.o_stride_t, p.o_stride_h = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
+    p.kv = kv.to_c()
+    p.block_idx, p.counts = _ptr(block_idx), _ptr(counts)
+    p.block_idx_stride = 0 if block_idx is None else block_idx.shape[-1]
+    p.B, p.Q, p.Hq, p.Hkv, p.D = B, Q, Hq, num_kv_heads, D
+    p.kv_len, p.block_size, p.dtype = kv_len, block_size, _DTYPES[q.dtype]
+    p.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    p.lse, p.status = _ptr(lse), _ptr(status)
+    _lib.check(_lib.load().ca_attn_compact_static_scratch(C.byref(p), _stream()), "ca_attn_compact_static_scratch")
+    return out
+
+
 # ---------------------------------------------------------------------------------------------
 # Block selection
 # ---------------------------------------------------------------------------------------------

@@ -107,6 +107,23 @@ typedef struct ca_attn_params {
 int ca_attn_workspace_bytes(const ca_attn_params* p, size_t* bytes_out);
 int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream);
 
+/*
+ * ca_attn_compact for callers that cannot allocate device memory.  (No counterpart in the
+ * reference: it exists for hosts such as a serving engine that has handed all of HBM to its own
+ * pool, or a latency-critical loop in which cudaMalloc and its implicit synchronisation are
+ * banned, and which therefore cannot obtain the workspace that lets the kernel cut work units
+ * across SMs.)  The partial accumulators live in a buffer built into the library instead:
+ * 41.6 MiB of device memory per GPU that loads the library, enough for a device of up to 160 SMs;
+ * a larger device is refused with CA_ERR_CAPACITY.  p->workspace and p->workspace_bytes are
+ * ignored; inputs and outputs are still the caller's.  Nothing is allocated or freed by this
+ * call.  The first call on a device looks up the buffer's device address (one runtime query, no
+ * allocation), so make that first call outside any stream capture.  All calls on a device share
+ * the one buffer and it keeps what the previous call left (each launch re-initialises the slot
+ * descriptors it reads): calls whose kernels may overlap on the GPU (different streams) race and
+ * must be ordered by the caller.
+ */
+int ca_attn_compact_static_scratch(const ca_attn_params* p, ca_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Block selection
  * ---------------------------------------------------------------------------------------- */
