@@ -173,9 +173,12 @@ def run_native(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group(backend="nccl", device_id=dev)
-    if HKV % world:
-        raise SystemExit(f"{world} ranks do not divide {HKV} KV heads")
-    hkv, hq = HKV // world, HQ // world
+    from compactattention_b200 import tp
+    try:
+        shard = tp.HeadShard(world, rank, HQ, HKV)
+    except ValueError as exc:
+        raise SystemExit(str(exc))
+    hkv, hq = len(shard.kv_heads), len(shard.q_heads)
     K, Q = args.kv_len, args.chunk
     Kb, Qb = K // BS, Q // BS
     Pb = Kb - Qb
@@ -229,8 +232,7 @@ def run_native(args):
             e1.record()
             attn_events.append((e0, e1))
         if world > 1:
-            import torch.distributed as dist
-            dist.all_reduce(reduce_buf)
+            tp.reduce_layer_output(reduce_buf)
 
     def barrier():
         if world > 1:
