@@ -37,10 +37,11 @@ sys.path.insert(0, str(ROOT))
 
 HQ, HKV, D, BS = 32, 8, 128, 64
 METRIC = "per-chunk attn latency @128K ctx, chunk 1024"
-# DRAM bytes (read + write) of one attention launch of this workload from the ncu capture summarised
-# in profiles/attn_compact_kernel_c3_128k.md (captured on a 32K-context case and scaled by selected
-# blocks, traffic is proportional to them); None until a capture exists.
-NCU_ATTN_TRAFFIC_BYTES = None
+# DRAM bytes (read + write) of one attention launch from the ncu capture summarised in
+# profiles/attn_compact_kernel_128k_20pct.md: 123.61 MB measured on a launch whose algorithmic bytes
+# are 127.40 MB (same shape, 406 selected blocks per KV head).  K/V traffic is proportional to the
+# selected blocks, so the benchmark's launch is scaled by its own algorithmic bytes.
+NCU_ATTN_CAPTURE = {"dram_bytes": 123.61e6, "algorithmic_bytes": 127.40e6}
 
 
 def parse_args():
@@ -281,7 +282,8 @@ def run_native(args):
         "bound": "tensor" if t_tensor >= t_hbm else "hbm",
         "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
         "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{peaks['source']} (cuBLAS bf16 burst)",
-        "traffic": NCU_ATTN_TRAFFIC_BYTES, "kernel": "attn_compact_kernel", "kernel_us": round(attn_ms * 1e3, 1),
+        "traffic": round(NCU_ATTN_CAPTURE["dram_bytes"] * kv_bytes / NCU_ATTN_CAPTURE["algorithmic_bytes"]),
+        "kernel": "attn_compact_kernel", "kernel_us": round(attn_ms * 1e3, 1),
         "algorithmic_flops": flops, "algorithmic_bytes": kv_bytes,
         "roofline_us": round(max(t_tensor, t_hbm) * 1e6, 1),
         "path_frac_of_roofline": round(max(t_tensor, t_hbm) * 1e3 / ms_per_step, 4),
