@@ -699,6 +699,10 @@ static bool dtype_ok(int dt) { return dt == CA_DTYPE_F32 || dt == CA_DTYPE_BF16 
 }  // namespace score
 }  // namespace ca
 
+namespace ca {
+int launch_fp_score_sm100(const ca_flashprefill_score_params* p, cudaStream_t stream);  // ca_fpscore_sm100.cu
+}
+
 extern "C" {
 
 int ca_pool_blocks(const ca_pool_params* p, ca_stream_t stream_) {
@@ -887,10 +891,16 @@ int ca_flashprefill_score(const ca_flashprefill_score_params* p, ca_stream_t str
   a.P = p->kv_len - p->Q;
   a.sm_scale = (1.0f / sqrtf(static_cast<float>(p->D))) * 1.4426950408889634f;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  const size_t smem = (static_cast<size_t>(2) * kFpTile * (p->D + 1) + kFpTile * (kFpTile + 1)) * sizeof(float);
-  CA_CUDA(cudaFuncSetAttribute(flashprefill_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  flashprefill_score_kernel<<<dim3(ceil_div(p->Kb, kFpTile), a.Qb, p->B * p->Hq), kFpThreads, smem, stream>>>(a);
-  CA_LAUNCH_CHECK("flashprefill_score_kernel");
+  // 16-bit inputs with d = 128 and block 64/128 run on the tensor cores; everything else (fp32
+  // inputs, other shapes) on the CUDA-core kernel below
+  const int rc_tc = launch_fp_score_sm100(p, stream);
+  if (rc_tc != CA_OK && rc_tc != CA_ERR_UNSUPPORTED) return rc_tc;
+  if (rc_tc == CA_ERR_UNSUPPORTED) {
+    const size_t smem = (static_cast<size_t>(2) * kFpTile * (p->D + 1) + kFpTile * (kFpTile + 1)) * sizeof(float);
+    CA_CUDA(cudaFuncSetAttribute(flashprefill_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    flashprefill_score_kernel<<<dim3(ceil_div(p->Kb, kFpTile), a.Qb, p->B * p->Hq), kFpThreads, smem, stream>>>(a);
+    CA_LAUNCH_CHECK("flashprefill_score_kernel");
+  }
   if (p->score_norm) {
     const int threads = 256;
     const size_t nsmem = static_cast<size_t>(threads / p->Hq) * p->Hq * sizeof(float);

@@ -162,7 +162,9 @@ def test_flashprefill_score_golden(ops, golden):
 
 
 @pytest.mark.parametrize("Q,K,Hq,Hkv,bs,dtype", [(1024, 8192, 8, 2, 64, torch.bfloat16), (512, 4096, 4, 4, 128, torch.bfloat16),
-                                                 (192, 704, 28, 4, 64, torch.float16), (100, 1060, 4, 1, 64, torch.float32)])
+                                                 (192, 704, 28, 4, 64, torch.float16), (100, 1060, 4, 1, 64, torch.float32),
+                                                 (100, 1060, 4, 1, 64, torch.bfloat16), (1024, 32768, 32, 8, 128, torch.bfloat16),
+                                                 (256, 256, 8, 2, 64, torch.bfloat16)])
 def test_flashprefill_score_random(ops, Q, K, Hq, Hkv, bs, dtype):
     g = torch.Generator().manual_seed(Q + K)
     q = torch.randn((1, Q, Hq, 128), generator=g).to(dtype)
