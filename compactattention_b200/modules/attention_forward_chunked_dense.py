@@ -58,21 +58,34 @@ def _effective_threshold(threshold):
     return threshold
 
 
-def _check_common(query_states, key_states, value_states, query_length, block_size, indexed_impl):
+def _kv_dims(key_states, kv_len: Optional[int]):
+    """``(kv_len, num_kv_heads)`` of a ``[B,K,Hkv,D]`` tensor or of a paged ``ops.KvCacheView`` (whose
+    logical length must be given by the caller)."""
+    if isinstance(key_states, ops.KvCacheView):
+        if kv_len is None:
+            raise ValueError("kv_len is required when key_states is a KvCacheView")
+        return int(kv_len), int(key_states.k.shape[-2])
+    return int(key_states.shape[1]), int(key_states.shape[2])
+
+
+def _check_common(query_states, key_states, value_states, query_length, block_size, indexed_impl, kv_len=None):
     if query_length <= 1:
         raise ValueError("chunked compact attention expects query_length > 1.")
     if block_size <= 0:
         raise ValueError("block_size must be positive.")
     if indexed_impl not in _INDEXED_IMPLS:
         raise ValueError(f"Unsupported indexed_impl: {indexed_impl}")
-    if not (query_states.is_cuda and key_states.is_cuda and value_states.is_cuda):
+    k_t = key_states.k if isinstance(key_states, ops.KvCacheView) else key_states
+    v_t = value_states.v if isinstance(value_states, ops.KvCacheView) else value_states
+    if not (query_states.is_cuda and k_t.is_cuda and v_t.is_cuda):
         raise RuntimeError("compactattention_b200 has no CPU path: tensors must live on a CUDA device")
-    if query_states.dtype not in (torch.float16, torch.bfloat16) or key_states.dtype != query_states.dtype \
-            or value_states.dtype != query_states.dtype:
+    if query_states.dtype not in (torch.float16, torch.bfloat16) or k_t.dtype != query_states.dtype \
+            or v_t.dtype != query_states.dtype:
         raise NotImplementedError("the B200 path computes in bf16/f16; q, k, v must share one of these dtypes")
     if query_states.shape[-1] != 128:
         raise NotImplementedError("the B200 path supports head_dim 128 only")
-    q_len, kv_len = query_states.shape[1], key_states.shape[1]
+    q_len = query_states.shape[1]
+    kv_len, _ = _kv_dims(key_states, kv_len)
     if block_size % 64 or q_len % block_size or kv_len % block_size:
         raise NotImplementedError(
             f"q_len ({q_len}) and kv_len ({kv_len}) must be multiples of block_size ({block_size}), itself a multiple of 64")
@@ -112,6 +125,7 @@ def chunked_prefill_column_dense_attention_from_keep_block(
     v_hf: Optional[torch.Tensor] = None,
     _row_bits: Optional[torch.Tensor] = None,  # packed bits [B, H, Qin, W] from ops.select_rows (internal)
     _keep_recent: int = 0,
+    kv_len: Optional[int] = None,  # logical length when key_states is a paged ops.KvCacheView
 ) -> Tuple[torch.Tensor, Optional[Dict[str, float]]]:
     """Block-Union KV selection from a keep mask, then dense causal attention over the kept blocks.
 
@@ -119,11 +133,10 @@ def chunked_prefill_column_dense_attention_from_keep_block(
     per-query-head column mask, ``keep_block_kv_preprojected`` the per-KV-head one (wins when both
     are given); the chunk's own blocks are always attended.
     """
-    _check_common(query_states, key_states, value_states, query_length, block_size, indexed_impl)
+    _check_common(query_states, key_states, value_states, query_length, block_size, indexed_impl, kv_len)
     bsz, q_len, num_q_heads, _ = query_states.shape
-    kv_len = key_states.shape[1]
+    kv_len, num_kv_heads = _kv_dims(key_states, kv_len)
     kv_blocks = (kv_len + block_size - 1) // block_size
-    num_kv_heads = key_states.shape[2]
     if keep_block is None and keep_block_kv_preprojected is None and _row_bits is None:
         raise ValueError("Either keep_block or keep_block_kv_preprojected must be provided.")
     if keep_block is not None and keep_block.shape != (bsz, num_q_heads, kv_blocks):
@@ -203,6 +216,7 @@ def chunked_prefill_column_dense_attention_forward(
     attn_module=None,
     k_hf: Optional[torch.Tensor] = None,
     v_hf: Optional[torch.Tensor] = None,
+    kv_len: Optional[int] = None,  # logical length when key_states is a paged ops.KvCacheView
 ) -> Tuple[torch.Tensor, Optional[Dict[str, float]]]:
     """Threshold selection on gate scores, Block-Union, then compact attention.
 
@@ -213,15 +227,14 @@ def chunked_prefill_column_dense_attention_forward(
     """
     if attn_gate_score is None:
         raise ValueError("attn_gate_score is required for chunked column-dense attention.")
-    _check_common(query_states, key_states, value_states, query_length, block_size, indexed_impl)
+    _check_common(query_states, key_states, value_states, query_length, block_size, indexed_impl, kv_len)
     threshold = _effective_threshold(threshold)
     if isinstance(threshold, torch.Tensor):
         if threshold.numel() != 1:
             raise NotImplementedError("per-batch threshold tensors are not supported by the B200 path")
         threshold = float(threshold.item())
     bsz, q_len, num_q_heads, head_dim = query_states.shape
-    kv_len = key_states.shape[1]
-    num_kv_heads = key_states.shape[2]
+    kv_len, num_kv_heads = _kv_dims(key_states, kv_len)
     kv_blocks = kv_len // block_size
     q_blocks = q_len // block_size
     if attn_gate_score.dim() != 4 or attn_gate_score.shape[0] != bsz or attn_gate_score.shape[2] != q_blocks:
@@ -263,14 +276,15 @@ def chunked_prefill_column_dense_attention_forward(
             attention_mask=attention_mask, query_length=query_length, softmax_scale=softmax_scale, block_size=block_size,
             num_key_value_groups=num_key_value_groups, pack_impl=pack_impl, indexed_impl=indexed_impl,
             cache_fill_backend=cache_fill_backend, return_stats=return_stats, allow_indexed_dense=True,
-            keep_block_kv_preprojected=keep if attn_gate_is_kv_group_aware else None, attn_module=attn_module, k_hf=k_hf, v_hf=v_hf)
+            keep_block_kv_preprojected=keep if attn_gate_is_kv_group_aware else None, attn_module=attn_module, k_hf=k_hf, v_hf=v_hf, kv_len=kv_len)
     else:
         out, stats = chunked_prefill_column_dense_attention_from_keep_block(
             query_states, key_states, value_states, keep_block=None, attention_mask=attention_mask,
             query_length=query_length, softmax_scale=softmax_scale, block_size=block_size,
             num_key_value_groups=num_key_value_groups, pack_impl=pack_impl, indexed_impl=indexed_impl,
             cache_fill_backend=cache_fill_backend, return_stats=return_stats, allow_indexed_dense=True,
-            attn_module=attn_module, k_hf=k_hf, v_hf=v_hf, _row_bits=bits, _keep_recent=max(int(keep_recent_blocks), 0))
+            attn_module=attn_module, k_hf=k_hf, v_hf=v_hf, _row_bits=bits, _keep_recent=max(int(keep_recent_blocks), 0),
+            kv_len=kv_len)
     if not return_stats:
         return out, None
     stats.update({

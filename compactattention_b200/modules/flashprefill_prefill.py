@@ -17,6 +17,7 @@ from .. import ops
 from .attention_forward_chunked_dense import (
     COMPACTATTN_VERSION,
     _check_common,
+    _kv_dims,
     _kv_view,
     _timed,
     chunked_prefill_column_dense_attention_from_keep_block,
@@ -45,13 +46,13 @@ def flashprefill_compactattn_prefill_full_kv(
     k_hf: Optional[torch.Tensor] = None,
     v_hf: Optional[torch.Tensor] = None,
     mean_k_cache: Optional[torch.Tensor] = None,  # [B, Kb, Hkv, D]
+    kv_len: Optional[int] = None,  # logical length when key_states is a paged ops.KvCacheView
 ) -> Tuple[torch.Tensor, Dict[str, float]]:
     q_len = int(query_states.shape[1])
-    kv_len = int(key_states.shape[1])
-    num_kv_heads = key_states.shape[2]
+    kv_len, num_kv_heads = _kv_dims(key_states, kv_len)
     if q_len <= 1:
         raise NotImplementedError("decode (q_len == 1) is not on the chunked-prefill path of this library")
-    _check_common(query_states, key_states, value_states, q_len, block_size, indexed_impl)
+    _check_common(query_states, key_states, value_states, q_len, block_size, indexed_impl, kv_len)
     if kv_len <= q_len:
         # first chunk: dense causal attention (the reference takes its dense route here, :904-935)
         kv = _kv_view(key_states, value_states, k_hf, v_hf)
@@ -65,6 +66,8 @@ def flashprefill_compactattn_prefill_full_kv(
     past_blocks = kv_blocks - q_blocks
 
     def _score():
+        if mean_k_cache is None and isinstance(key_states, ops.KvCacheView):
+            raise ValueError("a paged KvCacheView needs a mean_k_cache (the pooled keys are kept beside the cache)")
         mean_k = mean_k_cache if mean_k_cache is not None else ops.pool_blocks(
             key_states, block_size, ("avg",), out_dtype=key_states.dtype)
         if mean_k.shape[1] != kv_blocks:
@@ -85,7 +88,7 @@ def flashprefill_compactattn_prefill_full_kv(
         query_states, key_states, value_states, keep_block=None, attention_mask=attention_mask, query_length=q_len,
         softmax_scale=softmax_scale, block_size=block_size, num_key_value_groups=num_key_value_groups, pack_impl=pack_impl,
         indexed_impl=indexed_impl, cache_fill_backend=cache_fill_backend, return_stats=measure_timing,
-        allow_indexed_dense=True, attn_module=attn_module, k_hf=k_hf, v_hf=v_hf, _row_bits=bits)
+        allow_indexed_dense=True, attn_module=attn_module, k_hf=k_hf, v_hf=v_hf, _row_bits=bits, kv_len=kv_len)
     if not measure_timing:
         return out, {}
     stats = dict(compact_stats or {})
