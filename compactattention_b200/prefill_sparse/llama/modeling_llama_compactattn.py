@@ -56,7 +56,10 @@ class CompactAttnLlamaConfig:
     seerattn_gate_block_size: int = 64
     seerattn_gate_hidden_size: int = 128
     seerattn_gate_force_double: bool = False
-    seerattn_sparsity_method: str = "threshold"  # threshold | topk (per-row top-k, ties to the lower block)
+    # threshold | topk (per-row top-k of the gate scores, ties to the lower block) | synthetic_topk (per-row
+    # top-k of a fixed random per-KV-head block importance: imposes an exact union density on
+    # random-init stacks, whose gate scores are uncorrelated across heads and Q-blocks)
+    seerattn_sparsity_method: str = "threshold"
     seerattn_threshold: float = 5e-4
     seerattn_topk_ratio: Tuple[int, int] = (1, 5)
     seerattn_compactattn_keep_recent_blocks: int = 2
@@ -181,6 +184,7 @@ class LlamaSeerAttentionChunkedDense(_CompactAttnBase):
             self.num_key_value_heads, self.num_heads, force_double=config.seerattn_gate_force_double)
         self.compactattn_keep_recent_blocks = config.seerattn_compactattn_keep_recent_blocks
         self.compactattn_disable_first_chunk_dense = config.seerattn_compactattn_disable_first_chunk_dense
+        self._synthetic_importance = None
 
     # -- hook: the attention itself (the reference's _do_chunked_compactattn_attention, :538-545) --
     def _do_chunked_compactattn_attention(self, query_states, key_states, value_states, **kwargs):
@@ -232,6 +236,20 @@ class LlamaSeerAttentionChunkedDense(_CompactAttnBase):
         if force_dense or (first_chunk and not self.compactattn_disable_first_chunk_dense):
             attn = self._dense(q, kv_view, kv_len, bs)
             path = "first_chunk_dense" if first_chunk else "forced_dense"
+        elif self.config.seerattn_sparsity_method == "synthetic_topk":
+            Qb, Kb = logits.shape[2], logits.shape[3]
+            if self._synthetic_importance is None or self._synthetic_importance.shape[-1] < Kb:
+                g = torch.Generator(device=hidden_states.device).manual_seed(1234 + self.layer_idx)
+                self._synthetic_importance = torch.rand((1, self.num_key_value_heads, 1, past_key_value.max_tokens // bs),
+                                                        generator=g, device=hidden_states.device)
+            score = self._synthetic_importance[..., :Kb].expand(hidden_states.shape[0], self.num_key_value_heads, Qb, Kb)
+            bits = ops.select_rows(score, Kb - Qb, "topk", topk_ratio=tuple(self.config.seerattn_topk_ratio), sink=1,
+                                   local=self.compactattn_keep_recent_blocks)
+            table = ops.union_table(bits=bits, num_kv_heads=self.num_key_value_heads, kv_blocks=Kb, past_blocks=Kb - Qb,
+                                    block_size=bs)
+            attn = ops.attn_compact(q, kv_view, kv_len, self.num_key_value_heads, table.block_idx, table.counts,
+                                    block_size=bs, softmax_scale=self.scaling)
+            path = "chunked_selected"
         elif self.config.seerattn_sparsity_method == "topk":
             Qb, Kb = logits.shape[2], logits.shape[3]
             bits = ops.select_rows(logits, Kb - Qb, "topk", topk_ratio=tuple(self.config.seerattn_topk_ratio), sink=1,
