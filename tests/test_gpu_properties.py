@@ -65,7 +65,9 @@ def test_config2_paged_permutation_full_dense_linearity(ops):
 @pytest.mark.parametrize("K,density", [(131072, 0.2), (32768, 0.5)])
 def test_gather_then_dense_equals_indexed_attention(ops, K, density):
     """Config 3 size: copying the selected blocks into a compact cache and running the dense kernel on
-    each row's compact sequence gives bit-identical output to reading the blocks in place."""
+    each row's compact sequence gives bit-identical output to reading the blocks in place, when both
+    runs walk their KV in one piece per work unit (cutting units across SMs changes the fp32
+    summation order, so the default launches are compared within one bf16 step)."""
     g = torch.Generator().manual_seed(1234 + 3)
     Q, Hq, Hkv, D, bs = 1024, 32, 8, 128, 64
     G = Hq // Hkv
@@ -75,7 +77,9 @@ def test_gather_then_dense_equals_indexed_attention(ops, K, density):
     v = torch.randn((1, K, Hkv, D), generator=g).to(torch.bfloat16).cuda()
     kv = ops.KvCacheView.from_seq_first(k, v)
     idx, counts = rand_table(Hkv, Pb, density, g)
-    indexed = ops.attn_compact(q, kv, K, Hkv, idx, counts)
+    indexed = ops.attn_compact(q, kv, K, Hkv, idx, counts, use_workspace=False)
+    indexed_cut = ops.attn_compact(q, kv, K, Hkv, idx, counts)
+    assert (indexed.float() - indexed_cut.float()).abs().max().item() < 2e-3
     cap = (Pb + Q // bs) * bs
     kd = torch.zeros((Hkv * cap, D), dtype=torch.bfloat16, device="cuda")
     vd = torch.zeros_like(kd)
@@ -92,8 +96,11 @@ def test_gather_then_dense_equals_indexed_attention(ops, K, density):
         if first is not None:
             assert torch.equal(kr[0, :bs, 0], k[0, first * bs:(first + 1) * bs, r])
         assert torch.equal(vr[0, L - Q:, 0], v[0, K - Q:, r])
-        dense = ops.attn_compact(q[:, :, r * G:(r + 1) * G].contiguous(), ops.KvCacheView.from_seq_first(kr, vr), L, 1, None, None)
+        qr = q[:, :, r * G:(r + 1) * G].contiguous()
+        dense = ops.attn_compact(qr, ops.KvCacheView.from_seq_first(kr, vr), L, 1, None, None, use_workspace=False)
         assert torch.equal(dense, indexed[:, :, r * G:(r + 1) * G])
+        dense_cut = ops.attn_compact(qr, ops.KvCacheView.from_seq_first(kr, vr), L, 1, None, None)
+        assert (dense_cut.float() - dense.float()).abs().max().item() < 2e-3
 
 
 def test_selection_rule_properties_full_size(ops):
