@@ -52,12 +52,32 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units; lazy accumulator resca
 #ifndef CA_ATTN_P_PARTS
 #define CA_ATTN_P_PARTS 2
 #endif
-#ifndef CA_ATTN_POLY_EXP
-#define CA_ATTN_POLY_EXP 0
+#ifndef CA_ATTN_POLY_PAIRS
+#define CA_ATTN_POLY_PAIRS 0
+#endif
+#ifndef CA_ATTN_PROFILE
+#define CA_ATTN_PROFILE 0
+#endif
+#ifndef CA_ATTN_EXPERIMENT
+#define CA_ATTN_EXPERIMENT 0  // development timing experiments; any value but 0 produces wrong results
 #endif
 static_assert(CA_ATTN_P_PARTS == 1 || CA_ATTN_P_PARTS == 2, "P is handed over in one or two pieces");
 constexpr int kPParts = CA_ATTN_P_PARTS;  // P is handed to the MMA warp in this many pieces so P.V overlaps the softmax
-constexpr bool kPolyExp = CA_ATTN_POLY_EXP != 0;  // one exponential in four on the FMA pipe
+constexpr int kPolyPairs = CA_ATTN_POLY_PAIRS;  // of every 16 pairs of exponentials, this many run on the FMA pipe
+static_assert(kPolyPairs >= 0 && kPolyPairs <= 16, "polynomial pairs per 16");
+
+// Optional cycle accounting (development builds only, -DCA_ATTN_PROFILE=1): one thread of each role
+// adds the clock cycles between consecutive marks to per-CTA counters.
+#if CA_ATTN_PROFILE
+__device__ long long g_prof[160][32];
+#define CA_PROF_DECL long long prof_t = clock64(); long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+#define CA_PROF(i) { const long long prof_n = clock64(); prof_acc[i] += prof_n - prof_t; prof_t = prof_n; }
+#define CA_PROF_FLUSH(base) { for (int prof_i = 0; prof_i < 10; ++prof_i) g_prof[blockIdx.x][(base) + prof_i] = prof_acc[prof_i]; }
+#else
+#define CA_PROF_DECL
+#define CA_PROF(i) {}
+#define CA_PROF_FLUSH(base) {}
+#endif
 
 // Partial results of one segment of a split unit.
 constexpr int kPartialOFloats = 2 * kTileM * kHeadDim;  // [tile][col/4][row][4]
@@ -202,36 +222,70 @@ __device__ void plan_segments(const KernelArgs& a, Shared* sh, long long x, long
   sh->more = (x < span_end && row < R) ? 1 : 0;
 }
 
+// 2^x for two values on the FMA/ALU pipes (no MUFU), with the packed fp32 instructions of sm_100:
+// x = n + f by the 1.5*2^23 rounding trick, degree-3 polynomial for 2^f on [-0.5, 0.5] (relative
+// error 1.9e-4, below the 16-bit rounding of P), n added to the exponent bits.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -126.0f);
+  x.y = fmaxf(x.y, -126.0f);
+  const float2 magic = make_float2(12582912.0f, 12582912.0f);
+  const float2 t = __fadd2_rn(x, magic);
+  const float2 u = __fadd2_rn(t, make_float2(-12582912.0f, -12582912.0f));
+  const float2 f = __ffma2_rn(u, make_float2(-1.0f, -1.0f), x);
+  float2 p = __ffma2_rn(make_float2(0.0558755025267601f, 0.0558755025267601f), f,
+                        make_float2(0.24229444563388824f, 0.24229444563388824f));
+  p = __ffma2_rn(p, f, make_float2(0.6931272745132446f, 0.6931272745132446f));
+  p = __ffma2_rn(p, f, make_float2(0.999948263168335f, 0.999948263168335f));
+  p.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23));
+  p.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23));
+  return p;
+}
+
 // P = exp2(S*sc + neg_m) for one 128-column row held in registers: packs to 16 bit, stores the four
-// 32-column chunks over S in TMEM, signals the first half after two chunks.  kPoly offloads one
-// exponential in four to the FMA pipe (never used for masked steps, whose -inf entries must give
-// exact zeros).  Returns the row sum of P.
-template <typename T, bool kPoly>
+// 32-column chunks over S in TMEM, signals the MMA warp after each of the kPParts pieces.  The scale
+// and the row sum use packed fp32 pairs; kPolyPairs of every 16 pairs take their exponentials from
+// the FMA pipe (never for masked steps, whose -inf entries must give exact zeros).  Returns the row
+// sum of P.
+template <typename T, int kPolyPairs>
 __device__ __forceinline__ float exp_pack_store(const uint32_t (&sv)[128], float sc, float neg_m, uint32_t tS,
                                                 uint32_t p_part_bar) {
-  float l0 = 0.f, l1 = 0.f;
+  float2 l2 = make_float2(0.f, 0.f);
+  const float2 sc2 = make_float2(sc, sc);
+  const float2 nm2 = make_float2(neg_m, neg_m);
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     uint32_t pk[16];
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
-      const float x0 = fmaf(__uint_as_float(sv[c * 32 + i]), sc, neg_m);
-      const float x1 = fmaf(__uint_as_float(sv[c * 32 + i + 1]), sc, neg_m);
-      const float p0 = ptx::ex2(x0);
-      const float p1 = (kPoly && (i & 3) == 2) ? ptx::ex2_poly(x1) : ptx::ex2(x1);
-      l0 += p0;
-      l1 += p1;
-      pk[i >> 1] = pack2<T>(p0, p1);
+      const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[c * 32 + i]), __uint_as_float(sv[c * 32 + i + 1])), sc2, nm2);
+      float2 pr;
+      // spread the polynomial pairs evenly over the 16 pairs of the chunk
+      const int pi = i >> 1;
+      const bool poly = kPolyPairs > 0 && ((pi * kPolyPairs) / 16 != ((pi + 1) * kPolyPairs) / 16);
+      if (poly) {
+        pr = ex2_poly2(x);
+      } else {
+#if CA_ATTN_EXPERIMENT == 3
+        pr = x;  // timing experiment: no MUFU
+#else
+        pr.x = ptx::ex2(x.x);
+        pr.y = ptx::ex2(x.y);
+#endif
+      }
+      l2 = __fadd2_rn(l2, pr);
+      pk[i >> 1] = pack2<T>(pr.x, pr.y);
     }
     ptx::tmem_st16(tS + c * 16, pk);
     if ((c + 1) % (4 / kPParts) == 0) {
       // a piece of P is in TMEM: let the MMA warp run P.V on it (the last piece completes P)
+#if CA_ATTN_EXPERIMENT != 2
       ptx::tc_wait_st();
+#endif
       ptx::tc_fence_before();
       ptx::mbar_arrive(p_part_bar + static_cast<uint32_t>(((c + 1) / (4 / kPParts) - 1) * sizeof(uint64_t)));
     }
   }
-  return l0 + l1;
+  return l2.x + l2.y;
 }
 
 template <typename T>
@@ -469,6 +523,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(bar), parity, abort_flag, limit);
             return ok;
           };
+          CA_PROF_DECL
           for (int si = 0; si < n_segs && ok; ++si) {
             const Segment sg = sh->segs[si];
             const uint32_t qpar = seg_seq & 1;
@@ -494,10 +549,14 @@ __global__ void __launch_bounds__(kThreads, 1)
               if (more) ++ring_n;
               const int ksteps = ((2 * j + 1) < sg.n_sub) ? 8 : 4;
               const bool first = j == sg.j0;
+              CA_PROF(0)
               if (!wait(&sh->ring_full[v_slot], v_phase)) break;
+              CA_PROF(1)
               // P arrives in pieces so P.V starts while the softmax still works
               for (int q = 0; q < kPParts && ok; ++q) {
+                if (q > 0) CA_PROF(0)
                 if (!wait(&sh->p_part[0][q], it & 1)) break;
+                CA_PROF(2 + q)
                 // the accumulator is free once the previous segment's epilogue has read it
                 if (q == 0 && first && seg_seq > 0 && !wait(&sh->o_free[0], (seg_seq - 1) & 1)) break;
                 ptx::tc_fence_after();
@@ -505,14 +564,18 @@ __global__ void __launch_bounds__(kThreads, 1)
                 issue_pv(0, v_slot, q * (8 / kPParts), k1 < ksteps ? k1 : ksteps, first);
               }
               if (!ok) break;
+              CA_PROF(0)
               if (more) {
                 if (!wait(&sh->ring_full[k_slot], k_phase)) break;
+                CA_PROF(4)
                 ptx::tc_fence_after();
                 issue_s(0, k_slot);
                 ptx::tc_commit(ptx::smem_u32(&sh->s_full[0]));
               }
               for (int q = 0; q < kPParts && ok; ++q) {
+                CA_PROF(0)
                 if (!wait(&sh->p_part[1][q], it & 1)) break;
+                CA_PROF(5 + q)
                 // the accumulator is free once the previous segment's epilogue has read it
                 if (q == 0 && first && seg_seq > 0 && !wait(&sh->o_free[1], (seg_seq - 1) & 1)) break;
                 ptx::tc_fence_after();
@@ -529,7 +592,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             if (ok) ptx::tc_commit(ptx::smem_u32(&sh->o_done));
             ++seg_seq;
+            CA_PROF(7)
           }
+          CA_PROF_FLUSH(0)
         }
       }
       ok = __syncthreads_and(ok ? 1 : 0) != 0;  // all roles finished this batch (or aborted)
@@ -552,6 +617,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t tO = tmem + lane_base + 256u + tile * 128u;
         const float sc = a.scale_log2;
         uint32_t v[32];
+        CA_PROF_DECL
         for (int si = 0; si < n_segs && ok; ++si) {
           const Segment sg = sh->segs[si];
           const int b = sg.row / a.Hkv, hkv = sg.row % a.Hkv;
@@ -560,9 +626,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           float m_run = -INFINITY;
           float l_run = 0.f;
           for (int j = sg.j0; j < sg.j1; ++j, ++it) {
+            CA_PROF(0)
             ok = ptx::mbar_wait_bounded(ptx::smem_u32(&sh->s_full[tile]), it & 1, abort_flag, limit);
             ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the collective TMEM ops
             if (!ok) break;
+            CA_PROF(1)
             ptx::tc_fence_after();
             const bool masked = (2 * j + 1) >= sg.n_past_sub;  // a chunk or tail sub-block is in this step
             int lim0 = kSub, lim1 = kSub;
@@ -570,6 +638,12 @@ __global__ void __launch_bounds__(kThreads, 1)
               lim0 = visible_cols(2 * j, sg.n_sub, sg.n_past_sub, t);
               lim1 = visible_cols(2 * j + 1, sg.n_sub, sg.n_past_sub, t);
             }
+#if CA_ATTN_EXPERIMENT == 1
+            // timing experiment: no softmax work at all, P "ready" at once
+            ptx::tc_fence_before();
+            for (int q = 0; q < kPParts; ++q) ptx::mbar_arrive(ptx::smem_u32(&sh->p_part[tile][q]));
+            continue;
+#endif
             // the whole S row (128 fp32) comes into registers with one wait
             uint32_t sv[128];
             ptx::tmem_ld32_row<0>(tS + 0, sv);
@@ -577,6 +651,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             ptx::tmem_ld32_row<64>(tS + 64, sv);
             ptx::tmem_ld32_row<96>(tS + 96, sv);
             ptx::tc_wait_ld();
+            CA_PROF(2)
             if (masked) {
   #pragma unroll
               for (int i = 0; i < 128; ++i) {
@@ -616,8 +691,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             // that has seen nothing yet (m = -inf) produces zeros.
             const float neg_m = m_run == -INFINITY ? 0.f : -m_run * sc;
             const uint32_t half_bar = ptx::smem_u32(&sh->p_part[tile][0]);
-            l_run += masked ? exp_pack_store<T, false>(sv, sc, neg_m, tS, half_bar)
-                            : exp_pack_store<T, kPolyExp>(sv, sc, neg_m, tS, half_bar);
+            CA_PROF(3)
+            l_run += masked ? exp_pack_store<T, 0>(sv, sc, neg_m, tS, half_bar)
+                            : exp_pack_store<T, kPolyPairs>(sv, sc, neg_m, tS, half_bar);
+            CA_PROF(4)
 
           }
           if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&sh->o_done), seg_seq & 1, abort_flag, limit);
@@ -672,7 +749,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::tc_fence_before();
           ptx::mbar_arrive(ptx::smem_u32(&sh->o_free[tile]));
           ++seg_seq;
+          CA_PROF(5)
         }
+        if ((tid & 127) == 0) CA_PROF_FLUSH(10 + 10 * tile)
       }
       ok = __syncthreads_and(ok ? 1 : 0) != 0;  // all roles finished this batch (or aborted)
       if (!ok) break;
@@ -1027,3 +1106,10 @@ int ca_attn_compact_static_scratch(const ca_attn_params* p, ca_stream_t stream) 
 }
 
 }  // extern "C"
+
+#if CA_ATTN_PROFILE
+// Development builds only: copies the cycle counters of the last launch to the host.
+extern "C" int ca_debug_attn_profile(long long* dst) {
+  return cudaMemcpyFromSymbol(dst, ca::attn::g_prof, sizeof(long long) * 160 * 32) == cudaSuccess ? 0 : -3;
+}
+#endif
