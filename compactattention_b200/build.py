@@ -5,6 +5,10 @@ static CUDA runtime, so it loads on a machine without a GPU driver (symbols can 
 there) and runs on a B200.
 
 Usage: ``python -m compactattention_b200.build [--force] [--verbose]``
+
+Development builds (cycle accounting, timing experiments) go to a separate file and never replace
+the product library: ``python -m compactattention_b200.build --define CA_ATTN_PROFILE=1 --output
+compactattention_b200/libcompactattn_b200_profile.so``.
 """
 from __future__ import annotations
 
@@ -69,12 +73,36 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+def build_variant(defines: list[str], output: Path, verbose: bool = False) -> Path:
+    """Compile the same sources with extra ``-D`` macros into ``output`` (a development build)."""
+    output = Path(output).resolve()
+    if output == LIB_PATH:
+        raise ValueError("a development build must not overwrite the product library")
+    cmd = [find_nvcc(), *NVCC_FLAGS, *[f"-D{d}" for d in defines]]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    cmd += ["-o", str(output), *[str(s) for s in sources()]]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or proc.returncode != 0:
+        sys.stderr.write(proc.stdout + proc.stderr)
+    if proc.returncode != 0:
+        raise RuntimeError(f"nvcc failed with exit code {proc.returncode}")
+    return output
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--define", action="append", default=[], help="extra macro NAME=VALUE (development build; needs --output)")
+    ap.add_argument("--output", default=None, help="where a development build is written")
     args = ap.parse_args()
-    print(build(force=args.force, verbose=args.verbose))
+    if args.define or args.output:
+        if not (args.define and args.output):
+            ap.error("--define and --output go together")
+        print(build_variant(args.define, Path(args.output), verbose=args.verbose))
+    else:
+        print(build(force=args.force, verbose=args.verbose))
 
 
 if __name__ == "__main__":

@@ -59,7 +59,10 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units; lazy accumulator resca
 #define CA_ATTN_PROFILE 0
 #endif
 #ifndef CA_ATTN_EXPERIMENT
-#define CA_ATTN_EXPERIMENT 0  // development timing experiments; any value but 0 produces wrong results
+// Development timing experiments (results are wrong, only the timing means something):
+// 1 = no softmax work at all (the MMA/TMA pipeline alone), 2 = the softmax's TMEM traffic without
+// its arithmetic.
+#define CA_ATTN_EXPERIMENT 0
 #endif
 static_assert(CA_ATTN_P_PARTS == 1 || CA_ATTN_P_PARTS == 2, "P is handed over in one or two pieces");
 constexpr int kPParts = CA_ATTN_P_PARTS;  // P is handed to the MMA warp in this many pieces so P.V overlaps the softmax
@@ -265,12 +268,8 @@ __device__ __forceinline__ float exp_pack_store(const uint32_t (&sv)[128], float
       if (poly) {
         pr = ex2_poly2(x);
       } else {
-#if CA_ATTN_EXPERIMENT == 3
-        pr = x;  // timing experiment: no MUFU
-#else
         pr.x = ptx::ex2(x.x);
         pr.y = ptx::ex2(x.y);
-#endif
       }
       l2 = __fadd2_rn(l2, pr);
       pk[i >> 1] = pack2<T>(pr.x, pr.y);
@@ -278,9 +277,7 @@ __device__ __forceinline__ float exp_pack_store(const uint32_t (&sv)[128], float
     ptx::tmem_st16(tS + c * 16, pk);
     if ((c + 1) % (4 / kPParts) == 0) {
       // a piece of P is in TMEM: let the MMA warp run P.V on it (the last piece completes P)
-#if CA_ATTN_EXPERIMENT != 2
       ptx::tc_wait_st();
-#endif
       ptx::tc_fence_before();
       ptx::mbar_arrive(p_part_bar + static_cast<uint32_t>(((c + 1) / (4 / kPParts) - 1) * sizeof(uint64_t)));
     }
@@ -651,6 +648,22 @@ __global__ void __launch_bounds__(kThreads, 1)
             ptx::tmem_ld32_row<64>(tS + 64, sv);
             ptx::tmem_ld32_row<96>(tS + 96, sv);
             ptx::tc_wait_ld();
+#if CA_ATTN_EXPERIMENT == 2
+            {
+              // timing experiment: TMEM traffic of the softmax (load S, store P), no arithmetic
+  #pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                uint32_t pk[16];
+  #pragma unroll
+                for (int i = 0; i < 16; ++i) pk[i] = sv[c * 32 + i] & 0x3f7f3f7fu;
+                ptx::tmem_st16(tS + c * 16, pk);
+              }
+              ptx::tc_wait_st();
+              ptx::tc_fence_before();
+              for (int q = 0; q < kPParts; ++q) ptx::mbar_arrive(ptx::smem_u32(&sh->p_part[tile][q]));
+              continue;
+            }
+#endif
             CA_PROF(2)
             if (masked) {
   #pragma unroll

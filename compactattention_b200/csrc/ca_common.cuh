@@ -97,6 +97,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+// One poll of the barrier phase.  Measured on B200 in the attention kernel: the plain form below is
+// the fastest; a suspend-time hint (1 us or 20 us) made the hand-offs between roles slower (+18 %
+// kernel time, the parked warps wake late) and a non-blocking test_wait spin took issue slots from
+// the warps that share the scheduler (+4 %).
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
