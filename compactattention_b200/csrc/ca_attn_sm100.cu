@@ -46,9 +46,10 @@ constexpr int kMaxRows = 1024;  // (batch x kv heads) rows per launch
 constexpr int kMaxSegs = 64;    // segments planned per batch
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; lazy accumulator rescale
 // Measured on B200 (sustained 300-launch loop, 128K context, 20 % density): handing P to the MMA warp
-// in two halves 434 us, in one piece 450 us; a polynomial exp2 on the FMA pipe for one exponential
-// in four made it slower (the kernel is limited by issue slots and board power, not by the MUFU
-// pipe), so it stays off.
+// in two halves 434 us, in one piece 450 us; packed fp32 pairs for the scale and the row sum 421 us;
+// a polynomial exp2 on the FMA pipe (packed, 2 to 8 of every 16 pairs) 432 to 464 us.  The tensor
+// pipe slows down with every arithmetic instruction the softmax warps add (it is not the MUFU pipe
+// that limits), so the polynomial stays off.
 #ifndef CA_ATTN_P_PARTS
 #define CA_ATTN_P_PARTS 2
 #endif
