@@ -195,6 +195,27 @@ class GatherParams(C.Structure):
     ]
 
 
+class RopeAppendParams(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("q_out", C.c_void_p),
+        ("q_stride_b", C.c_int64), ("q_stride_t", C.c_int64), ("q_stride_h", C.c_int64),
+        ("qo_stride_b", C.c_int64), ("qo_stride_t", C.c_int64), ("qo_stride_h", C.c_int64),
+        ("k", C.c_void_p),
+        ("k_stride_b", C.c_int64), ("k_stride_t", C.c_int64), ("k_stride_h", C.c_int64),
+        ("v", C.c_void_p),
+        ("v_stride_b", C.c_int64), ("v_stride_t", C.c_int64), ("v_stride_h", C.c_int64),
+        ("cos", C.c_void_p), ("sin", C.c_void_p),
+        ("cs_stride_b", C.c_int64), ("cs_stride_t", C.c_int64),
+        ("rope_dtype", C.c_int32), ("dtype", C.c_int32),
+        ("cache", KvLayout),
+        ("mean_k", C.c_void_p),
+        ("mk_stride_b", C.c_int64), ("mk_stride_blk", C.c_int64), ("mk_stride_h", C.c_int64),
+        ("B", C.c_int32), ("Q", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("D", C.c_int32),
+        ("position", C.c_int32), ("block_size", C.c_int32), ("reserved", C.c_int32),
+        ("status", C.c_void_p),
+    ]
+
+
 CA_RULE_THRESHOLD, CA_RULE_ALPHA_ROWMAX, CA_RULE_TOPK, CA_RULE_CUMMASS, CA_RULE_MASK = 0, 1, 2, 3, 4
 CA_POOL_MAX, CA_POOL_MIN, CA_POOL_AVG = 1, 2, 4
 
@@ -215,6 +236,7 @@ _SIGNATURES = {
     "ca_gate_scores": (C.c_int, [C.POINTER(GateScoreParams), C.c_void_p]),
     "ca_flashprefill_score": (C.c_int, [C.POINTER(FlashPrefillScoreParams), C.c_void_p]),
     "ca_gather_kv": (C.c_int, [C.POINTER(GatherParams), C.c_void_p]),
+    "ca_rope_append": (C.c_int, [C.POINTER(RopeAppendParams), C.c_void_p]),
 }
 
 _lib = None

@@ -599,6 +599,72 @@ def gather_kv(
     _lib.check(_lib.load().ca_gather_kv(C.byref(p), _stream()), "ca_gather_kv")
 
 
+def rope_append(
+    q: Optional[torch.Tensor],  # [B, Q, Hq, D] pre-RoPE queries (or None)
+    k: torch.Tensor,            # [B, Q, Hkv, D] pre-RoPE keys
+    v: torch.Tensor,            # [B, Q, Hkv, D]
+    cos: torch.Tensor,          # [B or 1, Q, D], the tensors' dtype or fp32
+    sin: torch.Tensor,
+    cache: KvCacheView,         # destination pages (written)
+    position: int,
+    *,
+    mean_k: Optional[torch.Tensor] = None,  # [B, blocks, Hkv, D], block position/block_size + i is written
+    block_size: int = 64,
+    q_out: Optional[torch.Tensor] = None,
+    status: Optional[torch.Tensor] = None,
+) -> Optional[torch.Tensor]:
+    """One launch for a chunk: RoPE(q) -> q_out, RoPE(k) -> cache pages (+ per-block mean -> mean_k),
+    v -> cache pages.  Returns q_out (allocated when q is given and q_out is not)."""
+    _require_cuda(q, k, v, cos, sin, cache.k, cache.v, mean_k, q_out, status)
+    if k.dim() != 4 or v.shape != k.shape or k.dtype != v.dtype or k.dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError("k and v must be [B, Q, Hkv, D] of one 16-bit dtype")
+    B, Q, Hkv, D = k.shape
+    if cache.k.dtype != k.dtype or cache.k.shape[-1] != D:
+        raise ValueError("the cache must have the chunk's dtype and head dimension")
+    if cos.shape != sin.shape or cos.dim() != 3 or cos.shape[1] != Q or cos.shape[2] != D or cos.shape[0] not in (1, B):
+        raise ValueError("cos/sin must be [B or 1, Q, D] (the full head dimension is rotated)")
+    if cos.dtype != sin.dtype or cos.dtype not in (k.dtype, torch.float32):
+        raise ValueError("cos/sin must be fp32 or the tensors' dtype")
+    for t in (q, k, v, cos, sin, mean_k, q_out):
+        if t is not None and t.stride(-1) != 1:
+            raise ValueError("the last dimension must be contiguous")
+    p = _lib.RopeAppendParams()
+    Hq = 0
+    if q is not None:
+        if q.dim() != 4 or q.shape[0] != B or q.shape[1] != Q or q.shape[3] != D or q.dtype != k.dtype:
+            raise ValueError("q must be [B, Q, Hq, D] of the keys' dtype")
+        Hq = q.shape[2]
+        if q_out is None:
+            q_out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        if q_out.shape != q.shape or q_out.dtype != q.dtype:
+            raise ValueError("q_out must match q")
+        p.q, p.q_out = q.data_ptr(), q_out.data_ptr()
+        p.q_stride_b, p.q_stride_t, p.q_stride_h = q.stride(0), q.stride(1), q.stride(2)
+        p.qo_stride_b, p.qo_stride_t, p.qo_stride_h = q_out.stride(0), q_out.stride(1), q_out.stride(2)
+    p.k, p.v = k.data_ptr(), v.data_ptr()
+    p.k_stride_b, p.k_stride_t, p.k_stride_h = k.stride(0), k.stride(1), k.stride(2)
+    p.v_stride_b, p.v_stride_t, p.v_stride_h = v.stride(0), v.stride(1), v.stride(2)
+    p.cos, p.sin = cos.data_ptr(), sin.data_ptr()
+    if cos.stride() != sin.stride():
+        raise ValueError("cos and sin must share their strides")
+    p.cs_stride_b = 0 if cos.shape[0] == 1 else cos.stride(0)
+    p.cs_stride_t = cos.stride(1)
+    p.rope_dtype, p.dtype = _DTYPES[cos.dtype], _DTYPES[k.dtype]
+    p.cache = cache.to_c()
+    if mean_k is not None:
+        if mean_k.dim() != 4 or mean_k.shape[0] != B or mean_k.shape[2] != Hkv or mean_k.shape[3] != D or mean_k.dtype != k.dtype:
+            raise ValueError("mean_k must be [B, blocks, Hkv, D] of the keys' dtype")
+        if position % block_size or position // block_size + -(-Q // block_size) > mean_k.shape[1]:
+            raise ValueError("the chunk's blocks do not fit in mean_k at this position")
+        p.mean_k = mean_k.data_ptr()
+        p.mk_stride_b, p.mk_stride_blk, p.mk_stride_h = mean_k.stride(0), mean_k.stride(1), mean_k.stride(2)
+    p.B, p.Q, p.Hq, p.Hkv, p.D = B, Q, Hq, Hkv, D
+    p.position, p.block_size = int(position), block_size
+    p.status = _ptr(status)
+    _lib.check(_lib.load().ca_rope_append(C.byref(p), _stream()), "ca_rope_append")
+    return q_out
+
+
 def unpack_bits(bits: torch.Tensor, kv_blocks: int) -> torch.Tensor:
     """Packed keep bits [..., W] -> bool [..., Kb] (host-side helper for tests and statistics)."""
     shifts = torch.arange(32, device=bits.device, dtype=torch.int64)

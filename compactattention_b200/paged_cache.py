@@ -47,5 +47,20 @@ class PagedKVCache:
         self.length = max(self.length, pos + Q)
         return self.length
 
+    def append_rope(self, q: Optional[torch.Tensor], k_chunk: torch.Tensor, v_chunk: torch.Tensor, cos: torch.Tensor,
+                    sin: torch.Tensor, position: Optional[int] = None, mean_k: Optional[torch.Tensor] = None,
+                    block_size: int = 64, q_out: Optional[torch.Tensor] = None):
+        """Fused form of ``apply_rotary_pos_emb`` + ``append`` (+ mean-K pooling): pre-RoPE
+        ``q/k_chunk`` in, rotated queries out, rotated keys and the values written to the chunk's
+        pages in one launch.  Any token position is accepted (no page-boundary rule).  Returns
+        ``(q_rotated, new_length)``."""
+        pos = self.length if position is None else int(position)
+        Q = k_chunk.shape[1]
+        if pos + Q > self.pages_per_seq * self.page_size:
+            raise ValueError("chunk does not fit in the cache")
+        q_rot = ops.rope_append(q, k_chunk, v_chunk, cos, sin, self.view(), pos, mean_k=mean_k, block_size=block_size, q_out=q_out)
+        self.length = max(self.length, pos + Q)
+        return q_rot, self.length
+
     def view(self) -> ops.KvCacheView:
         return ops.KvCacheView.from_paged(self.k_pages, self.v_pages, self.page_table)

@@ -150,6 +150,28 @@ class _CompactAttnBase(nn.Module):
         kv_len = st.kv.append(key_states, value_states, position=pos)
         return st.kv.view(), kv_len, 0.0
 
+    def _do_rope_and_kv_cache_update(self, q_nope, k_nope, value_states, past_key_value, cos, sin, cache_position,
+                                     mean_k=None, block_size: int = 64):
+        """Default route of both modules: RoPE on q and k, the paged append and (for the training-free
+        selector) the mean-K pooling in ONE launch (``ops.rope_append``).  Returns
+        ``(q_rotated, KvCacheView, kv_len)``.  A subclass that overrides ``_do_kv_cache_update`` (the
+        reference's documented hook, which receives already rotated keys) is routed through that hook
+        with the separate torch RoPE instead."""
+        st = past_key_value.layer(self.layer_idx, self.num_key_value_heads, self.head_dim)
+        if type(self)._do_kv_cache_update is not _CompactAttnBase._do_kv_cache_update:
+            q, k = apply_rotary_pos_emb(q_nope, k_nope, cos, sin)
+            kv_view, kv_len, _ = self._do_kv_cache_update(k, value_states, past_key_value, sin, cos, cache_position,
+                                                          self.compactattn_debug)
+            if mean_k is not None:
+                ops.pool_blocks(k, block_size, ("avg",), out=mean_k, out_block_offset=(kv_len - k.shape[1]) // block_size)
+            return q, kv_view, kv_len
+        pos = st.kv.length  # chunks are appended in order; no device-to-host read of cache_position
+        if cache_position is not None and not torch.is_tensor(cache_position):
+            pos = int(cache_position[0])
+        q, kv_len = st.kv.append_rope(q_nope, k_nope, value_states, cos, sin, position=pos, mean_k=mean_k,
+                                      block_size=block_size)
+        return q, st.kv.view(), kv_len
+
     def _project(self, hidden_states):
         B, L, _ = hidden_states.shape
         q = self.q_proj(hidden_states).view(B, L, self.num_heads, self.head_dim)
@@ -216,9 +238,8 @@ class LlamaSeerAttentionChunkedDense(_CompactAttnBase):
         bs = self.config.seerattn_gate_block_size
         q_nope, k_nope, v = self._project(hidden_states)
         cos, sin = position_embeddings
-        q, k = apply_rotary_pos_emb(q_nope, k_nope, cos, sin)
         st = past_key_value.layer(self.layer_idx, self.num_key_value_heads, self.head_dim)
-        kv_view, kv_len, _ = self._do_kv_cache_update(k, v, past_key_value, sin, cos, cache_position, self.compactattn_debug)
+        q, kv_view, kv_len = self._do_rope_and_kv_cache_update(q_nope, k_nope, v, past_key_value, cos, sin, cache_position)
         # the gate sees pre-RoPE q/k pooled to blocks, with RoPE at block positions; its K-block cache
         # is appended for every chunk, also when the chunk itself runs dense
         if st.gate is None:
@@ -300,16 +321,16 @@ class LlamaFlashPrefillCompactAttnAttention(_CompactAttnBase):
         bs = cfg.seerattn_flashprefill_block_size
         q, k, v = self._project(hidden_states)
         cos, sin = position_embeddings
-        q, k = apply_rotary_pos_emb(q, k, cos, sin)
         st = past_key_value.layer(self.layer_idx, self.num_key_value_heads, self.head_dim)
-        kv_view, kv_len, _ = self._do_kv_cache_update(k, v, past_key_value, sin, cos, cache_position, self.compactattn_debug)
-        # mean-K cache of the post-RoPE keys, appended in place (the reference re-concatenates a list
-        # of parts every chunk, modeling_llama_flashprefill_compactattn.py:121-150)
+        # mean-K cache of the post-RoPE keys, appended in place by the same launch that rotates and
+        # stores the keys (the reference re-concatenates a list of parts every chunk,
+        # modeling_llama_flashprefill_compactattn.py:121-150)
         if st.mean_k is None:
             st.mean_k = MeanKSelectorState(hidden_states.shape[0], past_key_value.max_tokens // bs, self.num_key_value_heads,
                                            self.head_dim, bs, hidden_states.device, hidden_states.dtype)
-        ops.pool_blocks(k, bs, ("avg",), out=st.mean_k.mean_k, out_block_offset=st.mean_k.length)
-        st.mean_k.length += q_len // bs
+        q, kv_view, kv_len = self._do_rope_and_kv_cache_update(q, k, v, past_key_value, cos, sin, cache_position,
+                                                               mean_k=st.mean_k.mean_k, block_size=bs)
+        st.mean_k.length = kv_len // bs
         if kv_len > q_len and not cfg.seerattn_chunked_prefill_force_dense:
             attn, stats = flashprefill_compactattn_prefill_full_kv(
                 q, kv_view, kv_view, attention_mask, softmax_scale=self.scaling,

@@ -383,6 +383,54 @@ typedef struct ca_gather_params {
 
 int ca_gather_kv(const ca_gather_params* p, ca_stream_t stream);
 
+/*
+ * Chunk append: RoPE on the chunk's queries and keys, the keys and values written into the paged
+ * cache at token `position`, and (optionally) the mean of the rotated keys of every block appended
+ * to the training-free selector's mean-K cache.  One launch, every element read and written once.
+ * Replaces, for one chunk of one layer:
+ *   apply_rotary_pos_emb (compact_attn/modules/common.py:49-75; out = x*cos + rotate_half(x)*sin,
+ *     half-rotation, products and sum rounded separately as torch does, so the result is
+ *     bit-identical for 16-bit tables and for fp32 tables),
+ *   the KV cache update behind the _do_kv_cache_update hook
+ *     (compact_attn/prefill_sparse/llama/modeling_llama_seerattn_chunked_dense.py:518-536;
+ *     DynamicCache.update concatenates the whole layer cache, HeadsFirstDynamicCache adds a
+ *     permute, modeling_llama_seerattn_chunked_dense_hf.py:29-82), and
+ *   compute_mean_vector over the new keys plus the torch.cat of the mean-K parts
+ *     (compact_attn/prefill_sparse/llama/modeling_llama_flashprefill_compactattn.py:121-150).
+ * q/k/v are [B, Q, H, D] with element strides (D contiguous); q may be NULL (Hq = 0).  q_out may
+ * alias q.  cos/sin are [B or 1, Q, D] (cs_stride_b = 0 broadcasts one table), the full head
+ * dimension is rotated.  cache.k / cache.v are written (the struct's const is for the readers).
+ * mean_k is [B, blocks, Hkv, D] in the tensors' type; block `position / block_size + i` receives
+ * chunk block i; it needs position % block_size == 0.  All strides multiples of 8 elements, all
+ * pointers 16-byte aligned.  A page-table entry out of range skips that token and sets
+ * CA_STATUS_BAD_INDEX.
+ */
+typedef struct ca_rope_append_params {
+  const void* q;
+  void* q_out;
+  int64_t q_stride_b, q_stride_t, q_stride_h;
+  int64_t qo_stride_b, qo_stride_t, qo_stride_h;
+  const void* k;
+  int64_t k_stride_b, k_stride_t, k_stride_h;
+  const void* v;
+  int64_t v_stride_b, v_stride_t, v_stride_h;
+  const void* cos;
+  const void* sin;
+  int64_t cs_stride_b, cs_stride_t;
+  int32_t rope_dtype; /* CA_DTYPE_F32 or the tensors' dtype */
+  int32_t dtype;      /* CA_DTYPE_BF16 or CA_DTYPE_F16 */
+  ca_kv_layout cache;
+  void* mean_k; /* optional */
+  int64_t mk_stride_b, mk_stride_blk, mk_stride_h;
+  int32_t B, Q, Hq, Hkv, D;
+  int32_t position;   /* first token of the chunk in its sequence */
+  int32_t block_size; /* selector block (mean-K granularity, CTA tile) */
+  int32_t reserved;
+  int32_t* status; /* optional */
+} ca_rope_append_params;
+
+int ca_rope_append(const ca_rope_append_params* p, ca_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

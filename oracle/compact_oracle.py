@@ -53,6 +53,40 @@ def mean_pool_blocks(x: torch.Tensor, block_size: int) -> torch.Tensor:
     return (sums / cnt.view(1, nb, 1, 1)).to(x.dtype)
 
 
+def rotate_half(x: torch.Tensor) -> torch.Tensor:
+    """``[-x2, x1]`` over the two halves of the last dimension (compact_attn/modules/common.py:36-40)."""
+    h = x.shape[-1] // 2
+    return torch.cat((-x[..., h:], x[..., :h]), dim=-1)
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """``(x * cos) + (rotate_half(x) * sin)`` on ``[B, L, H, D]`` with ``cos/sin [B or 1, L, D]``, in the
+    operands' own dtypes exactly as the reference writes it (compact_attn/modules/common.py:49-75 with
+    ``unsqueeze_dim=2``); the result is cast back to x's dtype (a no-op for 16-bit tables)."""
+    c, s = cos.unsqueeze(2), sin.unsqueeze(2)
+    return ((x * c) + (rotate_half(x) * s)).to(x.dtype)
+
+
+def rope_append(q, k, v, cos, sin, k_pages, v_pages, page_table, position: int, block_size: int):
+    """What one chunk does to the per-layer state before attention: RoPE on q and k
+    (``apply_rope``), the rotated keys and the values written at tokens ``position ..`` of a paged
+    cache ``[pages, page_size, Hkv, D]`` through ``page_table [B, pages_per_seq]`` (the reference
+    appends to a contiguous cache, modeling_llama_seerattn_chunked_dense.py:518-536; the page table
+    only renames where a token lives), and the per-block mean of the rotated keys
+    (``mean_pool_blocks``).  Returns ``(q_rot, mean_k_chunk)`` and updates the page tensors in place."""
+    q_rot = apply_rope(q, cos, sin) if q is not None else None
+    k_rot = apply_rope(k, cos, sin)
+    B, Q = k.shape[0], k.shape[1]
+    page_size = k_pages.shape[1]
+    for b in range(B):
+        for t in range(Q):
+            tok = position + t
+            page = int(page_table[b, tok // page_size])
+            k_pages[page, tok % page_size] = k_rot[b, t]
+            v_pages[page, tok % page_size] = v[b, t]
+    return q_rot, mean_pool_blocks(k_rot, block_size)
+
+
 def flashprefill_block_score_raw(
     q: torch.Tensor, mean_k: torch.Tensor, key_len: int, block_size: int
 ) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -273,6 +273,24 @@ def group_gather_attention(ref) -> None:
          meta=np.array([B, Q, K, Hq, Hkv, D, bs]))
 
 
+def group_rope(ref) -> None:
+    """apply_rotary_pos_emb (compact_attn/modules/common.py:49-75) on [B, L, H, D] bf16 tensors with
+    bf16 tables (the dtype the model passes) and with fp32 tables (type promotion to fp32)."""
+    g = gen(8)
+    B, L, Hq, Hkv, D = 1, 96, 4, 2, 64
+    q = torch.randn((B, L, Hq, D), generator=g).to(torch.bfloat16)
+    k = torch.randn((B, L, Hkv, D), generator=g).to(torch.bfloat16)
+    inv = 1.0 / (500000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    ang = torch.arange(1000, 1000 + L, dtype=torch.float32)[:, None] * inv[None]
+    emb = torch.cat((ang, ang), dim=-1)
+    cos, sin = emb.cos()[None], emb.sin()[None]
+    q16, k16 = ref.common.apply_rotary_pos_emb(q, k, cos.to(torch.bfloat16), sin.to(torch.bfloat16), unsqueeze_dim=2)
+    q32, k32 = ref.common.apply_rotary_pos_emb(q, k, cos, sin, unsqueeze_dim=2)
+    assert q16.dtype == torch.bfloat16 and q32.dtype == torch.float32
+    save("rope", q=q, k=k, cos=cos, sin=sin, q_rot_bf16_tables=q16, k_rot_bf16_tables=k16,
+         q_rot_f32_tables=q32, k_rot_f32_tables=k32)
+
+
 def main() -> None:
     ref = reference_loader.load()
     torch.set_num_threads(max(1, os.cpu_count() or 1))
@@ -283,6 +301,7 @@ def main() -> None:
     group_topk(ref)
     group_block_mask(ref)
     group_gather_attention(ref)
+    group_rope(ref)
 
 
 if __name__ == "__main__":

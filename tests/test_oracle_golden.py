@@ -156,3 +156,17 @@ def test_cummass_rule_definition():
     # invalid entries never enter; an unreachable tau keeps every valid entry
     valid2 = torch.tensor([[[[True, True, False, True, True]]]])
     assert co.cummass_rows(p, valid2, 2.0).flatten().tolist() == [True, True, False, True, True]
+
+
+def test_rope_matches_reference(golden):
+    """apply_rope against the reference's apply_rotary_pos_emb, bit for bit, for 16-bit and fp32 tables."""
+    f = golden("rope")
+    q = torch.from_numpy(f["q"]).to(torch.bfloat16)
+    k = torch.from_numpy(f["k"]).to(torch.bfloat16)
+    cos, sin = torch.from_numpy(f["cos"]), torch.from_numpy(f["sin"])
+    c16, s16 = cos.to(torch.bfloat16), sin.to(torch.bfloat16)
+    assert torch.equal(co.apply_rope(q, c16, s16).float(), torch.from_numpy(f["q_rot_bf16_tables"]))
+    assert torch.equal(co.apply_rope(k, c16, s16).float(), torch.from_numpy(f["k_rot_bf16_tables"]))
+    # fp32 tables: the reference returns fp32; the cache stores it rounded to the tensors' type
+    assert torch.equal(co.apply_rope(q, cos, sin), torch.from_numpy(f["q_rot_f32_tables"]).to(torch.bfloat16))
+    assert torch.equal(co.apply_rope(k, cos, sin), torch.from_numpy(f["k_rot_f32_tables"]).to(torch.bfloat16))
