@@ -1075,12 +1075,25 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
     a.part_o = reinterpret_cast<float*>(ws + desc_bytes(grid) + ml_bytes(grid));
   }
 
-  // the opt-in shared-memory size is a per-device function attribute; setting it is cheap
+  // the opt-in shared-memory size is a per-device function attribute: set once per device and type
+  // (the call costs a few microseconds of host time, which short contexts notice)
+  {
+    static std::mutex mu;
+    static bool done[2][64] = {};
+    const int ti = p->dtype == CA_DTYPE_BF16 ? 0 : 1;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done[ti][dev.ordinal]) {
+      if (ti == 0) {
+        CA_CUDA(cudaFuncSetAttribute(attn_compact_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+      } else {
+        CA_CUDA(cudaFuncSetAttribute(attn_compact_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+      }
+      done[ti][dev.ordinal] = true;
+    }
+  }
   if (p->dtype == CA_DTYPE_BF16) {
-    CA_CUDA(cudaFuncSetAttribute(attn_compact_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     attn_compact_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(q_map, k_map, v_map, a);
   } else {
-    CA_CUDA(cudaFuncSetAttribute(attn_compact_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     attn_compact_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(q_map, k_map, v_map, a);
   }
   CA_LAUNCH_CHECK("attn_compact_kernel");

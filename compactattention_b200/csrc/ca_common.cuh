@@ -62,6 +62,7 @@ tensor_map_encode_fn get_tensor_map_encoder();
 
 // Device properties cached per device (SM count, opt-in shared memory).
 struct DeviceInfo {
+  int ordinal;  // CUDA device of the calling thread
   int sm_count;
   int smem_optin;
   int cc_major;

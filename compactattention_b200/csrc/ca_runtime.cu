@@ -40,6 +40,7 @@ int get_device_info(DeviceInfo* out) {
   std::lock_guard<std::mutex> lock(mu);
   if (!have[dev]) {
     DeviceInfo info;
+    info.ordinal = dev;
     CA_CUDA(cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, dev));
     CA_CUDA(cudaDeviceGetAttribute(&info.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
     CA_CUDA(cudaDeviceGetAttribute(&info.cc_major, cudaDevAttrComputeCapabilityMajor, dev));

@@ -20,7 +20,15 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """Handle of torch's current stream on the current device.  The raw accessor costs well under a
+    microsecond; ``torch.cuda.current_stream()`` builds a Stream object and costs ~12 us per call,
+    which was a third of a wrapper's host time."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 

@@ -1,12 +1,13 @@
 """Shape / density sweep of the attention and gather kernels on one GPU (single layer):
 
-    python -m compactattention_b200.sweep [--quick] [--positions]
+    python -m compactattention_b200.sweep [--quick] [--positions | --append]
 
 For every point: latency of ``ca_attn_compact`` over a synthetic block table with the exact density,
 effective TFLOP/s (algorithmic FLOPs / time) and its fraction of the cuBLAS bf16 peak, latency of the
 dense kernel of the same shape (speed-up), and the compact KV gather's HBM throughput (read + write
 bytes / time).  ``--positions`` walks all chunk positions of a 128K-token prefill (chunk 1024) at
-10 / 20 / 30 % density.  Prints one JSON line per point.
+10 / 20 / 30 % density.  ``--append`` times the chunk append (RoPE + paged write + mean-K pooling,
+``ca_rope_append``) against the three torch steps it replaces.  Prints one JSON line per point.
 """
 from __future__ import annotations
 
@@ -81,14 +82,62 @@ def point(hq, hkv, q_len, kv_len, density, dev, g, kv_cache, iters, with_dense, 
     return rec
 
 
+def append_points(dev, g, iters):
+    """ca_rope_append: HBM bytes = q, k, v read once and written once (+ tables, + mean-K).  The
+    inputs rotate over enough chunk-sized sets to exceed L2, and the destination walks through the
+    cache, so no launch finds its data in L2."""
+    from .paged_cache import PagedKVCache
+    from .prefill_sparse.llama.modeling_llama_compactattn import apply_rotary_pos_emb
+    hbm = peaks()[1]
+    for hq, hkv in ((32, 8), (28, 4)):
+        for q_len in (256, 1024, 2048, 8192):
+            max_tokens = 131072
+            set_bytes = 2 * q_len * (hq + 2 * hkv) * D
+            n_sets = max(2, -(-300 * 2 ** 20 // set_bytes))
+            cache = PagedKVCache(1, max_tokens, hkv, D, dev)
+            qs = torch.randn((n_sets, q_len, hq, D), device=dev, dtype=torch.bfloat16, generator=g)
+            ks = torch.randn((n_sets, q_len, hkv, D), device=dev, dtype=torch.bfloat16, generator=g)
+            vs = torch.randn((n_sets, q_len, hkv, D), device=dev, dtype=torch.bfloat16, generator=g)
+            cos = torch.rand((1, q_len, D), device=dev, generator=g).to(torch.bfloat16)
+            sin = torch.rand((1, q_len, D), device=dev, generator=g).to(torch.bfloat16)
+            mean_k = torch.empty((1, max_tokens // BS, hkv, D), device=dev, dtype=torch.bfloat16)
+            q_out = torch.empty_like(qs)
+            state = {"i": 0}
+
+            def step(fused):
+                i = state["i"]
+                state["i"] = i + 1
+                s_, pos = i % n_sets, (i * q_len) % (max_tokens - q_len + 1) // BS * BS
+                q, k, v = qs[s_: s_ + 1], ks[s_: s_ + 1], vs[s_: s_ + 1]
+                if fused:
+                    ops.rope_append(q, k, v, cos, sin, cache.view(), pos, mean_k=mean_k, block_size=BS, q_out=q_out[s_: s_ + 1])
+                else:
+                    _, kr = apply_rotary_pos_emb(q, k, cos, sin)
+                    cache.append(kr, v, position=pos)
+                    ops.pool_blocks(kr, BS, ("avg",), out=mean_k, out_block_offset=pos // BS)
+
+            n_it = max(iters, 2 * n_sets)
+            us = timed(lambda: step(True), n_it)
+            us_torch = timed(lambda: step(False), n_it)
+            nbytes = 2 * set_bytes + 2 * 2 * q_len * D + 2 * (q_len // BS) * hkv * D
+            rec = {"op": "rope_append", "hq": hq, "hkv": hkv, "chunk": q_len, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
+                   "frac_of_hbm_peak": round(nbytes / us / 1e3 / hbm, 3), "algorithmic_bytes": nbytes,
+                   "torch_rope_plus_append_plus_pool_us": round(us_torch, 2)}
+            print(json.dumps(rec), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true", help="a small subset of the grid")
     ap.add_argument("--positions", action="store_true", help="all chunk positions of a 128K prefill, chunk 1024")
+    ap.add_argument("--append", action="store_true", help="the chunk append kernel against its torch equivalent")
     ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
     dev = torch.device("cuda")
     g = torch.Generator(device=dev).manual_seed(1234 + 5)
+    if args.append:
+        append_points(dev, g, args.iters)
+        return
     max_kv = 131072 if (args.positions or args.quick) else 262144
     caches = {}
     for hkv in (8, 4):
