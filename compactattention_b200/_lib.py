@@ -224,6 +224,7 @@ _SIGNATURES = {
     "ca_last_error": (C.c_char_p, []),
     "ca_abi_version": (C.c_int, []),
     "ca_launch_count": (C.c_int64, []),
+    "ca_set_programmatic_launch": (C.c_int, [C.c_int]),
     "ca_attn_workspace_bytes": (C.c_int, [C.POINTER(AttnParams), C.POINTER(C.c_size_t)]),
     "ca_attn_compact": (C.c_int, [C.POINTER(AttnParams), C.c_void_p]),
     "ca_attn_compact_static_scratch": (C.c_int, [C.POINTER(AttnParams), C.c_void_p]),
@@ -274,6 +275,12 @@ def check(rc: int, what: str) -> None:
     if rc != CA_OK:
         msg = load().ca_last_error().decode("utf-8", "replace")
         raise RuntimeError(f"{what} failed (code {rc}): {msg}")
+
+
+def set_programmatic_launch(enabled: bool) -> bool:
+    """Turns programmatic dependent launch of the library's kernels on or off (on by default);
+    returns the previous setting."""
+    return bool(load().ca_set_programmatic_launch(1 if enabled else 0))
 
 
 def launch_count() -> int:

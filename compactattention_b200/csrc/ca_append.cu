@@ -122,6 +122,8 @@ __device__ __forceinline__ void rope8(Vec8& lo, Vec8& hi, const void* cos, const
 // 8-element group of the low half); it also handles the matching group of the high half.
 template <typename T, bool kF32>
 __global__ void __launch_bounds__(kThreads) rope_append_kernel(const Args a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   extern __shared__ float mk_smem[];  // [phases][D] partial sums of the rotated keys
   const int half = a.D / 2;
   const int groups = half / 8;               // threads per token row
@@ -242,11 +244,11 @@ extern "C" int ca_rope_append(const ca_rope_append_params* p, ca_stream_t stream
   CA_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "too many heads or batch entries for one launch");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (a.is_bf16) {
-    if (a.rope_f32) rope_append_kernel<__nv_bfloat16, true><<<grid, kThreads, smem, stream>>>(a);
-    else rope_append_kernel<__nv_bfloat16, false><<<grid, kThreads, smem, stream>>>(a);
+    if (a.rope_f32) launch_kernel(rope_append_kernel<__nv_bfloat16, true>, dim3(grid), dim3(kThreads), smem, stream, a);
+    else launch_kernel(rope_append_kernel<__nv_bfloat16, false>, dim3(grid), dim3(kThreads), smem, stream, a);
   } else {
-    if (a.rope_f32) rope_append_kernel<__half, true><<<grid, kThreads, smem, stream>>>(a);
-    else rope_append_kernel<__half, false><<<grid, kThreads, smem, stream>>>(a);
+    if (a.rope_f32) launch_kernel(rope_append_kernel<__half, true>, dim3(grid), dim3(kThreads), smem, stream, a);
+    else launch_kernel(rope_append_kernel<__half, false>, dim3(grid), dim3(kThreads), smem, stream, a);
   }
   CA_LAUNCH_CHECK("rope_append_kernel");
   return CA_OK;

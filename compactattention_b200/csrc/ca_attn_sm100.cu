@@ -45,6 +45,7 @@ constexpr int kTmemCols = 512;
 constexpr int kMaxRows = 1024;  // (batch x kv heads) rows per launch
 constexpr int kMaxSegs = 64;    // segments planned per batch
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; lazy accumulator rescale
+constexpr int kMinSpanSteps = 8;           // shortest span worth a CTA of its own when units are cut
 // Measured on B200 (sustained 300-launch loop, 128K context, 20 % density): handing P to the MMA warp
 // in two halves 434 us, in one piece 450 us; packed fp32 pairs for the scale and the row sum 421 us;
 // a polynomial exp2 on the FMA pipe (packed, 2 to 8 of every 16 pairs) 432 to 464 us.  The tensor
@@ -305,22 +306,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint64_t limit = a.wait_limit_ns;
   bool bad_index = false;
 
-  // ---- per-row KV-step totals and their prefix (every CTA; a few thousand integer operations) ----
-  for (int r = tid; r < R; r += kThreads) {
-    int count = a.past_blocks;
-    if (a.block_idx != nullptr) {
-      count = a.counts[r];
-      const int cap = a.block_idx_stride < a.past_blocks ? a.block_idx_stride : a.past_blocks;
-      if (count < 0 || count > cap) {
-        bad_index = true;
-        count = count < 0 ? 0 : cap;
-      }
-    }
-    sh->row_count[r] = count;
-    long long tot = 0;
-    for (int p = 0; p < a.n_pairs; ++p) tot += unit_iters(a, count, p);
-    sh->row_prefix[r + 1] = tot;  // turned into a prefix below
-  }
+  // ---- on-chip set-up first: it needs nothing from global memory, so under a programmatic
+  // dependent launch it overlaps the tail of the previous kernel (the table builder) ----
+  ptx::grid_launch_dependents();
   if (tid == 0) {
     sh->row_prefix[0] = 0;
     sh->abort_flag = 0;
@@ -342,30 +330,62 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::mbar_init(ptx::smem_u32(&sh->drain), 1);
     ptx::mbar_fence_init();
     ptx::fence_proxy_async_smem();
-    if (a.descs) {
-      SegDesc none;
-      none.unit = -1, none.j0 = 0, none.j1 = 0, none.n_iter = 0;
-      a.descs[2 * blockIdx.x] = none;
-      a.descs[2 * blockIdx.x + 1] = none;
-    }
   }
   if (warp == 8) {
     ptx::tmem_alloc(ptx::smem_u32(&sh->tmem_base), kTmemCols);
     ptx::tmem_relinquish();
   }
+  if (warp == 9 && lane == 0) {
+    ptx::tma_prefetch_desc(&q_map);
+    ptx::tma_prefetch_desc(&k_map);
+    ptx::tma_prefetch_desc(&v_map);
+  }
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
+
+  // ---- per-row KV-step totals and their prefix (every CTA; a few thousand integer operations) ----
+  for (int r = tid; r < R; r += kThreads) {
+    int count = a.past_blocks;
+    if (a.block_idx != nullptr) {
+      count = a.counts[r];
+      const int cap = a.block_idx_stride < a.past_blocks ? a.block_idx_stride : a.past_blocks;
+      if (count < 0 || count > cap) {
+        bad_index = true;
+        count = count < 0 ? 0 : cap;
+      }
+    }
+    sh->row_count[r] = count;
+    long long tot = 0;
+    for (int p = 0; p < a.n_pairs; ++p) tot += unit_iters(a, count, p);
+    sh->row_prefix[r + 1] = tot;  // turned into a prefix below
+  }
+  if (tid == 0 && a.descs) {
+    SegDesc none;
+    none.unit = -1, none.j0 = 0, none.j1 = 0, none.n_iter = 0;
+    a.descs[2 * blockIdx.x] = none;
+    a.descs[2 * blockIdx.x + 1] = none;
+  }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
-
   long long span_begin = 0, span_end = 0;
   if (tid == 0) {
     for (int r = 0; r < R; ++r) sh->row_prefix[r + 1] += sh->row_prefix[r];
     const long long total = sh->row_prefix[R];
-    const long long nc = gridDim.x, c = blockIdx.x;
+    long long nc = gridDim.x;
+    const long long c = blockIdx.x;
     if (a.split) {
-      span_begin = total * c / nc;
-      span_end = total * (c + 1) / nc;
+      // A span costs a prologue, an epilogue and (when it cuts a unit) 128 KB of partials, about
+      // as much as kMinSpanSteps KV steps: with little work, fewer CTAs take longer spans and the
+      // others leave at once.
+      const long long nu = static_cast<long long>(R) * a.n_pairs;
+      const long long by_work = total / kMinSpanSteps;
+      const long long cap = by_work > nu ? by_work : nu;
+      if (cap < nc) nc = cap;
+      if (c < nc) {
+        span_begin = total * c / nc;
+        span_end = total * (c + 1) / nc;
+      }
     } else {
       // whole units only: equal unit counts per CTA
       const long long nu = static_cast<long long>(R) * a.n_pairs;
@@ -803,6 +823,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 // is complete.  Thread = tile row.
 template <typename T>
 __global__ void __launch_bounds__(kTileM) attn_combine_kernel(const KernelArgs a, int n_slots) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   const int slot = blockIdx.x, tile = blockIdx.y, r = threadIdx.x;
   const SegDesc first = a.descs[slot];
   if (first.unit < 0 || first.j0 != 0) return;
@@ -1092,16 +1114,16 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
     }
   }
   if (p->dtype == CA_DTYPE_BF16) {
-    attn_compact_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(q_map, k_map, v_map, a);
+    launch_kernel(attn_compact_kernel<__nv_bfloat16>, dim3(grid), dim3(kThreads), kSmemBytes, stream, q_map, k_map, v_map, a);
   } else {
-    attn_compact_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(q_map, k_map, v_map, a);
+    launch_kernel(attn_compact_kernel<__half>, dim3(grid), dim3(kThreads), kSmemBytes, stream, q_map, k_map, v_map, a);
   }
   CA_LAUNCH_CHECK("attn_compact_kernel");
   if (a.split) {
     if (p->dtype == CA_DTYPE_BF16) {
-      attn_combine_kernel<__nv_bfloat16><<<dim3(2 * grid, 2), kTileM, 0, stream>>>(a, 2 * grid);
+      launch_kernel(attn_combine_kernel<__nv_bfloat16>, dim3(2 * grid, 2), dim3(kTileM), 0, stream, a, 2 * grid);
     } else {
-      attn_combine_kernel<__half><<<dim3(2 * grid, 2), kTileM, 0, stream>>>(a, 2 * grid);
+      launch_kernel(attn_combine_kernel<__half>, dim3(2 * grid, 2), dim3(kTileM), 0, stream, a, 2 * grid);
     }
     CA_LAUNCH_CHECK("attn_combine_kernel");
   }

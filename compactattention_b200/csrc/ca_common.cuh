@@ -52,6 +52,28 @@ inline int fail(int code, const char* fmt, ...) {
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// Programmatic dependent launch: every kernel of the library may be enqueued so that its CTAs
+// become resident and run their prologue while the previous kernel in the stream drains; each
+// kernel executes griddepcontrol.wait before its first global-memory access, which holds it until
+// the previous kernel has completed and its writes are visible (a no-op for a plain launch).
+std::atomic<int>& programmatic_launch_flag();
+
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (programmatic_launch_flag().load(std::memory_order_relaxed) != 0) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // Resolves cuTensorMapEncodeTiled through the runtime so the library has no link-time
 // dependency on libcuda (it must load on machines without a driver).
 typedef CUresult (*tensor_map_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -73,6 +95,12 @@ int get_device_info(DeviceInfo* out);
 #ifdef __CUDACC__
 // ---------------------------------------------------------------- device side --------------
 namespace ptx {
+
+// Lets the next kernel in the stream (if it was launched as a programmatic dependent) start its
+// CTAs once every CTA of this grid has got here; it still waits for this grid to finish.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Holds until the previous kernel in the stream has completed and flushed (no-op for a plain launch).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -46,6 +46,8 @@ struct Shared {
 
 __global__ void __launch_bounds__(kThreads, 1)
     fp_score_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map, const Args a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
@@ -282,7 +284,7 @@ int launch_fp_score_sm100(const ca_flashprefill_score_params* p, cudaStream_t st
   a.wait_limit_ns = 2000000000ull;
   a.status = nullptr;
   CA_CUDA(cudaFuncSetAttribute(fp_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  fp_score_kernel<<<dim3(a.Qb, p->Hkv, p->B), kThreads, smem, stream>>>(q_map, k_map, a);
+  launch_kernel(fp_score_kernel, dim3(a.Qb, p->Hkv, p->B), dim3(kThreads), smem, stream, q_map, k_map, a);
   CA_LAUNCH_CHECK("fp_score_kernel");
   return CA_OK;
 }

@@ -32,6 +32,8 @@ struct Args {
 };
 
 __global__ void __launch_bounds__(kThreads) gather_kv_kernel(const Args a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   __shared__ int prefix[kMaxRows + 1];  // exclusive prefix of sub-block items per row
   __shared__ int warp_sums[kThreads / 32];
   // prefix over rows (R <= kMaxRows), recomputed by every CTA: a few hundred integer adds
@@ -171,7 +173,7 @@ int ca_gather_kv(const ca_gather_params* p, ca_stream_t stream_) {
   a.status = p->status;
   // persistent grid: a multiple of the SM count, 8 CTAs of 256 threads per SM
   const int grid = dev.sm_count * 8;
-  gather_kv_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream_)>>>(a);
+  launch_kernel(gather_kv_kernel, dim3(grid), dim3(kThreads), 0, static_cast<cudaStream_t>(stream_), a);
   CA_LAUNCH_CHECK("gather_kv_kernel");
   return CA_OK;
 }

@@ -11,6 +11,11 @@ char* last_error_buffer() {
   return buf;
 }
 
+std::atomic<int>& programmatic_launch_flag() {
+  static std::atomic<int> flag{1};
+  return flag;
+}
+
 std::atomic<long long>& launch_counter() {
   static std::atomic<long long> counter{0};
   return counter;
@@ -59,6 +64,10 @@ extern "C" {
 const char* ca_last_error(void) { return ca::last_error_buffer(); }
 
 int ca_abi_version(void) { return 1; }
+
+int ca_set_programmatic_launch(int enabled) {
+  return ca::programmatic_launch_flag().exchange(enabled != 0 ? 1 : 0, std::memory_order_relaxed);
+}
 
 int64_t ca_launch_count(void) { return ca::launch_counter().load(std::memory_order_relaxed); }
 

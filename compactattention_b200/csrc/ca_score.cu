@@ -86,6 +86,8 @@ struct PoolArgs {
 constexpr int kPoolThreads = 128;
 
 __global__ void __launch_bounds__(kPoolThreads) pool_blocks_kernel(const PoolArgs a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   // thread = (token phase, 8-dim group); D/8 groups, kPoolThreads/(D/8) phases
   extern __shared__ float pool_smem[];  // [3][phases][D]
   const int groups = a.D / 8;
@@ -152,6 +154,8 @@ constexpr int kProjSlices = 4;  // the Cin reduction is split over this many thr
 // blockDim = (min(Cout,128), kProjSlices).  Weight loads are issued eight at a time so their
 // latencies overlap; slice partial sums meet in shared memory.
 __global__ void __launch_bounds__(128 * kProjSlices) proj_rope_kernel(const ProjArgs a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   extern __shared__ float proj_smem[];  // x tile [kProjBlocks][Cin], partials [kProjSlices][kProjBlocks][Cout]
   float* xs = proj_smem;
   float* ys = proj_smem + kProjBlocks * a.Cin;
@@ -256,6 +260,8 @@ __device__ __forceinline__ void widen8(const uint4& raw, float (&v)[8]) {
 // overlap, then widened to f32.
 template <int KDT>
 __global__ void __launch_bounds__(kGateThreads) gate_scores_kernel(const GateArgs a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   extern __shared__ float gate_smem[];  // q rows [Qb][C]
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (a.Hq / a.Hk);
@@ -352,6 +358,8 @@ __device__ __forceinline__ void load_k32(const void* base, long long off, float 
 
 template <int KDT>
 __global__ void __launch_bounds__(kGateThreads) gate_scores2_kernel(const GateArgs a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   extern __shared__ float gate_smem[];  // q rows [ceil16(Qb)][C], zero padded
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (a.Hq / a.Hk);
@@ -429,6 +437,8 @@ constexpr int kFpThreads = 256;
 constexpr int kFpTile = 64;  // tokens per pass and key blocks per CTA
 
 __global__ void __launch_bounds__(kFpThreads) flashprefill_score_kernel(const FpScoreArgs a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   // shared: key tile [64][D+1], query tile [64][D+1], S tile [64][65]
   extern __shared__ float fp_smem[];
   const int ld = a.D + 1;
@@ -515,6 +525,8 @@ __global__ void __launch_bounds__(kFpThreads) flashprefill_score_kernel(const Fp
 //   w_j = 2^(max_j - max_j' max), out_j = score_j * w_j / (sum_j score_j * w_j + 1e-9); 0 where max = -inf.
 __global__ void __launch_bounds__(256) flashprefill_normalize_kernel(const float* score, const float* mx, float* out,
                                                                      int Kb, int Hq) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   // one CTA per (b, i); thread -> head tid % Hq, key phase tid / Hq
   extern __shared__ float nz_smem[];  // [phases][Hq]
   const long long base = static_cast<long long>(blockIdx.x) * Kb * Hq;
@@ -580,6 +592,8 @@ constexpr int kPrepThreads = 128;
 
 template <int XDT, int WDT>
 __global__ void __launch_bounds__(kPrepThreads) gate_prepare_kernel(const PrepArgs a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   extern __shared__ float prep_smem[];  // partials [3][phases][D], pooled [3*D], y [C]
   const bool is_q = static_cast<int>(blockIdx.y) < a.q.Hw;
   const PrepSide& sd = is_q ? a.q : a.k;
@@ -726,7 +740,7 @@ int ca_pool_blocks(const ca_pool_params* p, ca_stream_t stream_) {
   const int nb = ceil_div(p->L, p->block_size);
   const int phases = kPoolThreads / (p->D / 8);
   const size_t smem = static_cast<size_t>(3) * phases * p->D * sizeof(float);
-  pool_blocks_kernel<<<dim3(nb, p->B * p->H), kPoolThreads, smem, static_cast<cudaStream_t>(stream_)>>>(a);
+  launch_kernel(pool_blocks_kernel, dim3(nb, p->B * p->H), dim3(kPoolThreads), smem, static_cast<cudaStream_t>(stream_), a);
   CA_LAUNCH_CHECK("pool_blocks_kernel");
   return CA_OK;
 }
@@ -774,7 +788,7 @@ int ca_gate_prepare(const ca_gate_prepare_params* p, ca_stream_t stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 #define CA_PREP_CASE(XD, WD)                                                            \
   if (p->q.x_dtype == XD && wdt == WD) {                                                \
-    gate_prepare_kernel<XD, WD><<<grid, kPrepThreads, smem, stream>>>(a);               \
+    launch_kernel(gate_prepare_kernel<XD, WD>, dim3(grid), dim3(kPrepThreads), smem, stream, a);               \
   } else
   CA_PREP_CASE(CA_DTYPE_BF16, CA_DTYPE_BF16)
   CA_PREP_CASE(CA_DTYPE_BF16, CA_DTYPE_F32)
@@ -811,7 +825,7 @@ int ca_gate_project(const ca_project_params* p, ca_stream_t stream_) {
   const size_t smem = static_cast<size_t>(kProjBlocks) * (p->Cin + kProjSlices * p->Cout) * sizeof(float);
   CA_REQUIRE(smem <= 48 * 1024, "Cin + Cout too large");
   const dim3 threads(p->Cout >= 128 ? 128 : (p->Cout >= 64 ? 64 : 32), kProjSlices);
-  proj_rope_kernel<<<dim3(ceil_div(p->nb, kProjBlocks), p->Hout, p->B), threads, smem, static_cast<cudaStream_t>(stream_)>>>(a);
+  launch_kernel(proj_rope_kernel, dim3(ceil_div(p->nb, kProjBlocks), p->Hout, p->B), dim3(threads), smem, static_cast<cudaStream_t>(stream_), a);
   CA_LAUNCH_CHECK("proj_rope_kernel");
   return CA_OK;
 }
@@ -846,13 +860,13 @@ int ca_gate_scores(const ca_gate_score_params* p, ca_stream_t stream_) {
     const dim3 grid2(ceil_div(p->Kb, 2 * kGateThreads), p->Hq, p->B);
     if (p->k_dtype == CA_DTYPE_BF16) {
       if (smem2 > 48 * 1024) CA_CUDA(cudaFuncSetAttribute(gate_scores2_kernel<CA_DTYPE_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
-      gate_scores2_kernel<CA_DTYPE_BF16><<<grid2, kGateThreads, smem2, stream>>>(a);
+      launch_kernel(gate_scores2_kernel<CA_DTYPE_BF16>, dim3(grid2), dim3(kGateThreads), smem2, stream, a);
     } else if (p->k_dtype == CA_DTYPE_F16) {
       if (smem2 > 48 * 1024) CA_CUDA(cudaFuncSetAttribute(gate_scores2_kernel<CA_DTYPE_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
-      gate_scores2_kernel<CA_DTYPE_F16><<<grid2, kGateThreads, smem2, stream>>>(a);
+      launch_kernel(gate_scores2_kernel<CA_DTYPE_F16>, dim3(grid2), dim3(kGateThreads), smem2, stream, a);
     } else {
       if (smem2 > 48 * 1024) CA_CUDA(cudaFuncSetAttribute(gate_scores2_kernel<CA_DTYPE_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
-      gate_scores2_kernel<CA_DTYPE_F32><<<grid2, kGateThreads, smem2, stream>>>(a);
+      launch_kernel(gate_scores2_kernel<CA_DTYPE_F32>, dim3(grid2), dim3(kGateThreads), smem2, stream, a);
     }
     CA_LAUNCH_CHECK("gate_scores2_kernel");
     return CA_OK;
@@ -860,13 +874,13 @@ int ca_gate_scores(const ca_gate_score_params* p, ca_stream_t stream_) {
   const dim3 grid(ceil_div(p->Kb, kGateThreads), p->Hq, p->B);
   if (p->k_dtype == CA_DTYPE_BF16) {
     if (smem > 48 * 1024) CA_CUDA(cudaFuncSetAttribute(gate_scores_kernel<CA_DTYPE_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    gate_scores_kernel<CA_DTYPE_BF16><<<grid, kGateThreads, smem, stream>>>(a);
+    launch_kernel(gate_scores_kernel<CA_DTYPE_BF16>, dim3(grid), dim3(kGateThreads), smem, stream, a);
   } else if (p->k_dtype == CA_DTYPE_F16) {
     if (smem > 48 * 1024) CA_CUDA(cudaFuncSetAttribute(gate_scores_kernel<CA_DTYPE_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    gate_scores_kernel<CA_DTYPE_F16><<<grid, kGateThreads, smem, stream>>>(a);
+    launch_kernel(gate_scores_kernel<CA_DTYPE_F16>, dim3(grid), dim3(kGateThreads), smem, stream, a);
   } else {
     if (smem > 48 * 1024) CA_CUDA(cudaFuncSetAttribute(gate_scores_kernel<CA_DTYPE_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    gate_scores_kernel<CA_DTYPE_F32><<<grid, kGateThreads, smem, stream>>>(a);
+    launch_kernel(gate_scores_kernel<CA_DTYPE_F32>, dim3(grid), dim3(kGateThreads), smem, stream, a);
   }
   CA_LAUNCH_CHECK("gate_scores_kernel");
   return CA_OK;
@@ -898,13 +912,13 @@ int ca_flashprefill_score(const ca_flashprefill_score_params* p, ca_stream_t str
   if (rc_tc == CA_ERR_UNSUPPORTED) {
     const size_t smem = (static_cast<size_t>(2) * kFpTile * (p->D + 1) + kFpTile * (kFpTile + 1)) * sizeof(float);
     CA_CUDA(cudaFuncSetAttribute(flashprefill_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    flashprefill_score_kernel<<<dim3(ceil_div(p->Kb, kFpTile), a.Qb, p->B * p->Hq), kFpThreads, smem, stream>>>(a);
+    launch_kernel(flashprefill_score_kernel, dim3(ceil_div(p->Kb, kFpTile), a.Qb, p->B * p->Hq), dim3(kFpThreads), smem, stream, a);
     CA_LAUNCH_CHECK("flashprefill_score_kernel");
   }
   if (p->score_norm) {
     const int threads = 256;
     const size_t nsmem = static_cast<size_t>(threads / p->Hq) * p->Hq * sizeof(float);
-    flashprefill_normalize_kernel<<<p->B * a.Qb, threads, nsmem, stream>>>(p->score_raw, p->max_raw, p->score_norm, p->Kb, p->Hq);
+    launch_kernel(flashprefill_normalize_kernel, dim3(p->B * a.Qb), dim3(threads), nsmem, stream, p->score_raw, p->max_raw, p->score_norm, p->Kb, p->Hq);
     CA_LAUNCH_CHECK("flashprefill_normalize_kernel");
   }
   return CA_OK;

@@ -190,6 +190,8 @@ __device__ void bitonic_sort(unsigned long long* comp, int n2) {
 }
 
 __global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   extern __shared__ unsigned char dyn_smem[];
   float* s = reinterpret_cast<float*>(dyn_smem);                    // [Kb]
   uint8_t* keep = reinterpret_cast<uint8_t*>(s + a.Kb);              // [Kb]
@@ -352,6 +354,8 @@ struct UnionArgs {
 };
 
 __global__ void __launch_bounds__(kRowThreads) union_table_kernel(const UnionArgs a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   __shared__ int warp_sums[kRowThreads / 32];
   __shared__ int sh_total;
   const int row = blockIdx.x;
@@ -425,6 +429,8 @@ __global__ void __launch_bounds__(kRowThreads) union_table_kernel(const UnionArg
 __global__ void __launch_bounds__(kRowThreads) paged_metadata_kernel(const int32_t* pages_per_row, int R,
                                                                      int32_t* page_offsets, int32_t* block_table,
                                                                      int max_pages) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   __shared__ int warp_sums[kRowThreads / 32];
   __shared__ int sh_total;
   int running = 0;
@@ -491,7 +497,7 @@ int ca_select_rows(const ca_select_params* p, ca_stream_t stream_) {
   if (smem > 48 * 1024) {
     CA_CUDA(cudaFuncSetAttribute(select_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   }
-  select_rows_kernel<<<p->B * p->H * p->Qb, kRowThreads, smem, static_cast<cudaStream_t>(stream_)>>>(a);
+  launch_kernel(select_rows_kernel, dim3(p->B * p->H * p->Qb), dim3(kRowThreads), smem, static_cast<cudaStream_t>(stream_), a);
   CA_LAUNCH_CHECK("select_rows_kernel");
   return CA_OK;
 }
@@ -519,7 +525,7 @@ int ca_union_table(const ca_union_params* p, ca_stream_t stream_) {
   a.block_idx = p->block_idx, a.idx_stride = p->idx_stride, a.counts = p->counts;
   a.cache_seqlens = p->cache_seqlens, a.pages_per_row = p->pages_per_row;
   a.keep_kv = static_cast<uint8_t*>(p->keep_kv);
-  union_table_kernel<<<p->B * p->Hkv, kRowThreads, 0, static_cast<cudaStream_t>(stream_)>>>(a);
+  launch_kernel(union_table_kernel, dim3(p->B * p->Hkv), dim3(kRowThreads), 0, static_cast<cudaStream_t>(stream_), a);
   CA_LAUNCH_CHECK("union_table_kernel");
   return CA_OK;
 }
@@ -531,7 +537,7 @@ int ca_paged_metadata(const int32_t* pages_per_row, int rows, int32_t* page_offs
   CA_REQUIRE(pages_per_row && page_offsets, "pages_per_row and page_offsets must be non-null");
   CA_REQUIRE(rows > 0, "rows must be positive");
   CA_REQUIRE(block_table == nullptr || max_pages > 0, "max_pages must be positive with a block_table");
-  paged_metadata_kernel<<<1, kRowThreads, 0, static_cast<cudaStream_t>(stream_)>>>(pages_per_row, rows, page_offsets,
+  launch_kernel(paged_metadata_kernel, dim3(1), dim3(kRowThreads), 0, static_cast<cudaStream_t>(stream_), pages_per_row, rows, page_offsets,
                                                                                     block_table, max_pages);
   CA_LAUNCH_CHECK("paged_metadata_kernel");
   return CA_OK;
