@@ -57,8 +57,8 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=1234 + 3)
     ap.add_argument("--no-dense", action="store_true", help="skip the dense comparator")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--plain-launch", action="store_true",
-                    help="enqueue plain launches instead of programmatic dependent launches (for A/B timing)")
+    ap.add_argument("--dependent-launch", action="store_true",
+                    help="enqueue programmatic dependent launches instead of plain ones (for A/B timing)")
     return ap.parse_args()
 
 
@@ -162,7 +162,7 @@ def block_rope_tables(n_blocks, block_size, device):
 
 def run_native(args):
     from compactattention_b200 import _lib, ops
-    _lib.set_programmatic_launch(not args.plain_launch)
+    _lib.set_programmatic_launch(args.dependent_launch)
     from compactattention_b200.chunk_driver import GateSelectorState, SelectionRule, select_and_attend
     from compactattention_b200.paged_cache import PagedKVCache
     from compactattention_b200.prefill_sparse.attn_gate import ATTNGATE_CLASSES
@@ -365,7 +365,7 @@ def run_native(args):
             "parallelism": f"tp{world} (KV-head sharded)" if world > 1 else "single GPU",
             "l2": f"steps rotate over {len(layers)} layer states ({len(layers) * 2 * K * hkv * D * 2 / 2**30:.1f} GiB of KV), more than L2",
             "launches_per_step": launches / args.steps,
-            "programmatic_dependent_launch": not args.plain_launch,
+            "programmatic_dependent_launch": args.dependent_launch,
             "dense_same_shape_us": None if dense_us is None else round(dense_us, 1),
             "speedup_vs_dense": None if dense_us is None else round(dense_us / value_us, 2),
             "attention_effective_tflops": round(achieved, 1),

@@ -278,7 +278,7 @@ def check(rc: int, what: str) -> None:
 
 
 def set_programmatic_launch(enabled: bool) -> bool:
-    """Turns programmatic dependent launch of the library's kernels on or off (on by default);
+    """Turns programmatic dependent launch of the library's kernels on or off (off by default);
     returns the previous setting."""
     return bool(load().ca_set_programmatic_launch(1 if enabled else 0))
 

@@ -46,6 +46,7 @@ constexpr int kMaxRows = 1024;  // (batch x kv heads) rows per launch
 constexpr int kMaxSegs = 64;    // segments planned per batch
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; lazy accumulator rescale
 constexpr int kMinSpanSteps = 8;           // shortest span worth a CTA of its own when units are cut
+constexpr int kMinUnitStepsToCut = 24;     // average KV steps per unit below which units stay whole
 // Measured on B200 (sustained 300-launch loop, 128K context, 20 % density): handing P to the MMA warp
 // in two halves 434 us, in one piece 450 us; packed fp32 pairs for the scale and the row sum 421 us;
 // a polynomial exp2 on the FMA pipe (packed, 2 to 8 of every 16 pairs) 432 to 464 us.  The tensor
@@ -374,13 +375,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     const long long total = sh->row_prefix[R];
     long long nc = gridDim.x;
     const long long c = blockIdx.x;
-    if (a.split) {
+    const long long n_units_all = static_cast<long long>(R) * a.n_pairs;
+    // Cutting units pays only when a unit is long: measured on B200, units of ~6 KV steps ran 2x
+    // slower cut (partials + the merge) than whole (45 vs 22 us), units of ~50 steps 20 % faster.
+    const bool cut = a.split && total >= n_units_all * kMinUnitStepsToCut;
+    if (cut) {
       // A span costs a prologue, an epilogue and (when it cuts a unit) 128 KB of partials, about
       // as much as kMinSpanSteps KV steps: with little work, fewer CTAs take longer spans and the
       // others leave at once.
-      const long long nu = static_cast<long long>(R) * a.n_pairs;
       const long long by_work = total / kMinSpanSteps;
-      const long long cap = by_work > nu ? by_work : nu;
+      const long long cap = by_work > n_units_all ? by_work : n_units_all;
       if (cap < nc) nc = cap;
       if (c < nc) {
         span_begin = total * c / nc;

@@ -12,7 +12,7 @@ char* last_error_buffer() {
 }
 
 std::atomic<int>& programmatic_launch_flag() {
-  static std::atomic<int> flag{1};
+  static std::atomic<int> flag{0};
   return flag;
 }
 

@@ -165,3 +165,31 @@ def test_edge_shapes(ops):
         want = co.compact_attention(q, k, v, idx, counts, 64)
         err = (out.float().cpu() - want).abs()
         assert int(status.item()) == 0 and err.max().item() < 2e-2 and err.mean().item() < 2e-3, (B, Q, K, Hq, Hkv)
+
+
+def test_programmatic_launch_does_not_change_results(ops):
+    """The same selection + attention chain with dependent launches and with plain launches: every
+    kernel waits for its predecessor before touching global memory, so outputs are bit-identical."""
+    from compactattention_b200 import _lib
+    g = torch.Generator().manual_seed(99)
+    Q, K, Hq, Hkv, D, bs = 512, 16384, 16, 4, 128, 64
+    Pb, Kb = (K - Q) // bs, K // bs
+    q = torch.randn((1, Q, Hq, D), generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn((1, K, Hkv, D), generator=g).to(torch.bfloat16).cuda()
+    v = torch.randn((1, K, Hkv, D), generator=g).to(torch.bfloat16).cuda()
+    score = torch.randn((1, Hq, Q // bs, Kb), generator=g).cuda()
+    kv = ops.KvCacheView.from_seq_first(k, v)
+    results = []
+    try:
+        for on in (True, False):
+            _lib.set_programmatic_launch(on)
+            for _ in range(3):   # back-to-back chains, so launches do overlap when allowed
+                bits = ops.select_rows(score, Pb, "topk", topk_ratio=(1, 5), sink=1, local=2)
+                table = ops.union_table(bits=bits, num_kv_heads=Hkv, kv_blocks=Kb, past_blocks=Pb, block_size=bs)
+                out = ops.attn_compact(q, kv, K, Hkv, table.block_idx, table.counts, use_workspace=False)
+            torch.cuda.synchronize()
+            results.append((bits.clone(), table.block_idx.clone(), table.counts.clone(), out.clone()))
+    finally:
+        _lib.set_programmatic_launch(False)
+    for a, b in zip(*results):
+        assert torch.equal(a, b)

@@ -89,3 +89,13 @@ def test_ops_refuse_cpu_tensors():
 
     with pytest.raises(ValueError, match="CUDA tensors only"):
         ops.union_table(mask=torch.zeros((1, 4, 8), dtype=torch.bool), num_kv_heads=1, kv_blocks=8, past_blocks=4)
+
+
+def test_programmatic_launch_toggle_is_host_state_only():
+    """The launch-mode switch is a process-wide flag; flipping it needs no device."""
+    from compactattention_b200 import _lib
+
+    was = _lib.set_programmatic_launch(True)
+    assert was is False           # plain launches by default
+    assert _lib.set_programmatic_launch(False) is True
+    assert _lib.set_programmatic_launch(False) is False
