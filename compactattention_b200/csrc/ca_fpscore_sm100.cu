@@ -10,13 +10,18 @@
 // one CTA handles (batch, kv head, q-block), loads the q-block's tokens of all G heads once, and
 // walks the visible key-block tiles with a 2-stage TMA ring and a double-buffered TMEM accumulator
 // (2 x 256 columns), so the MMAs of the next tile overlap the reductions of the current one.
-// One warp issues TMA and tcgen05.mma (lane 0), four warps reduce.  Every wait is bounded.
+// One warp issues TMA and tcgen05.mma (lane 0); two warpgroups reduce, one per accumulator buffer,
+// so every scheduler has two reduction warps to interleave.  A thread takes a head's whole row of
+// tokens into registers with one TMEM read, masks it only on the diagonal tiles (-inf entries
+// contribute exp2(-inf) = 0 to the sum, so the sum needs no select), and uses packed fp32 pairs
+// for the scale and the sum.  Every wait is bounded.
 #include "ca_common.cuh"
 
 namespace ca {
 namespace fpscore {
 
-constexpr int kThreads = 160;       // 4 epilogue warps + 1 producer warp
+constexpr int kThreads = 288;       // 2 x 4 reduction warps + 1 producer warp
+constexpr int kProducerWarp = 8;
 constexpr int kTileKeys = 128;      // key blocks per tile = UMMA M
 constexpr int kD = 128;
 constexpr int kHalfBytesK = kTileKeys * 128;  // one [128 key blocks][64 x 16-bit] swizzled half
@@ -43,6 +48,49 @@ struct Shared {
   uint32_t tmem_base;
   int abort_flag;
 };
+
+// max_t S and sum_t 2^((S - max) * scale) over one head's kBs token columns of this thread's key
+// block.  Columns outside [c_min, c_max) are not counted; `all_counted` (warp-uniform) skips the mask.
+template <int kBs>
+__device__ __forceinline__ void reduce_row(uint32_t taddr, float scale, int c_min, int c_max, bool all_counted,
+                                           float& m_scaled, float& p_sum) {
+  uint32_t v[128];
+  ptx::tmem_ld32_row<0>(taddr, v);
+  ptx::tmem_ld32_row<32>(taddr + 32, v);
+  if (kBs == 128) {
+    ptx::tmem_ld32_row<64>(taddr + 64, v);
+    ptx::tmem_ld32_row<96>(taddr + 96, v);
+  }
+  ptx::tc_wait_ld();
+  if (!all_counted) {
+#pragma unroll
+    for (int c = 0; c < kBs; ++c)
+      if (c < c_min || c >= c_max) v[c] = 0xff800000u;  // -inf
+  }
+  float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+  for (int c = 0; c < kBs; c += 8) {
+    m0 = fmaxf(m0, fmaxf(__uint_as_float(v[c + 0]), __uint_as_float(v[c + 1])));
+    m1 = fmaxf(m1, fmaxf(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3])));
+    m2 = fmaxf(m2, fmaxf(__uint_as_float(v[c + 4]), __uint_as_float(v[c + 5])));
+    m3 = fmaxf(m3, fmaxf(__uint_as_float(v[c + 6]), __uint_as_float(v[c + 7])));
+  }
+  const float m = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+  m_scaled = m * scale;
+  const float neg = m == -INFINITY ? 0.f : -m_scaled;
+  const float2 sc2 = make_float2(scale, scale), neg2 = make_float2(neg, neg);
+  float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int c = 0; c < kBs; c += 4) {
+    float2 x0 = __ffma2_rn(make_float2(__uint_as_float(v[c + 0]), __uint_as_float(v[c + 1])), sc2, neg2);
+    float2 x1 = __ffma2_rn(make_float2(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3])), sc2, neg2);
+    x0.x = ptx::ex2(x0.x), x0.y = ptx::ex2(x0.y);
+    x1.x = ptx::ex2(x1.x), x1.y = ptx::ex2(x1.y);
+    acc0 = __fadd2_rn(acc0, x0);
+    acc1 = __fadd2_rn(acc1, x1);
+  }
+  p_sum = m == -INFINITY ? -INFINITY : (acc0.x + acc0.y) + (acc1.x + acc1.y);
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
     fp_score_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map, const Args a) {
@@ -84,7 +132,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::mbar_fence_init();
     ptx::fence_proxy_async_smem();
   }
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     ptx::tmem_alloc(ptx::smem_u32(&sh->tmem_base), 512);
     ptx::tmem_relinquish();
   }
@@ -106,7 +154,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 
   bool ok = true;
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // =============================== TMA + MMA issuer ===============================
     if (lane == 0 && n_work > 0) {
       auto wait = [&](uint64_t* bar, uint32_t parity) {
@@ -158,64 +206,55 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else {
     // =============================== reduction over tokens ===============================
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    for (int w = 0; w < n_work; ++w) {
+    // warpgroup g owns accumulator buffer g and the work items of its parity
+    const int wg = warp >> 2;
+    const int row = tid & 127;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int c_max = t_end - i * a.bs;  // one past the last real token of the q-block
+    for (int w = wg; w < n_work; w += 2) {
       const int tile = w / a.passes, pass = w % a.passes;
-      const int buf = w & 1;
+      const int buf = wg;
       ok = ptx::mbar_wait_bounded(ptx::smem_u32(&sh->t_full[buf]), (w >> 1) & 1, abort_flag, limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after();
-      const int j = tile * kTileKeys + tid;  // this thread's key block
+      const int j = tile * kTileKeys + row;  // this thread's key block
       const int h0 = pass * a.heads_per_pass;
       const int nh = min(a.heads_per_pass, a.G - h0);
       // token t of the q-block is counted iff P + t >= (j+1)*bs - 1  <=>  t >= (j+1)*bs - 1 - P
       const long long t_min_ll = static_cast<long long>(j + 1) * a.bs - 1 - a.P - static_cast<long long>(i) * a.bs;
       const int c_min = t_min_ll < 0 ? 0 : (t_min_ll > a.bs ? a.bs : static_cast<int>(t_min_ll));  // first counted column
-      const int c_max = t_end - i * a.bs;                                                         // one past the last real token
-      for (int hh = 0; hh < nh; ++hh) {
-        const uint32_t taddr = tmem + lane_base + buf * kMaxCols + hh * a.bs;
-        float m = -INFINITY;
-        for (int c0 = 0; c0 < a.bs; c0 += 32) {
-          uint32_t v[32];
-          ptx::tmem_ld32(taddr + c0, v);
-          ptx::tc_wait_ld();
+      const bool all_counted = __all_sync(0xffffffffu, c_min == 0 && c_max == a.bs);
+      float res_p[4], res_m[4];
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const bool vis = (c0 + c) >= c_min && (c0 + c) < c_max;
-            m = fmaxf(m, vis ? __uint_as_float(v[c]) : -INFINITY);
-          }
-        }
-        // second pass for every lane alike: tcgen05.ld is a warp-wide instruction and must not sit
-        // under a per-lane condition (a key block with no counted token just sums zeros)
-        float p = 0.f;
-        const float ms = m * a.sm_scale;
-        const float neg = m == -INFINITY ? 0.f : -ms;
-        for (int c0 = 0; c0 < a.bs; c0 += 32) {
-          uint32_t v[32];
-          ptx::tmem_ld32(taddr + c0, v);
-          ptx::tc_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const bool vis = (c0 + c) >= c_min && (c0 + c) < c_max;
-            const float e = ptx::ex2(fmaf(__uint_as_float(v[c]), a.sm_scale, neg));
-            p += vis ? e : 0.f;
-          }
-        }
-        if (j < a.Kb) {
-          const long long o = ((static_cast<long long>(b) * a.Qb + i) * a.Kb + j) * a.Hq + hkv * a.G + h0 + hh;
-          a.score[o] = m == -INFINITY ? -INFINITY : p;
-          a.mx[o] = ms;
+      for (int hh = 0; hh < 4; ++hh) {
+        if (hh < nh) {  // warp-uniform
+          const uint32_t taddr = tmem + lane_base + buf * kMaxCols + hh * a.bs;
+          if (a.bs == 64) reduce_row<64>(taddr, a.sm_scale, c_min, c_max, all_counted, res_m[hh], res_p[hh]);
+          else reduce_row<128>(taddr, a.sm_scale, c_min, c_max, all_counted, res_m[hh], res_p[hh]);
         }
       }
+      // the accumulator buffer is free as soon as its rows are in registers
       ptx::tc_fence_before();
       ptx::mbar_arrive(ptx::smem_u32(&sh->t_empty[buf]));
+      if (j < a.Kb) {
+        const long long o = ((static_cast<long long>(b) * a.Qb + i) * a.Kb + j) * a.Hq + hkv * a.G + h0;
+        if (nh == 4 && (o & 3) == 0) {
+          *reinterpret_cast<float4*>(a.score + o) = make_float4(res_p[0], res_p[1], res_p[2], res_p[3]);
+          *reinterpret_cast<float4*>(a.mx + o) = make_float4(res_m[0], res_m[1], res_m[2], res_m[3]);
+        } else {
+#pragma unroll
+          for (int hh = 0; hh < 4; ++hh) {
+            if (hh < nh) a.score[o + hh] = res_p[hh], a.mx[o + hh] = res_m[hh];
+          }
+        }
+      }
     }
   }
 
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     if (lane == 0 && sh->abort_flag) {
       // after an expired wait: give the few copies and MMAs that may still be in flight 200 us to
       // land before shared memory and TMEM are released

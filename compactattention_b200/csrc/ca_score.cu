@@ -560,6 +560,63 @@ __global__ void __launch_bounds__(256) flashprefill_normalize_kernel(const float
     }
 }
 
+// The same normalisation with enough CTAs to fill the GPU: one CTA per (b, i, group of 4 query
+// heads), thread = key-block phase, the 4 heads of a key block move as one 16-byte vector.
+// (The one-CTA-per-(b, i) form above runs 16 CTAs for a 1024-token chunk and took longer than the
+// tensor-core score kernel it follows.)
+__global__ void __launch_bounds__(256) flashprefill_normalize4_kernel(const float* score, const float* mx, float* out,
+                                                                      int Kb, int Hq) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
+  __shared__ float4 red[8];
+  const long long base = static_cast<long long>(blockIdx.x) * Kb * Hq + blockIdx.y * 4;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  auto block_reduce = [&](float4 v, bool is_max) -> float4 {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float4 w;
+      w.x = __shfl_xor_sync(0xffffffffu, v.x, o), w.y = __shfl_xor_sync(0xffffffffu, v.y, o);
+      w.z = __shfl_xor_sync(0xffffffffu, v.z, o), w.w = __shfl_xor_sync(0xffffffffu, v.w, o);
+      if (is_max) v = make_float4(fmaxf(v.x, w.x), fmaxf(v.y, w.y), fmaxf(v.z, w.z), fmaxf(v.w, w.w));
+      else v = make_float4(v.x + w.x, v.y + w.y, v.z + w.z, v.w + w.w);
+    }
+    __syncthreads();  // red is reused
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float4 r = red[0];
+    for (int w = 1; w < 8; ++w) {
+      const float4 t = red[w];
+      if (is_max) r = make_float4(fmaxf(r.x, t.x), fmaxf(r.y, t.y), fmaxf(r.z, t.z), fmaxf(r.w, t.w));
+      else r = make_float4(r.x + t.x, r.y + t.y, r.z + t.z, r.w + t.w);
+    }
+    return r;
+  };
+  float4 m = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+  for (int j = tid; j < Kb; j += 256) {
+    const float4 v = *reinterpret_cast<const float4*>(mx + base + static_cast<long long>(j) * Hq);
+    m = make_float4(fmaxf(m.x, v.x), fmaxf(m.y, v.y), fmaxf(m.z, v.z), fmaxf(m.w, v.w));
+  }
+  m = block_reduce(m, true);
+  auto weigh = [](float sc, float mj, float mm) { return mj == -INFINITY ? 0.f : sc * exp2f(mj - mm); };
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j = tid; j < Kb; j += 256) {
+    const long long o = base + static_cast<long long>(j) * Hq;
+    const float4 mj = *reinterpret_cast<const float4*>(mx + o);
+    const float4 sc = *reinterpret_cast<const float4*>(score + o);
+    sum.x += weigh(sc.x, mj.x, m.x), sum.y += weigh(sc.y, mj.y, m.y);
+    sum.z += weigh(sc.z, mj.z, m.z), sum.w += weigh(sc.w, mj.w, m.w);
+  }
+  sum = block_reduce(sum, false);
+  const float4 inv = make_float4(1.0f / (sum.x + 1e-9f), 1.0f / (sum.y + 1e-9f), 1.0f / (sum.z + 1e-9f), 1.0f / (sum.w + 1e-9f));
+  for (int j = tid; j < Kb; j += 256) {
+    const long long o = base + static_cast<long long>(j) * Hq;
+    const float4 mj = *reinterpret_cast<const float4*>(mx + o);
+    const float4 sc = *reinterpret_cast<const float4*>(score + o);
+    *reinterpret_cast<float4*>(out + o) = make_float4(weigh(sc.x, mj.x, m.x) * inv.x, weigh(sc.y, mj.y, m.y) * inv.y,
+                                                      weigh(sc.z, mj.z, m.z) * inv.z, weigh(sc.w, mj.w, m.w) * inv.w);
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // Fused gate preparation for one chunk: block pooling of Q and K, per-head projection, block RoPE,
 // Q blocks to their buffer and K blocks appended to the gate cache -- one launch.
@@ -918,7 +975,15 @@ int ca_flashprefill_score(const ca_flashprefill_score_params* p, ca_stream_t str
   if (p->score_norm) {
     const int threads = 256;
     const size_t nsmem = static_cast<size_t>(threads / p->Hq) * p->Hq * sizeof(float);
-    launch_kernel(flashprefill_normalize_kernel, dim3(p->B * a.Qb), dim3(threads), nsmem, stream, p->score_raw, p->max_raw, p->score_norm, p->Kb, p->Hq);
+    const bool vec4 = p->Hq % 4 == 0 && ((reinterpret_cast<uintptr_t>(p->score_raw) | reinterpret_cast<uintptr_t>(p->max_raw) |
+                                          reinterpret_cast<uintptr_t>(p->score_norm)) & 15u) == 0;
+    if (vec4) {
+      launch_kernel(flashprefill_normalize4_kernel, dim3(p->B * a.Qb, p->Hq / 4), dim3(256), 0, stream, p->score_raw, p->max_raw,
+                    p->score_norm, p->Kb, p->Hq);
+    } else {
+      launch_kernel(flashprefill_normalize_kernel, dim3(p->B * a.Qb), dim3(threads), nsmem, stream, p->score_raw, p->max_raw,
+                    p->score_norm, p->Kb, p->Hq);
+    }
     CA_LAUNCH_CHECK("flashprefill_normalize_kernel");
   }
   return CA_OK;
