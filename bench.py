@@ -313,6 +313,31 @@ def run_native(args):
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             dense_us = float(tt[0])
 
+    # ---- the reference's own dense comparator on the same GPU (library call, timing only) ----
+    # compact_attn/modules/dense_prefill.py:304-310 calls flash_attn_func(causal=True); the library is
+    # part of the image, not of this repository, and is only timed here, never used by the path.
+    ref_dense_us = None
+    if not args.no_dense and rank == 0:
+        try:
+            from flash_attn import flash_attn_func
+            kd = torch.randn((1, K, hkv, D), device=dev, dtype=torch.bfloat16)
+            vd = torch.randn((1, K, hkv, D), device=dev, dtype=torch.bfloat16)
+            qd = layers[0]["q"]
+            for _ in range(2):
+                flash_attn_func(qd, kd, vd, causal=True)
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            f0.record()
+            for _ in range(3):
+                flash_attn_func(qd, kd, vd, causal=True)
+            f1.record()
+            torch.cuda.synchronize()
+            ref_dense_us = f0.elapsed_time(f1) / 3 * 1e3
+            del kd, vd
+        except Exception as exc:  # the comparator is optional: absent library, unsupported device
+            ref_dense_us = None
+            print(f"[bench] flash_attn dense comparator not timed: {exc!r}", file=sys.stderr)
+
     # ---- end to end through the public operator with host buffers ----
     from compactattention_b200.modules import chunked_prefill_column_dense_attention_from_keep_block  # noqa: F401
     host_out = torch.empty((1, Q, hq, D), dtype=torch.bfloat16).pin_memory()
@@ -368,6 +393,8 @@ def run_native(args):
             "programmatic_dependent_launch": args.dependent_launch,
             "dense_same_shape_us": None if dense_us is None else round(dense_us, 1),
             "speedup_vs_dense": None if dense_us is None else round(dense_us / value_us, 2),
+            "dense_flash_attn2_same_shape_us": None if ref_dense_us is None else round(ref_dense_us, 1),
+            "speedup_vs_flash_attn2_dense": None if ref_dense_us is None else round(ref_dense_us / value_us, 2),
             "attention_effective_tflops": round(achieved, 1),
             "status_word": status,
         },
