@@ -63,4 +63,7 @@ class PagedKVCache:
         return q_rot, self.length
 
     def view(self) -> ops.KvCacheView:
-        return ops.KvCacheView.from_paged(self.k_pages, self.v_pages, self.page_table)
+        v = getattr(self, "_view", None)
+        if v is None:  # pages and table never move: build the addressing once
+            v = self._view = ops.KvCacheView.from_paged(self.k_pages, self.v_pages, self.page_table)
+        return v

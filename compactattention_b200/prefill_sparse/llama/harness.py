@@ -33,8 +33,9 @@ class RMSNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x):
-        xf = x.float()
-        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype) * self.weight
+        # one fused torch kernel (the norm is outside the attention path; six elementwise launches
+        # per norm made a tensor-parallel rank wait for its host)
+        return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
 
 
 class ShardedMLP(nn.Module):

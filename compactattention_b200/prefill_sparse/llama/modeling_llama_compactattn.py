@@ -105,6 +105,31 @@ class CompactAttnCache:
         st = self.layers.get(idx)
         return 0 if st is None else st.kv.length
 
+    def selection_scratch(self, heads: int, num_kv_heads: int, q_blocks: int, block_size: int):
+        """Keep bits and block table shared by every layer (the layers run one after the other on
+        one stream and each consumes its table at once), sized for the longest context, so a chunk
+        allocates nothing: returns ``(bits_for(kv_blocks), table)``."""
+        key = (heads, num_kv_heads, q_blocks, block_size)
+        sc = getattr(self, "_scratch", None)
+        if sc is None or sc[0] != key:
+            max_blocks = self.max_tokens // block_size
+            words = ops.words_for(max_blocks)
+            flat = torch.empty(self.batch * heads * q_blocks * words, dtype=torch.int32, device=self.device)
+            table = ops.BlockTable(
+                torch.empty((self.batch, num_kv_heads, max_blocks), dtype=torch.int32, device=self.device),
+                torch.empty((self.batch, num_kv_heads), dtype=torch.int32, device=self.device),
+                torch.empty((self.batch, num_kv_heads), dtype=torch.int32, device=self.device),
+                torch.empty((self.batch, num_kv_heads), dtype=torch.int32, device=self.device))
+            sc = (key, flat, table)
+            self._scratch = sc
+        _, flat, table = sc
+
+        def bits_for(kv_blocks: int) -> torch.Tensor:
+            w = ops.words_for(kv_blocks)
+            return flat[: self.batch * heads * q_blocks * w].view(self.batch, heads, q_blocks, w)
+
+        return bits_for, table
+
 
 def rotate_half(x: torch.Tensor) -> torch.Tensor:
     h = x.shape[-1] // 2
@@ -264,19 +289,21 @@ class LlamaSeerAttentionChunkedDense(_CompactAttnBase):
                 self._synthetic_importance = torch.rand((1, self.num_key_value_heads, 1, past_key_value.max_tokens // bs),
                                                         generator=g, device=hidden_states.device)
             score = self._synthetic_importance[..., :Kb].expand(hidden_states.shape[0], self.num_key_value_heads, Qb, Kb)
+            bits_for, table = past_key_value.selection_scratch(self.num_key_value_heads, self.num_key_value_heads, Qb, bs)
             bits = ops.select_rows(score, Kb - Qb, "topk", topk_ratio=tuple(self.config.seerattn_topk_ratio), sink=1,
-                                   local=self.compactattn_keep_recent_blocks)
+                                   local=self.compactattn_keep_recent_blocks, bits=bits_for(Kb))
             table = ops.union_table(bits=bits, num_kv_heads=self.num_key_value_heads, kv_blocks=Kb, past_blocks=Kb - Qb,
-                                    block_size=bs)
+                                    block_size=bs, out=table)
             attn = ops.attn_compact(q, kv_view, kv_len, self.num_key_value_heads, table.block_idx, table.counts,
                                     block_size=bs, softmax_scale=self.scaling)
             path = "chunked_selected"
         elif self.config.seerattn_sparsity_method == "topk":
             Qb, Kb = logits.shape[2], logits.shape[3]
+            bits_for, table = past_key_value.selection_scratch(self.num_heads, self.num_key_value_heads, Qb, bs)
             bits = ops.select_rows(logits, Kb - Qb, "topk", topk_ratio=tuple(self.config.seerattn_topk_ratio), sink=1,
-                                   local=self.compactattn_keep_recent_blocks)
+                                   local=self.compactattn_keep_recent_blocks, bits=bits_for(Kb))
             table = ops.union_table(bits=bits, num_kv_heads=self.num_key_value_heads, kv_blocks=Kb, past_blocks=Kb - Qb,
-                                    block_size=bs)
+                                    block_size=bs, out=table)
             attn = ops.attn_compact(q, kv_view, kv_len, self.num_key_value_heads, table.block_idx, table.counts,
                                     block_size=bs, softmax_scale=self.scaling)
             path = "chunked_selected"
