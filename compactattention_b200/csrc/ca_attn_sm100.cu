@@ -307,6 +307,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint64_t limit = a.wait_limit_ns;
   bool bad_index = false;
 
+#if CA_ATTN_PROFILE
+  const long long prof_kernel_t0 = clock64();
+#endif
   // ---- on-chip set-up first: it needs nothing from global memory, so under a programmatic
   // dependent launch it overlaps the tail of the previous kernel (the table builder) ----
   ptx::grid_launch_dependents();
@@ -409,6 +412,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
   __syncthreads();
 
+#if CA_ATTN_PROFILE
+  if (tid == 0) g_prof[blockIdx.x][30] = clock64() - prof_kernel_t0;  // prologue
+#endif
   // role state that lives across segments
   int ring_n = 0;        // ring entries issued (loader) / consumed (MMA)
   uint32_t it = 0;       // KV steps processed so far: parity of s_full / p_part
@@ -820,33 +826,51 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::tmem_dealloc(tmem, kTmemCols);
   }
   if (tid == 0 && sh->abort_flag && a.status) atomicOr(a.status, CA_STATUS_TIMEOUT);
+#if CA_ATTN_PROFILE
+  if (tid == 0) g_prof[blockIdx.x][31] = clock64() - prof_kernel_t0;  // whole kernel
+#endif
 }
 
-// Merges the segments of every split unit.  One CTA per (workspace slot, tile); the CTA whose slot
-// holds the first segment of a unit (j0 == 0) walks the following CTAs' head slots until the unit
-// is complete.  Thread = tile row.
+// Merges the segments of every split unit.  One CTA per (workspace slot, tile, 16-column part);
+// the CTAs whose slot holds the first segment of a unit (j0 == 0) walk the following CTAs' head
+// slots until the unit is complete.  Thread = tile row.  The per-segment weights are computed once
+// and kept in shared memory; the loads of the partial accumulators of different segments are
+// independent, so several are in flight per thread.  (The first form of this kernel, one CTA per
+// (slot, tile) with the weights recomputed inside the column loop, took 70-80 us for the 16 units
+// of a tensor-parallel rank with one KV head - longer than the attention kernel itself.)
+constexpr int kCombineParts = 8;                        // column parts per tile
+constexpr int kCombineC8 = kHeadDim / 8 / kCombineParts;  // 8-column groups per part
+constexpr int kCombineMaxChain = 64;                    // segments whose weights are cached in shared memory
+
 template <typename T>
 __global__ void __launch_bounds__(kTileM) attn_combine_kernel(const KernelArgs a, int n_slots) {
   ptx::grid_launch_dependents();
   ptx::grid_dependency_wait();  // nothing in global memory is touched before this
-  const int slot = blockIdx.x, tile = blockIdx.y, r = threadIdx.x;
+  __shared__ int chain_sh[256];
+  __shared__ float w_sh[kCombineMaxChain][kTileM];
+  const int slot = blockIdx.x, tile = blockIdx.y, part = blockIdx.z, r = threadIdx.x;
   const SegDesc first = a.descs[slot];
   if (first.unit < 0 || first.j0 != 0) return;
   // chain of slots: this one, then the head slots (even) of the following CTAs
   // (CTAs whose span is empty leave their slots unused and are skipped)
-  int chain[256];
-  int n = 0;
-  chain[n++] = slot;
-  int reached = first.j1;
-  for (int s = (slot / 2 + 1) * 2; s < n_slots && reached < first.n_iter && n < 256; s += 2) {
-    const SegDesc d = a.descs[s];
-    if (d.unit < 0) continue;
-    if (d.unit != first.unit || d.j0 != reached) break;
-    chain[n++] = s;
-    reached = d.j1;
+  __shared__ int n_sh;
+  if (r == 0) {
+    int n = 0;
+    chain_sh[n++] = slot;
+    int reached = first.j1;
+    for (int s = (slot / 2 + 1) * 2; s < n_slots && reached < first.n_iter && n < 256; s += 2) {
+      const SegDesc d = a.descs[s];
+      if (d.unit < 0) continue;
+      if (d.unit != first.unit || d.j0 != reached) break;
+      chain_sh[n++] = s;
+      reached = d.j1;
+    }
+    n_sh = reached == first.n_iter ? n : -1;
   }
-  if (reached != first.n_iter) {
-    if (r == 0 && a.status) atomicOr(a.status, CA_STATUS_BAD_INDEX);
+  __syncthreads();
+  const int n = n_sh;
+  if (n < 0) {
+    if (r == 0 && part == 0 && a.status) atomicOr(a.status, CA_STATUS_BAD_INDEX);
     return;
   }
   const int row = first.unit / a.n_pairs, pair = first.unit % a.n_pairs;
@@ -855,23 +879,32 @@ __global__ void __launch_bounds__(kTileM) attn_combine_kernel(const KernelArgs a
   const int g = r % a.G;
   const bool live = (r < a.tpt * a.G) && (t < a.Q);
   const float sc = a.scale_log2;
+  auto ml_of = [&](int i) { return a.part_ml + static_cast<long long>(chain_sh[i]) * kPartialMLFloats + (tile * kTileM + r) * 2; };
   float m = -INFINITY;
-  for (int i = 0; i < n; ++i)
-    m = fmaxf(m, a.part_ml[static_cast<long long>(chain[i]) * kPartialMLFloats + (tile * kTileM + r) * 2]);
+  for (int i = 0; i < n; ++i) m = fmaxf(m, ml_of(i)[0]);
   float l = 0.f;
   for (int i = 0; i < n; ++i) {
-    const float* pml = a.part_ml + static_cast<long long>(chain[i]) * kPartialMLFloats + (tile * kTileM + r) * 2;
-    l += pml[0] == -INFINITY ? 0.f : pml[1] * ptx::ex2((pml[0] - m) * sc);
+    const float2 ml = *reinterpret_cast<const float2*>(ml_of(i));
+    const float w = ml.x == -INFINITY ? 0.f : ptx::ex2((ml.x - m) * sc);
+    if (i < kCombineMaxChain) w_sh[i][r] = w;
+    l += ml.y * w;
   }
   const float inv_l = 1.0f / l;
+  auto weight = [&](int i) {
+    if (i < kCombineMaxChain) return w_sh[i][r];  // written by this very thread
+    const float ms = ml_of(i)[0];
+    return ms == -INFINITY ? 0.f : ptx::ex2((ms - m) * sc);
+  };
   T* orow = reinterpret_cast<T*>(a.out) + b * a.o_stride_b + static_cast<long long>(t) * a.o_stride_t +
             static_cast<long long>(hkv * a.G + g) * a.o_stride_h;
-  for (int c8 = 0; c8 < kHeadDim / 8; ++c8) {
+#pragma unroll
+  for (int cc = 0; cc < kCombineC8; ++cc) {
+    const int c8 = part * kCombineC8 + cc;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
     for (int i = 0; i < n; ++i) {
-      const float ms = a.part_ml[static_cast<long long>(chain[i]) * kPartialMLFloats + (tile * kTileM + r) * 2];
-      const float w = ms == -INFINITY ? 0.f : ptx::ex2((ms - m) * sc);
-      const float* po = a.part_o + static_cast<long long>(chain[i]) * kPartialOFloats + tile * (kTileM * kHeadDim);
+      const float w = weight(i);
+      const float* po = a.part_o + static_cast<long long>(chain_sh[i]) * kPartialOFloats + tile * (kTileM * kHeadDim);
       const float4 x0 = *reinterpret_cast<const float4*>(po + (static_cast<long long>(2 * c8) * kTileM + r) * 4);
       const float4 x1 = *reinterpret_cast<const float4*>(po + (static_cast<long long>(2 * c8 + 1) * kTileM + r) * 4);
       acc[0] += w * x0.x, acc[1] += w * x0.y, acc[2] += w * x0.z, acc[3] += w * x0.w;
@@ -886,7 +919,7 @@ __global__ void __launch_bounds__(kTileM) attn_combine_kernel(const KernelArgs a
       *reinterpret_cast<uint4*>(orow + c8 * 8) = w;
     }
   }
-  if (live && a.lse) {
+  if (live && part == 0 && a.lse) {
     a.lse[(static_cast<long long>(b) * (a.Hkv * a.G) + hkv * a.G + g) * a.Q + t] = 0.6931471805599453f * (m * sc + log2f(l));
   }
 }
@@ -1125,9 +1158,9 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
   CA_LAUNCH_CHECK("attn_compact_kernel");
   if (a.split) {
     if (p->dtype == CA_DTYPE_BF16) {
-      launch_kernel(attn_combine_kernel<__nv_bfloat16>, dim3(2 * grid, 2), dim3(kTileM), 0, stream, a, 2 * grid);
+      launch_kernel(attn_combine_kernel<__nv_bfloat16>, dim3(2 * grid, 2, kCombineParts), dim3(kTileM), 0, stream, a, 2 * grid);
     } else {
-      launch_kernel(attn_combine_kernel<__half>, dim3(2 * grid, 2), dim3(kTileM), 0, stream, a, 2 * grid);
+      launch_kernel(attn_combine_kernel<__half>, dim3(2 * grid, 2, kCombineParts), dim3(kTileM), 0, stream, a, 2 * grid);
     }
     CA_LAUNCH_CHECK("attn_combine_kernel");
   }

@@ -36,6 +36,8 @@ def main() -> None:
     ap.add_argument("--density", type=float, default=0.2)
     ap.add_argument("--kv-len", type=int, default=131072)
     ap.add_argument("--launches", type=int, default=50)
+    ap.add_argument("--kv-heads", type=int, default=8, help="KV heads (4 query heads each); 1 = one rank of TP8")
+    ap.add_argument("--cut", action="store_true", help="let the launch cut work units across SMs (default: whole units)")
     args = ap.parse_args()
 
     defines = ["CA_ATTN_PROFILE=1"]
@@ -47,7 +49,8 @@ def main() -> None:
     from . import ops
 
     torch.manual_seed(1)
-    B, Q, Hq, Hkv, K, bs, D = 1, 1024, 32, 8, args.kv_len, 64, 128
+    B, Q, Hkv, K, bs, D = 1, 1024, args.kv_heads, args.kv_len, 64, 128
+    Hq = 4 * Hkv
     q = torch.randn(B, Q, Hq, D, device="cuda", dtype=torch.bfloat16)
     k = torch.randn(B, K, Hkv, D, device="cuda", dtype=torch.bfloat16)
     v = torch.randn(B, K, Hkv, D, device="cuda", dtype=torch.bfloat16)
@@ -58,7 +61,7 @@ def main() -> None:
     kv = ops.KvCacheView.from_seq_first(k, v)
     out = torch.empty_like(q)
     for _ in range(args.launches):
-        ops.attn_compact(q, kv, K, Hkv, idx, counts, out=out, use_workspace=False)
+        ops.attn_compact(q, kv, K, Hkv, idx, counts, out=out, use_workspace=args.cut)
     torch.cuda.synchronize()
 
     raw = (ctypes.c_longlong * (160 * 32))()
@@ -68,7 +71,11 @@ def main() -> None:
     prof = np.frombuffer(raw, dtype=np.int64).reshape(160, 32)
     # KV steps of one work unit: selected blocks in pairs + the chunk's blocks up to the pair's diagonal
     steps = (n * bs + Q // 2 + 127) // 128
+    if args.cut:
+        steps = max(1, steps * Hkv * 16 // 148)   # 16 tile pairs per KV head, laid end to end over 148 CTAs
     print(f"defines: {' '.join(defines)}; {n} of {Pb} past blocks per KV head; ~{steps} KV steps per CTA")
+    print(f"whole kernel per CTA (cycles): median {int(np.median(prof[:148, 31]))}, max {int(prof[:148, 31].max())}; "
+          f"prologue median {int(np.median(prof[:148, 30]))}")
     for cta in (0, 1, 64, 127):
         print(f"CTA {cta}: cycles per KV step")
         mma = prof[cta, :8] / steps

@@ -48,7 +48,10 @@ def main() -> None:
     ap.add_argument("--chunk", type=int, default=1024)
     ap.add_argument("--density", type=float, default=0.2)
     ap.add_argument("--launches", type=int, default=4)
+    ap.add_argument("--kv-heads", type=int, default=8, help="KV heads with 4 query heads each (1 = one rank of TP8)")
     args = ap.parse_args()
+    global HQ, HKV
+    HKV, HQ = args.kv_heads, 4 * args.kv_heads
     dev = torch.device("cuda")
     g = torch.Generator(device=dev).manual_seed(1234)
     K, Q = args.kv_len, args.chunk
