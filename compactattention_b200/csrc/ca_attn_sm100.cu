@@ -831,7 +831,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #endif
 }
 
-// Merges the segments of every split unit.  One CTA per (workspace slot, tile, 16-column part);
+// Merges the segments of every split unit.  One CTA per (attention CTA, tile, 16-column part);
 // the CTAs whose slot holds the first segment of a unit (j0 == 0) walk the following CTAs' head
 // slots until the unit is complete.  Thread = tile row.  The per-segment weights are computed once
 // and kept in shared memory; the loads of the partial accumulators of different segments are
@@ -840,7 +840,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 // of a tensor-parallel rank with one KV head - longer than the attention kernel itself.)
 constexpr int kCombineParts = 8;                        // column parts per tile
 constexpr int kCombineC8 = kHeadDim / 8 / kCombineParts;  // 8-column groups per part
-constexpr int kCombineMaxChain = 64;                    // segments whose weights are cached in shared memory
+constexpr int kCombineMaxChain = 32;                    // segments whose weights are cached in shared memory
 
 template <typename T>
 __global__ void __launch_bounds__(kTileM) attn_combine_kernel(const KernelArgs a, int n_slots) {
@@ -848,9 +848,16 @@ __global__ void __launch_bounds__(kTileM) attn_combine_kernel(const KernelArgs a
   ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   __shared__ int chain_sh[256];
   __shared__ float w_sh[kCombineMaxChain][kTileM];
-  const int slot = blockIdx.x, tile = blockIdx.y, part = blockIdx.z, r = threadIdx.x;
-  const SegDesc first = a.descs[slot];
-  if (first.unit < 0 || first.j0 != 0) return;
+  // blockIdx.x = attention CTA; at most one of its two slots holds the first segment of a cut unit
+  // (slot 0 when a unit starts exactly at the span's start, else slot 1)
+  const int tile = blockIdx.y, part = blockIdx.z, r = threadIdx.x;
+  int slot = 2 * blockIdx.x;
+  SegDesc first = a.descs[slot];
+  if (first.unit < 0 || first.j0 != 0) {
+    slot += 1;
+    first = a.descs[slot];
+    if (first.unit < 0 || first.j0 != 0) return;
+  }
   // chain of slots: this one, then the head slots (even) of the following CTAs
   // (CTAs whose span is empty leave their slots unused and are skipped)
   __shared__ int n_sh;
@@ -1158,9 +1165,9 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
   CA_LAUNCH_CHECK("attn_compact_kernel");
   if (a.split) {
     if (p->dtype == CA_DTYPE_BF16) {
-      launch_kernel(attn_combine_kernel<__nv_bfloat16>, dim3(2 * grid, 2, kCombineParts), dim3(kTileM), 0, stream, a, 2 * grid);
+      launch_kernel(attn_combine_kernel<__nv_bfloat16>, dim3(grid, 2, kCombineParts), dim3(kTileM), 0, stream, a, 2 * grid);
     } else {
-      launch_kernel(attn_combine_kernel<__half>, dim3(2 * grid, 2, kCombineParts), dim3(kTileM), 0, stream, a, 2 * grid);
+      launch_kernel(attn_combine_kernel<__half>, dim3(grid, 2, kCombineParts), dim3(kTileM), 0, stream, a, 2 * grid);
     }
     CA_LAUNCH_CHECK("attn_combine_kernel");
   }

@@ -318,19 +318,6 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-// 2^x on the FMA/ALU pipes (no MUFU): round-to-nearest split x = n + f with the 1.5*2^23 trick,
-// degree-3 polynomial for 2^f on [-0.5, 0.5] (relative error 1.9e-4), exponent added to the bits.
-// Valid for x <= ~100; inputs below -126 are clamped (result ~1e-38).
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -126.0f);
-  const float t = x + 12582912.0f;
-  const float f = x - (t - 12582912.0f);
-  float p = fmaf(0.0558755025267601f, f, 0.24229444563388824f);
-  p = fmaf(p, f, 0.6931272745132446f);
-  p = fmaf(p, f, 0.999948263168335f);
-  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
-}
-
 }  // namespace ptx
 #endif  // __CUDACC__
 
