@@ -861,15 +861,26 @@ __global__ void __launch_bounds__(kTileM) attn_combine_kernel(const KernelArgs a
   // chain of slots: this one, then the head slots (even) of the following CTAs
   // (CTAs whose span is empty leave their slots unused and are skipped)
   __shared__ int n_sh;
+  __shared__ SegDesc cand_sh[2 * kTileM];
+  // the head slots of the following CTAs, fetched by all threads at once (a one-thread walk over
+  // global memory costs a dependent load per segment)
+  for (int i = r; i < 2 * kTileM; i += kTileM) {
+    const int s = (slot / 2 + 1 + i) * 2;
+    SegDesc d;
+    d.unit = -1, d.j0 = 0, d.j1 = 0, d.n_iter = 0;
+    if (s < n_slots) d = a.descs[s];
+    cand_sh[i] = d;
+  }
+  __syncthreads();
   if (r == 0) {
     int n = 0;
     chain_sh[n++] = slot;
     int reached = first.j1;
-    for (int s = (slot / 2 + 1) * 2; s < n_slots && reached < first.n_iter && n < 256; s += 2) {
-      const SegDesc d = a.descs[s];
+    for (int i = 0; i < 2 * kTileM && reached < first.n_iter && n < 256; ++i) {
+      const SegDesc d = cand_sh[i];
       if (d.unit < 0) continue;
       if (d.unit != first.unit || d.j0 != reached) break;
-      chain_sh[n++] = s;
+      chain_sh[n++] = (slot / 2 + 1 + i) * 2;
       reached = d.j1;
     }
     n_sh = reached == first.n_iter ? n : -1;
@@ -888,10 +899,12 @@ __global__ void __launch_bounds__(kTileM) attn_combine_kernel(const KernelArgs a
   const float sc = a.scale_log2;
   auto ml_of = [&](int i) { return a.part_ml + static_cast<long long>(chain_sh[i]) * kPartialMLFloats + (tile * kTileM + r) * 2; };
   float m = -INFINITY;
-  for (int i = 0; i < n; ++i) m = fmaxf(m, ml_of(i)[0]);
+#pragma unroll 8
+  for (int i = 0; i < n; ++i) m = fmaxf(m, __ldg(ml_of(i)));
   float l = 0.f;
+#pragma unroll 8
   for (int i = 0; i < n; ++i) {
-    const float2 ml = *reinterpret_cast<const float2*>(ml_of(i));
+    const float2 ml = __ldg(reinterpret_cast<const float2*>(ml_of(i)));
     const float w = ml.x == -INFINITY ? 0.f : ptx::ex2((ml.x - m) * sc);
     if (i < kCombineMaxChain) w_sh[i][r] = w;
     l += ml.y * w;
