@@ -1142,7 +1142,11 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
   // clock for the busy ones; it pays only when whole units would leave many SMs idle (few rows per
   // rank under tensor parallelism, or a nearly empty last wave).
   const long long waves = (n_units + dev.sm_count - 1) / dev.sm_count;
+#ifdef CA_ATTN_SPLIT_PERCENT
+  const bool want_split = n_units * 100 < waves * dev.sm_count * CA_ATTN_SPLIT_PERCENT;
+#else
   const bool want_split = n_units * 100 < waves * dev.sm_count * 80;
+#endif
   const bool can_split = p->workspace != nullptr && p->workspace_bytes >= workspace_bytes_for(grid);
   a.split = (want_split && can_split) ? 1 : 0;
   if (!a.split && n_units < grid) grid = static_cast<int>(n_units);
