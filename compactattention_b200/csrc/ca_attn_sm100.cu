@@ -1140,7 +1140,9 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
   int grid = dev.sm_count;
   // Cutting units costs partial traffic and a combine launch, and under the power cap idle SMs buy
   // clock for the busy ones; it pays only when whole units would leave many SMs idle (few rows per
-  // rank under tensor parallelism, or a nearly empty last wave).
+  // rank under tensor parallelism, or a nearly empty last wave).  Measured on B200 in fresh
+  // processes, 128 units on 148 SMs: whole units 425-430 us, cut 442-453 us; 16 units: 442 vs 91 us.
+  // (CA_ATTN_SPLIT_PERCENT overrides the 80 % threshold in development builds.)
   const long long waves = (n_units + dev.sm_count - 1) / dev.sm_count;
 #ifdef CA_ATTN_SPLIT_PERCENT
   const bool want_split = n_units * 100 < waves * dev.sm_count * CA_ATTN_SPLIT_PERCENT;
