@@ -14,7 +14,9 @@ import sys
 import types
 from pathlib import Path
 
-DEFAULT_ROOT = os.environ.get("COMPACTATTN_REFERENCE_ROOT", "/root/reference")
+# A checkout of the reference project: COMPACTATTN_REFERENCE_ROOT, else a `reference` directory next
+# to this repository.
+DEFAULT_ROOT = os.environ.get("COMPACTATTN_REFERENCE_ROOT", str(Path(__file__).resolve().parent.parent.parent / "reference"))
 
 _STUB_PACKAGES = [
     "compact_attn",

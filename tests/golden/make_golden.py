@@ -1,6 +1,6 @@
 """Generates the golden fixtures in this directory by executing the reference project's own
 functions for the path on seeded CPU inputs.  Needs a checkout of the reference
-(``COMPACTATTN_REFERENCE_ROOT``, default ``/root/reference``); the fixtures it writes are committed
+(``COMPACTATTN_REFERENCE_ROOT``, default: a ``reference`` directory next to this repository); the fixtures it writes are committed
 so the tests run without it.
 
     python tests/golden/make_golden.py
