@@ -27,7 +27,7 @@ class KvLayout(C.Structure):
         ("page_size", C.c_int32),
         ("num_pages", C.c_int32),
         ("pages_per_seq", C.c_int32),
-        ("reserved", C.c_int32),
+        ("head_div", C.c_int32),
         ("page_table", C.c_void_p),
     ]
 

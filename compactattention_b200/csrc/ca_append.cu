@@ -210,6 +210,7 @@ extern "C" int ca_rope_append(const ca_rope_append_params* p, ca_stream_t stream
   CA_REQUIRE(p->mean_k == nullptr || p->position % p->block_size == 0, "mean_k needs a chunk that starts on a block boundary");
   const ca_kv_layout& c = p->cache;
   CA_REQUIRE(c.page_size > 0 && c.pages_per_seq > 0 && c.num_pages > 0, "cache layout must be positive");
+  CA_REQUIRE(c.head_div <= 1, "cache.head_div is read by ca_attn_compact only");
   CA_REQUIRE(static_cast<long long>(p->position) + p->Q <= static_cast<long long>(c.pages_per_seq) * c.page_size,
              "chunk does not fit in the cache (position %d + Q %d > %lld tokens)", p->position, p->Q,
              static_cast<long long>(c.pages_per_seq) * c.page_size);

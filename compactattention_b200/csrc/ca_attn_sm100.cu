@@ -126,6 +126,7 @@ struct KernelArgs {
   // K/V tensor-map dimensions 1..3 are ordered by ascending stride at encode time; these give the
   // coordinate slot (0..2) of the token, page and head coordinates.
   int slot_tok, slot_page, slot_head;
+  int kv_head_div;     // block-table rows per KV head (1 unless per-query-head / sub-group tables)
   int split;           // 1: spans may cut units (needs the workspace)
   SegDesc* descs;      // [2 * gridDim.x]
   float* part_ml;      // [2 * gridDim.x][kPartialMLFloats]
@@ -501,8 +502,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                   const uint32_t dst = ring_smem + slot * kTileBytes;
                   ptx::mbar_expect_tx(bar, two ? 4u * kBoxBytes : 2u * kBoxBytes);
                   int c0[3], c1[3];
-                  c0[a.slot_tok] = o0, c0[a.slot_page] = p0, c0[a.slot_head] = hkv;
-                  c1[a.slot_tok] = o1, c1[a.slot_page] = p1, c1[a.slot_head] = hkv;
+                  c0[a.slot_tok] = o0, c0[a.slot_page] = p0, c0[a.slot_head] = hkv / a.kv_head_div;
+                  c1[a.slot_tok] = o1, c1[a.slot_page] = p1, c1[a.slot_head] = hkv / a.kv_head_div;
                   for (int h = 0; h < 2; ++h) {
                     ptx::tma_load_4d(dst + h * kHalfBytes, map, bar, h * 64, c0[0], c0[1], c0[2]);
                     if (two) ptx::tma_load_4d(dst + h * kHalfBytes + kBoxBytes, map, bar, h * 64, c1[0], c1[1], c1[2]);
@@ -963,6 +964,8 @@ static int validate(const ca_attn_params* p) {
   CA_REQUIRE(p->dtype == CA_DTYPE_BF16 || p->dtype == CA_DTYPE_F16, "dtype must be bf16 or f16");
   CA_REQUIRE(p->B > 0 && p->Q > 0 && p->Hq > 0 && p->Hkv > 0, "B, Q, Hq, Hkv must be positive");
   CA_REQUIRE(p->Hq % p->Hkv == 0, "Hq (%d) must be a multiple of Hkv (%d)", p->Hq, p->Hkv);
+  CA_REQUIRE(p->kv.head_div >= 0 && (p->kv.head_div <= 1 || p->Hkv % p->kv.head_div == 0),
+             "kv.head_div (%d) must divide the number of block-table rows per batch entry (Hkv = %d)", p->kv.head_div, p->Hkv);
   CA_REQUIRE(p->Hq / p->Hkv <= 128, "GQA group larger than 128 is not supported");
   CA_REQUIRE(static_cast<long long>(p->B) * p->Hkv <= kMaxRows, "more than %d (batch x kv head) rows are not supported", kMaxRows);
   CA_REQUIRE(p->block_size > 0 && p->block_size % kSub == 0, "block_size must be a positive multiple of 64");
@@ -1077,7 +1080,8 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
   }
   {
     // roles: 0 token-in-page, 1 page, 2 head; outer dimensions sorted by ascending stride
-    const cuuint64_t role_dim[3] = {(cuuint64_t)p->kv.page_size, (cuuint64_t)p->kv.num_pages, (cuuint64_t)p->Hkv};
+    const cuuint64_t role_dim[3] = {(cuuint64_t)p->kv.page_size, (cuuint64_t)p->kv.num_pages,
+                                    (cuuint64_t)(p->Hkv / (p->kv.head_div > 1 ? p->kv.head_div : 1))};
     const cuuint64_t role_stride[3] = {(cuuint64_t)p->kv.token_stride * 2, (cuuint64_t)p->kv.page_stride * 2,
                                        (cuuint64_t)p->kv.head_stride * 2};
     const cuuint32_t role_box[3] = {64, 1, 1};
@@ -1131,6 +1135,7 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
   a.idesc_qk = ptx::make_idesc_f16(fmt, kTileM, kTileN, 0, 0);
   a.idesc_pv = ptx::make_idesc_f16(fmt, kTileM, kHeadDim, 0, 1);
   a.wait_limit_ns = 2000000000ull;
+  a.kv_head_div = p->kv.head_div > 1 ? p->kv.head_div : 1;
   a.slot_tok = slot_tok;
   a.slot_page = slot_page;
   a.slot_head = slot_head;

@@ -137,6 +137,7 @@ int ca_gather_kv(const ca_gather_params* p, ca_stream_t stream_) {
   using namespace ca;
   using namespace ca::gather;
   CA_REQUIRE(p != nullptr, "params is null");
+  CA_REQUIRE(p->kv.head_div <= 1, "kv.head_div is read by ca_attn_compact only");
   CA_REQUIRE(p->kv.k && p->kv.v && p->k_dst && p->v_dst, "kv.k, kv.v, k_dst and v_dst must be non-null");
   CA_REQUIRE(p->block_idx && p->counts, "block_idx and counts must be non-null");
   CA_REQUIRE(p->dtype == CA_DTYPE_BF16 || p->dtype == CA_DTYPE_F16, "dtype must be bf16 or f16");

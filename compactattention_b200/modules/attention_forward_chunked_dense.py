@@ -11,6 +11,11 @@ and the block-table-indexed tcgen05 attention kernel that reads the selected KV 
 Differences a caller can observe, all deliberate:
 * ``pack_impl`` / ``indexed_impl`` / ``cache_fill_backend`` are accepted (every value the
   reference accepts, plus ``"b200_native"``) but select nothing: there is one implementation.
+  Two values keep their meaning because they change the result, not the backend:
+  ``"fi_zero_copy_per_query"`` builds one block table per query head (no GQA union) and
+  ``"fi_zero_copy_subgroup"`` one per sub-group of ``SEER_ZC_QUERY_SUBGROUP_SIZE`` query heads
+  (reference :863-895, :2185-2196); both run the same attention kernel with several table rows
+  per KV head.
 * Padded batches (an ``attention_mask`` containing zeros), lengths that are not multiples of the
   block size and head dims other than 128 raise ``NotImplementedError`` instead of falling down the
   reference's ladder of slower paths; the reference only takes its indexed path under the same
@@ -141,9 +146,25 @@ def chunked_prefill_column_dense_attention_from_keep_block(
         raise ValueError("Either keep_block or keep_block_kv_preprojected must be provided.")
     if keep_block is not None and keep_block.shape != (bsz, num_q_heads, kv_blocks):
         raise ValueError(f"keep_block shape mismatch: expected {(bsz, num_q_heads, kv_blocks)}, got {tuple(keep_block.shape)}")
-    if keep_block_kv_preprojected is not None and keep_block_kv_preprojected.shape != (bsz, num_kv_heads, kv_blocks):
+    # block-table rows per KV head: 1 (Block-Union over the GQA group), G (per query head) or G / sub-group size
+    rows_per_kv = 1
+    if indexed_impl == "fi_zero_copy_per_query":
+        if keep_block is None and _row_bits is None:
+            raise ValueError("fi_zero_copy_per_query requires q-head keep_block")
+        rows_per_kv = num_key_value_groups
+    elif indexed_impl == "fi_zero_copy_subgroup":
+        query_subgroup_size = int(os.environ.get("SEER_ZC_QUERY_SUBGROUP_SIZE", "4"))
+        if query_subgroup_size <= 0 or num_key_value_groups % query_subgroup_size != 0:
+            raise ValueError("SEER_ZC_QUERY_SUBGROUP_SIZE must divide num_key_value_groups: "
+                             f"{query_subgroup_size} vs {num_key_value_groups}")
+        if keep_block_kv_preprojected is None:
+            raise ValueError("fi_zero_copy_subgroup requires subgroup keep_block")
+        rows_per_kv = num_key_value_groups // query_subgroup_size
+    table_rows = num_kv_heads * rows_per_kv
+    expected_kv_projected_shape = (bsz, table_rows if indexed_impl == "fi_zero_copy_subgroup" else num_kv_heads, kv_blocks)
+    if keep_block_kv_preprojected is not None and keep_block_kv_preprojected.shape != expected_kv_projected_shape:
         raise ValueError("keep_block_kv_preprojected shape mismatch: "
-                         f"expected {(bsz, num_kv_heads, kv_blocks)}, got {tuple(keep_block_kv_preprojected.shape)}")
+                         f"expected {expected_kv_projected_shape}, got {tuple(keep_block_kv_preprojected.shape)}")
     if valid_block is not None:
         if keep_block is None:
             raise ValueError("valid_block requires keep_block to be provided.")
@@ -156,19 +177,23 @@ def chunked_prefill_column_dense_attention_from_keep_block(
 
     def _build():
         if _row_bits is not None:
-            return ops.union_table(bits=_row_bits, num_kv_heads=num_kv_heads, kv_blocks=kv_blocks, past_blocks=past_blocks,
+            return ops.union_table(bits=_row_bits, num_kv_heads=table_rows, kv_blocks=kv_blocks, past_blocks=past_blocks,
                                    block_size=block_size, keep_recent=_keep_recent, want_keep_kv=timing)
         src = keep_block_kv_preprojected if keep_block_kv_preprojected is not None else keep_block
+        if indexed_impl == "fi_zero_copy_per_query":
+            src = keep_block  # the per-query route ignores a KV-head mask, like the reference (:863-871)
         if valid_block is not None and keep_block_kv_preprojected is None:
             src = src & valid_block.to(torch.bool)
         src = src if src.dtype in (torch.bool, torch.uint8) else src.to(torch.bool)
-        return ops.union_table(mask=src, num_kv_heads=num_kv_heads, kv_blocks=kv_blocks, past_blocks=past_blocks,
+        return ops.union_table(mask=src, num_kv_heads=table_rows, kv_blocks=kv_blocks, past_blocks=past_blocks,
                                block_size=block_size, keep_recent=_keep_recent, want_keep_kv=timing)
 
     table, index_ms = _timed(_build, timing)
     kv = _kv_view(key_states, value_states, k_hf, v_hf)
+    if rows_per_kv > 1:
+        kv = kv.with_head_div(rows_per_kv)
     out, attn_ms = _timed(
-        lambda: ops.attn_compact(query_states, kv, kv_len, num_kv_heads, table.block_idx, table.counts,
+        lambda: ops.attn_compact(query_states, kv, kv_len, table_rows, table.block_idx, table.counts,
                                  block_size=block_size, softmax_scale=softmax_scale),
         timing,
     )

@@ -54,6 +54,17 @@ class KvCacheView:
     num_pages: int
     pages_per_seq: int
     page_table: Optional[torch.Tensor] = None  # int32 [B, pages_per_seq]
+    head_div: int = 0  # > 1: block-table row r reads KV head r // head_div (see ``with_head_div``)
+
+    def with_head_div(self, rows_per_kv_head: int) -> "KvCacheView":
+        """The same cache addressed by ``rows_per_kv_head`` block-table rows per KV head: per-query-head
+        tables (``rows_per_kv_head = G``) or query-sub-group tables (``G // sub-group size``), the
+        reference's ``fi_zero_copy_per_query`` / ``fi_zero_copy_subgroup`` routes.  Only
+        ``attn_compact`` accepts such a view."""
+        if rows_per_kv_head < 1:
+            raise ValueError("rows_per_kv_head must be positive")
+        import dataclasses
+        return dataclasses.replace(self, head_div=int(rows_per_kv_head))
 
     @staticmethod
     def from_seq_first(k: torch.Tensor, v: torch.Tensor) -> "KvCacheView":
@@ -92,7 +103,7 @@ class KvCacheView:
 
     def to_c(self) -> _lib.KvLayout:
         return _lib.KvLayout(self.k.data_ptr(), self.v.data_ptr(), self.page_stride, self.token_stride,
-                             self.head_stride, self.page_size, self.num_pages, self.pages_per_seq, 0,
+                             self.head_stride, self.page_size, self.num_pages, self.pages_per_seq, self.head_div,
                              _ptr(self.page_table))
 
 

@@ -77,7 +77,11 @@ typedef struct ca_kv_layout {
   int32_t page_size;     /* tokens per page, multiple of 64 */
   int32_t num_pages;     /* physical pages addressable from k / v */
   int32_t pages_per_seq; /* logical pages per sequence */
-  int32_t reserved;
+  int32_t head_div;      /* 0 or 1: table row r of a batch entry reads KV head r.  d > 1: row r reads KV head
+                            r / d - per-query-head (d = G) or query-sub-group (d = G / sub-group size) block
+                            tables, the reference's fi_zero_copy_per_query / fi_zero_copy_subgroup routes
+                            (compact_attn/kernels/varlen/flashinfer_zero_copy_prefill.py:761, 930).  Read by
+                            ca_attn_compact only; the other entry points require 0 or 1. */
   const int32_t* page_table; /* [B, pages_per_seq] int32 or NULL */
 } ca_kv_layout;
 
