@@ -57,6 +57,7 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=1234 + 3)
     ap.add_argument("--no-dense", action="store_true", help="skip the dense comparator")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="skip the CUDA-graph replay of the step")
     ap.add_argument("--dependent-launch", action="store_true",
                     help="enqueue programmatic dependent launches instead of plain ones (for A/B timing)")
     return ap.parse_args()
@@ -292,6 +293,27 @@ def run_native(args):
         "path_frac_of_roofline": round(max(t_tensor, t_hbm) * 1e3 / ms_per_step, 4),
     }
 
+    # ---- the same step replayed from CUDA graphs (informational; `value` stays the eager loop) ----
+    graph_us = None
+    if world == 1 and not args.no_graph:
+        try:
+            from compactattention_b200.chunk_driver import capture_step
+            graphs = [capture_step(lambda L=L: step(L)) for L in layers]
+            for i in range(4):
+                graphs[i % len(graphs)].replay()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            g0.record()
+            for i in range(args.steps):
+                graphs[i % len(graphs)].replay()
+            g1.record()
+            torch.cuda.synchronize()
+            graph_us = g0.elapsed_time(g1) / args.steps * 1e3
+            del graphs
+        except Exception as exc:  # graph capture is optional evidence, never the measured path
+            graph_us = None
+            print(f"[bench] graph replay not timed: {exc!r}", file=sys.stderr)
+
     # ---- dense comparator: same shape, same kernel, every past block ----
     dense_us = None
     if not args.no_dense:
@@ -391,6 +413,7 @@ def run_native(args):
             "l2": f"steps rotate over {len(layers)} layer states ({len(layers) * 2 * K * hkv * D * 2 / 2**30:.1f} GiB of KV), more than L2",
             "launches_per_step": launches / args.steps,
             "programmatic_dependent_launch": args.dependent_launch,
+            "step_replayed_from_cuda_graph_us": None if graph_us is None else round(graph_us, 1),
             "dense_same_shape_us": None if dense_us is None else round(dense_us, 1),
             "speedup_vs_dense": None if dense_us is None else round(dense_us / value_us, 2),
             "dense_flash_attn2_same_shape_us": None if ref_dense_us is None else round(ref_dense_us, 1),

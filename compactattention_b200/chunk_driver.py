@@ -111,3 +111,27 @@ def select_and_attend(
     out = ops.attn_compact(q, kv, kv_len, num_kv_heads, table.block_idx, table.counts, block_size=block_size,
                            softmax_scale=softmax_scale, out=out, status=status)
     return out, table
+
+
+def capture_step(fn, warmup: int = 2) -> "torch.cuda.CUDAGraph":
+    """Captures ``fn()`` — a fixed sequence of this library's launches on pre-allocated buffers, e.g.
+    selector scores -> row rule -> Block-Union table -> attention at one chunk position — into a CUDA
+    graph and returns it; ``graph.replay()`` then enqueues the whole step with one host call.
+
+    The entry points need nothing special for this: they allocate nothing, never synchronise, and
+    their per-device attributes and the attention workspace of the capturing stream are set up by
+    the warm-up calls, which run on a side stream before the capture as torch requires.  A step is
+    only replayable while its shapes hold (the chunk position is baked into the launch parameters),
+    which is the case for a layer stack at one chunk position and for a benchmark loop.
+    """
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(max(warmup, 1)):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    return graph
+

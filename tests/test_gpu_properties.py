@@ -193,3 +193,40 @@ def test_programmatic_launch_does_not_change_results(ops):
         _lib.set_programmatic_launch(False)
     for a, b in zip(*results):
         assert torch.equal(a, b)
+
+
+def test_step_replays_from_a_cuda_graph(ops):
+    """Selection + table + attention captured once and replayed: same bits, table and output as the
+    eager launches, also after the inputs changed in place."""
+    from compactattention_b200.chunk_driver import capture_step
+    g = torch.Generator().manual_seed(5)
+    Q, K, Hq, Hkv, D, bs = 256, 8192, 8, 2, 128, 64
+    Pb, Kb = (K - Q) // bs, K // bs
+    q = torch.randn((1, Q, Hq, D), generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn((1, K, Hkv, D), generator=g).to(torch.bfloat16).cuda()
+    v = torch.randn((1, K, Hkv, D), generator=g).to(torch.bfloat16).cuda()
+    score = torch.randn((1, Hq, Q // bs, Kb), generator=g).cuda()
+    kv = ops.KvCacheView.from_seq_first(k, v)
+    bits = ops.select_rows(score, Pb, "topk", topk_ratio=(1, 5), sink=1, local=2)
+    table = ops.union_table(bits=bits, num_kv_heads=Hkv, kv_blocks=Kb, past_blocks=Pb, block_size=bs)
+    out = torch.empty_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def step():
+        ops.select_rows(score, Pb, "topk", topk_ratio=(1, 5), sink=1, local=2, bits=bits)
+        ops.union_table(bits=bits, num_kv_heads=Hkv, kv_blocks=Kb, past_blocks=Pb, block_size=bs, out=table)
+        ops.attn_compact(q, kv, K, Hkv, table.block_idx, table.counts, out=out, status=status)
+
+    graph = capture_step(step)
+    for trial in range(2):
+        step()
+        torch.cuda.synchronize()
+        want = (bits.clone(), table.block_idx.clone(), table.counts.clone(), out.clone())
+        bits.zero_(), table.block_idx.zero_(), table.counts.zero_(), out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        for a, b in zip(want, (bits, table.block_idx, table.counts, out)):
+            assert torch.equal(a, b)
+        score.copy_(torch.randn(score.shape, generator=g))   # new scores, same buffers: the graph follows
+        q.copy_(torch.randn(q.shape, generator=g).to(torch.bfloat16))
