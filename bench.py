@@ -72,7 +72,10 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons during the timed region."""
+    """Samples the SM clock and the throttle reasons DURING the timed region.  The region lasts tens of
+    milliseconds, so the samples come from NVML inside this process (about one per millisecond, read
+    only); ``nvidia-smi -lms`` (one sample per 100 ms at best) is the fallback when NVML cannot be
+    loaded."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -80,8 +83,44 @@ class ClockSampler:
     def __init__(self, device_index: int):
         self.rows, self.proc = [], None
         self.device_index = device_index
+        self.nvml, self.handle, self.samples, self.stop_flag = None, None, [], False
+
+    def _open_nvml(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = None
+            try:
+                uuid = str(torch.cuda.get_device_properties(self.device_index).uuid)
+                handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(self.device_index)
+            self.nvml, self.handle = pynvml, handle
+            return True
+        except Exception:
+            self.nvml = None
+            return False
+
+    def _poll_nvml(self):
+        nv, h = self.nvml, self.handle
+        while not self.stop_flag:
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                power = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                self.samples.append((sm, reasons, power))
+            except Exception:
+                break
+            time.sleep(0.002)
 
     def start(self):
+        if self._open_nvml():
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                                           "-lms", "100", "-i", str(self.device_index)], stdout=subprocess.PIPE, text=True)
@@ -95,6 +134,21 @@ class ClockSampler:
             self.rows.append([x.strip() for x in line.split(",")])
 
     def stop(self):
+        if self.nvml is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            nv = self.nvml
+            try:
+                mx = float(nv.nvmlDeviceGetMaxClockInfo(self.handle, nv.NVML_CLOCK_SM))
+            except Exception:
+                mx = None
+            names = (("hw_slowdown", nv.nvmlClocksEventReasonHwSlowdown), ("hw_thermal_slowdown", nv.nvmlClocksEventReasonHwThermalSlowdown),
+                     ("sw_thermal_slowdown", nv.nvmlClocksEventReasonSwThermalSlowdown), ("sw_power_cap", nv.nvmlClocksEventReasonSwPowerCap),
+                     ("hw_power_brake_slowdown", nv.nvmlClocksEventReasonHwPowerBrakeSlowdown))
+            sm = [float(x[0]) for x in self.samples]
+            reasons = sorted({n for x in self.samples for n, bit in names if x[1] & bit})
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "samples": len(sm),
+                    "power_w_max": round(max((x[2] for x in self.samples), default=0.0), 1), "source": "nvml", "reasons": reasons}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -113,7 +167,7 @@ class ClockSampler:
                 if len(r) > idx and r[idx].lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "source": "nvidia-smi", "reasons": sorted(reasons)}
 
 
 def make_layer_inputs(seed, kv_len, chunk, hq, hkv, device):
@@ -293,27 +347,6 @@ def run_native(args):
         "path_frac_of_roofline": round(max(t_tensor, t_hbm) * 1e3 / ms_per_step, 4),
     }
 
-    # ---- the same step replayed from CUDA graphs (informational; `value` stays the eager loop) ----
-    graph_us = None
-    if world == 1 and not args.no_graph:
-        try:
-            from compactattention_b200.chunk_driver import capture_step
-            graphs = [capture_step(lambda L=L: step(L)) for L in layers]
-            for i in range(4):
-                graphs[i % len(graphs)].replay()
-            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            g0.record()
-            for i in range(args.steps):
-                graphs[i % len(graphs)].replay()
-            g1.record()
-            torch.cuda.synchronize()
-            graph_us = g0.elapsed_time(g1) / args.steps * 1e3
-            del graphs
-        except Exception as exc:  # graph capture is optional evidence, never the measured path
-            graph_us = None
-            print(f"[bench] graph replay not timed: {exc!r}", file=sys.stderr)
-
     # ---- dense comparator: same shape, same kernel, every past block ----
     dense_us = None
     if not args.no_dense:
@@ -387,6 +420,28 @@ def run_native(args):
         tt = torch.tensor([e2e_us], dtype=torch.float64, device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         e2e_us = float(tt[0])
+    # ---- the same step replayed from CUDA graphs (informational, last of all so that a failed
+    # capture cannot touch a required number; `value` stays the eager loop) ----
+    graph_us = None
+    if world == 1 and not args.no_graph:
+        try:
+            from compactattention_b200.chunk_driver import capture_step
+            graphs = [capture_step(lambda L=L: step(L)) for L in layers]
+            for i in range(4):
+                graphs[i % len(graphs)].replay()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            g0.record()
+            for i in range(args.steps):
+                graphs[i % len(graphs)].replay()
+            g1.record()
+            torch.cuda.synchronize()
+            graph_us = g0.elapsed_time(g1) / args.steps * 1e3
+            del graphs
+        except Exception as exc:  # graph capture is optional evidence, never the measured path
+            graph_us = None
+            print(f"[bench] graph replay not timed: {exc!r}", file=sys.stderr)
+
     h2d = (Q * hq * D + 2 * Q * hkv * D) * 2
     d2h = Q * hq * D * 2
 
