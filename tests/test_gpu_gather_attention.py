@@ -99,6 +99,8 @@ def test_attention_golden(ops, golden):
     (1, 128, 1152, 2, 2, 64, 0.0, torch.bfloat16, "seq"),       # nothing selected: chunk only
     (1, 192, 1216, 16, 2, 64, 1.0, torch.bfloat16, "paged"),    # everything selected, G = 8
     (1, 2048, 6144, 8, 8, 64, 0.5, torch.bfloat16, "seq"),      # long chunk, G = 1
+    (1, 1024, 131072, 4, 1, 64, 0.2, torch.bfloat16, "seq"),    # the benchmark's size for one KV head (a TP8 rank):
+                                                                # 16 work units cut over all SMs, ~9 segments merged per unit
 ])
 def test_attention_random(ops, B, Q, K, Hq, Hkv, bs, density, dtype, layout):
     g = torch.Generator().manual_seed(Q * 7 + K)
