@@ -99,3 +99,10 @@ def test_programmatic_launch_toggle_is_host_state_only():
     assert was is False           # plain launches by default
     assert _lib.set_programmatic_launch(False) is True
     assert _lib.set_programmatic_launch(False) is False
+
+
+def test_measurement_drivers_import_without_a_gpu():
+    """The drivers quoted in profiles/ must at least import and parse their arguments on a CPU box."""
+    import importlib
+    for name in ("sweep", "kernel_case", "cycle_accounting", "chunk_driver", "prefill_sparse.llama.run_prefill"):
+        importlib.import_module(f"compactattention_b200.{name}")
