@@ -101,6 +101,8 @@ def test_attention_golden(ops, golden):
     (1, 2048, 6144, 8, 8, 64, 0.5, torch.bfloat16, "seq"),      # long chunk, G = 1
     (1, 1024, 131072, 4, 1, 64, 0.2, torch.bfloat16, "seq"),    # the benchmark's size for one KV head (a TP8 rank):
                                                                 # 16 work units cut over all SMs, ~9 segments merged per unit
+    (1, 256, 131072, 4, 1, 64, None, torch.bfloat16, "seq"),    # 4 dense units over all SMs: ~37 segments per unit, more
+                                                                # than the merge kernel caches weights for
 ])
 def test_attention_random(ops, B, Q, K, Hq, Hkv, bs, density, dtype, layout):
     g = torch.Generator().manual_seed(Q * 7 + K)
