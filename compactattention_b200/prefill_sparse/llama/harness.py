@@ -53,6 +53,8 @@ class ShardedMLP(nn.Module):
 
 
 class DecoderLayer(nn.Module):
+    _graph_pool = None
+
     def __init__(self, config, layer_idx, selector, shard):
         super().__init__()
         cls = LlamaSeerAttentionChunkedDense if selector == "gate" else LlamaFlashPrefillCompactAttnAttention
@@ -60,6 +62,14 @@ class DecoderLayer(nn.Module):
         self.mlp = ShardedMLP(config, shard.world)
         self.input_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps)
+        self.graph_mlp = False   # set by the driver: replay the MLP half of the layer from a CUDA graph
+        self._mlp_graph = None
+
+    def _mlp_local(self, x, attn):
+        """Residual add, norm and this rank's slice of the MLP (no collective): ``(x + attn, partial MLP output)``."""
+        x = x + attn
+        h = self.post_attention_layernorm(x)
+        return x, self.mlp.down_proj(F.silu(self.mlp.gate_proj(h)) * self.mlp.up_proj(h))
 
     def forward(self, x, position_embeddings, cache, block_position_embeddings):
         kwargs = {}
@@ -67,8 +77,32 @@ class DecoderLayer(nn.Module):
             kwargs["block_position_embeddings"] = block_position_embeddings
         attn = self.self_attn(self.input_layernorm(x), position_embeddings, None, past_key_value=cache, **kwargs)[0]
         self.self_attn.wait_pending_reduce()
-        x = x + attn
-        return x + self.mlp(self.post_attention_layernorm(x))
+        if not self.graph_mlp:
+            x = x + attn
+            return x + self.mlp(self.post_attention_layernorm(x))
+        # The residual + norm + MLP half of the layer has the same shapes in every chunk: its local part
+        # (no collective inside the capture) is captured once per layer and replayed, one host call
+        # instead of eight; the all-reduce of the partial MLP output and the last add stay eager.
+        g = self._mlp_graph
+        if g is None or g[1].shape != x.shape:
+            xin, ain = torch.empty_like(x), torch.empty_like(attn)
+            xin.copy_(x), ain.copy_(attn)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._mlp_local(xin, ain)   # warm-up outside the capture (cuBLAS workspaces)
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            if DecoderLayer._graph_pool is None:   # the layers replay one after the other: one pool for all
+                DecoderLayer._graph_pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(graph, pool=DecoderLayer._graph_pool):
+                x2, part = self._mlp_local(xin, ain)
+            g = self._mlp_graph = (graph, xin, ain, x2, part)
+        graph, xin, ain, x2, part = g
+        xin.copy_(x), ain.copy_(attn)
+        graph.replay()
+        tp.reduce_layer_output(part)
+        return x2 + part
 
 
 class LlamaCompactAttnStack(nn.Module):

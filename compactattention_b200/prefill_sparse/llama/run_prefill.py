@@ -33,6 +33,8 @@ def main():
     ap.add_argument("--rule", choices=["topk", "synthetic_topk", "threshold"], default="synthetic_topk",
                     help="synthetic_topk imposes the union density exactly (random-init gates do not agree across heads)")
     ap.add_argument("--dense", action="store_true", help="force dense attention in every chunk (comparator)")
+    ap.add_argument("--graph-mlp", action="store_true",
+                    help="replay the local part of the residual + norm + MLP half of every layer from a CUDA graph")
     ap.add_argument("--seed", type=int, default=1234 + 4)
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -48,6 +50,8 @@ def main():
     shard = tp.HeadShard(world, rank, cfg.num_attention_heads, cfg.num_key_value_heads)
     model = LlamaCompactAttnStack(cfg, args.selector, shard).to(torch.bfloat16).to(dev)
     model.init_weights(seed=args.seed)
+    for layer in model.layers:
+        layer.graph_mlp = args.graph_mlp
     # token ids seeded like the reference's synthetic prompts (seed + seq_len * 104729)
     g = torch.Generator().manual_seed(args.seed + args.prompt * 104729)
     ids = torch.randint(0, cfg.vocab_size, (1, args.prompt), generator=g).to(dev)
@@ -81,7 +85,8 @@ def main():
     if rank == 0:
         print(json.dumps({
             "workload": f"{args.layers}-layer Llama-3.1-8B-shaped stack, prompt {args.prompt}, chunk {args.chunk}, "
-                        f"selector {args.selector}/{args.rule} {args.topk:.0%}{' (dense forced)' if args.dense else ''}, tp{world}",
+                        f"selector {args.selector}/{args.rule} {args.topk:.0%}{' (dense forced)' if args.dense else ''}"
+                        f"{', MLP half from CUDA graphs' if args.graph_mlp else ''}, tp{world}",
             "prefill_ms": round(vals[0], 2), "chunks": n_chunks,
             "attn_per_chunk_ms": round(vals[1] / n_chunks, 3),
             "attn_last_chunk_ms": round(vals[2], 3),
