@@ -10,7 +10,7 @@ used as a fallback for, the product path.
 Pinning: the reference ships no tests or golden vectors for this path.  The restatements below are
 pinned against the reference's own Python functions executed on seeded inputs
 (``tests/golden/make_golden.py`` imports them and writes the fixtures that
-``tests/test_oracle_golden.py`` replays).  Two rules have no counterpart in the reference and are
+``tests/test_oracle_golden.py`` replays), RoPE (``apply_rotary_pos_emb``) included.  Two rules have no counterpart in the reference and are
 defined here alone ("parity unpinned" for them): the cumulative-mass rule and the tie order of the
 per-row top-k rule (lower block index wins).
 
