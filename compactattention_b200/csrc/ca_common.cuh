@@ -59,6 +59,22 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 std::atomic<int>& programmatic_launch_flag();
 
 #ifdef __CUDACC__
+// `dependent`: enqueue as a programmatic dependent launch whatever the process-wide setting says
+// (used for a kernel that always follows another kernel of the same entry point).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_as(bool dependent, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (dependent || programmatic_launch_flag().load(std::memory_order_relaxed) != 0) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                  Args&&... args) {
