@@ -106,3 +106,20 @@ def test_measurement_drivers_import_without_a_gpu():
     import importlib
     for name in ("sweep", "kernel_case", "cycle_accounting", "chunk_driver", "prefill_sparse.llama.run_prefill"):
         importlib.import_module(f"compactattention_b200.{name}")
+
+
+def test_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` runs the oracle port on the host cores and prints one JSON line with
+    the keys the benchmark contract names (no GPU needed)."""
+    import json
+    import subprocess
+    import sys
+
+    out = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=600, cwd=str(ROOT))
+    assert out.returncode == 0, out.stderr[-500:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unit"] == "us" and line["higher_is_better"] is False
+    assert line["metric"].startswith("per-chunk attn latency") and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"] == {"value": line["value"], "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
