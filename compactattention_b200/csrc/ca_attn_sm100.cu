@@ -846,7 +846,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 // independent, so several are in flight per thread.  (The first form of this kernel, one CTA per
 // (slot, tile) with the weights recomputed inside the column loop, took 70-80 us for the 16 units
 // of a tensor-parallel rank with one KV head - longer than the attention kernel itself.)
-constexpr int kCombineParts = 8;                        // column parts per tile
+#ifndef CA_ATTN_COMBINE_PARTS
+#define CA_ATTN_COMBINE_PARTS 8
+#endif
+// Measured (us, attention + merge): 1 KV head 95.3 / 87.4 / 85.4 with 4 / 8 / 16 parts, 4 KV heads
+// 229.5 / 227 / 235, a small shape with whole units 30.4 / 30.8 / 32.9: 8 is the balanced choice.
+constexpr int kCombineParts = CA_ATTN_COMBINE_PARTS;    // column parts per tile (16 must be divisible by it)
 constexpr int kCombineC8 = kHeadDim / 8 / kCombineParts;  // 8-column groups per part
 constexpr int kCombineMaxChain = 32;                    // segments whose weights are cached in shared memory
 
