@@ -46,7 +46,12 @@ constexpr int kMaxRows = 1024;  // (batch x kv heads) rows per launch
 constexpr int kMaxSegs = 64;    // segments planned per batch
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; lazy accumulator rescale
 constexpr int kMinSpanSteps = 8;           // shortest span worth a CTA of its own when units are cut
-constexpr int kMinUnitStepsToCut = 24;     // average KV steps per unit below which units stay whole
+#ifndef CA_ATTN_MIN_UNIT_STEPS
+#define CA_ATTN_MIN_UNIT_STEPS 24
+#endif
+// (units of 27-30 KV steps: 44 us cut against 66 us whole, so the threshold must stay below that;
+// units of ~6 steps: 22 us whole against 45 us cut)
+constexpr int kMinUnitStepsToCut = CA_ATTN_MIN_UNIT_STEPS;  // average KV steps per unit below which units stay whole
 // Measured on B200 (sustained 300-launch loop, 128K context, 20 % density): handing P to the MMA warp
 // in two halves 434 us, in one piece 450 us; packed fp32 pairs for the scale and the row sum 421 us;
 // a polynomial exp2 on the FMA pipe (packed, 2 to 8 of every 16 pairs) 432 to 464 us.  The tensor
