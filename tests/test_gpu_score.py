@@ -31,6 +31,23 @@ def rel_err(got, want):
     return ((got - want).abs() / scale).max().item()
 
 
+def fp_row_err(got, want):
+    """Training-free scores are [B, Qb, Kb, Hq]: a row of the selection rule runs over the key blocks
+    (dim 2), and the rule cuts at alpha x the row's maximum, so the error is bounded against it."""
+    scale = want.abs().amax(dim=2, keepdim=True).clamp_min(1e-30)
+    return ((got - want).abs() / scale).max().item()
+
+
+def check_alpha_rule_on_gpu_scores(ops, norm_gpu, Q, K, bs, G):
+    """The alpha x row-max rule on the scores the GPU produced: the kernel's packed bits against the
+    oracle's rule on the same (read-back) numbers, bit for bit."""
+    Qb, Kb = norm_gpu.shape[1], norm_gpu.shape[2]
+    bits = ops.select_rows(norm_gpu.permute(0, 3, 1, 2), Kb - Qb, "alpha_rowmax", alpha=0.06, sink=2, local=4)
+    got = ops.unpack_bits(bits, Kb).any(dim=2).cpu()  # [B, Hq, Kb]
+    keep_q, _, _ = co.flashprefill_keep_rowwise(norm_gpu.cpu(), Q, K, bs, G, 2, 4, 0.06, 0, 0)
+    assert torch.equal(got, keep_q)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("L,bs", [(1024, 64), (674, 64), (256, 128), (64, 64)])
 def test_pool_blocks(ops, dtype, L, bs):
@@ -40,10 +57,21 @@ def test_pool_blocks(ops, dtype, L, bs):
         got = ops.pool_blocks(x.cuda(), bs, kinds).cpu()
         want = co.pool_blocks(x.float(), bs, kinds)
         assert torch.allclose(got, want, rtol=1e-5, atol=1e-6), kinds
-    # mean-K as the training-free selector stores it: in the input dtype
+    # mean-K as the training-free selector stores it, in the input dtype: the fp32 mean rounded once,
+    # i.e. bit-identical to rounding the kernel's own fp32 result, which in turn is within fp32
+    # summation-order error of the oracle's
     got = ops.pool_blocks(x.cuda(), bs, ("avg",), out_dtype=dtype).cpu()
+    got32 = ops.pool_blocks(x.cuda(), bs, ("avg",)).cpu()
     assert got.dtype == dtype
-    assert torch.equal(got, co.mean_pool_blocks(x, bs)) or torch.allclose(got.float(), co.mean_pool_blocks(x, bs).float(), rtol=1e-2, atol=1e-3)
+    assert torch.equal(got, got32.to(dtype))
+    want = co.mean_pool_blocks(x, bs)
+    assert torch.allclose(got32, co.pool_blocks(x.float(), bs, ("avg",)), rtol=1e-5, atol=1e-6)
+    if dtype != torch.float32:
+        # against the oracle's stored value: equal except where the two fp32 means straddle a rounding
+        # boundary of the 16-bit type (then one unit in the last place apart)
+        assert (got != want).float().mean().item() < 1e-3
+        ulp = want.float().abs().clamp_min(1e-3) * (2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10)
+        assert ((got.float() - want.float()).abs() <= ulp).all()
 
 
 def test_pool_append_into_cache(ops):
@@ -158,7 +186,8 @@ def test_flashprefill_score_golden(ops, golden):
     assert torch.equal(torch.isfinite(mx.cpu()), fin)
     assert torch.allclose(mx.cpu()[fin], ref_mx[fin], rtol=1e-4, atol=1e-4)
     assert torch.allclose(raw.cpu()[fin], ref_sc[fin], rtol=1e-3, atol=1e-5)
-    assert ((norm.cpu() - ref_norm).abs().max() / ref_norm.max()).item() < REL
+    assert fp_row_err(norm.cpu(), ref_norm) < REL
+    check_alpha_rule_on_gpu_scores(ops, norm, Q, K, bs, Hq // Hkv)
 
 
 @pytest.mark.parametrize("Q,K,Hq,Hkv,bs,dtype", [(1024, 8192, 8, 2, 64, torch.bfloat16), (512, 4096, 4, 4, 128, torch.bfloat16),
@@ -176,4 +205,6 @@ def test_flashprefill_score_random(ops, Q, K, Hq, Hkv, bs, dtype):
     fin = torch.isfinite(o_mx)
     assert torch.equal(torch.isfinite(mx.cpu()), fin)
     assert torch.allclose(mx.cpu()[fin], o_mx[fin], rtol=1e-4, atol=1e-4)
-    assert ((norm.cpu() - o_norm).abs().max() / o_norm.max()).item() < REL
+    assert fp_row_err(norm.cpu(), o_norm) < REL
+    if Q % bs == 0 and K % bs == 0:
+        check_alpha_rule_on_gpu_scores(ops, norm, Q, K, bs, Hq // Hkv)
