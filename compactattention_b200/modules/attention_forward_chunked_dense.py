@@ -20,6 +20,17 @@ Differences a caller can observe, all deliberate:
   block size and head dims other than 128 raise ``NotImplementedError`` instead of falling down the
   reference's ladder of slower paths; the reference only takes its indexed path under the same
   preconditions (:993-999, :2267-2277).
+* ``block_attention_mask=None`` selects with block-causal validity for a chunk at the end of the cache
+  (row i sees key block j iff j <= Pb + i).  The reference's generic mask builder uses
+  ``torch.tril`` over the ``[Qb, Kb]`` slice instead (j <= i, :374), which is only meaningful for a
+  first chunk; every model integration passes the mask, and with a mask the two agree.
+* ``keep_recent_blocks`` forces the last N columns on; the reference forces the last N *valid*
+  columns (:398-401).  The two agree whenever the last columns are visible to some row, which holds
+  for every block-causal mask.
+* The reference's debug switches ``SEERATTN_DEBUG_COMPACTATTN_QUERY_BLOCK_MODE=last`` (only the chunk's
+  last Q-block votes, :377-379), ``..._KV_HEAD_MODE=first`` and ``..._DISABLE_CURRENT_OPEN`` (:127-141)
+  are refused with ``NotImplementedError``; ``..._THRESHOLD_OVERRIDE`` and ``..._KEEP_RECENT_OVERRIDE``
+  are honoured.
 * ``attention_mask`` is assumed all-ones when given (checking would need a device-to-host sync,
   which the reference performs once and caches, :529-543); pass ``None`` for the common case.
 """
@@ -61,6 +72,30 @@ def _effective_threshold(threshold):
         except ValueError:
             pass
     return threshold
+
+
+def _effective_keep_recent(default: int) -> int:
+    """``SEERATTN_DEBUG_COMPACTATTN_KEEP_RECENT_OVERRIDE`` is honoured like the reference (:142-150)."""
+    raw = os.environ.get("SEERATTN_DEBUG_COMPACTATTN_KEEP_RECENT_OVERRIDE")
+    if raw is None:
+        return int(default)
+    try:
+        return max(int(raw), 0)
+    except ValueError:
+        return int(default)
+
+
+def _refuse_debug_modes() -> None:
+    """The reference's debug switches that change which blocks are selected (:127-141) have no
+    counterpart in the kernels; running with one of them set would silently select differently."""
+    def mode(name):
+        return os.environ.get(name, "").strip().lower()
+    if mode("SEERATTN_DEBUG_COMPACTATTN_QUERY_BLOCK_MODE") == "last":
+        raise NotImplementedError("SEERATTN_DEBUG_COMPACTATTN_QUERY_BLOCK_MODE=last is not supported by the B200 path")
+    if mode("SEERATTN_DEBUG_COMPACTATTN_KV_HEAD_MODE") == "first":
+        raise NotImplementedError("SEERATTN_DEBUG_COMPACTATTN_KV_HEAD_MODE=first is not supported by the B200 path")
+    if mode("SEERATTN_DEBUG_COMPACTATTN_DISABLE_CURRENT_OPEN") in {"1", "true", "yes", "on"}:
+        raise NotImplementedError("SEERATTN_DEBUG_COMPACTATTN_DISABLE_CURRENT_OPEN is not supported by the B200 path")
 
 
 def _kv_dims(key_states, kv_len: Optional[int]):
@@ -254,6 +289,8 @@ def chunked_prefill_column_dense_attention_forward(
         raise ValueError("attn_gate_score is required for chunked column-dense attention.")
     _check_common(query_states, key_states, value_states, query_length, block_size, indexed_impl, kv_len)
     threshold = _effective_threshold(threshold)
+    _refuse_debug_modes()
+    keep_recent_blocks = _effective_keep_recent(keep_recent_blocks)
     if isinstance(threshold, torch.Tensor):
         if threshold.numel() != 1:
             raise NotImplementedError("per-batch threshold tensors are not supported by the B200 path")
@@ -281,6 +318,7 @@ def chunked_prefill_column_dense_attention_forward(
         raise NotImplementedError("gate scores must at least cover the chunk's own key blocks")
     valid = None
     if block_attention_mask is not None:
+        # nonzero = visible, the conversion the reference's mask builder applies (:372)
         valid = block_attention_mask[..., -q_blocks:, -score_blocks:].to(torch.bool)
 
     def _select():

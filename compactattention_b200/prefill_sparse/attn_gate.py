@@ -95,19 +95,37 @@ class AttnGate(nn.Module):
             k = ops.gate_project(k.to(torch.float32).contiguous(), None, cos, sin)
         return q, k
 
+    @staticmethod
+    def block_mask_to_valid(attention_mask: torch.Tensor) -> torch.Tensor:
+        """The reference accepts two mask forms (prefill_sparse/attn_gate.py:196-199): bool (True =
+        visible) and additive floating point (0 = visible, finfo.min / -inf = masked, added to the
+        logits).  Both become a bool validity mask here; an additive mask must therefore hold only
+        zeros and large negative values.  Integer masks are refused (their meaning is ambiguous)."""
+        if attention_mask.dtype == torch.bool:
+            return attention_mask
+        if attention_mask.is_floating_point():
+            return attention_mask == 0
+        raise TypeError(f"block attention mask must be bool or floating point (additive), got {attention_mask.dtype}")
+
     def score_compressed_blocks(self, q, k, attention_mask, use_softmax: bool = True) -> torch.Tensor:
-        """``[B, Hq, Qb, Kb]`` float32 scores; ``attention_mask`` is the block mask ``[B, 1, Qb, Kb]``
-        (``None`` = block-causal for a chunk at the end of the cache)."""
+        """``[B, Hq, Qb, Kb]`` float32 scores; ``attention_mask`` is the block mask ``[B, 1, Qb, Kb]``,
+        bool or additive (see ``block_mask_to_valid``).  ``None`` means no masking at all, as in the
+        reference (:194-195) - every model integration passes the block-causal mask."""
         Qb, Kb = q.shape[1], k.shape[1]
-        logits = ops.gate_scores(q, k, Kb - Qb, scale=self.scale)
-        valid = None
-        if attention_mask is not None:
-            valid = attention_mask[..., -Qb:, -Kb:].to(torch.bool)
+        fill = torch.finfo(torch.float32).min
+        if attention_mask is None:
+            logits = ops.gate_scores(q, k, Kb, scale=self.scale)  # past_blocks = Kb: no entry lies above the diagonal
+            if not use_softmax:
+                return logits
+            valid = torch.ones((1, 1, 1, 1), dtype=torch.bool, device=logits.device).expand(q.shape[0], 1, Qb, Kb)
+        else:
+            logits = ops.gate_scores(q, k, Kb - Qb, scale=self.scale)
+            valid = self.block_mask_to_valid(attention_mask[..., -Qb:, -Kb:])
             if valid.dim() == 3:
                 valid = valid.unsqueeze(1)
-            logits = logits.masked_fill(~valid, torch.finfo(torch.float32).min)
-        if not use_softmax:
-            return logits
+            logits = logits.masked_fill(~valid, fill)
+            if not use_softmax:
+                return logits
         prob = torch.empty_like(logits)
         ops.select_rows(logits, Kb - Qb, "threshold", softmax=True, valid=valid, prob_out=prob)
         return prob

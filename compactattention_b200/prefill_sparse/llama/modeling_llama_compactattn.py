@@ -105,6 +105,11 @@ class CompactAttnCache:
         st = self.layers.get(idx)
         return 0 if st is None else st.kv.length
 
+    def get_mask_sizes(self, query_length: int, layer_idx: int = 0):
+        """``(kv_length, kv_offset)`` the way a HuggingFace cache reports them to the stock model's mask
+        builder: the tokens held plus the chunk about to be appended, no offset."""
+        return self.get_seq_length(layer_idx) + int(query_length), 0
+
     def selection_scratch(self, heads: int, num_kv_heads: int, q_blocks: int, block_size: int):
         """Keep bits and block table shared by every layer (the layers run one after the other on
         one stream and each consumes its table at once), sized for the longest context, so a chunk
@@ -311,7 +316,7 @@ class LlamaSeerAttentionChunkedDense(_CompactAttnBase):
             # threshold on softmax-ed gate scores, exactly the operator the reference calls
             Qb, Kb = logits.shape[2], logits.shape[3]
             prob = torch.empty_like(logits)
-            valid = None if block_attention_mask is None else block_attention_mask[..., -Qb:, -Kb:].to(torch.bool)
+            valid = None if block_attention_mask is None else self.attn_gate.block_mask_to_valid(block_attention_mask[..., -Qb:, -Kb:])
             ops.select_rows(logits, Kb - Qb, "threshold", softmax=True, valid=valid, prob_out=prob)
             attn, stats = self._do_chunked_compactattn_attention(
                 q, kv_view, kv_view, attention_mask=attention_mask, query_length=q_len, softmax_scale=self.scaling,

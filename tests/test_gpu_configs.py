@@ -100,8 +100,8 @@ def test_32k_paged_cache_training_free_selection_end_to_end(mods):
     o_raw, o_mx = co.flashprefill_block_score_raw(q, o_mean_k, K, bs)
     o_norm = co.flashprefill_normalize_scores(o_raw, o_mx)
     assert ((norm.cpu() - o_norm).abs() / o_norm.amax(dim=2, keepdim=True).clamp_min(1e-30)).max().item() < REL
-    keep_q, _, keep_kv = co.flashprefill_keep_rowwise(norm.cpu(), Q, K, bs, G, 2, 4, 0.06, 0, 0)
-    assert torch.equal(ops.unpack_bits(bits2, Kb).any(dim=2).cpu(), keep_q)
+    keep_row, _, keep_kv = co.flashprefill_keep_rowwise(norm.cpu(), Q, K, bs, G, 2, 4, 0.06, 0, 0)
+    assert torch.equal(ops.unpack_bits(bits2, Kb).cpu(), keep_row)
     idx2, counts2, _, _ = co.block_table_from_kv_keep(keep_kv, Q, K, bs)
     assert torch.equal(table2.block_idx.cpu(), idx2) and torch.equal(table2.counts.cpu(), counts2)
     check_attention(out2, co.compact_attention(q, k, v, idx2, counts2, bs))

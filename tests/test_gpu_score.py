@@ -43,9 +43,8 @@ def check_alpha_rule_on_gpu_scores(ops, norm_gpu, Q, K, bs, G):
     oracle's rule on the same (read-back) numbers, bit for bit."""
     Qb, Kb = norm_gpu.shape[1], norm_gpu.shape[2]
     bits = ops.select_rows(norm_gpu.permute(0, 3, 1, 2), Kb - Qb, "alpha_rowmax", alpha=0.06, sink=2, local=4)
-    got = ops.unpack_bits(bits, Kb).any(dim=2).cpu()  # [B, Hq, Kb]
-    keep_q, _, _ = co.flashprefill_keep_rowwise(norm_gpu.cpu(), Q, K, bs, G, 2, 4, 0.06, 0, 0)
-    assert torch.equal(got, keep_q)
+    keep_row, _, _ = co.flashprefill_keep_rowwise(norm_gpu.cpu(), Q, K, bs, G, 2, 4, 0.06, 0, 0)
+    assert torch.equal(ops.unpack_bits(bits, Kb).cpu(), keep_row)  # [B, Hq, Qb, Kb]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
