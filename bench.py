@@ -37,11 +37,6 @@ sys.path.insert(0, str(ROOT))
 
 HQ, HKV, D, BS = 32, 8, 128, 64
 METRIC = "per-chunk attn latency @128K ctx, chunk 1024"
-# DRAM bytes (read + write) of one attention launch from the ncu capture summarised in
-# profiles/attn_compact_kernel_128k_20pct.md: 123.61 MB measured on a launch whose algorithmic bytes
-# are 127.40 MB (same shape, 406 selected blocks per KV head).  K/V traffic is proportional to the
-# selected blocks, so the benchmark's launch is scaled by its own algorithmic bytes.
-NCU_ATTN_CAPTURE = {"dram_bytes": 123.61e6, "algorithmic_bytes": 127.40e6}
 
 
 def parse_args():
@@ -58,6 +53,8 @@ def parse_args():
     ap.add_argument("--no-dense", action="store_true", help="skip the dense comparator")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="skip the CUDA-graph replay of the step")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the seconds-long repeat of the timed loop")
+    ap.add_argument("--sustained-seconds", type=float, default=1.0)
     ap.add_argument("--dependent-launch", action="store_true",
                     help="enqueue programmatic dependent launches instead of plain ones (for A/B timing)")
     return ap.parse_args()
@@ -73,10 +70,11 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples the SM clock and the throttle reasons DURING the timed region.  The region lasts tens of
-    milliseconds, so the samples come from NVML inside this process (about one per millisecond, read
-    only); ``nvidia-smi -lms`` (one sample per 100 ms at best) is the fallback when NVML cannot be
-    loaded."""
+    """Samples the SM clock, power and the throttle reasons while the benchmark's timed regions run.
+    The samples come from NVML inside this process (read only), one every millisecond or two from a
+    thread that polls without sleeping long; ``nvidia-smi -lms`` (one sample per 100 ms at best) is the
+    fallback when NVML cannot be loaded.  ``mark(name)`` timestamps the region boundaries so the report
+    can say how many samples fell inside each region."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -85,6 +83,11 @@ class ClockSampler:
         self.rows, self.proc = [], None
         self.device_index = device_index
         self.nvml, self.handle, self.samples, self.stop_flag = None, None, [], False
+        self.marks = {}
+        self.started = False
+
+    def mark(self, name: str) -> None:
+        self.marks[name] = time.perf_counter()
 
     def _open_nvml(self):
         try:
@@ -112,12 +115,13 @@ class ClockSampler:
                 except Exception:
                     reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
                 power = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
-                self.samples.append((sm, reasons, power))
+                self.samples.append((sm, reasons, power, time.perf_counter()))
             except Exception:
                 break
-            time.sleep(0.002)
+            time.sleep(0.0005)
 
     def start(self):
+        self.started = True
         if self._open_nvml():
             self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
             self.thread.start()
@@ -134,6 +138,12 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([x.strip() for x in line.split(",")])
 
+    def _inside(self, begin: str, end: str):
+        t0, t1 = self.marks.get(begin), self.marks.get(end)
+        if t0 is None or t1 is None:
+            return []
+        return [x for x in self.samples if t0 <= x[3] <= t1]
+
     def stop(self):
         if self.nvml is not None:
             self.stop_flag = True
@@ -146,10 +156,22 @@ class ClockSampler:
             names = (("hw_slowdown", nv.nvmlClocksEventReasonHwSlowdown), ("hw_thermal_slowdown", nv.nvmlClocksEventReasonHwThermalSlowdown),
                      ("sw_thermal_slowdown", nv.nvmlClocksEventReasonSwThermalSlowdown), ("sw_power_cap", nv.nvmlClocksEventReasonSwPowerCap),
                      ("hw_power_brake_slowdown", nv.nvmlClocksEventReasonHwPowerBrakeSlowdown))
-            sm = [float(x[0]) for x in self.samples]
-            reasons = sorted({n for x in self.samples for n, bit in names if x[1] & bit})
-            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "samples": len(sm),
-                    "power_w_max": round(max((x[2] for x in self.samples), default=0.0), 1), "source": "nvml", "reasons": reasons}
+            timed = self._inside("timed_begin", "timed_end")
+            sus = self._inside("sustained_begin", "sustained_end")
+            load = timed + sus  # every sample taken while one of the two timed loops was running
+            sm = [float(x[0]) for x in load]
+            reasons = sorted({n for x in load for n, bit in names if x[1] & bit})
+            out = {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "samples": len(sm),
+                   "samples_in_timed_region": len(timed), "samples_in_sustained_loop": len(sus),
+                   "power_w_max": round(max((x[2] for x in load), default=0.0), 1),
+                   "power_w_median": round(statistics.median([x[2] for x in load]), 1) if load else None,
+                   "source": "nvml (in-process, while the timed loops ran)", "reasons": reasons}
+            if timed:
+                out["sm_mhz_timed_region"] = statistics.median(float(x[0]) for x in timed)
+            if sus:
+                out["sm_mhz_sustained_loop"] = statistics.median(float(x[0]) for x in sus)
+                out["sm_mhz_sustained_last_quarter"] = statistics.median(float(x[0]) for x in sus[-max(1, len(sus) // 4):])
+            return out
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -206,7 +228,7 @@ def make_layer_inputs(seed, kv_len, chunk, hq, hkv, device):
     a = torch.rand((kv_len // BS, hkv), generator=g, device=device) ** 3
     k = (k.float() + a.repeat_interleave(BS, dim=0).view(1, kv_len, hkv, 1) * x.float().view(1, 1, hkv, 128)).to(torch.bfloat16)
     q = (q.float() + 1.5 * y.float().view(1, 1, hq, 128)).to(torch.bfloat16)
-    return {"k": k, "v": v, "q": q, "wq": wq, "wk": wk, "perm": perm, "past": past}
+    return {"k": k, "v": v, "q": q, "wq": wq, "wk": wk, "perm": perm, "past": past, "q_lean": (1.5 * y.float()).to(torch.bfloat16)}
 
 
 def block_rope_tables(n_blocks, block_size, device):
@@ -216,12 +238,18 @@ def block_rope_tables(n_blocks, block_size, device):
     return ang.cos().unsqueeze(0).to(device), ang.sin().unsqueeze(0).to(device)
 
 
+def percentile(values, q):
+    """Nearest-rank percentile of a small sample (q in [0, 1])."""
+    v = sorted(values)
+    return v[min(len(v) - 1, max(0, int(math.ceil(q * len(v))) - 1))]
+
+
 def run_native(args):
-    from compactattention_b200 import _lib, ops
+    from compactattention_b200 import _lib, ops, tp
     _lib.set_programmatic_launch(args.dependent_launch)
-    from compactattention_b200.chunk_driver import GateSelectorState, SelectionRule, select_and_attend
-    from compactattention_b200.paged_cache import PagedKVCache
-    from compactattention_b200.prefill_sparse.attn_gate import ATTNGATE_CLASSES
+    from compactattention_b200.chunk_driver import GateSelectorState, SelectionRule
+    from compactattention_b200.prefill_sparse.llama.modeling_llama_compactattn import (
+        CompactAttnCache, CompactAttnLlamaConfig, LlamaSeerAttentionChunkedDense)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -233,7 +261,6 @@ def run_native(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group(backend="nccl", device_id=dev)
-    from compactattention_b200 import tp
     try:
         shard = tp.HeadShard(world, rank, HQ, HKV)
     except ValueError as exc:
@@ -245,25 +272,45 @@ def run_native(args):
     num, den = int(round(args.density * 1000)), 1000
     rule = SelectionRule(rule="topk", softmax=False, topk_ratio=(num, den), sink=1, local=2)
     cos, sin = block_rope_tables(Kb, BS, dev)
+    hidden_size = HQ * D
+
+    # The reference-facing plugin call of this workload is the attention module's forward (top-k
+    # method): hidden states in, layer output out, projections included.  Its q projection carries
+    # the per-head lean of the queries as a bias, so the module selects like the operator-level step.
+    cfg = CompactAttnLlamaConfig(hidden_size=hidden_size, num_attention_heads=HQ, num_key_value_heads=HKV, head_dim=D,
+                                 seerattn_gate_type="Qavg_Kavg", seerattn_gate_force_double=True, seerattn_gate_block_size=BS,
+                                 seerattn_sparsity_method="topk", seerattn_topk_ratio=(num, den),
+                                 seerattn_compactattn_keep_recent_blocks=2, max_position_embeddings=K, attention_bias=True)
+    inv = 1.0 / (500000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    ang = torch.arange(K - Q, K, dtype=torch.float32).view(-1, 1) * inv.view(1, -1)
+    ang = torch.cat([ang, ang], dim=-1)
+    tok_rope = (ang.cos().unsqueeze(0).to(dev).to(torch.bfloat16), ang.sin().unsqueeze(0).to(dev).to(torch.bfloat16))
 
     # ---- resident state of `layers` independent layers (each rank: its own heads) ----
     layers = []
     for li in range(args.layers):
         t = make_layer_inputs(args.seed + 1000 * li + 17 * rank, K, Q, hq, hkv, dev)
-        cache = PagedKVCache(1, K, hkv, D, dev, page_table=t["perm"].to(dev))
-        cache.append(t["k"].to(dev), t["v"].to(dev), position=0)
-        gate = ATTNGATE_CLASSES["Qavg_Kavg"](BS, D, 128, hkv, hq, force_double=True).to(dev).to(torch.bfloat16)
+        module = LlamaSeerAttentionChunkedDense(cfg, li, shard).to(dev).to(torch.bfloat16).eval()
+        g = torch.Generator(device=dev).manual_seed(args.seed + 1000 * li + 17 * rank + 7)
         with torch.no_grad():
-            gate.mask_linear_q.weight.copy_(t["wq"].to(dev))
-            gate.mask_linear_k.weight.copy_(t["wk"].to(dev))
-        sel = GateSelectorState(gate, 1, dev)
-        sel.cache.reserve(Kb)
-        k_dev = t["k"].to(dev)
-        gate.append_key_blocks(sel.cache, k_dev[:, : K - Q], (cos[:, :Pb], sin[:, :Pb]))  # past blocks
+            module.attn_gate.mask_linear_q.weight.copy_(t["wq"])
+            module.attn_gate.mask_linear_k.weight.copy_(t["wk"])
+            for lin in (module.q_proj, module.k_proj, module.v_proj, module.o_proj):
+                lin.weight.copy_(torch.randn(lin.weight.shape, generator=g, device=dev) * 0.02)
+                if lin.bias is not None:
+                    lin.bias.zero_()
+            module.q_proj.bias.copy_(t["q_lean"].reshape(-1))
+        pkv = CompactAttnCache(1, K, dev, torch.bfloat16, page_table=t["perm"])
+        st = pkv.layer(li, hkv, D)
+        st.kv.append(t["k"][:, : K - Q], t["v"][:, : K - Q], position=0)
+        st.gate = GateSelectorState(module.attn_gate, 1, dev)
+        st.gate.cache.reserve(Kb)
+        module.attn_gate.append_key_blocks(st.gate.cache, t["k"][:, : K - Q], (cos[:, :Pb], sin[:, :Pb]))  # past blocks
+        hidden = torch.randn((1, Q, hidden_size), generator=g, device=dev).to(torch.bfloat16)
         layers.append({
-            "cache": cache, "kv": cache.view(), "sel": sel, "gate": gate,
-            "q": t["q"].to(dev), "k_chunk": k_dev[:, K - Q:].contiguous(), "v_chunk": t["v"][:, K - Q:].to(dev),
-            "host": {n: (t[n][:, K - Q:] if n != "q" else t["q"]).contiguous().cpu().pin_memory() for n in ("q", "k", "v")},
+            "module": module, "pkv": pkv, "state": st, "cache": st.kv, "kv": st.kv.view(), "sel": st.gate,
+            "q": t["q"], "k_chunk": t["k"][:, K - Q:].contiguous(), "v_chunk": t["v"][:, K - Q:].contiguous(),
+            "hidden": hidden, "hidden_host": hidden.cpu().pin_memory(),
             "out": torch.empty((1, Q, hq, D), dtype=torch.bfloat16, device=dev),
             "table": ops.BlockTable(torch.empty((1, hkv, Pb), dtype=torch.int32, device=dev),
                                     torch.empty((1, hkv), dtype=torch.int32, device=dev),
@@ -272,27 +319,48 @@ def run_native(args):
             "bits": torch.empty((1, hq, Qb, ops.words_for(Kb)), dtype=torch.int32, device=dev),
             "status": torch.zeros(1, dtype=torch.int32, device=dev),
         })
-        del k_dev
+        st.kv.append(layers[-1]["k_chunk"], layers[-1]["v_chunk"], position=K - Q)
+        del t
     reduce_buf = torch.zeros((1, Q, HQ * D), dtype=torch.bfloat16, device=dev) if world > 1 else None
-    attn_events = []
+    rope_chunk = (cos[:, Pb:], sin[:, Pb:])
 
-    def step(L, record=False):
+    # ---- one step = one pass of the path for one chunk, as a list of stages (one launch each, the
+    # attention stage two when it cuts work units) so the same code runs timed as a whole and stage by stage
+    def stages(L):
         sel = L["sel"]
-        sel.cache.length = Pb  # the chunk's blocks are (re)appended at the end of the past blocks
-        logits = sel.append_and_score(L["q"], L["k_chunk"], (cos[:, Pb:], sin[:, Pb:]), (cos[:, Pb:], sin[:, Pb:]))
-        Qb_, Kb_ = logits.shape[2], logits.shape[3]
-        bits = ops.select_rows(logits, Kb_ - Qb_, rule.rule, softmax=rule.softmax, topk_ratio=rule.topk_ratio,
-                               sink=rule.sink, local=rule.local, bits=L["bits"])
-        table = ops.union_table(bits=bits, num_kv_heads=hkv, kv_blocks=Kb_, past_blocks=Pb, block_size=BS, out=L["table"])
-        if record:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-        ops.attn_compact(L["q"], L["kv"], K, hkv, table.block_idx, table.counts, block_size=BS, out=L["out"], status=L["status"])
-        if record:
-            e1.record()
-            attn_events.append((e0, e1))
+
+        def prepare():
+            sel.cache.length = Pb  # the chunk's blocks are (re)appended at the end of the past blocks
+            sel.append(L["q"], L["k_chunk"], rope_chunk, rope_chunk)
+
+        def select():
+            lg = sel.logits
+            return ops.select_rows(lg, Pb, rule.rule, softmax=rule.softmax, topk_ratio=rule.topk_ratio, sink=rule.sink,
+                                   local=rule.local, bits=L["bits"])
+
+        def table():
+            return ops.union_table(bits=L["bits"], num_kv_heads=hkv, kv_blocks=Kb, past_blocks=Pb, block_size=BS, out=L["table"])
+
+        def attention():
+            ops.attn_compact(L["q"], L["kv"], K, hkv, L["table"].block_idx, L["table"].counts, block_size=BS, out=L["out"],
+                             status=L["status"])
+
+        out = [("gate_prepare", prepare), ("gate_scores", sel.score), ("select_rows", select), ("union_table", table),
+               ("attention", attention)]
         if world > 1:
-            tp.reduce_layer_output(reduce_buf)
+            out.append(("all_reduce", lambda: tp.reduce_layer_output(reduce_buf)))
+        return out
+
+    def step(L, attn_events=None):
+        for name, fn in stages(L):
+            if name == "attention" and attn_events is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                attn_events.append((e0, e1))
+            else:
+                fn()
 
     def barrier():
         if world > 1:
@@ -300,31 +368,91 @@ def run_native(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_ranks(vals):
+        return tp.max_over_ranks(vals, dev)
+
     for i in range(max(args.warmup, 3)):
         step(layers[i % len(layers)])
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    # ---- the timed region: exactly `steps` steps, an event after every step ----
+    attn_events = []
     launches0 = _lib.launch_count()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     barrier()
-    t0.record()
+    sampler.mark("timed_begin")
+    marks[0].record()
     for i in range(args.steps):
-        step(layers[i % len(layers)], record=True)
-    t1.record()
+        step(layers[i % len(layers)], attn_events)
+        marks[i + 1].record()
     barrier()
+    sampler.mark("timed_end")
     launches = _lib.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
-    ms_total = t0.elapsed_time(t1)
-    attn_ms = statistics.mean(a.elapsed_time(b) for a, b in attn_events)
-    if world > 1:
-        import torch.distributed as dist
-        tt = torch.tensor([ms_total, attn_ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms_total, attn_ms = float(tt[0]), float(tt[1])
+    ms_total = marks[0].elapsed_time(marks[-1])
+    per_step_us = [marks[i].elapsed_time(marks[i + 1]) * 1e3 for i in range(args.steps)]
+    attn_us = [a.elapsed_time(b) * 1e3 for a, b in attn_events]
+    ms_total, attn_ms = max_ranks([ms_total, statistics.mean(attn_us) * 1e-3])
     ms_per_step = ms_total / args.steps
+    step_stats = {"mean": ms_per_step * 1e3, "median": statistics.median(per_step_us), "p10": percentile(per_step_us, 0.1),
+                  "p90": percentile(per_step_us, 0.9), "min": min(per_step_us), "max": max(per_step_us)}
+    attn_stats = {"mean": attn_ms * 1e3, "median": statistics.median(attn_us), "p10": percentile(attn_us, 0.1),
+                  "p90": percentile(attn_us, 0.9)}
+
+    # ---- sustained phase: the same loop repeated until >= 1 s has elapsed (the board reaches its
+    # power cap and the SM clock settles), clocks sampled throughout ----
+    sustained = None
+    if not args.no_sustained:
+        s_attn, n_sus = [], 0
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        sampler.mark("sustained_begin")
+        w0 = time.perf_counter()
+        s0.record()
+        while True:
+            for i in range(args.steps):
+                step(layers[i % len(layers)], s_attn)
+            n_sus += args.steps
+            torch.cuda.current_stream().synchronize()
+            go = 1.0 if time.perf_counter() - w0 < args.sustained_seconds else 0.0
+            if max_ranks([go])[0] == 0.0 or n_sus >= 100000:  # every rank leaves the loop in the same round
+                break
+        s1.record()
+        barrier()
+        sampler.mark("sustained_end")
+        sus_ms, sus_attn = max_ranks([s0.elapsed_time(s1) / n_sus, statistics.mean(a.elapsed_time(b) for a, b in s_attn[-200:])])
+        sustained = {"steps": n_sus, "step_us": round(sus_ms * 1e3, 1), "attention_us": round(sus_attn * 1e3, 1)}
+    clocks = sampler.stop() if rank == 0 else None
     status = max(int(L["status"].item()) for L in layers)
+
+    # ---- per-stage split: events between the launches of a step (a separate loop; the events cost a
+    # little, so its sum is not the value) ----
+    names = [n for n, _ in stages(layers[0])]
+    acc = {n: [] for n in names}
+    barrier()
+    rounds = []
+    for i in range(max(8, min(args.steps, 40))):
+        # no synchronisation inside the loop: while one step's attention runs, the host enqueues the next
+        # step's launches and events, so a stage's time is its time on the device, not the host's
+        evs = [torch.cuda.Event(enable_timing=True)]
+        evs[0].record()
+        for name, fn in stages(layers[i % len(layers)]):
+            fn()
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            evs.append(e)
+        rounds.append(evs)
+    torch.cuda.current_stream().synchronize()
+    for evs in rounds[2:]:
+        for j, name in enumerate(names):
+            acc[name].append(evs[j].elapsed_time(evs[j + 1]) * 1e3)
+    stage_vals = max_ranks([statistics.median(acc[n]) for n in names])
+    stage_us = {n: round(v, 1) for n, v in zip(names, stage_vals)}
+    launches_attention = _lib.launch_count()
+    stages(layers[0])[4][1]()
+    launches_attention = _lib.launch_count() - launches_attention
+    stage_us["attention_launches"] = launches_attention  # 2: the merge of cut work units ran inside the attention stage
 
     # ---- algorithmic work of one attention launch (this rank) ----
     G = hq // hkv
@@ -333,6 +461,7 @@ def run_native(args):
     flops = 4.0 * D * G * (Q * sel_blocks * BS + hkv * Q * (Q + 1) / 2.0)
     kv_bytes = 2.0 * D * 2 * (sel_blocks * BS + hkv * Q) + 2.0 * Q * hq * D * 2
     peaks = load_peaks()
+    capture = load_attention_capture()
     achieved = flops / (attn_ms * 1e-3) / 1e12
     # the slower of tensor time and HBM time bounds the launch; here it is the tensor pipe
     t_tensor = flops / (peaks["bf16_tflops"] * 1e12)
@@ -340,15 +469,19 @@ def run_native(args):
     roofline = {
         "bound": "tensor" if t_tensor >= t_hbm else "hbm",
         "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-        "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{peaks['source']} (cuBLAS bf16 burst)",
-        # for reference only: against the seconds-long cuBLAS figure (the timed loop is tens of milliseconds)
-        "frac_of_sustained_peak": round(achieved / peaks["bf16_tflops_sustained"], 4) if peaks.get("bf16_tflops_sustained") else None,
-        "traffic": round(NCU_ATTN_CAPTURE["dram_bytes"] * kv_bytes / NCU_ATTN_CAPTURE["algorithmic_bytes"]),
+        "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{peaks['source']} (cuBLAS bf16 burst; the timed region is short)",
+        "traffic": None if capture is None else round(capture["dram_bytes"] * kv_bytes / capture["algorithmic_bytes"]),
         "kernel": "attn_compact_kernel", "kernel_us": round(attn_ms * 1e3, 1),
         "algorithmic_flops": flops, "algorithmic_bytes": kv_bytes,
         "roofline_us": round(max(t_tensor, t_hbm) * 1e6, 1),
         "path_frac_of_roofline": round(max(t_tensor, t_hbm) * 1e3 / ms_per_step, 4),
     }
+    if sustained is not None and peaks.get("bf16_tflops_sustained"):
+        # the seconds-long loop against the seconds-long cuBLAS figure
+        sus_tf = flops / (sustained["attention_us"] * 1e-6) / 1e12
+        sustained["attention_tflops"] = round(sus_tf, 1)
+        sustained["frac_of_sustained_peak"] = round(sus_tf / peaks["bf16_tflops_sustained"], 4)
+        roofline["sustained"] = sustained
 
     # ---- dense comparator: same shape, same kernel, every past block ----
     dense_us = None
@@ -364,65 +497,55 @@ def run_native(args):
             ops.attn_compact(LL["q"], LL["kv"], K, hkv, None, None, block_size=BS, out=LL["out"])
         d1.record()
         barrier()
-        dense_us = d0.elapsed_time(d1) / 5 * 1e3
-        if world > 1:
-            import torch.distributed as dist
-            tt = torch.tensor([dense_us], dtype=torch.float64, device=dev)
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            dense_us = float(tt[0])
+        dense_us = max_ranks([d0.elapsed_time(d1) / 5 * 1e3])[0]
 
-    # ---- the reference's own dense comparator on the same GPU (library call, timing only) ----
-    # compact_attn/modules/dense_prefill.py:304-310 calls flash_attn_func(causal=True); the library is
-    # part of the image, not of this repository, and is only timed here, never used by the path.
-    ref_dense_us = None
+    # ---- the reference's own GPU routes on the same GPU (library calls, timing only, rank 0) ----
+    ref_gpu = {}
     if not args.no_dense and rank == 0:
-        try:
-            from flash_attn import flash_attn_func
-            kd = torch.randn((1, K, hkv, D), device=dev, dtype=torch.bfloat16)
-            vd = torch.randn((1, K, hkv, D), device=dev, dtype=torch.bfloat16)
-            qd = layers[0]["q"]
-            for _ in range(2):
-                flash_attn_func(qd, kd, vd, causal=True)
-            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            f0.record()
-            for _ in range(3):
-                flash_attn_func(qd, kd, vd, causal=True)
-            f1.record()
-            torch.cuda.synchronize()
-            ref_dense_us = f0.elapsed_time(f1) / 3 * 1e3
-            del kd, vd
-        except Exception as exc:  # the comparator is optional: absent library, unsupported device
-            ref_dense_us = None
-            print(f"[bench] flash_attn dense comparator not timed: {exc!r}", file=sys.stderr)
+        ref_gpu = time_reference_gpu_routes(layers[0], K, Q, hq, hkv, dev)
+    if world > 1:
+        barrier()
 
-    # ---- end to end through the public operator with host buffers ----
-    from compactattention_b200.modules import chunked_prefill_column_dense_attention_from_keep_block  # noqa: F401
-    host_out = torch.empty((1, Q, hq, D), dtype=torch.bfloat16).pin_memory()
+    # ---- end to end through the plugin call (the attention module's forward) with host buffers:
+    # hidden states from pinned host memory, layer output back to pinned host memory, every step ----
+    host_out = torch.empty((1, Q, hidden_size), dtype=torch.bfloat16).pin_memory()
 
     def e2e_step(L):
-        q = L["q"].copy_(L["host"]["q"], non_blocking=True)
-        kc = L["k_chunk"].copy_(L["host"]["k"], non_blocking=True)
-        vc = L["v_chunk"].copy_(L["host"]["v"], non_blocking=True)
-        L["cache"].append(kc, vc, position=K - Q)
-        step(L)
-        host_out.copy_(L["out"], non_blocking=True)
+        st = L["state"]
+        st.kv.length = K - Q        # the chunk is appended again at the end of the past tokens
+        st.gate.cache.length = Pb
+        x = L["hidden"].copy_(L["hidden_host"], non_blocking=True)
+        with torch.no_grad():
+            y = L["module"](x, tok_rope, None, past_key_value=L["pkv"], block_position_embeddings=rope_chunk)[0]
+        host_out.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for i in range(3):
         e2e_step(layers[i % len(layers)])
     barrier()
-    w0 = time.perf_counter()
-    n_e2e = max(5, min(args.steps, 20))
+    n_e2e = max(5, min(args.steps, 40))
+    e2e_each = []
+    w_all = time.perf_counter()
     for i in range(n_e2e):
+        w0 = time.perf_counter()
         e2e_step(layers[i % len(layers)])
+        e2e_each.append((time.perf_counter() - w0) * 1e6)
+    e2e_mean_local = (time.perf_counter() - w_all) / n_e2e * 1e6
     barrier()
-    e2e_us = (time.perf_counter() - w0) / n_e2e * 1e6
-    if world > 1:
-        import torch.distributed as dist
-        tt = torch.tensor([e2e_us], dtype=torch.float64, device=dev)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        e2e_us = float(tt[0])
+    e2e_us, e2e_med = max_ranks([e2e_mean_local, statistics.median(e2e_each)])
+    # the module's device time alone (CUDA events, inputs resident): what the plugin call costs on the GPU
+    m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    m0.record()
+    for i in range(n_e2e):
+        L = layers[i % len(layers)]
+        L["state"].kv.length, L["state"].gate.cache.length = K - Q, Pb
+        with torch.no_grad():
+            L["module"](L["hidden"], tok_rope, None, past_key_value=L["pkv"], block_position_embeddings=rope_chunk)
+    m1.record()
+    barrier()
+    module_us = max_ranks([m0.elapsed_time(m1) / n_e2e * 1e3])[0]
+
     # ---- the same step replayed from CUDA graphs (informational, last of all so that a failed
     # capture cannot touch a required number; `value` stays the eager loop) ----
     graph_us = None
@@ -445,8 +568,8 @@ def run_native(args):
             graph_us = None
             print(f"[bench] graph replay not timed: {exc!r}", file=sys.stderr)
 
-    h2d = (Q * hq * D + 2 * Q * hkv * D) * 2
-    d2h = Q * hq * D * 2
+    h2d = Q * hidden_size * 2
+    d2h = Q * hidden_size * 2
 
     if rank != 0:
         if world > 1:
@@ -457,6 +580,7 @@ def run_native(args):
     if world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline(args, sample_heads=1)
     value_us = ms_per_step * 1e3
+    sm_mhz = (clocks or {}).get("sm_mhz")
     line = {
         "metric": METRIC, "value": round(value_us, 1), "unit": "us", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": False,
@@ -471,12 +595,19 @@ def run_native(args):
             "l2": f"steps rotate over {len(layers)} layer states ({len(layers) * 2 * K * hkv * D * 2 / 2**30:.1f} GiB of KV), more than L2",
             "launches_per_step": launches / args.steps,
             "programmatic_dependent_launch": args.dependent_launch,
+            "step_us": {k: round(v, 1) for k, v in step_stats.items()},
+            "attention_us": {k: round(v, 1) for k, v in attn_stats.items()},
+            "stage_us": stage_us,
+            "attention_kernel_cycles_at_median_clock": None if not sm_mhz else round(attn_ms * 1e3 * sm_mhz),
             "step_replayed_from_cuda_graph_us": None if graph_us is None else round(graph_us, 1),
             "dense_same_shape_us": None if dense_us is None else round(dense_us, 1),
             "speedup_vs_dense": None if dense_us is None else round(dense_us / value_us, 2),
-            "dense_flash_attn2_same_shape_us": None if ref_dense_us is None else round(ref_dense_us, 1),
-            "speedup_vs_flash_attn2_dense": None if ref_dense_us is None else round(ref_dense_us / value_us, 2),
+            "reference_gpu_routes_us": ref_gpu,
             "attention_effective_tflops": round(achieved, 1),
+            "e2e_call": "LlamaSeerAttentionChunkedDense.forward (top-k method): hidden states from pinned host memory, "
+                        "q/k/v projections, RoPE + paged append, gate, rule, table, attention, o_proj"
+                        + (", all-reduce" if world > 1 else "") + ", output to pinned host memory",
+            "e2e_median_us": round(e2e_med, 1), "module_forward_device_us": round(module_us, 1),
             "status_word": status,
         },
         "roofline": roofline,
@@ -489,6 +620,169 @@ def run_native(args):
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
+
+
+def load_attention_capture():
+    """DRAM bytes of one attention launch from the committed ncu capture (a small JSON beside the
+    profile summaries: measured read + write bytes and the algorithmic bytes of the captured launch).
+    K/V traffic is proportional to the selected blocks, so the benchmark's launch is scaled by its own
+    algorithmic bytes.  None when the file is absent."""
+    path = ROOT / "profiles" / "attn_compact_kernel_capture.json"
+    if not path.exists():
+        return None
+    d = json.loads(path.read_text())
+    return {"dram_bytes": float(d["dram_bytes"]), "algorithmic_bytes": float(d["algorithmic_bytes"])}
+
+
+def time_reference_gpu_routes(L, K, Q, hq, hkv, dev, reps=3):
+    """Times, on the block table this library built, the library calls the reference's compact routes
+    bottom out in, plus its dense comparator.  These libraries are parts of the image, not of this
+    repository; they are only timed here (and their outputs compared with this library's at the
+    path's tolerance), never used by the path.  Returns {route: {"us": .., "max_abs_vs_ours": ..} |
+    {"error": text}}.
+      dense_flash_attn2       flash_attn_func(causal=True)  (compact_attn/modules/dense_prefill.py:304-310)
+      fa2_paged               flash_attn_with_kvcache over the compact cache this library's gather fills
+                              (compact_attn/kernels/varlen/indexed_dense_prefill_varlen.py:1563-1571)
+      fi_zero_copy            FlashInfer BatchPrefillWithPagedKVCacheWrapper.plan/run over the selected page ids,
+                              one pseudo-batch row per KV head (.../flashinfer_zero_copy_prefill.py:1284-1320)
+      cudnn_one_shot          flashinfer.cudnn_batch_prefill_with_kv_cache (same file, :1503-1540)
+    """
+    from compactattention_b200 import ops
+    G = hq // hkv
+    Kb, Qb = K // BS, Q // BS
+    Pb = Kb - Qb
+    q, table = L["q"], L["table"]
+    cache = L["cache"]
+    ours = ops.attn_compact(q, L["kv"], K, hkv, table.block_idx, table.counts, block_size=BS).float()
+    results = {}
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            out = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3, out
+
+    def compare(out_bqhd):
+        err = (out_bqhd.float() - ours).abs()
+        return {"max_abs_vs_ours": round(err.max().item(), 5), "mean_abs_vs_ours": round(err.mean().item(), 6)}
+
+    def attempt(name, fn):
+        try:
+            results[name] = fn()
+        except Exception as exc:  # an absent library, an unsupported device or build: recorded, not fatal
+            results[name] = {"error": f"{type(exc).__name__}: {str(exc)[:300]}"}
+            print(f"[bench] reference route {name} not timed: {exc!r}", file=sys.stderr)
+
+    # logical (un-permuted) copies of the layer's K and V, as the reference holds them
+    ids = cache.page_table[0].to(torch.long)
+    k_log = cache.k_pages[ids].reshape(1, K, hkv, D)
+    v_log = cache.v_pages[ids].reshape(1, K, hkv, D)
+    q_group = q.view(1, Q, hkv, G, D).permute(0, 2, 1, 3, 4).reshape(hkv, Q, G, D).contiguous()
+
+    def ungroup(o):  # [R, Q, G, D] -> [1, Q, Hq, D]
+        return o.view(1, hkv, Q, G, D).permute(0, 2, 1, 3, 4).reshape(1, Q, hq, D)
+
+    def dense_fa2():
+        from flash_attn import flash_attn_func
+        us, _ = timed(lambda: flash_attn_func(q, k_log, v_log, causal=True))
+        return {"us": round(us, 1)}
+
+    def fa2_paged():
+        from flash_attn import flash_attn_with_kvcache
+        offs, block_table = ops.paged_metadata(table.pages_per_row, max_pages=(Kb * BS + 255) // 256)
+        total_pages = hkv * ((Kb * BS + 255) // 256)
+        kc = torch.zeros((total_pages, 256, 1, D), dtype=q.dtype, device=dev)
+        vc = torch.zeros_like(kc)
+        kv = L["kv"]
+
+        def fill():
+            ops.gather_kv(kv, hkv, 1, Q, K, table.block_idx, table.counts, kc, vc, block_size=BS, page_offsets=offs,
+                          dst_page_size=256)
+
+        fill_us, _ = timed(fill)
+        seqlens = table.cache_seqlens.view(-1).contiguous()
+        attn_us, out = timed(lambda: flash_attn_with_kvcache(q=q_group, k_cache=kc, v_cache=vc, cache_seqlens=seqlens,
+                                                             block_table=block_table, softmax_scale=D ** -0.5, causal=True))
+        return {"us": round(fill_us + attn_us, 1), "cache_fill_us": round(fill_us, 1), "attention_us": round(attn_us, 1),
+                **compare(ungroup(out))}
+
+    def zero_copy_metadata():
+        # CSR over the selected blocks of every KV-head row followed by the chunk's own blocks; a page id
+        # is row * Kb + block in the heads-first view [Hkv * Kb, 64, 1, D]
+        counts = table.counts.view(-1).to(torch.long)
+        n = counts + Qb
+        indptr = torch.zeros(hkv + 1, dtype=torch.int32, device=dev)
+        indptr[1:] = torch.cumsum(n, 0).to(torch.int32)
+        rows = []
+        for r in range(hkv):
+            c = int(counts[r])
+            rows.append(torch.cat([table.block_idx.view(hkv, -1)[r, :c].to(torch.int32),
+                                   torch.arange(Pb, Kb, dtype=torch.int32, device=dev)]) + r * Kb)
+        indices = torch.cat(rows).contiguous()
+        last = torch.full((hkv,), BS, dtype=torch.int32, device=dev)
+        qo = torch.arange(0, (hkv + 1) * Q, Q, dtype=torch.int32, device=dev)
+        k_hf = k_log.permute(0, 2, 1, 3).contiguous().view(hkv * Kb, BS, 1, D)
+        v_hf = v_log.permute(0, 2, 1, 3).contiguous().view(hkv * Kb, BS, 1, D)
+        return indptr, indices, last, qo, k_hf, v_hf
+
+    def fi_zero_copy():
+        import flashinfer
+        indptr, indices, last, qo, k_hf, v_hf = zero_copy_metadata()
+        ws = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+        wrapper = flashinfer.BatchPrefillWithPagedKVCacheWrapper(ws, "NHD")
+        q_fi = q_group.reshape(hkv * Q, G, D)
+
+        def plan():
+            wrapper.plan(qo_indptr=qo, paged_kv_indptr=indptr, paged_kv_indices=indices, paged_kv_last_page_len=last,
+                         num_qo_heads=G, num_kv_heads=1, head_dim_qk=D, page_size=BS, causal=True, sm_scale=D ** -0.5,
+                         q_data_type=q.dtype)
+
+        plan()
+        w0 = time.perf_counter()
+        for _ in range(reps):
+            plan()
+        torch.cuda.synchronize()
+        plan_us = (time.perf_counter() - w0) / reps * 1e6
+        run_us, out = timed(lambda: wrapper.run(q_fi, (k_hf, v_hf)))
+        return {"us": round(plan_us + run_us, 1), "plan_host_us": round(plan_us, 1), "run_us": round(run_us, 1),
+                **compare(ungroup(out.view(hkv, Q, G, D)))}
+
+    def cudnn_one_shot():
+        from flashinfer.prefill import cudnn_batch_prefill_with_kv_cache as fn
+        indptr, indices, last, qo, k_hf, v_hf = zero_copy_metadata()
+        n = (indptr[1:] - indptr[:-1]).to(torch.int32)
+        max_pages = int(n.max())
+        block_tables = torch.zeros((hkv, max_pages), dtype=torch.int32, device=dev)
+        for r in range(hkv):
+            block_tables[r, : int(n[r])] = indices[int(indptr[r]): int(indptr[r + 1])]
+        q_fi = q_group.reshape(hkv * Q, G, D)
+        ws = torch.empty(128 * 1024 * 1024, dtype=torch.uint8, device=dev)
+        seq_q = torch.full((hkv, 1, 1, 1), Q, dtype=torch.int32, device=dev)
+        seq_kv = (n * BS).view(hkv, 1, 1, 1).to(torch.int32)
+        # this entry point takes pages as [pages, 1, 64, D] (the same memory) and element offsets of each row's queries
+        k_c, v_c = k_hf.view(hkv * Kb, 1, BS, D), v_hf.view(hkv * Kb, 1, BS, D)
+        offs = (qo * (G * D)).contiguous()
+
+        def run():
+            return fn(q_fi, k_c, v_c, D ** -0.5, ws, max_token_per_sequence=Q, max_sequence_kv=max_pages * BS,
+                      actual_seq_lens_q=seq_q, actual_seq_lens_kv=seq_kv, block_tables=block_tables, causal=True,
+                      return_lse=True, batch_offsets_q=offs, batch_offsets_o=offs, is_cuda_graph_compatible=False)
+
+        us, out = timed(run)
+        out = out[0] if isinstance(out, (tuple, list)) else out
+        return {"us": round(us, 1), **compare(ungroup(out.view(hkv, Q, G, D)))}
+
+    attempt("dense_flash_attn2", dense_fa2)
+    attempt("fa2_paged", fa2_paged)
+    attempt("fi_zero_copy", fi_zero_copy)
+    attempt("cudnn_one_shot", cudnn_one_shot)
+    return results
 
 
 def cpu_path_once(q, k, v, wq, wk, cos, sin, num, den, G):

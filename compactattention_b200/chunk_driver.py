@@ -47,9 +47,9 @@ class GateSelectorState:
         self.q_blocks = None  # [B, Qb, Hq, C] scratch of the current chunk
         self.logits = None    # [B, Hq, Qb, Kb] scratch of the current chunk
 
-    def append_and_score(self, q_nope: torch.Tensor, k_nope: torch.Tensor, block_rope_q=None, block_rope_k=None) -> torch.Tensor:
-        """Appends the chunk's K blocks, then scores the chunk's Q blocks against every cached block
-        (two launches).  Returns logits ``[B, Hq, Qb, Kb]`` (float32, acausal entries = finfo.min)."""
+    def append(self, q_nope: torch.Tensor, k_nope: torch.Tensor, block_rope_q=None, block_rope_k=None) -> int:
+        """Pools, projects and ropes the chunk's Q blocks (into scratch) and K blocks (appended to the
+        cache): one launch.  Returns the number of blocks appended."""
         gate = self.gate
         nb = (q_nope.shape[1] + gate.block_size - 1) // gate.block_size
         self.cache.reserve(self.cache.length + nb)
@@ -61,11 +61,22 @@ class GateSelectorState:
                          gate.mask_linear_k.weight.detach(), block_rope_q, block_rope_k, self.q_blocks,
                          self.cache.blocks_view(), self.cache.length)
         self.cache.length += nb
+        return nb
+
+    def score(self) -> torch.Tensor:
+        """Scores the chunk's Q blocks (from the last ``append``) against every cached block: one launch.
+        Returns logits ``[B, Hq, Qb, Kb]`` (float32, acausal entries = finfo.min)."""
+        gate, nb = self.gate, self.q_blocks.shape[1]
         kb = self.cache.blocks()
         if self.logits is None or self.logits.shape[3] != kb.shape[1] or self.logits.shape[2] != nb:
-            self.logits = torch.empty((q_nope.shape[0], gate.num_q_head, nb, kb.shape[1]), dtype=torch.float32,
-                                      device=q_nope.device)
+            self.logits = torch.empty((self.q_blocks.shape[0], gate.num_q_head, nb, kb.shape[1]), dtype=torch.float32,
+                                      device=self.q_blocks.device)
         return ops.gate_scores(self.q_blocks, kb, kb.shape[1] - nb, scale=gate.scale, out=self.logits)
+
+    def append_and_score(self, q_nope: torch.Tensor, k_nope: torch.Tensor, block_rope_q=None, block_rope_k=None) -> torch.Tensor:
+        """``append`` then ``score`` (two launches)."""
+        self.append(q_nope, k_nope, block_rope_q, block_rope_k)
+        return self.score()
 
 
 class MeanKSelectorState:
