@@ -53,15 +53,12 @@ constexpr int kMinSpanSteps = 8;           // shortest span worth a CTA of its o
 // units of ~6 steps: 22 us whole against 45 us cut)
 constexpr int kMinUnitStepsToCut = CA_ATTN_MIN_UNIT_STEPS;  // average KV steps per unit below which units stay whole
 // Measured on B200 (sustained 300-launch loop, 128K context, 20 % density): handing P to the MMA warp
-// in two halves 434 us, in one piece 450 us; packed fp32 pairs for the scale and the row sum 421 us;
-// a polynomial exp2 on the FMA pipe (packed, 2 to 8 of every 16 pairs) 432 to 464 us.  The tensor
-// pipe slows down with every arithmetic instruction the softmax warps add (it is not the MUFU pipe
-// that limits), so the polynomial stays off.
+// in two halves 434 us, in one piece 450 us; packed fp32 pairs for the scale and the row sum 421 us.
+// A polynomial exp2 on the FMA pipe for part of the exponentials (2 / 4 / 6 of every 16 pairs) took
+// 486 / 499 / 518 us against 485 us without: with the softmax warps of both tiles on every scheduler
+// the added instructions cost more than the MUFU operations they replace, so there is none.
 #ifndef CA_ATTN_P_PARTS
 #define CA_ATTN_P_PARTS 2
-#endif
-#ifndef CA_ATTN_POLY_PAIRS
-#define CA_ATTN_POLY_PAIRS 0
 #endif
 #ifndef CA_ATTN_PROFILE
 #define CA_ATTN_PROFILE 0
@@ -73,16 +70,8 @@ constexpr int kMinUnitStepsToCut = CA_ATTN_MIN_UNIT_STEPS;  // average KV steps 
 // shape whose units stay whole); 0 restores a plain launch.
 #define CA_ATTN_MERGE_DEPENDENT 1
 #endif
-#ifndef CA_ATTN_EXPERIMENT
-// Development timing experiments (results are wrong, only the timing means something):
-// 1 = no softmax work at all (the MMA/TMA pipeline alone), 2 = the softmax's TMEM traffic without
-// its arithmetic.
-#define CA_ATTN_EXPERIMENT 0
-#endif
 static_assert(CA_ATTN_P_PARTS == 1 || CA_ATTN_P_PARTS == 2, "P is handed over in one or two pieces");
 constexpr int kPParts = CA_ATTN_P_PARTS;  // P is handed to the MMA warp in this many pieces so P.V overlaps the softmax
-constexpr int kPolyPairs = CA_ATTN_POLY_PAIRS;  // of every 16 pairs of exponentials, this many run on the FMA pipe
-static_assert(kPolyPairs >= 0 && kPolyPairs <= 16, "polynomial pairs per 16");
 
 // Optional cycle accounting (development builds only, -DCA_ATTN_PROFILE=1): one thread of each role
 // adds the clock cycles between consecutive marks to per-CTA counters.
@@ -241,31 +230,10 @@ __device__ void plan_segments(const KernelArgs& a, Shared* sh, long long x, long
   sh->more = (x < span_end && row < R) ? 1 : 0;
 }
 
-// 2^x for two values on the FMA/ALU pipes (no MUFU), with the packed fp32 instructions of sm_100:
-// x = n + f by the 1.5*2^23 rounding trick, degree-3 polynomial for 2^f on [-0.5, 0.5] (relative
-// error 1.9e-4, below the 16-bit rounding of P), n added to the exponent bits.
-__device__ __forceinline__ float2 ex2_poly2(float2 x) {
-  x.x = fmaxf(x.x, -126.0f);
-  x.y = fmaxf(x.y, -126.0f);
-  const float2 magic = make_float2(12582912.0f, 12582912.0f);
-  const float2 t = __fadd2_rn(x, magic);
-  const float2 u = __fadd2_rn(t, make_float2(-12582912.0f, -12582912.0f));
-  const float2 f = __ffma2_rn(u, make_float2(-1.0f, -1.0f), x);
-  float2 p = __ffma2_rn(make_float2(0.0558755025267601f, 0.0558755025267601f), f,
-                        make_float2(0.24229444563388824f, 0.24229444563388824f));
-  p = __ffma2_rn(p, f, make_float2(0.6931272745132446f, 0.6931272745132446f));
-  p = __ffma2_rn(p, f, make_float2(0.999948263168335f, 0.999948263168335f));
-  p.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23));
-  p.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23));
-  return p;
-}
-
 // P = exp2(S*sc + neg_m) for one 128-column row held in registers: packs to 16 bit, stores the four
 // 32-column chunks over S in TMEM, signals the MMA warp after each of the kPParts pieces.  The scale
-// and the row sum use packed fp32 pairs; kPolyPairs of every 16 pairs take their exponentials from
-// the FMA pipe (never for masked steps, whose -inf entries must give exact zeros).  Returns the row
-// sum of P.
-template <typename T, int kPolyPairs>
+// and the row sum use packed fp32 pairs.  Returns the row sum of P.
+template <typename T>
 __device__ __forceinline__ float exp_pack_store(const uint32_t (&sv)[128], float sc, float neg_m, uint32_t tS,
                                                 uint32_t p_part_bar) {
   float2 l2 = make_float2(0.f, 0.f);
@@ -278,15 +246,8 @@ __device__ __forceinline__ float exp_pack_store(const uint32_t (&sv)[128], float
     for (int i = 0; i < 32; i += 2) {
       const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[c * 32 + i]), __uint_as_float(sv[c * 32 + i + 1])), sc2, nm2);
       float2 pr;
-      // spread the polynomial pairs evenly over the 16 pairs of the chunk
-      const int pi = i >> 1;
-      const bool poly = kPolyPairs > 0 && ((pi * kPolyPairs) / 16 != ((pi + 1) * kPolyPairs) / 16);
-      if (poly) {
-        pr = ex2_poly2(x);
-      } else {
-        pr.x = ptx::ex2(x.x);
-        pr.y = ptx::ex2(x.y);
-      }
+      pr.x = ptx::ex2(x.x);
+      pr.y = ptx::ex2(x.y);
       l2 = __fadd2_rn(l2, pr);
       pk[i >> 1] = pack2<T>(pr.x, pr.y);
     }
@@ -679,12 +640,6 @@ __global__ void __launch_bounds__(kThreads, 1)
               lim0 = visible_cols(2 * j, sg.n_sub, sg.n_past_sub, t);
               lim1 = visible_cols(2 * j + 1, sg.n_sub, sg.n_past_sub, t);
             }
-#if CA_ATTN_EXPERIMENT == 1
-            // timing experiment: no softmax work at all, P "ready" at once
-            ptx::tc_fence_before();
-            for (int q = 0; q < kPParts; ++q) ptx::mbar_arrive(ptx::smem_u32(&sh->p_part[tile][q]));
-            continue;
-#endif
             // the whole S row (128 fp32) comes into registers with one wait
             uint32_t sv[128];
             ptx::tmem_ld32_row<0>(tS + 0, sv);
@@ -692,22 +647,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             ptx::tmem_ld32_row<64>(tS + 64, sv);
             ptx::tmem_ld32_row<96>(tS + 96, sv);
             ptx::tc_wait_ld();
-#if CA_ATTN_EXPERIMENT == 2
-            {
-              // timing experiment: TMEM traffic of the softmax (load S, store P), no arithmetic
-  #pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                uint32_t pk[16];
-  #pragma unroll
-                for (int i = 0; i < 16; ++i) pk[i] = sv[c * 32 + i] & 0x3f7f3f7fu;
-                ptx::tmem_st16(tS + c * 16, pk);
-              }
-              ptx::tc_wait_st();
-              ptx::tc_fence_before();
-              for (int q = 0; q < kPParts; ++q) ptx::mbar_arrive(ptx::smem_u32(&sh->p_part[tile][q]));
-              continue;
-            }
-#endif
             CA_PROF(2)
             if (masked) {
   #pragma unroll
@@ -749,8 +688,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const float neg_m = m_run == -INFINITY ? 0.f : -m_run * sc;
             const uint32_t half_bar = ptx::smem_u32(&sh->p_part[tile][0]);
             CA_PROF(3)
-            l_run += masked ? exp_pack_store<T, 0>(sv, sc, neg_m, tS, half_bar)
-                            : exp_pack_store<T, kPolyPairs>(sv, sc, neg_m, tS, half_bar);
+            l_run += exp_pack_store<T>(sv, sc, neg_m, tS, half_bar);
             CA_PROF(4)
 
           }

@@ -1,9 +1,7 @@
 """Per-role cycle accounting of the attention kernel (development tool, needs a B200).
 
-Builds the library with ``-DCA_ATTN_PROFILE=1`` (optionally a timing experiment,
-``--experiment 1`` = no softmax work, ``2`` = the softmax's TMEM traffic only) into a separate
-``.so``, runs the kernel on the benchmark's attention shape (chunk 1024 at the end of a 131072-token
-cache, 32 query / 8 KV heads, 20 % of the past blocks, whole work units per CTA) and prints, for a
+Builds the library with ``-DCA_ATTN_PROFILE=1`` into a separate ``.so``, runs the kernel on the
+benchmark's attention shape (chunk 1024 at the end of a 131072-token cache, 32 query / 8 KV heads, 20 % of the past blocks, whole work units per CTA) and prints, for a
 few CTAs, the clock cycles per 128-token KV step that each role spent between its marks:
 
 * MMA issuer: issuing (which includes being held by the tensor pipe's queue), and the waits for the
@@ -13,7 +11,7 @@ few CTAs, the clock cycles per 128-token KV step that each role spent between it
 
 Each mark costs about 90 cycles of its own, so the buckets that show ~90 are empty waits.
 
-    python -m compactattention_b200.cycle_accounting [--experiment N] [--density 0.2]
+    python -m compactattention_b200.cycle_accounting [--density 0.2]
 """
 from __future__ import annotations
 
@@ -32,7 +30,6 @@ SOFTMAX_BUCKETS = ["loop", "wait S", "load S", "row max", "exp + store P", "epil
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--experiment", type=int, default=0)
     ap.add_argument("--density", type=float, default=0.2)
     ap.add_argument("--kv-len", type=int, default=131072)
     ap.add_argument("--launches", type=int, default=50)
@@ -41,9 +38,7 @@ def main() -> None:
     args = ap.parse_args()
 
     defines = ["CA_ATTN_PROFILE=1"]
-    if args.experiment:
-        defines.append(f"CA_ATTN_EXPERIMENT={args.experiment}")
-    lib_path = build.PKG_DIR / f"libcompactattn_b200_profile{args.experiment}.so"
+    lib_path = build.PKG_DIR / "libcompactattn_b200_profile.so"
     build.build_variant(defines, lib_path)
     _lib.LIB_PATH = Path(lib_path)   # must happen before the first ops call loads the library
     from . import ops
