@@ -109,16 +109,16 @@ def select_and_attend(
     bits: Optional[torch.Tensor] = None,
     status: Optional[torch.Tensor] = None,
 ):
-    """Row rule -> Block-Union table -> compact attention (three launches).  Returns (out, table)."""
+    """Row rule + Block-Union table (one launch) -> compact attention.  Returns (out, table).  ``bits`` is
+    only written when given (a caller that wants the per-row selection)."""
     Qb, Kb = score.shape[2], score.shape[3]
     rows_voting = 0
     if rule.last_n_block > 0 and Qb > 1:
         rows_voting = max(Qb - min(rule.last_n_block, Qb - 1), 1)
-    bits = ops.select_rows(score, Kb - Qb, rule.rule, softmax=rule.softmax, threshold=rule.threshold, alpha=rule.alpha,
-                           topk_k=rule.topk_k, topk_ratio=rule.topk_ratio, min_budget=rule.min_budget, sink=rule.sink,
-                           local=rule.local, rows_voting=rows_voting, bits=bits)
-    table = ops.union_table(bits=bits, num_kv_heads=num_kv_heads, kv_blocks=Kb, past_blocks=Kb - Qb, block_size=block_size,
-                            keep_recent=rule.keep_recent, out=table)
+    table = ops.select_union_table(score, Kb - Qb, rule.rule, num_kv_heads=num_kv_heads, block_size=block_size,
+                                   keep_recent=rule.keep_recent, softmax=rule.softmax, threshold=rule.threshold, alpha=rule.alpha,
+                                   topk_k=rule.topk_k, topk_ratio=rule.topk_ratio, min_budget=rule.min_budget, sink=rule.sink,
+                                   local=rule.local, rows_voting=rows_voting, bits=bits, out=table)
     out = ops.attn_compact(q, kv, kv_len, num_kv_heads, table.block_idx, table.counts, block_size=block_size,
                            softmax_scale=softmax_scale, out=out, status=status)
     return out, table

@@ -129,6 +129,7 @@ struct KernelArgs {
   int slot_tok, slot_page, slot_head;
   int kv_head_div;     // block-table rows per KV head (1 unless per-query-head / sub-group tables)
   int split;           // 1: spans may cut units (needs the workspace)
+  int max_cut_steps;   // > 0: units longer than this many KV steps on average stay whole
   SegDesc* descs;      // [2 * gridDim.x]
   float* part_ml;      // [2 * gridDim.x][kPartialMLFloats]
   float* part_o;       // [2 * gridDim.x][kPartialOFloats]
@@ -355,7 +356,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     const long long n_units_all = static_cast<long long>(R) * a.n_pairs;
     // Cutting units pays only when a unit is long: measured on B200, units of ~6 KV steps ran 2x
     // slower cut (partials + the merge) than whole (45 vs 22 us), units of ~50 steps 20 % faster.
-    const bool cut = a.split && total >= n_units_all * kMinUnitStepsToCut;
+    const bool cut = a.split && total >= n_units_all * kMinUnitStepsToCut &&
+                     (a.max_cut_steps <= 0 || total <= n_units_all * a.max_cut_steps);
     if (cut) {
       // A span costs a prologue, an epilogue and (when it cuts a unit) 128 KB of partials, about
       // as much as kMinSpanSteps KV steps: with little work, fewer CTAs take longer spans and the
@@ -1098,17 +1100,22 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
   // persistent grid: one CTA per SM, never more CTAs than units when units cannot be cut
   const long long n_units = static_cast<long long>(p->B) * p->Hkv * n_pairs;
   int grid = dev.sm_count;
-  // Cutting units costs partial traffic and a combine launch, and under the power cap idle SMs buy
-  // clock for the busy ones; it pays only when whole units would leave many SMs idle (few rows per
-  // rank under tensor parallelism, or a nearly empty last wave).  Measured on B200 in fresh
-  // processes, 128 units on 148 SMs: whole units 425-430 us, cut 442-453 us; 16 units: 442 vs 91 us.
-  // (CA_ATTN_SPLIT_PERCENT overrides the 80 % threshold in development builds.)
+  // Cutting units costs partial traffic and a combine launch; it pays when whole units would leave SMs
+  // idle (few rows per rank under tensor parallelism, a nearly empty last wave) or unevenly loaded (the
+  // rows of a block table differ in length).  Measured on B200, 128 units on 148 SMs, 128K context:
+  // with ~460 selected blocks per row (236 KV steps per unit) whole units 503 us, cut 450 us in a short
+  // run and 516 vs 512 us in a seconds-long loop (the board then holds a lower clock with every SM busy);
+  // dense attention of the same shape (1028 steps per unit, 2 ms per launch) 1923 us whole, 2028 us cut.
+  // So a launch that already fills more than 80 % of a wave is cut only while its units are short.
+  // 16 units (one KV head of a tensor-parallel rank): 442 us whole, 91 us cut.
+  // (CA_ATTN_SPLIT_PERCENT overrides the 90 % threshold in development builds.)
   const long long waves = (n_units + dev.sm_count - 1) / dev.sm_count;
 #ifdef CA_ATTN_SPLIT_PERCENT
   const bool want_split = n_units * 100 < waves * dev.sm_count * CA_ATTN_SPLIT_PERCENT;
 #else
-  const bool want_split = n_units * 100 < waves * dev.sm_count * 80;
+  const bool want_split = n_units * 100 < waves * dev.sm_count * 90;
 #endif
+  a.max_cut_steps = n_units * 100 >= waves * dev.sm_count * 80 ? 512 : 0;
   const bool can_split = p->workspace != nullptr && p->workspace_bytes >= workspace_bytes_for(grid);
   a.split = (want_split && can_split) ? 1 : 0;
   if (!a.split && n_units < grid) grid = static_cast<int>(n_units);

@@ -5,6 +5,8 @@
 // output is sized by capacity.
 #include "ca_common.cuh"
 
+#include <mutex>
+
 namespace ca {
 namespace select {
 
@@ -41,6 +43,18 @@ struct RowArgs {
   int min_budget;  // ALPHA_ROWMAX: also keep the top min_budget entries
   int sink, local; // forced blocks: j < sink, and 0 <= (Pb+i) - j < local
   int rows_voting; // rows i >= rows_voting produce no bits (FlashPrefill last_n_block)
+  // Fused Block-Union (optional, fuse != 0): every row CTA ORs its words into the KV-head row's word
+  // array in global memory and takes a ticket; the CTA that takes the last ticket of a KV-head row
+  // compacts that row into the block table and leaves the words and the ticket zeroed for the next call.
+  int fuse;
+  int G;                 // query heads per KV head (H = Hkv * G)
+  uint32_t* union_words; // [B*Hkv, W], zero on entry
+  uint32_t* tickets;     // [B*Hkv], zero on entry
+  int keep_recent, block_size, page_size, idx_stride;
+  int32_t* block_idx;
+  int32_t* counts;
+  int32_t* cache_seqlens;
+  int32_t* pages_per_row;
 };
 
 // Exclusive block-wide prefix sum of one int per thread (kRowThreads threads).
@@ -189,6 +203,52 @@ __device__ void bitonic_sort(unsigned long long* comp, int n2) {
   }
 }
 
+// Compacts one KV-head row: `words` (shared memory, W words, bit j%32 of word j/32 = key block j kept by
+// some query head / Q-block) -> ascending past block ids, -1 padded, count, seqlen, pages.  Columns
+// j >= Kb - keep_recent are forced on first; only past columns (j < Pb) enter the table.  All threads of
+// the CTA call it.
+__device__ void compact_row(uint32_t* words, int W, int Kb, int Pb, int Qb, int keep_recent, int block_size, int page_size,
+                            int32_t* idx_row, int idx_stride, int row, int32_t* counts, int32_t* cache_seqlens,
+                            int32_t* pages_per_row, uint8_t* keep_kv_row, int* warp_sums, int* sh_total) {
+  int running = 0;
+  for (int wbase = 0; wbase < W; wbase += kRowThreads) {
+    const int w = wbase + threadIdx.x;
+    uint32_t word = 0;
+    if (w < W) {
+      word = words[w];
+      const int j0 = w * 32;
+      // forced recent columns; bits beyond Kb cleared
+      const int first_recent = Kb - keep_recent;
+      if (j0 + 32 > first_recent) word |= first_recent <= j0 ? 0xffffffffu : (0xffffffffu << (first_recent - j0));
+      if (j0 + 32 > Kb) word &= Kb <= j0 ? 0u : (0xffffffffu >> (j0 + 32 - Kb));
+      if (keep_kv_row) {
+        for (int t = 0; t < 32 && j0 + t < Kb; ++t) keep_kv_row[j0 + t] = ((word >> t) & 1u) || (j0 + t >= Pb);
+      }
+      // keep past columns only
+      if (j0 + 32 > Pb) word = j0 >= Pb ? 0u : (word & ((1u << (Pb - j0)) - 1u));
+    }
+    const int pc = __popc(word);
+    const int off = running + block_exclusive_scan(pc, warp_sums, sh_total);
+    int o = off;
+    while (word) {
+      const int t = __ffs(word) - 1;
+      word &= word - 1;
+      if (o < idx_stride) idx_row[o] = w * 32 + t;
+      ++o;
+    }
+    running += *sh_total;
+    __syncthreads();
+  }
+  const int count = running < idx_stride ? running : idx_stride;
+  for (int o = count + threadIdx.x; o < idx_stride; o += kRowThreads) idx_row[o] = -1;
+  if (threadIdx.x == 0) {
+    counts[row] = count;
+    const int seqlen = (count + Qb) * block_size;
+    if (cache_seqlens) cache_seqlens[row] = seqlen;
+    if (pages_per_row) pages_per_row[row] = (seqlen + page_size - 1) / page_size;
+  }
+}
+
 __global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs a) {
   ptx::grid_launch_dependents();
   ptx::grid_dependency_wait();  // nothing in global memory is touched before this
@@ -207,12 +267,15 @@ __global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs 
   const int h = (blockIdx.x / a.Qb) % a.H;
   const int b = blockIdx.x / (a.Qb * a.H);
   const int diag = a.Pb + i;  // last causally valid key block of this row
-  uint32_t* bits_row = a.bits + ((static_cast<long long>(b) * a.H + h) * a.Qb + i) * a.W;
+  uint32_t* bits_row = a.bits ? a.bits + ((static_cast<long long>(b) * a.H + h) * a.Qb + i) * a.W : nullptr;
+  const int kv_row = a.fuse ? b * (a.H / a.G) + h / a.G : 0;
 
-  if (i >= a.rows_voting) {
-    for (int w = threadIdx.x; w < a.W; w += kRowThreads) bits_row[w] = 0u;
-    return;
+  const bool voting = i < a.rows_voting;
+  if (!voting) {
+    if (a.bits) for (int w = threadIdx.x; w < a.W; w += kRowThreads) bits_row[w] = 0u;
+    if (!a.fuse) return;
   }
+  if (voting) {
   const long long s_off = b * a.s_b + h * a.s_h + i * a.s_q;
   const long long v_off = a.valid ? (b * a.v_b + h * a.v_h + i * a.v_q) : 0;
 
@@ -333,8 +396,36 @@ __global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs 
       k = (keep[j] || forced) && ok;
     }
     const uint32_t word = __ballot_sync(0xffffffffu, k);
-    if ((threadIdx.x & 31) == 0 && (j >> 5) < a.W) bits_row[j >> 5] = word;
+    if ((threadIdx.x & 31) == 0 && (j >> 5) < a.W) {
+      if (bits_row) bits_row[j >> 5] = word;
+      if (a.fuse && word) atomicOr(&a.union_words[static_cast<long long>(kv_row) * a.W + (j >> 5)], word);
+    }
   }
+  }  // voting
+  if (!a.fuse) return;
+  // ---- fused Block-Union: the last row CTA of this KV-head row builds the table.  Nobody waits: a CTA
+  // publishes its words, takes a ticket and leaves unless the ticket is the last one. ----
+  __shared__ int sh_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int ticket = atomicAdd(&a.tickets[kv_row], 1u);
+    sh_last = ticket == static_cast<unsigned int>(a.G * a.Qb - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!sh_last) return;
+  __threadfence();
+  uint32_t* words = reinterpret_cast<uint32_t*>(dyn_smem);  // the row's score scratch is free now
+  uint32_t* gw = a.union_words + static_cast<long long>(kv_row) * a.W;
+  for (int w = threadIdx.x; w < a.W; w += kRowThreads) {
+    words[w] = __ldcg(&gw[w]);
+    gw[w] = 0u;  // left clean for the next call
+  }
+  if (threadIdx.x == 0) a.tickets[kv_row] = 0u;
+  __syncthreads();
+  compact_row(words, a.W, a.Kb, a.Pb, a.Qb, a.keep_recent, a.block_size, a.page_size,
+              a.block_idx + static_cast<long long>(kv_row) * a.idx_stride, a.idx_stride, kv_row, a.counts, a.cache_seqlens,
+              a.pages_per_row, nullptr, warp_sums, &sh_cut);
 }
 
 struct UnionArgs {
@@ -382,46 +473,9 @@ __global__ void __launch_bounds__(kRowThreads) union_table_kernel(const UnionArg
     if (word) atomicOr(&words[w], word);
   }
   __syncthreads();
-  int running = 0;
-  for (int wbase = 0; wbase < a.W; wbase += kRowThreads) {
-    const int w = wbase + threadIdx.x;
-    uint32_t word = 0;
-    if (w < a.W) {
-      word = words[w];
-      // forced recent columns, then split into past (table) and chunk (always on) parts
-      const int j0 = w * 32;
-      for (int t = 0; t < 32; ++t) {
-        const int j = j0 + t;
-        if (j < a.Kb && j >= a.Kb - a.keep_recent) word |= 1u << t;
-        if (j >= a.Kb) word &= ~(1u << t);
-      }
-      if (a.keep_kv) {
-        uint8_t* out = a.keep_kv + (static_cast<long long>(row)) * a.Kb;
-        for (int t = 0; t < 32 && j0 + t < a.Kb; ++t) out[j0 + t] = ((word >> t) & 1u) || (j0 + t >= a.Pb);
-      }
-      // keep past columns only
-      if (j0 + 32 > a.Pb) word = j0 >= a.Pb ? 0u : (word & ((1u << (a.Pb - j0)) - 1u));
-    }
-    const int pc = __popc(word);
-    const int off = running + block_exclusive_scan(pc, warp_sums, &sh_total);
-    int o = off;
-    while (word) {
-      const int t = __ffs(word) - 1;
-      word &= word - 1;
-      if (o < a.idx_stride) idx_row[o] = w * 32 + t;
-      ++o;
-    }
-    running += sh_total;
-    __syncthreads();
-  }
-  const int count = running < a.idx_stride ? running : a.idx_stride;
-  for (int o = count + threadIdx.x; o < a.idx_stride; o += kRowThreads) idx_row[o] = -1;
-  if (threadIdx.x == 0) {
-    a.counts[row] = count;
-    const int seqlen = (count + a.Qb) * a.block_size;
-    if (a.cache_seqlens) a.cache_seqlens[row] = seqlen;
-    if (a.pages_per_row) a.pages_per_row[row] = (seqlen + a.page_size - 1) / a.page_size;
-  }
+  compact_row(words, a.W, a.Kb, a.Pb, a.Qb, a.keep_recent, a.block_size, a.page_size, idx_row, a.idx_stride, row, a.counts,
+              a.cache_seqlens, a.pages_per_row, a.keep_kv ? a.keep_kv + static_cast<long long>(row) * a.Kb : nullptr, warp_sums,
+              &sh_total);
 }
 
 // Exclusive prefix over rows of pages_per_row -> page_offsets[R+1]; block_table[row,slot] =
@@ -457,11 +511,13 @@ __global__ void __launch_bounds__(kRowThreads) paged_metadata_kernel(const int32
 
 extern "C" {
 
-int ca_select_rows(const ca_select_params* p, ca_stream_t stream_) {
+// Validates a row-selection request, fills the kernel arguments and returns the dynamic shared memory it
+// needs (the opt-in attribute is raised once per device when a row is longer than 8K blocks' worth).
+static int fill_row_args(const ca_select_params* p, ca::select::RowArgs* out, size_t* smem_out, bool bits_required) {
   using namespace ca;
   using namespace ca::select;
   CA_REQUIRE(p != nullptr, "params is null");
-  CA_REQUIRE(p->score && p->bits, "score and bits must be non-null");
+  CA_REQUIRE(p->score && (p->bits || !bits_required), "score and bits must be non-null");
   CA_REQUIRE(p->B > 0 && p->H > 0 && p->Qb > 0 && p->Kb > 0, "B, H, Qb, Kb must be positive");
   CA_REQUIRE(p->Kb <= kMaxKb, "Kb %d exceeds the supported maximum %d", p->Kb, kMaxKb);
   CA_REQUIRE(p->Pb >= 0 && p->Pb + p->Qb <= p->Kb + p->Qb, "Pb out of range");
@@ -488,6 +544,10 @@ int ca_select_rows(const ca_select_params* p, ca_stream_t stream_) {
   a.min_budget = p->min_budget;
   a.sink = p->sink, a.local = p->local;
   a.rows_voting = p->rows_voting > 0 ? p->rows_voting : p->Qb;
+  a.fuse = 0, a.G = 1;
+  a.union_words = nullptr, a.tickets = nullptr;
+  a.keep_recent = 0, a.block_size = 0, a.page_size = 0, a.idx_stride = 0;
+  a.block_idx = nullptr, a.counts = nullptr, a.cache_seqlens = nullptr, a.pages_per_row = nullptr;
   size_t smem = ((static_cast<size_t>(p->Kb) * 6 + 15) / 16) * 16;
   if (p->rule == CA_RULE_CUMMASS) {
     size_t n2 = 1;
@@ -495,8 +555,74 @@ int ca_select_rows(const ca_select_params* p, ca_stream_t stream_) {
     smem += n2 * 8;
   }
   if (smem > 48 * 1024) {
-    CA_CUDA(cudaFuncSetAttribute(select_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    // a per-device function attribute: raised once per device to the largest size the kernel can be asked for
+    static std::mutex mu;
+    static bool done[64] = {};
+    DeviceInfo dev;
+    int rc = get_device_info(&dev);
+    if (rc != CA_OK) return rc;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done[dev.ordinal]) {
+      const int max_smem = ((kMaxKb * 6 + 15) / 16) * 16 + kMaxKb * 8;
+      CA_CUDA(cudaFuncSetAttribute(select_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+      done[dev.ordinal] = true;
+    }
   }
+  *out = a;
+  *smem_out = smem;
+  return CA_OK;
+}
+
+int ca_select_rows(const ca_select_params* p, ca_stream_t stream_) {
+  using namespace ca;
+  using namespace ca::select;
+  RowArgs a;
+  size_t smem = 0;
+  int rc = fill_row_args(p, &a, &smem, true);
+  if (rc != CA_OK) return rc;
+  launch_kernel(select_rows_kernel, dim3(p->B * p->H * p->Qb), dim3(kRowThreads), smem, static_cast<cudaStream_t>(stream_), a);
+  CA_LAUNCH_CHECK("select_rows_kernel");
+  return CA_OK;
+}
+
+int ca_select_union_scratch_bytes(int B, int Hkv, int Kb, size_t* bytes_out) {
+  using namespace ca;
+  CA_REQUIRE(bytes_out != nullptr, "bytes_out is null");
+  CA_REQUIRE(B > 0 && Hkv > 0 && Kb > 0, "B, Hkv, Kb must be positive");
+  const size_t rows = static_cast<size_t>(B) * Hkv;
+  *bytes_out = (rows * ((Kb + 31) / 32) + rows) * sizeof(uint32_t);
+  return CA_OK;
+}
+
+int ca_select_union_table(const ca_select_params* p, const ca_union_params* u, void* scratch, size_t scratch_bytes,
+                          ca_stream_t stream_) {
+  using namespace ca;
+  using namespace ca::select;
+  RowArgs a;
+  size_t smem = 0;
+  int rc = fill_row_args(p, &a, &smem, false);
+  if (rc != CA_OK) return rc;
+  CA_REQUIRE(u != nullptr, "union params is null");
+  CA_REQUIRE(u->block_idx && u->counts, "block_idx and counts must be non-null");
+  CA_REQUIRE(u->B == p->B && u->Kb == p->Kb && u->Pb == p->Pb, "selection and union must agree on B, Kb and Pb");
+  CA_REQUIRE(u->Hkv > 0 && u->G > 0 && u->Hkv * u->G == p->H, "Hkv * G (%d * %d) must equal the selection's head count %d", u->Hkv,
+             u->G, p->H);
+  CA_REQUIRE(u->Qin == p->Qb, "the union takes every Q-block row of the selection (Qin %d, Qb %d)", u->Qin, p->Qb);
+  CA_REQUIRE(u->Pb <= u->Kb && u->Kb - u->Pb == p->Qb, "Kb - Pb must equal the chunk's Q-block count");
+  CA_REQUIRE(u->idx_stride >= (u->Pb > 0 ? u->Pb : 1), "block_idx capacity %d is smaller than the past block count %d",
+             u->idx_stride, u->Pb);
+  CA_REQUIRE(u->block_size > 0 && u->page_size > 0, "block_size and page_size must be positive");
+  CA_REQUIRE(u->keep_kv == nullptr && u->bits == nullptr && u->mask == nullptr,
+             "the fused form takes its input from the selection; keep_kv is not produced");
+  size_t need = 0;
+  ca_select_union_scratch_bytes(u->B, u->Hkv, u->Kb, &need);
+  CA_REQUIRE(scratch != nullptr && reinterpret_cast<uintptr_t>(scratch) % 4 == 0, "scratch must be a 4-byte aligned device pointer");
+  if (scratch_bytes < need) return fail(CA_ERR_CAPACITY, "scratch holds %zu bytes, %zu are needed", scratch_bytes, need);
+  a.fuse = 1, a.G = u->G;
+  a.union_words = static_cast<uint32_t*>(scratch);
+  a.tickets = a.union_words + static_cast<size_t>(u->B) * u->Hkv * a.W;
+  a.keep_recent = u->keep_recent, a.block_size = u->block_size, a.page_size = u->page_size, a.idx_stride = u->idx_stride;
+  a.block_idx = u->block_idx, a.counts = u->counts, a.cache_seqlens = u->cache_seqlens, a.pages_per_row = u->pages_per_row;
   launch_kernel(select_rows_kernel, dim3(p->B * p->H * p->Qb), dim3(kRowThreads), smem, static_cast<cudaStream_t>(stream_), a);
   CA_LAUNCH_CHECK("select_rows_kernel");
   return CA_OK;

@@ -244,6 +244,47 @@ def words_for(kv_blocks: int) -> int:
     return (kv_blocks + 31) // 32
 
 
+def _select_params(score, past_blocks, rule, valid, softmax, threshold, alpha, topk_k, topk_ratio, min_budget, sink, local,
+                   rows_voting, bits, prob_out, bits_required=True):
+    """Fills ``ca_select_params`` from torch arguments; returns (params, bits, tensors to keep alive)."""
+    _require_cuda(score, valid, bits, prob_out)
+    B, H, Qb, Kb = score.shape
+    p = _lib.SelectParams()
+    if rule == "mask":
+        if score.dtype not in (torch.bool, torch.uint8):
+            raise ValueError("rule 'mask' needs a bool/uint8 tensor")
+        p.score_dtype = 0
+    else:
+        if score.dtype not in _DTYPES:
+            raise ValueError(f"unsupported score dtype {score.dtype}")
+        p.score_dtype = _DTYPES[score.dtype]
+    if bits is None and bits_required:
+        bits = torch.empty((B, H, Qb, words_for(Kb)), dtype=torch.int32, device=score.device)
+    if bits is not None and (bits.dtype != torch.int32 or not bits.is_contiguous() or bits.shape != (B, H, Qb, words_for(Kb))):
+        raise ValueError("bits must be a contiguous int32 [B,H,Qb,ceil(Kb/32)] tensor")
+    if prob_out is not None and (prob_out.dtype != torch.float32 or not prob_out.is_contiguous() or prob_out.shape != (B, H, Qb, Kb)):
+        raise ValueError("prob_out must be a contiguous float32 [B,H,Qb,Kb] tensor")
+    p.score = score.data_ptr()
+    p.score_stride_b, p.score_stride_h, p.score_stride_q, p.score_stride_k = score.stride()
+    p.rule = RULES[rule]
+    if valid is not None:
+        if valid.dtype not in (torch.bool, torch.uint8) or valid.dim() != 4:
+            raise ValueError("valid must be a bool [B,1|H,Qb,Kb] tensor")
+        valid = valid.expand(B, valid.shape[1], Qb, Kb)
+        p.valid = valid.data_ptr()
+        sb, sh, sq, sk = valid.stride()
+        p.valid_stride_b, p.valid_stride_h, p.valid_stride_q, p.valid_stride_k = sb, (sh if valid.shape[1] > 1 else 0), sq, sk
+    p.bits = _ptr(bits)
+    p.prob_out = _ptr(prob_out)
+    p.B, p.H, p.Qb, p.Kb, p.Pb = B, H, Qb, Kb, past_blocks
+    p.softmax = int(softmax)
+    p.threshold, p.alpha = float(threshold), float(alpha)
+    p.topk_k = int(topk_k)
+    p.topk_num, p.topk_den = (topk_ratio if topk_ratio is not None else (0, 1))
+    p.min_budget, p.sink, p.local, p.rows_voting = int(min_budget), int(sink), int(local), int(rows_voting)
+    return p, bits, valid
+
+
 def select_rows(
     score: torch.Tensor,  # [B, H, Qb, Kb] (any strides); bool/uint8 for rule "mask"
     past_blocks: int,
@@ -263,43 +304,89 @@ def select_rows(
     prob_out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Per-row selection rule -> packed keep bits int32 [B, H, Qb, ceil(Kb/32)]."""
-    _require_cuda(score, valid, bits, prob_out)
-    B, H, Qb, Kb = score.shape
-    p = _lib.SelectParams()
-    if rule == "mask":
-        if score.dtype not in (torch.bool, torch.uint8):
-            raise ValueError("rule 'mask' needs a bool/uint8 tensor")
-        p.score_dtype = 0
-    else:
-        if score.dtype not in _DTYPES:
-            raise ValueError(f"unsupported score dtype {score.dtype}")
-        p.score_dtype = _DTYPES[score.dtype]
-    if bits is None:
-        bits = torch.empty((B, H, Qb, words_for(Kb)), dtype=torch.int32, device=score.device)
-    if bits.dtype != torch.int32 or not bits.is_contiguous() or bits.shape != (B, H, Qb, words_for(Kb)):
-        raise ValueError("bits must be a contiguous int32 [B,H,Qb,ceil(Kb/32)] tensor")
-    if prob_out is not None and (prob_out.dtype != torch.float32 or not prob_out.is_contiguous() or prob_out.shape != (B, H, Qb, Kb)):
-        raise ValueError("prob_out must be a contiguous float32 [B,H,Qb,Kb] tensor")
-    p.score = score.data_ptr()
-    p.score_stride_b, p.score_stride_h, p.score_stride_q, p.score_stride_k = score.stride()
-    p.rule = RULES[rule]
-    if valid is not None:
-        if valid.dtype not in (torch.bool, torch.uint8) or valid.dim() != 4:
-            raise ValueError("valid must be a bool [B,1|H,Qb,Kb] tensor")
-        valid = valid.expand(B, valid.shape[1], Qb, Kb)
-        p.valid = valid.data_ptr()
-        sb, sh, sq, sk = valid.stride()
-        p.valid_stride_b, p.valid_stride_h, p.valid_stride_q, p.valid_stride_k = sb, (sh if valid.shape[1] > 1 else 0), sq, sk
-    p.bits = bits.data_ptr()
-    p.prob_out = _ptr(prob_out)
-    p.B, p.H, p.Qb, p.Kb, p.Pb = B, H, Qb, Kb, past_blocks
-    p.softmax = int(softmax)
-    p.threshold, p.alpha = float(threshold), float(alpha)
-    p.topk_k = int(topk_k)
-    p.topk_num, p.topk_den = (topk_ratio if topk_ratio is not None else (0, 1))
-    p.min_budget, p.sink, p.local, p.rows_voting = int(min_budget), int(sink), int(local), int(rows_voting)
+    p, bits, keep = _select_params(score, past_blocks, rule, valid, softmax, threshold, alpha, topk_k, topk_ratio, min_budget,
+                                   sink, local, rows_voting, bits, prob_out)
     _lib.check(_lib.load().ca_select_rows(C.byref(p), _stream()), "ca_select_rows")
+    del keep
     return bits
+
+
+_UNION_SCRATCH: dict = {}
+
+
+def union_scratch(device: torch.device, batch: int, num_kv_heads: int, kv_blocks: int) -> torch.Tensor:
+    """Zeroed scratch of the fused selection + table launch (the per-KV-head union words and tickets).  The
+    kernel leaves it zeroed, so one buffer per (device, stream) serves every call on that stream; it only
+    grows."""
+    key = (device.index, _stream())
+    need = C.c_size_t(0)
+    _lib.check(_lib.load().ca_select_union_scratch_bytes(batch, num_kv_heads, kv_blocks, C.byref(need)), "ca_select_union_scratch_bytes")
+    buf = _UNION_SCRATCH.get(key)
+    if buf is None or buf.numel() * 4 < need.value:
+        buf = torch.zeros((int(need.value) + 3) // 4, dtype=torch.int32, device=device)
+        _UNION_SCRATCH[key] = buf
+    return buf
+
+
+def select_union_table(
+    score: torch.Tensor,  # [B, Hkv*G, Qb, Kb]
+    past_blocks: int,
+    rule: str,
+    *,
+    num_kv_heads: int,
+    block_size: int = 64,
+    page_size: int = 256,
+    keep_recent: int = 0,
+    valid: Optional[torch.Tensor] = None,
+    softmax: bool = False,
+    threshold: float = 0.0,
+    alpha: float = 0.0,
+    topk_k: int = 0,
+    topk_ratio: Optional[tuple[int, int]] = None,
+    min_budget: int = 0,
+    sink: int = 0,
+    local: int = 0,
+    rows_voting: int = 0,
+    bits: Optional[torch.Tensor] = None,  # optional: the per-row bits are written only when given
+    prob_out: Optional[torch.Tensor] = None,
+    out: Optional["BlockTable"] = None,
+    scratch: Optional[torch.Tensor] = None,
+) -> "BlockTable":
+    """``select_rows`` followed by ``union_table`` in ONE launch (see ``ca_select_union_table``): row rule,
+    Q-block union, GQA union and the per-KV-head block table.  ``scratch`` must be zero on first use and
+    must not be shared by calls that can overlap on the device (default: a cached per-stream buffer)."""
+    B, H, Qb, Kb = score.shape
+    if H % num_kv_heads != 0:
+        raise ValueError(f"{H} score heads is not a multiple of {num_kv_heads} kv heads")
+    if Kb - past_blocks != Qb:
+        raise ValueError("the score must cover the chunk's own key blocks: Kb - past_blocks must equal Qb")
+    p, bits, keep = _select_params(score, past_blocks, rule, valid, softmax, threshold, alpha, topk_k, topk_ratio, min_budget,
+                                   sink, local, rows_voting, bits, prob_out, bits_required=False)
+    dev = score.device
+    if out is None:
+        cap = max(past_blocks, 1)
+        out = BlockTable(
+            torch.empty((B, num_kv_heads, cap), dtype=torch.int32, device=dev),
+            torch.empty((B, num_kv_heads), dtype=torch.int32, device=dev),
+            torch.empty((B, num_kv_heads), dtype=torch.int32, device=dev),
+            torch.empty((B, num_kv_heads), dtype=torch.int32, device=dev),
+        )
+    u = _lib.UnionParams()
+    u.B, u.Hkv, u.G, u.Qin, u.Kb, u.Pb = B, num_kv_heads, H // num_kv_heads, Qb, Kb, past_blocks
+    u.keep_recent = int(keep_recent)
+    u.block_size, u.page_size = block_size, page_size
+    u.block_idx, u.idx_stride = out.block_idx.data_ptr(), out.block_idx.shape[-1]
+    u.counts = out.counts.data_ptr()
+    u.cache_seqlens = out.cache_seqlens.data_ptr()
+    u.pages_per_row = out.pages_per_row.data_ptr()
+    if scratch is None:
+        scratch = union_scratch(dev, B, num_kv_heads, Kb)
+    if scratch.dtype != torch.int32 or not scratch.is_contiguous():
+        raise ValueError("scratch must be a contiguous int32 tensor (zero on first use)")
+    _lib.check(_lib.load().ca_select_union_table(C.byref(p), C.byref(u), scratch.data_ptr(), scratch.numel() * 4, _stream()),
+               "ca_select_union_table")
+    del keep
+    return out
 
 
 @dataclass

@@ -294,21 +294,19 @@ class LlamaSeerAttentionChunkedDense(_CompactAttnBase):
                 self._synthetic_importance = torch.rand((1, self.num_key_value_heads, 1, past_key_value.max_tokens // bs),
                                                         generator=g, device=hidden_states.device)
             score = self._synthetic_importance[..., :Kb].expand(hidden_states.shape[0], self.num_key_value_heads, Qb, Kb)
-            bits_for, table = past_key_value.selection_scratch(self.num_key_value_heads, self.num_key_value_heads, Qb, bs)
-            bits = ops.select_rows(score, Kb - Qb, "topk", topk_ratio=tuple(self.config.seerattn_topk_ratio), sink=1,
-                                   local=self.compactattn_keep_recent_blocks, bits=bits_for(Kb))
-            table = ops.union_table(bits=bits, num_kv_heads=self.num_key_value_heads, kv_blocks=Kb, past_blocks=Kb - Qb,
-                                    block_size=bs, out=table)
+            _, table = past_key_value.selection_scratch(self.num_key_value_heads, self.num_key_value_heads, Qb, bs)
+            table = ops.select_union_table(score, Kb - Qb, "topk", num_kv_heads=self.num_key_value_heads, block_size=bs,
+                                           topk_ratio=tuple(self.config.seerattn_topk_ratio), sink=1,
+                                           local=self.compactattn_keep_recent_blocks, out=table)
             attn = ops.attn_compact(q, kv_view, kv_len, self.num_key_value_heads, table.block_idx, table.counts,
                                     block_size=bs, softmax_scale=self.scaling)
             path = "chunked_selected"
         elif self.config.seerattn_sparsity_method == "topk":
             Qb, Kb = logits.shape[2], logits.shape[3]
-            bits_for, table = past_key_value.selection_scratch(self.num_heads, self.num_key_value_heads, Qb, bs)
-            bits = ops.select_rows(logits, Kb - Qb, "topk", topk_ratio=tuple(self.config.seerattn_topk_ratio), sink=1,
-                                   local=self.compactattn_keep_recent_blocks, bits=bits_for(Kb))
-            table = ops.union_table(bits=bits, num_kv_heads=self.num_key_value_heads, kv_blocks=Kb, past_blocks=Kb - Qb,
-                                    block_size=bs, out=table)
+            _, table = past_key_value.selection_scratch(self.num_heads, self.num_key_value_heads, Qb, bs)
+            table = ops.select_union_table(logits, Kb - Qb, "topk", num_kv_heads=self.num_key_value_heads, block_size=bs,
+                                           topk_ratio=tuple(self.config.seerattn_topk_ratio), sink=1,
+                                           local=self.compactattn_keep_recent_blocks, out=table)
             attn = ops.attn_compact(q, kv_view, kv_len, self.num_key_value_heads, table.block_idx, table.counts,
                                     block_size=bs, softmax_scale=self.scaling)
             path = "chunked_selected"

@@ -222,6 +222,25 @@ typedef struct ca_union_params {
 int ca_union_table(const ca_union_params* p, ca_stream_t stream);
 
 /*
+ * ca_select_rows and ca_union_table in ONE launch: every row CTA of the selection ORs its packed bits
+ * into its KV-head row of a small word array and takes a ticket; the CTA that takes the last ticket
+ * of a KV-head row (nobody waits for anybody) compacts that row into the block table.  It replaces the
+ * same reference functions as the two calls it fuses, in particular the pair
+ * build_keep_past_fast_kernel / build_keep_curr_fast_kernel followed by
+ * build_past_indices_and_metadata_from_keep_block_kernel
+ * (compact_attn/csrc/compactattn/cache_fill_kernel.cu:275-385) and the fused Triton
+ * _flashprefill_kv_union_from_scores_kernel (compact_attn/modules/flashprefill_prefill.py:307-376).
+ * sel->bits may be NULL (the per-row bits are then not written).  un gives the table outputs and
+ * Hkv, G (sel->H = Hkv*G), Qin = sel->Qb, Kb, Pb, keep_recent, block_size, page_size; its bits, mask
+ * and keep_kv must be NULL.  scratch: ca_select_union_scratch_bytes() bytes of device memory that is
+ * ZERO on the first call; the kernel leaves it zero, so one buffer serves every later call on the same
+ * stream (calls that may overlap on the device need a buffer each).
+ */
+int ca_select_union_scratch_bytes(int B, int Hkv, int Kb, size_t* bytes_out);
+int ca_select_union_table(const ca_select_params* sel, const ca_union_params* un, void* scratch, size_t scratch_bytes,
+                          ca_stream_t stream);
+
+/*
  * Paged metadata of the compact cache: page_offsets[r] = exclusive prefix of pages_per_row
  * (page_offsets[rows] = total) and block_table[r, slot] = page_offsets[r] + slot for
  * slot < pages_per_row[r], else 0.  Replaces build_block_table_kernel

@@ -111,7 +111,8 @@ def test_32k_paged_cache_training_free_selection_end_to_end(mods):
 
 def test_128k_context_all_kv_heads_against_oracle(mods):
     """The shape the benchmark times: 32/8 heads, chunk 1024 at the end of a 128K-token paged cache with
-    permuted pages, about 20 % of the past blocks per KV head; 128 whole work units in one launch."""
+    permuted pages, about 20 % of the past blocks per KV head: 128 work units in one launch, whole (one
+    unit per SM) and cut over all SMs with the pieces merged (the default at this size)."""
     ops, PagedKVCache = mods
     g = torch.Generator().manual_seed(1234 + 3)
     Q, K, Hq, Hkv, D, bs = 1024, 131072, 32, 8, 128, 64
@@ -132,12 +133,15 @@ def test_128k_context_all_kv_heads_against_oracle(mods):
     lse = torch.empty((1, Hq, Q), dtype=torch.float32, device="cuda")
     from compactattention_b200 import _lib
     n0 = _lib.launch_count()
+    whole = ops.attn_compact(q.cuda(), cache.view(), K, Hkv, idx.cuda(), counts.cuda(), block_size=bs, status=status,
+                             use_workspace=False).cpu()
+    assert _lib.launch_count() - n0 == 1  # without a workspace every unit stays on one SM: no merge launch
     out = ops.attn_compact(q.cuda(), cache.view(), K, Hkv, idx.cuda(), counts.cuda(), block_size=bs, status=status, lse=lse)
-    assert _lib.launch_count() - n0 == 1  # 128 units on the device's SMs stay whole: no merge launch
     out, lse = out.cpu(), lse.cpu()
     assert int(status.item()) == 0
     for h in range(Hkv):  # one KV head at a time keeps the oracle's score tensor small
         want, want_lse = co.compact_attention(q[:, :, h * G:(h + 1) * G], k[:, :, h:h + 1], v[:, :, h:h + 1], idx[:, h:h + 1],
                                               counts[:, h:h + 1], bs, return_lse=True)
         check_attention(out[:, :, h * G:(h + 1) * G], want)
+        check_attention(whole[:, :, h * G:(h + 1) * G], want)
         assert torch.allclose(lse[:, h * G:(h + 1) * G], want_lse, rtol=1e-3, atol=2e-2)

@@ -186,3 +186,53 @@ def test_capacity_and_contract_errors(ops):
         ops.union_table(mask=mask, num_kv_heads=1, kv_blocks=16, past_blocks=12, out=small)
     with pytest.raises(ValueError):
         ops.union_table(mask=mask, num_kv_heads=3, kv_blocks=16, past_blocks=12)
+
+
+@pytest.mark.parametrize("rule,kw", [
+    ("topk", dict(topk_ratio=(1, 5), sink=1, local=2)),
+    ("threshold", dict(softmax=True, threshold=2e-3, keep_recent=2)),
+    ("alpha_rowmax", dict(alpha=0.3, sink=2, local=4, rows_voting=3)),
+    ("cummass", dict(softmax=True, threshold=0.8, sink=1, local=1)),
+])
+@pytest.mark.parametrize("B,Hkv,G,Qb,Kb", [(1, 8, 4, 16, 2048), (2, 2, 7, 4, 130), (1, 1, 1, 1, 33)])
+def test_fused_select_union_table_equals_the_two_launches(ops, rule, kw, B, Hkv, G, Qb, Kb):
+    """One launch (row rule + ticketed Block-Union + table) against select_rows followed by union_table:
+    bits, table, counts, seqlens and pages bit for bit, on three calls in a row with different scores (the
+    kernel must leave its scratch clean), with and without the per-row bits output."""
+    Pb = Kb - Qb
+    H = Hkv * G
+    kw = dict(kw)
+    keep_recent = kw.pop("keep_recent", 0)
+    if "rows_voting" in kw:
+        kw["rows_voting"] = min(kw["rows_voting"], Qb)
+    g = torch.Generator().manual_seed(Kb * 7 + Qb)
+    for call in range(3):
+        score = (torch.randn((B, H, Qb, Kb), generator=g) * 2).cuda()
+        bits = ops.select_rows(score, Pb, rule, **kw)
+        want = ops.union_table(bits=bits, num_kv_heads=Hkv, kv_blocks=Kb, past_blocks=Pb, block_size=64, keep_recent=keep_recent)
+        got_bits = torch.full_like(bits, -1) if call != 1 else None
+        got = ops.select_union_table(score, Pb, rule, num_kv_heads=Hkv, block_size=64, keep_recent=keep_recent, bits=got_bits, **kw)
+        for name in ("block_idx", "counts", "cache_seqlens", "pages_per_row"):
+            assert torch.equal(getattr(got, name), getattr(want, name)), (name, call)
+        if got_bits is not None:
+            assert torch.equal(got_bits, bits)
+    # and against the oracle's union of the rows the kernel selected
+    keep_rows = ops.unpack_bits(bits, Kb).cpu()
+    keep_block = keep_rows.any(dim=2)
+    if keep_recent:
+        keep_block[..., Kb - keep_recent:] = True
+    idx, counts = co.block_union_table(keep_block, Qb * 64, Kb * 64, 64, G)
+    assert torch.equal(got.block_idx.cpu(), idx) and torch.equal(got.counts.cpu(), counts)
+    scratch = ops.union_scratch(torch.device("cuda", torch.cuda.current_device()), B, Hkv, Kb)
+    assert int(scratch.abs().sum().item()) == 0  # left clean
+
+
+def test_fused_select_union_contract_errors(ops):
+    score = torch.randn((1, 8, 4, 64), device="cuda")
+    with pytest.raises(ValueError, match="multiple"):
+        ops.select_union_table(score, 60, "topk", num_kv_heads=3, topk_k=4)
+    with pytest.raises(ValueError, match="Kb - past_blocks"):
+        ops.select_union_table(score, 50, "topk", num_kv_heads=2, topk_k=4)
+    small = torch.zeros(4, dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match="scratch holds"):
+        ops.select_union_table(score, 60, "topk", num_kv_heads=2, topk_k=4, scratch=small)
