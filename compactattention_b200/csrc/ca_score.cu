@@ -415,6 +415,61 @@ __global__ void __launch_bounds__(kGateThreads) gate_scores2_kernel(const GateAr
   }
 }
 
+// Variant for 16-bit key blocks with C == 128 and Qb <= 16 (the learned gate's usual shape): a thread
+// owns ONE key block and fetches all of its 128 channels as sixteen 128-bit loads issued back to back,
+// so the row costs one memory latency instead of four; half as much work per thread gives twice the
+// CTAs of the two-blocks-per-thread form (latency-bound: 20.4 us -> see profiles/ for the figure).
+template <int KDT>
+__global__ void __launch_bounds__(kGateThreads) gate_scores3_kernel(const GateArgs a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
+  extern __shared__ float gate_smem[];  // q rows [16][128], zero padded
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (a.Hq / a.Hk);
+  const int j = blockIdx.x * kGateThreads + threadIdx.x;
+  const int jc = j < a.Kb ? j : a.Kb - 1;
+  // the key block's loads go out first; the q rows are staged while they are in flight
+  const uint16_t* kp = reinterpret_cast<const uint16_t*>(a.k) + b * a.k_b + static_cast<long long>(jc) * a.k_blk + hk * a.k_h;
+  uint4 raw[16];
+#pragma unroll
+  for (int u = 0; u < 16; ++u) raw[u] = __ldg(reinterpret_cast<const uint4*>(kp + u * 8));
+  for (int e = threadIdx.x * 8; e < kGateRows * 128; e += kGateThreads * 8) {
+    const int i = e / 128, c = e % 128;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (i < a.Qb) load8(a.q, b * a.q_b + i * a.q_blk + h * a.q_h + c, a.q_dtype, v);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) gate_smem[e + u] = v[u];
+  }
+  __syncthreads();
+  if (j >= a.Kb) return;
+  float acc[kGateRows];
+#pragma unroll
+  for (int r = 0; r < kGateRows; ++r) acc[r] = 0.f;
+#pragma unroll
+  for (int u = 0; u < 16; ++u) {
+    float kv[8];
+    widen8<KDT>(raw[u], kv);
+#pragma unroll
+    for (int r = 0; r < kGateRows; ++r) {
+      const float4 q0 = *reinterpret_cast<const float4*>(&gate_smem[r * 128 + u * 8]);
+      const float4 q1 = *reinterpret_cast<const float4*>(&gate_smem[r * 128 + u * 8 + 4]);
+      acc[r] = fmaf(q0.x, kv[0], acc[r]);
+      acc[r] = fmaf(q0.y, kv[1], acc[r]);
+      acc[r] = fmaf(q0.z, kv[2], acc[r]);
+      acc[r] = fmaf(q0.w, kv[3], acc[r]);
+      acc[r] = fmaf(q1.x, kv[4], acc[r]);
+      acc[r] = fmaf(q1.y, kv[5], acc[r]);
+      acc[r] = fmaf(q1.z, kv[6], acc[r]);
+      acc[r] = fmaf(q1.w, kv[7], acc[r]);
+    }
+  }
+  float* obase = a.out + ((static_cast<long long>(b) * a.Hq + h) * a.Qb) * a.Kb;
+#pragma unroll
+  for (int r = 0; r < kGateRows; ++r) {
+    if (r < a.Qb) obase[static_cast<long long>(r) * a.Kb + j] = (j <= a.Pb + r) ? acc[r] * a.scale : a.masked_value;
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // FlashPrefill block score: for q-block i, head h, key block j:
 //   S[t,j] = (q_t . meanK_j) * D^-0.5 * log2e over tokens t of the q-block with P + t >= (j+1)*bs - 1
@@ -910,6 +965,17 @@ int ca_gate_scores(const ca_gate_score_params* p, ca_stream_t stream_) {
   const size_t smem = static_cast<size_t>(p->Qb) * p->C * sizeof(float);
   CA_REQUIRE(smem <= 160 * 1024, "Qb * C too large for the gate score kernel");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (p->C == 128 && p->Qb <= kGateRows && (p->k_dtype == CA_DTYPE_BF16 || p->k_dtype == CA_DTYPE_F16)) {
+    const dim3 grid3(ceil_div(p->Kb, kGateThreads), p->Hq, p->B);
+    const size_t smem3 = static_cast<size_t>(kGateRows) * 128 * sizeof(float);
+    if (p->k_dtype == CA_DTYPE_BF16) {
+      launch_kernel(gate_scores3_kernel<CA_DTYPE_BF16>, dim3(grid3), dim3(kGateThreads), smem3, stream, a);
+    } else {
+      launch_kernel(gate_scores3_kernel<CA_DTYPE_F16>, dim3(grid3), dim3(kGateThreads), smem3, stream, a);
+    }
+    CA_LAUNCH_CHECK("gate_scores3_kernel");
+    return CA_OK;
+  }
   if (p->C % 32 == 0) {
     const int q_pad = ceil_div(p->Qb, kGateRows) * kGateRows;
     const size_t smem2 = static_cast<size_t>(q_pad) * p->C * sizeof(float);
