@@ -72,6 +72,8 @@ class SelectParams(C.Structure):
         ("min_budget", C.c_int32),
         ("sink", C.c_int32), ("local", C.c_int32),
         ("rows_voting", C.c_int32),
+        ("threshold_ptr", C.c_void_p),
+        ("threshold_stride_b", C.c_int64),
     ]
 
 

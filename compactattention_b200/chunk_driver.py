@@ -88,7 +88,7 @@ class MeanKSelectorState:
         self.length = 0
 
     def append_and_score(self, q: torch.Tensor, k_chunk: torch.Tensor, kv_len: int) -> torch.Tensor:
-        nb = k_chunk.shape[1] // self.block_size
+        nb = -(-k_chunk.shape[1] // self.block_size)
         ops.pool_blocks(k_chunk, self.block_size, ("avg",), out=self.mean_k, out_block_offset=self.length)
         self.length += nb
         _, _, norm = ops.flashprefill_score(q, self.mean_k[:, : self.length], kv_len, self.block_size)

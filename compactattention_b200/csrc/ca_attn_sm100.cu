@@ -111,7 +111,8 @@ struct KernelArgs {
   int past_blocks;  // Pb
   int spb;          // 64-token sub-blocks per block
   int block_size;
-  int past_tokens;  // P
+  int past_tokens;  // tokens before the chunk region (a multiple of block_size)
+  int q_off;        // tokens of the chunk region that precede the first query (0 unless a dense launch has an unaligned past)
   int page_size, pages_per_seq, num_pages;
   const int32_t* block_idx;
   int block_idx_stride;
@@ -171,6 +172,7 @@ __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
 
 // Number of visible columns (0..64) of 64-token sub-block u for chunk token t.
 __device__ __forceinline__ int visible_cols(int u, int n_sub, int n_past_sub, int t) {
+  // t counts from the start of the chunk region (query token index + q_off)
   if (u >= n_sub) return 0;
   if (u < n_past_sub) return kSub;
   int lim = t - (u - n_past_sub) * kSub + 1;
@@ -181,7 +183,7 @@ __device__ __forceinline__ int visible_cols(int u, int n_sub, int n_past_sub, in
 __device__ __forceinline__ int chunk_subs(const KernelArgs& a, int pair) {
   int t_last = (2 * pair + 2) * a.tpt - 1;
   if (t_last > a.Q - 1) t_last = a.Q - 1;
-  return t_last / kSub + 1;
+  return (t_last + a.q_off) / kSub + 1;
 }
 __device__ __forceinline__ int unit_iters(const KernelArgs& a, int count, int pair) {
   return (count * a.spb + chunk_subs(a, pair) + 1) >> 1;
@@ -639,8 +641,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             const bool masked = (2 * j + 1) >= sg.n_past_sub;  // a chunk or tail sub-block is in this step
             int lim0 = kSub, lim1 = kSub;
             if (masked) {
-              lim0 = visible_cols(2 * j, sg.n_sub, sg.n_past_sub, t);
-              lim1 = visible_cols(2 * j + 1, sg.n_sub, sg.n_past_sub, t);
+              lim0 = visible_cols(2 * j, sg.n_sub, sg.n_past_sub, t + a.q_off);
+              lim1 = visible_cols(2 * j + 1, sg.n_sub, sg.n_past_sub, t + a.q_off);
             }
             // the whole S row (128 fp32) comes into registers with one wait
             uint32_t sv[128];
@@ -927,8 +929,11 @@ static int validate(const ca_attn_params* p) {
   CA_REQUIRE(static_cast<long long>(p->B) * p->Hkv <= kMaxRows, "more than %d (batch x kv head) rows are not supported", kMaxRows);
   CA_REQUIRE(p->block_size > 0 && p->block_size % kSub == 0, "block_size must be a positive multiple of 64");
   CA_REQUIRE(p->kv_len >= p->Q, "kv_len (%d) must be >= Q (%d)", p->kv_len, p->Q);
-  CA_REQUIRE((p->kv_len - p->Q) % p->block_size == 0, "past length must be a multiple of block_size");
-  CA_REQUIRE(p->kv.page_size > 0 && p->kv.page_size % kSub == 0, "page_size must be a positive multiple of 64");
+  CA_REQUIRE((p->kv_len - p->Q) % p->block_size == 0 || p->block_idx == nullptr,
+             "with a block table the past length (kv_len - Q = %d) must be a multiple of block_size (%d)", p->kv_len - p->Q,
+             p->block_size);
+  CA_REQUIRE(p->kv.page_size > 0 && (p->kv.page_size % kSub == 0 || p->kv.pages_per_seq == 1),
+             "page_size must be a positive multiple of 64 (any length when a sequence is one page)");
   CA_REQUIRE(p->kv.num_pages > 0 && p->kv.pages_per_seq > 0, "num_pages and pages_per_seq must be positive");
   CA_REQUIRE((long long)p->kv.pages_per_seq * p->kv.page_size >= p->kv_len,
              "pages_per_seq*page_size (%lld) does not cover kv_len (%d)",
@@ -1071,7 +1076,9 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
   a.tpt = tpt;
   a.n_pairs = n_pairs;
   a.block_size = p->block_size;
-  a.past_tokens = p->kv_len - p->Q;
+  // a dense launch whose past is not a block multiple treats the remainder as the head of the chunk region
+  a.q_off = (p->kv_len - p->Q) % p->block_size;
+  a.past_tokens = p->kv_len - p->Q - a.q_off;
   a.past_blocks = a.past_tokens / p->block_size;
   a.spb = p->block_size / kSub;
   a.page_size = p->kv.page_size;

@@ -63,7 +63,7 @@ extern "C" {
 
 const char* ca_last_error(void) { return ca::last_error_buffer(); }
 
-int ca_abi_version(void) { return 1; }
+int ca_abi_version(void) { return 2; }
 
 int ca_set_programmatic_launch(int enabled) {
   return ca::programmatic_launch_flag().exchange(enabled != 0 ? 1 : 0, std::memory_order_relaxed);

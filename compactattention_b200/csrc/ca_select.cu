@@ -37,6 +37,8 @@ struct RowArgs {
   int rule;
   int softmax;     // apply a masked softmax to the row before the rule
   float threshold; // THRESHOLD: keep s > threshold.  CUMMASS: tau
+  const float* threshold_ptr;  // optional device value(s) replacing `threshold`: element b * threshold_stride
+  long long threshold_stride;
   float alpha;     // ALPHA_ROWMAX: keep s >= alpha * rowmax
   int topk_k;      // TOPK: absolute k when > 0 ...
   int topk_num, topk_den;  // ... else k = max(1, (num * n_valid + den/2) / den)
@@ -317,8 +319,9 @@ __global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs 
   }
 
   // ---- the rule ----
+  const float thr = a.threshold_ptr ? __ldg(a.threshold_ptr + b * a.threshold_stride) : a.threshold;
   if (a.rule == CA_RULE_THRESHOLD) {
-    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) keep[j] = s[j] > a.threshold;  // -inf never passes
+    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) keep[j] = s[j] > thr;  // -inf never passes
   } else if (a.rule == CA_RULE_MASK) {
     for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) keep[j] = s[j] > 0.5f;
   } else if (a.rule == CA_RULE_ALPHA_ROWMAX) {
@@ -369,7 +372,7 @@ __global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs 
         const int j = static_cast<int>(comp[r] & 0xffffffffu);
         const float p = s[j] == -INFINITY ? 0.f : s[j];
         acc = __fadd_rn(acc, p);
-        if (acc >= a.threshold) {
+        if (acc >= thr) {
           cut = r + 1;
           break;
         }
@@ -539,6 +542,8 @@ static int fill_row_args(const ca_select_params* p, ca::select::RowArgs* out, si
   a.rule = p->rule;
   a.softmax = p->softmax;
   a.threshold = p->threshold;
+  a.threshold_ptr = p->threshold_ptr;
+  a.threshold_stride = p->threshold_stride_b;
   a.alpha = p->alpha;
   a.topk_k = p->topk_k, a.topk_num = p->topk_num, a.topk_den = p->topk_den;
   a.min_budget = p->min_budget;

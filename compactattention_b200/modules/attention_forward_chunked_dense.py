@@ -108,6 +108,28 @@ def _kv_dims(key_states, kv_len: Optional[int]):
     return int(key_states.shape[1]), int(key_states.shape[2])
 
 
+_MASK_VERIFIED: Dict[Tuple[str, int, int], bool] = {}
+
+
+def clear_fast_path_content_cache() -> None:
+    """Forget which (device, batch, kv_len) attention masks were verified all-ones (the reference's
+    function of this name, :551-553; call between sequences)."""
+    _MASK_VERIFIED.clear()
+
+
+def _check_attention_mask(attention_mask, kv_len: int) -> None:
+    """Token masks must be all ones on this path.  The content check costs a device-to-host read, so it
+    runs once per (device, batch, kv_len) - the reference caches its verification the same way."""
+    if attention_mask is None:
+        return
+    key = (str(attention_mask.device), int(attention_mask.shape[0]), int(kv_len))
+    if _MASK_VERIFIED.get(key):
+        return
+    if attention_mask.dim() == 2 and not bool(attention_mask[:, -kv_len:].to(torch.bool).all().item()):
+        raise NotImplementedError("padded batches (an attention_mask with zeros) are not supported by the B200 path")
+    _MASK_VERIFIED[key] = True
+
+
 def _check_common(query_states, key_states, value_states, query_length, block_size, indexed_impl, kv_len=None):
     if query_length <= 1:
         raise ValueError("chunked compact attention expects query_length > 1.")
@@ -124,11 +146,21 @@ def _check_common(query_states, key_states, value_states, query_length, block_si
         raise NotImplementedError("the B200 path computes in bf16/f16; q, k, v must share one of these dtypes")
     if query_states.shape[-1] != 128:
         raise NotImplementedError("the B200 path supports head_dim 128 only")
-    q_len = query_states.shape[1]
-    kv_len, _ = _kv_dims(key_states, kv_len)
-    if block_size % 64 or q_len % block_size or kv_len % block_size:
-        raise NotImplementedError(
-            f"q_len ({q_len}) and kv_len ({kv_len}) must be multiples of block_size ({block_size}), itself a multiple of 64")
+    if block_size % 64:
+        raise NotImplementedError(f"block_size ({block_size}) must be a multiple of 64")
+
+
+def _dense_fallback(query_states, key_states, value_states, k_hf, v_hf, kv_len, num_kv_heads, block_size, softmax_scale, timing,
+                    path: str):
+    """Dense causal attention over the whole cache with the same kernel: the reference's route for a
+    past length that is not a block multiple (``_dense_prefill_full_kv``, :2413-2423)."""
+    kv = _kv_view(key_states, value_states, k_hf, v_hf)
+    out, ms = _timed(lambda: ops.attn_compact(query_states, kv, kv_len, num_kv_heads, None, None, block_size=block_size,
+                                              softmax_scale=softmax_scale), timing)
+    if not timing:
+        return out, None
+    return out, {"dense_kernel_ms": ms, "col_indexed_dense_kernel_ms": 0.0, "col_index_build_ms": 0.0, "fallback_used": 1.0,
+                 "col_indexed_dense_tail_dense_fallback_calls": 1.0, "path": path, "compactattn_version": COMPACTATTN_VERSION}
 
 
 def _kv_view(key_states, value_states, k_hf, v_hf) -> ops.KvCacheView:
@@ -136,7 +168,8 @@ def _kv_view(key_states, value_states, k_hf, v_hf) -> ops.KvCacheView:
     viewed in place, seq-first ``[B,K,Hkv,D]`` or, for B == 1, heads-first ``k_hf [B,Hkv,K,D]``."""
     if isinstance(key_states, ops.KvCacheView):
         return key_states
-    if key_states.stride(3) == 1 and (key_states.shape[0] == 1 or key_states.stride(0) == key_states.shape[1] * key_states.stride(1)):
+    if key_states.stride(3) == 1 and (key_states.shape[0] == 1 or key_states.shape[1] % 64 != 0
+                                      or key_states.stride(0) == key_states.shape[1] * key_states.stride(1)):
         return ops.KvCacheView.from_seq_first(key_states, value_states)
     if k_hf is not None and v_hf is not None and k_hf.shape[0] == 1:
         return ops.KvCacheView.from_heads_first(k_hf, v_hf)
@@ -207,8 +240,12 @@ def chunked_prefill_column_dense_attention_from_keep_block(
             raise ValueError(f"valid_block shape mismatch: expected {tuple(keep_block.shape)}, got {tuple(valid_block.shape)}")
     if num_q_heads != num_kv_heads * num_key_value_groups:
         raise ValueError("num_key_value_groups does not match the head counts")
+    _check_attention_mask(attention_mask, kv_len)
     past_blocks = (kv_len - q_len) // block_size
     timing = bool(return_stats)
+    if (kv_len - q_len) % block_size != 0:
+        return _dense_fallback(query_states, key_states, value_states, k_hf, v_hf, kv_len, num_kv_heads, block_size,
+                               softmax_scale, timing, "dense_misaligned_past")
 
     def _build():
         if _row_bits is not None:
@@ -291,14 +328,18 @@ def chunked_prefill_column_dense_attention_forward(
     threshold = _effective_threshold(threshold)
     _refuse_debug_modes()
     keep_recent_blocks = _effective_keep_recent(keep_recent_blocks)
-    if isinstance(threshold, torch.Tensor):
-        if threshold.numel() != 1:
-            raise NotImplementedError("per-batch threshold tensors are not supported by the B200 path")
-        threshold = float(threshold.item())
     bsz, q_len, num_q_heads, head_dim = query_states.shape
     kv_len, num_kv_heads = _kv_dims(key_states, kv_len)
-    kv_blocks = kv_len // block_size
-    q_blocks = q_len // block_size
+    if isinstance(threshold, torch.Tensor) and (threshold.dim() > 1 or threshold.numel() not in (1, bsz)):
+        raise ValueError(f"Expected scalar or 1D batch threshold tensor, got shape={tuple(threshold.shape)}")
+    if softmax_scale is None:
+        softmax_scale = head_dim ** -0.5
+    if (kv_len - q_len) % block_size != 0:
+        _check_attention_mask(attention_mask, kv_len)
+        return _dense_fallback(query_states, key_states, value_states, k_hf, v_hf, kv_len, num_kv_heads, block_size,
+                               softmax_scale, bool(return_stats), "dense_misaligned_past")
+    kv_blocks = (kv_len + block_size - 1) // block_size
+    q_blocks = (q_len + block_size - 1) // block_size
     if attn_gate_score.dim() != 4 or attn_gate_score.shape[0] != bsz or attn_gate_score.shape[2] != q_blocks:
         raise ValueError(f"attn_gate_score must be [B, H, {q_blocks}, Kb], got {tuple(attn_gate_score.shape)}")
     gate_heads = attn_gate_score.shape[1]
@@ -322,7 +363,8 @@ def chunked_prefill_column_dense_attention_forward(
         valid = block_attention_mask[..., -q_blocks:, -score_blocks:].to(torch.bool)
 
     def _select():
-        return ops.select_rows(attn_gate_score, past_blocks - missing, "threshold", threshold=float(threshold), valid=valid)
+        return ops.select_rows(attn_gate_score, past_blocks - missing, "threshold", valid=valid,
+                               threshold=threshold if isinstance(threshold, torch.Tensor) else float(threshold))
 
     bits, select_ms = _timed(_select, timing)
     if missing:

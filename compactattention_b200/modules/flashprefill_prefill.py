@@ -62,8 +62,14 @@ def flashprefill_compactattn_prefill_full_kv(
                  "flashprefill_selected_blocks": 0.0, "flashprefill_query_blocks": 0.0, "flashprefill_key_blocks": 0.0}
         return out, (stats if measure_timing else {})
 
-    q_blocks, kv_blocks = q_len // block_size, kv_len // block_size
-    past_blocks = kv_blocks - q_blocks
+    if (kv_len - q_len) % block_size != 0:
+        # a past that is not a block multiple: dense over the whole cache (the reference's dense fallback, :904-935)
+        from .attention_forward_chunked_dense import _dense_fallback
+        out, stats = _dense_fallback(query_states, key_states, value_states, k_hf, v_hf, kv_len, num_kv_heads, block_size,
+                                     softmax_scale, measure_timing, "dense_misaligned_past")
+        return out, (stats or {})
+    q_blocks, kv_blocks = -(-q_len // block_size), -(-kv_len // block_size)
+    past_blocks = (kv_len - q_len) // block_size
 
     def _score():
         if mean_k_cache is None and isinstance(key_states, ops.KvCacheView):

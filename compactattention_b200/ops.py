@@ -68,26 +68,28 @@ class KvCacheView:
 
     @staticmethod
     def from_seq_first(k: torch.Tensor, v: torch.Tensor) -> "KvCacheView":
-        """``[B, K, Hkv, D]`` tensors (the reference's ``key_states`` layout); K % 64 == 0."""
+        """``[B, K, Hkv, D]`` tensors (the reference's ``key_states`` layout).  A length that is a
+        multiple of 64 is viewed as 64-token pages; any other length as one page per sequence, whose
+        ragged end the attention kernel's loads fill with zeros (only ``attn_compact`` takes such a view)."""
         B, K, Hkv, D = k.shape
-        if K % 64 != 0:
-            raise ValueError(f"kv_len {K} must be a multiple of 64")
         if k.stride() != v.stride() or k.stride(3) != 1:
             raise ValueError("k and v must share strides and have a contiguous head dim")
+        if K % 64 != 0:
+            return KvCacheView(k, v, k.stride(0), k.stride(1), k.stride(2), K, B, 1)
         if B > 1 and k.stride(0) != K * k.stride(1):
             raise ValueError("batch stride must equal K * token stride")
         return KvCacheView(k, v, 64 * k.stride(1), k.stride(1), k.stride(2), 64, B * (K // 64), K // 64)
 
     @staticmethod
     def from_heads_first(k: torch.Tensor, v: torch.Tensor) -> "KvCacheView":
-        """``[B, Hkv, K, D]`` tensors (the reference's ``k_hf`` layout); K % 64 == 0."""
+        """``[B, Hkv, K, D]`` tensors (the reference's ``k_hf`` layout), B == 1; a ragged K is one page."""
         B, Hkv, K, D = k.shape
-        if K % 64 != 0:
-            raise ValueError(f"kv_len {K} must be a multiple of 64")
         if k.stride() != v.stride() or k.stride(3) != 1:
             raise ValueError("k and v must share strides and have a contiguous head dim")
         if B > 1:
             raise ValueError("heads-first views are supported for B == 1; use a paged cache for batches")
+        if K % 64 != 0:
+            return KvCacheView(k, v, k.stride(0), k.stride(2), k.stride(1), K, 1, 1)
         return KvCacheView(k, v, 64 * k.stride(2), k.stride(2), k.stride(1), 64, K // 64, K // 64)
 
     @staticmethod
@@ -278,11 +280,19 @@ def _select_params(score, past_blocks, rule, valid, softmax, threshold, alpha, t
     p.prob_out = _ptr(prob_out)
     p.B, p.H, p.Qb, p.Kb, p.Pb = B, H, Qb, Kb, past_blocks
     p.softmax = int(softmax)
+    keep_thr = None
+    if isinstance(threshold, torch.Tensor):
+        # a scalar or per-batch threshold tensor stays on the device: the kernel reads it (no .item() sync)
+        if threshold.numel() not in (1, B) or threshold.dim() > 1:
+            raise ValueError(f"Expected scalar or 1D batch threshold tensor, got shape={tuple(threshold.shape)}")
+        keep_thr = threshold.detach().to(device=score.device, dtype=torch.float32).reshape(-1).contiguous()
+        p.threshold_ptr, p.threshold_stride_b = keep_thr.data_ptr(), (1 if keep_thr.numel() > 1 else 0)
+        threshold = 0.0
     p.threshold, p.alpha = float(threshold), float(alpha)
     p.topk_k = int(topk_k)
     p.topk_num, p.topk_den = (topk_ratio if topk_ratio is not None else (0, 1))
     p.min_budget, p.sink, p.local, p.rows_voting = int(min_budget), int(sink), int(local), int(rows_voting)
-    return p, bits, valid
+    return p, bits, (valid, keep_thr)
 
 
 def select_rows(
@@ -292,7 +302,7 @@ def select_rows(
     *,
     valid: Optional[torch.Tensor] = None,  # bool [B, 1|H, Qb, Kb]; None = block-causal
     softmax: bool = False,
-    threshold: float = 0.0,
+    threshold=0.0,  # float, or a scalar / per-batch tensor read on the device
     alpha: float = 0.0,
     topk_k: int = 0,
     topk_ratio: Optional[tuple[int, int]] = None,  # (num, den): k = max(1, round_half_up(num*n_valid/den))

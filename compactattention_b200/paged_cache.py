@@ -22,8 +22,10 @@ class PagedKVCache:
         self.batch, self.page_size = batch, page_size
         self.pages_per_seq = max_tokens // page_size
         n = batch * self.pages_per_seq
-        self.k_pages = torch.empty((n, page_size, num_kv_heads, head_dim), dtype=dtype, device=device)
-        self.v_pages = torch.empty_like(self.k_pages)
+        # zero-filled: a chunk that ends inside a page leaves the page's tail unwritten, and the attention
+        # kernel multiplies those value rows by exact zeros, which must not meet NaN or Inf bit patterns
+        self.k_pages = torch.zeros((n, page_size, num_kv_heads, head_dim), dtype=dtype, device=device)
+        self.v_pages = torch.zeros_like(self.k_pages)
         if page_table is None:
             page_table = torch.arange(n, dtype=torch.int32, device=device).view(batch, self.pages_per_seq)
         if page_table.shape != (batch, self.pages_per_seq) or page_table.dtype != torch.int32:

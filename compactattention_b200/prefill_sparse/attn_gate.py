@@ -26,7 +26,10 @@ class MultiHeadLinear(nn.Module):
         self.in_channel = in_channel_size
         self.hidden_size = hidden_size
         self.num_head = num_head
-        self.weight = nn.Parameter(torch.empty(num_head, in_channel_size, hidden_size))
+        # N(0, 0.02) like the reference's model initialisation of the gate (initializer_range,
+        # prefill_sparse/llama/modeling_llama_seerattn.py:765-777); a checkpoint overwrites it.  Never left
+        # uninitialised: stray NaN bit patterns in a fresh allocation would silently deselect every block.
+        self.weight = nn.Parameter(torch.empty(num_head, in_channel_size, hidden_size).normal_(mean=0.0, std=0.02))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:  # x [B, S, h, I] float32 pooled blocks
         return ops.gate_project(x.to(torch.float32).contiguous(), self.weight.detach().contiguous())

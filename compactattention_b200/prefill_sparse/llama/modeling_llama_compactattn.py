@@ -12,7 +12,10 @@ Both return the reference's 5-tuple ``(attn_output, mask_loss, None, attn_gate_o
 What differs by design: the KV cache is a paged cache that is appended in place
 (``paged_cache.PagedKVCache``) instead of a ``DynamicCache`` that is concatenated every chunk; the
 selector state (gate K-block cache, mean-K cache) lives beside it in ``CompactAttnCache``; inference
-only (no distillation loss); decode (``q_len == 1``) is not on this path and raises.  Under tensor
+only (no distillation loss); decode (``q_len == 1``) appends to the paged cache and runs dense attention
+with the same kernel, as the reference runs decode dense (:880-891).  A chunk that is not a block
+multiple (a prompt's last chunk) is handled; once the cache length is not a block multiple every later
+call is dense.  Under tensor
 parallelism a module holds the projections of its rank's heads (``tp.HeadShard``) and the row-parallel
 ``o_proj`` output is summed with one all-reduce.
 """
@@ -263,13 +266,18 @@ class LlamaSeerAttentionChunkedDense(_CompactAttnBase):
             raise ValueError("the B200 path needs a CompactAttnCache as past_key_value")
         input_shape = hidden_states.shape[:-1]
         q_len = hidden_states.shape[1]
-        if q_len <= 1:
-            raise NotImplementedError("decode (q_len == 1) is dense in the reference and not on this path")
         bs = self.config.seerattn_gate_block_size
         q_nope, k_nope, v = self._project(hidden_states)
         cos, sin = position_embeddings
         st = past_key_value.layer(self.layer_idx, self.num_key_value_heads, self.head_dim)
+        past_len = st.kv.length
         q, kv_view, kv_len = self._do_rope_and_kv_cache_update(q_nope, k_nope, v, past_key_value, cos, sin, cache_position)
+        if q_len == 1 or past_len % bs != 0:
+            # decode, or a call after a chunk that ended inside a block: dense, the gate is not consulted
+            # (reference :741-742, :880-891)
+            out = self._finish(self._dense(q, kv_view, kv_len, bs), input_shape)
+            self._compactattn_last_stats = {"path": "other"} if self.compactattn_debug else None
+            return out, 0.0, None, None, None
         # the gate sees pre-RoPE q/k pooled to blocks, with RoPE at block positions; its K-block cache
         # is appended for every chunk, also when the chunk itself runs dense
         if st.gate is None:
@@ -278,7 +286,7 @@ class LlamaSeerAttentionChunkedDense(_CompactAttnBase):
         rope_blocks = None
         if block_position_embeddings is not None:
             bcos, bsin = block_position_embeddings
-            nb = q_len // bs
+            nb = -(-q_len // bs)
             rope_blocks = (bcos[..., -nb:, :], bsin[..., -nb:, :])
         logits = st.gate.append_and_score(q_nope, k_nope, rope_blocks, rope_blocks)
         first_chunk = kv_len == q_len
@@ -345,13 +353,17 @@ class LlamaFlashPrefillCompactAttnAttention(_CompactAttnBase):
             raise ValueError("the B200 path needs a CompactAttnCache as past_key_value")
         input_shape = hidden_states.shape[:-1]
         q_len = hidden_states.shape[1]
-        if q_len <= 1:
-            raise NotImplementedError("decode (q_len == 1) is dense in the reference and not on this path")
         cfg = self.config
         bs = cfg.seerattn_flashprefill_block_size
         q, k, v = self._project(hidden_states)
         cos, sin = position_embeddings
         st = past_key_value.layer(self.layer_idx, self.num_key_value_heads, self.head_dim)
+        if q_len == 1 or st.kv.length % bs != 0:
+            # decode, or a call after a chunk that ended inside a block: dense, no selector state is touched
+            q, kv_view, kv_len = self._do_rope_and_kv_cache_update(q, k, v, past_key_value, cos, sin, cache_position)
+            out = self._finish(self._dense(q, kv_view, kv_len, bs), input_shape)
+            self._compactattn_last_stats = {"path": "dense_fallback"} if self.compactattn_debug else None
+            return out, 0.0, None, None, None
         # mean-K cache of the post-RoPE keys, appended in place by the same launch that rotates and
         # stores the keys (the reference re-concatenates a list of parts every chunk,
         # modeling_llama_flashprefill_compactattn.py:121-150)
@@ -360,7 +372,7 @@ class LlamaFlashPrefillCompactAttnAttention(_CompactAttnBase):
                                            self.head_dim, bs, hidden_states.device, hidden_states.dtype)
         q, kv_view, kv_len = self._do_rope_and_kv_cache_update(q, k, v, past_key_value, cos, sin, cache_position,
                                                                mean_k=st.mean_k.mean_k, block_size=bs)
-        st.mean_k.length = kv_len // bs
+        st.mean_k.length = -(-kv_len // bs)
         if kv_len > q_len and not cfg.seerattn_chunked_prefill_force_dense:
             attn, stats = flashprefill_compactattn_prefill_full_kv(
                 q, kv_view, kv_view, attention_mask, softmax_scale=self.scaling,

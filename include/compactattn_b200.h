@@ -42,7 +42,7 @@ extern "C" {
 typedef void* ca_stream_t; /* cudaStream_t */
 
 const char* ca_last_error(void);
-/* ABI version; bumped when a struct below changes. */
+/* ABI version; bumped when a struct below changes (2: ca_select_params.threshold_ptr). */
 int ca_abi_version(void);
 /* Number of kernel launches the library has enqueued in this process (all entry points). */
 int64_t ca_launch_count(void);
@@ -187,6 +187,12 @@ typedef struct ca_select_params {
   int32_t min_budget;
   int32_t sink, local;
   int32_t rows_voting;
+  /* Optional threshold in device memory (f32), read by the kernel instead of `threshold`: element
+   * b * threshold_stride_b for batch entry b (stride 0 = one value for all).  The reference accepts a
+   * scalar or per-batch threshold tensor (compact_attn/modules/attention_forward_chunked_dense.py:381-392);
+   * reading it on the device keeps the call free of a device-to-host synchronisation. */
+  const float* threshold_ptr;
+  int64_t threshold_stride_b;
 } ca_select_params;
 
 int ca_select_rows(const ca_select_params* p, ca_stream_t stream);

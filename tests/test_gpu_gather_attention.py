@@ -165,8 +165,15 @@ def test_attention_contract_errors(ops):
         ops.attn_compact(q, ops.KvCacheView.from_seq_first(k, k), 128, 1, None, None)
     q = torch.zeros((1, 64, 2, 128), dtype=torch.bfloat16, device="cuda")
     k = torch.zeros((1, 160 + 64, 1, 128), dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(ValueError, match="multiple of 64"):
-        ops.KvCacheView.from_seq_first(k, k)
+    # a cache whose length is not a multiple of 64 is one page per sequence; the attention kernel takes it
+    # (its loads zero-fill the ragged end), the gather (a plain block copy) does not
+    ragged = ops.KvCacheView.from_seq_first(k, k)
+    assert ragged.pages_per_seq == 1 and ragged.page_size == 224
+    idx = torch.zeros((1, 1, 2), dtype=torch.int32, device="cuda")
+    cnt = torch.zeros((1, 1), dtype=torch.int32, device="cuda")
+    dst = torch.zeros((512, 128), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="multiple of 64"):
+        ops.gather_kv(ragged, 1, 1, 64, 224, idx, cnt, dst, dst.clone(), dst_row_stride_tokens=512)
 
 
 @pytest.mark.parametrize("B,Q,K,Hkv,bs,density,layout,page", [(1, 128, 640, 2, 64, 0.2, "seq", 256), (2, 256, 4096, 4, 64, 0.3, "paged", 256),

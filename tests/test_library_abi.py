@@ -37,7 +37,7 @@ def test_binding_table_matches_header(lib):
 
 
 def test_abi_version_and_error_string(lib):
-    assert lib.ca_abi_version() == 1
+    assert lib.ca_abi_version() == 2
     assert isinstance(lib.ca_last_error(), bytes)
     assert lib.ca_launch_count() >= 0
 

@@ -77,8 +77,8 @@ def test_replaced_model_prefills_like_the_stock_model(variant):
         pytest.skip("needs a CUDA device")
     from transformers import DynamicCache
     from compactattention_b200.load_attention_replacement import load_llama_attention_replacement_model, new_cache
-    L, chunk = 1024, 256
-    ids = torch.randint(0, 1024, (1, L), generator=torch.Generator().manual_seed(5)).cuda()
+    L, chunk, decode = 1000, 256, 3  # the last chunk has 232 tokens (not a block multiple); then three decode steps
+    ids = torch.randint(0, 1024, (1, L + decode), generator=torch.Generator().manual_seed(5)).cuda()
     stock = tiny_llama(seed=3).cuda()
     with torch.no_grad():
         want = stock.model(input_ids=ids, use_cache=False).last_hidden_state.float()
@@ -87,16 +87,18 @@ def test_replaced_model_prefills_like_the_stock_model(variant):
                                                                           flashprefill_block_size=64)
     model = load_llama_attention_replacement_model(model_id=None, base_model=tiny_llama(seed=3).cuda(), variant=variant,
                                                    torch_dtype=torch.bfloat16, **kw)
-    for cache in (new_cache(model, 1, L), DynamicCache(config=model.config)):  # the library's cache, and an adopted stock cache
-        model.config.compactattn_max_tokens = L
+    model.config.compactattn_max_tokens = 1024
+    for cache in (new_cache(model, 1, 1024), DynamicCache(config=model.config)):  # the library's cache, and an adopted stock cache
         outs = []
         with torch.no_grad():
-            for s in range(0, L, chunk):
-                o = model.model(input_ids=ids[:, s:s + chunk], past_key_values=cache, use_cache=True)
+            bounds = list(range(0, L, chunk)) + [L] + [L + i + 1 for i in range(decode)]
+            for s, e in zip(bounds[:-1], bounds[1:]):
+                o = model.model(input_ids=ids[:, s:e], past_key_values=cache, use_cache=True)
                 outs.append(o.last_hidden_state.float())
-                assert cache.get_seq_length() == s + chunk
+                assert cache.get_seq_length() == e
         got = torch.cat(outs, dim=1)
         err = (got - want).abs()
         scale = want.abs().mean().item()
+        per_call = [round(err[:, s:e].mean().item(), 4) for s, e in zip(bounds[:-1], bounds[1:])]
         assert err.mean().item() < 0.02 * scale and err.max().item() < 0.25 * want.abs().max().item(), \
-            (err.mean().item(), err.max().item(), scale)
+            (type(cache).__name__, per_call, err.max().item(), scale)
