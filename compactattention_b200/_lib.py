@@ -218,6 +218,20 @@ class RopeAppendParams(C.Structure):
     ]
 
 
+class ChunkStepParams(C.Structure):
+    _fields_ = [
+        ("append", RopeAppendParams),
+        ("prepare", GatePrepareParams),
+        ("score", GateScoreParams),
+        ("fp_score", FlashPrefillScoreParams),
+        ("select", SelectParams),
+        ("table", UnionParams),
+        ("union_scratch", C.c_void_p),
+        ("union_scratch_bytes", C.c_size_t),
+        ("attn", AttnParams),
+    ]
+
+
 CA_RULE_THRESHOLD, CA_RULE_ALPHA_ROWMAX, CA_RULE_TOPK, CA_RULE_CUMMASS, CA_RULE_MASK = 0, 1, 2, 3, 4
 CA_POOL_MAX, CA_POOL_MIN, CA_POOL_AVG = 1, 2, 4
 
@@ -242,6 +256,7 @@ _SIGNATURES = {
     "ca_flashprefill_score": (C.c_int, [C.POINTER(FlashPrefillScoreParams), C.c_void_p]),
     "ca_gather_kv": (C.c_int, [C.POINTER(GatherParams), C.c_void_p]),
     "ca_rope_append": (C.c_int, [C.POINTER(RopeAppendParams), C.c_void_p]),
+    "ca_chunk_step": (C.c_int, [C.POINTER(ChunkStepParams), C.c_void_p]),
 }
 
 _lib = None

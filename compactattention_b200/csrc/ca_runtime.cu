@@ -65,6 +65,26 @@ const char* ca_last_error(void) { return ca::last_error_buffer(); }
 
 int ca_abi_version(void) { return 2; }
 
+int ca_chunk_step(const ca_chunk_step_params* p, ca_stream_t stream) {
+  using namespace ca;
+  CA_REQUIRE(p != nullptr, "params is null");
+  int rc = CA_OK;
+  if (p->append.k != nullptr && (rc = ca_rope_append(&p->append, stream)) != CA_OK) return rc;
+  if (p->prepare.q.x != nullptr && (rc = ca_gate_prepare(&p->prepare, stream)) != CA_OK) return rc;
+  if (p->score.q != nullptr && (rc = ca_gate_scores(&p->score, stream)) != CA_OK) return rc;
+  if (p->fp_score.q != nullptr && (rc = ca_flashprefill_score(&p->fp_score, stream)) != CA_OK) return rc;
+  if (p->select.score != nullptr) {
+    if (p->union_scratch != nullptr) {
+      if ((rc = ca_select_union_table(&p->select, &p->table, p->union_scratch, p->union_scratch_bytes, stream)) != CA_OK) return rc;
+    } else {
+      if ((rc = ca_select_rows(&p->select, stream)) != CA_OK) return rc;
+      if ((rc = ca_union_table(&p->table, stream)) != CA_OK) return rc;
+    }
+  }
+  if (p->attn.q != nullptr && (rc = ca_attn_compact(&p->attn, stream)) != CA_OK) return rc;
+  return CA_OK;
+}
+
 int ca_set_programmatic_launch(int enabled) {
   return ca::programmatic_launch_flag().exchange(enabled != 0 ? 1 : 0, std::memory_order_relaxed);
 }

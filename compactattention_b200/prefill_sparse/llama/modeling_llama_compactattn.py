@@ -21,6 +21,7 @@ parallelism a module holds the projections of its rank's heads (``tp.HeadShard``
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Dict, Optional, Tuple
 
@@ -28,13 +29,20 @@ import torch
 import torch.nn as nn
 
 from ... import ops, tp
-from ...chunk_driver import GateSelectorState, MeanKSelectorState
+from ...chunk_driver import GateLayerStep, GateSelectorState, MeanKSelectorState, SelectionRule, StepScratch
 from ...modules import (
     chunked_prefill_column_dense_attention_forward,
     flashprefill_compactattn_prefill_full_kv,
 )
 from ...paged_cache import PagedKVCache
 from ..attn_gate import ATTNGATE_CLASSES
+
+
+# the reference's debug switches that the operator route honours or refuses; with one of them set the module
+# goes through the operator instead of the one-call step
+_DEBUG_ENV = ("SEERATTN_DEBUG_COMPACTATTN_THRESHOLD_OVERRIDE", "SEERATTN_DEBUG_COMPACTATTN_KEEP_RECENT_OVERRIDE",
+              "SEERATTN_DEBUG_COMPACTATTN_QUERY_BLOCK_MODE", "SEERATTN_DEBUG_COMPACTATTN_KV_HEAD_MODE",
+              "SEERATTN_DEBUG_COMPACTATTN_DISABLE_CURRENT_OPEN")
 
 
 @dataclass
@@ -86,6 +94,7 @@ class _LayerState:
     kv: PagedKVCache
     gate: Optional[GateSelectorState] = None
     mean_k: Optional[MeanKSelectorState] = None
+    plan: Optional[GateLayerStep] = None
 
 
 class CompactAttnCache:
@@ -112,6 +121,16 @@ class CompactAttnCache:
         """``(kv_length, kv_offset)`` the way a HuggingFace cache reports them to the stock model's mask
         builder: the tokens held plus the chunk about to be appended, no offset."""
         return self.get_seq_length(layer_idx) + int(query_length), 0
+
+    def step_scratch(self, heads: int, num_kv_heads: int, q_blocks: int, block_size: int, channels: int) -> StepScratch:
+        """Scratch of the one-call layer step, shared by the layers, sized for the longest context; rebuilt
+        when a larger chunk arrives."""
+        sc = getattr(self, "_step_scratch", None)
+        max_blocks = -(-self.max_tokens // block_size)
+        if sc is None or sc.key[:3] != (self.batch, heads, num_kv_heads) or sc.key[3] < q_blocks or sc.key[4:] != (max_blocks, channels):
+            sc = StepScratch(self.batch, heads, num_kv_heads, q_blocks, max_blocks, channels, self.device)
+            self._step_scratch = sc
+        return sc
 
     def selection_scratch(self, heads: int, num_kv_heads: int, q_blocks: int, block_size: int):
         """Keep bits and block table shared by every layer (the layers run one after the other on
@@ -246,6 +265,65 @@ class LlamaSeerAttentionChunkedDense(_CompactAttnBase):
         return chunked_prefill_column_dense_attention_forward(
             query_states=query_states, key_states=key_states, value_states=value_states, **kwargs)
 
+    def _synthetic_scores(self, hidden_states, max_blocks: int, Qb: int, Kb: int) -> torch.Tensor:
+        """A fixed random importance per (KV head, key block), seen alike by every Q-block row: per-row top-k
+        of it imposes an exact union density on random-init stacks."""
+        if self._synthetic_importance is None or self._synthetic_importance.shape[-1] < Kb:
+            g = torch.Generator(device=hidden_states.device).manual_seed(1234 + self.layer_idx)
+            self._synthetic_importance = torch.rand((1, self.num_key_value_heads, 1, max(max_blocks, Kb)), generator=g,
+                                                    device=hidden_states.device)
+        return self._synthetic_importance[..., :Kb].expand(hidden_states.shape[0], self.num_key_value_heads, Qb, Kb)
+
+    # -- the default route: the whole layer step as one library call ---------------------------------
+    def _one_call_step_applies(self, q_len, past_len, block_attention_mask, cache_position) -> bool:
+        """The one-call step serves the plain case: a chunk (not decode) on a block-aligned past, the
+        threshold or top-k method, no caller-made block mask, no statistics, and neither documented hook
+        overridden (a subclass that overrides one is served through the hooks)."""
+        cls = type(self)
+        return (q_len > 1 and past_len % self.config.seerattn_gate_block_size == 0 and block_attention_mask is None
+                and not self.compactattn_debug and self.config.seerattn_sparsity_method in ("threshold", "topk", "synthetic_topk")
+                and not any(os.environ.get(k) for k in _DEBUG_ENV)
+                and cls._do_kv_cache_update is _CompactAttnBase._do_kv_cache_update
+                and cls._do_chunked_compactattn_attention is LlamaSeerAttentionChunkedDense._do_chunked_compactattn_attention
+                and (cache_position is None or torch.is_tensor(cache_position) or int(cache_position[0]) == past_len))
+
+    def _forward_one_call(self, hidden_states, q_nope, k_nope, v, cos, sin, st, past_key_value, block_position_embeddings,
+                          past_len, input_shape):
+        cfg, bs = self.config, self.config.seerattn_gate_block_size
+        q_len = hidden_states.shape[1]
+        if st.gate is None:
+            st.gate = GateSelectorState(self.attn_gate, hidden_states.shape[0], hidden_states.device, cache_dtype=hidden_states.dtype)
+        if st.plan is None:
+            if cfg.seerattn_sparsity_method in ("topk", "synthetic_topk"):
+                rule = SelectionRule(rule="topk", softmax=False, topk_ratio=tuple(cfg.seerattn_topk_ratio), sink=1,
+                                     local=self.compactattn_keep_recent_blocks)
+            else:  # threshold on soft-maxed gate scores, the last keep_recent columns forced on
+                rule = SelectionRule(rule="threshold", softmax=True, threshold=float(cfg.seerattn_threshold),
+                                     keep_recent=max(int(self.compactattn_keep_recent_blocks), 0))
+            scratch = past_key_value.step_scratch(self.num_heads, self.num_key_value_heads, -(-q_len // bs), bs,
+                                                  cfg.seerattn_gate_hidden_size)
+            st.plan = GateLayerStep(self.attn_gate, st.gate, st.kv, rule, scratch, self.num_key_value_heads, self.scaling)
+        elif st.plan.scratch.q_blocks.shape[1] < -(-q_len // bs):
+            st.plan.scratch = past_key_value.step_scratch(self.num_heads, self.num_key_value_heads, -(-q_len // bs), bs,
+                                                          cfg.seerattn_gate_hidden_size)
+            st.plan._static_done = False
+        rope_blocks = None
+        if block_position_embeddings is not None:
+            bcos, bsin = block_position_embeddings
+            nb = -(-q_len // bs)
+            rope_blocks = (bcos[..., -nb:, :], bsin[..., -nb:, :])
+        first_chunk = past_len == 0
+        dense = bool(cfg.seerattn_chunked_prefill_force_dense) or (first_chunk and not self.compactattn_disable_first_chunk_dense)
+        attn = torch.empty_like(q_nope)
+        score = None
+        if cfg.seerattn_sparsity_method == "synthetic_topk" and not dense:
+            Qb, Kb = -(-q_len // bs), -(-(past_len + q_len) // bs)
+            score = self._synthetic_scores(hidden_states, past_key_value.max_tokens // bs, Qb, Kb)
+        st.plan.run(q_nope, k_nope, v, cos, sin, rope_blocks, past_len, attn, dense=dense, score=score)
+        out = self._finish(attn, input_shape)
+        self._compactattn_last_stats = None
+        return out, 0.0, None, None, None
+
     def forward(
         self,
         hidden_states: torch.Tensor,
@@ -271,6 +349,9 @@ class LlamaSeerAttentionChunkedDense(_CompactAttnBase):
         cos, sin = position_embeddings
         st = past_key_value.layer(self.layer_idx, self.num_key_value_heads, self.head_dim)
         past_len = st.kv.length
+        if self._one_call_step_applies(q_len, past_len, block_attention_mask, cache_position):
+            return self._forward_one_call(hidden_states, q_nope, k_nope, v, cos, sin, st, past_key_value, block_position_embeddings,
+                                          past_len, input_shape)
         q, kv_view, kv_len = self._do_rope_and_kv_cache_update(q_nope, k_nope, v, past_key_value, cos, sin, cache_position)
         if q_len == 1 or past_len % bs != 0:
             # decode, or a call after a chunk that ended inside a block: dense, the gate is not consulted
@@ -297,11 +378,7 @@ class LlamaSeerAttentionChunkedDense(_CompactAttnBase):
             path = "first_chunk_dense" if first_chunk else "forced_dense"
         elif self.config.seerattn_sparsity_method == "synthetic_topk":
             Qb, Kb = logits.shape[2], logits.shape[3]
-            if self._synthetic_importance is None or self._synthetic_importance.shape[-1] < Kb:
-                g = torch.Generator(device=hidden_states.device).manual_seed(1234 + self.layer_idx)
-                self._synthetic_importance = torch.rand((1, self.num_key_value_heads, 1, past_key_value.max_tokens // bs),
-                                                        generator=g, device=hidden_states.device)
-            score = self._synthetic_importance[..., :Kb].expand(hidden_states.shape[0], self.num_key_value_heads, Qb, Kb)
+            score = self._synthetic_scores(hidden_states, past_key_value.max_tokens // bs, Qb, Kb)
             _, table = past_key_value.selection_scratch(self.num_key_value_heads, self.num_key_value_heads, Qb, bs)
             table = ops.select_union_table(score, Kb - Qb, "topk", num_kv_heads=self.num_key_value_heads, block_size=bs,
                                            topk_ratio=tuple(self.config.seerattn_topk_ratio), sink=1,

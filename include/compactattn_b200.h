@@ -469,6 +469,40 @@ typedef struct ca_rope_append_params {
 
 int ca_rope_append(const ca_rope_append_params* p, ca_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * One chunk of one layer in one call
+ * ---------------------------------------------------------------------------------------- */
+/*
+ * Enqueues the whole per-layer step of the path with one host call, in this order, each stage exactly
+ * as its own entry point would (a stage whose first pointer is NULL is skipped):
+ *   append   ca_rope_append          RoPE on q/k, K/V into the paged cache (+ mean-K)      [append.k]
+ *   prepare  ca_gate_prepare         pool + project + RoPE the chunk's Q and K blocks      [prepare.q.x]
+ *   score    ca_gate_scores          gate logits against every cached K block              [score.q]
+ *   fp_score ca_flashprefill_score   training-free block scores                            [fp_score.q]
+ *   select + table  ca_select_union_table (one launch) when union_scratch is given, else
+ *            ca_select_rows then ca_union_table                                            [select.score]
+ *   attn     ca_attn_compact                                                               [attn.q]
+ * It stands where the reference runs its per-layer Python between the KV-cache update and o_proj:
+ * _compute_chunked_gate_from_cache, the keep-mask / index builders and the indexed attention call
+ * (compact_attn/prefill_sparse/llama/modeling_llama_seerattn_chunked_dense.py:547-938,
+ * compact_attn/modules/attention_forward_chunked_dense.py:2732-2912), dozens of host-side launches per
+ * layer there.  A caller that keeps the struct between chunks only updates the fields that change
+ * (lengths, block offsets, the chunk's tensors).  Returns the first failing stage's code.
+ */
+typedef struct ca_chunk_step_params {
+  ca_rope_append_params append;
+  ca_gate_prepare_params prepare;
+  ca_gate_score_params score;
+  ca_flashprefill_score_params fp_score;
+  ca_select_params select;
+  ca_union_params table;
+  void* union_scratch;
+  size_t union_scratch_bytes;
+  ca_attn_params attn;
+} ca_chunk_step_params;
+
+int ca_chunk_step(const ca_chunk_step_params* p, ca_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -252,3 +252,46 @@ def test_seer_module_selects_and_reports(gpu):
     want = want_attn.reshape(B, chunk, -1) @ attn.o_proj.weight.float().cpu().T
     err = (outs[-1].float().cpu() - want).abs()
     assert err.max().item() < 5e-2 and err.mean().item() < 5e-3, (err.max().item(), err.mean().item())
+
+
+@pytest.mark.parametrize("method,kw", [("threshold", dict(seerattn_threshold=2e-3)), ("topk", dict(seerattn_topk_ratio=(1, 4))),
+                                        ("synthetic_topk", dict(seerattn_topk_ratio=(1, 3)))])
+def test_one_call_layer_step_equals_the_operator_route(gpu, method, kw):
+    """The module's default route enqueues the whole layer step with one library call (``ca_chunk_step``:
+    RoPE + append, gate preparation, logits, rule + table, attention); with statistics switched on the same
+    module goes stage by stage through the operator functions.  Same kernels, same order: identical bits,
+    over four chunks the last of which is not a block multiple."""
+    from compactattention_b200 import _lib
+    from compactattention_b200.prefill_sparse.llama import CompactAttnCache, LlamaSeerAttentionChunkedDense
+    B, L, chunk, bs = 1, 1000, 256, 64
+    outs = {}
+    for debug in (False, True):
+        cfg = _tiny_config(seerattn_sparsity_method=method, compactattn_debug=debug, num_hidden_layers=1, **kw)
+        torch.manual_seed(0)
+        attn = LlamaSeerAttentionChunkedDense(cfg, 0).to(gpu).to(torch.bfloat16)
+        for p in attn.parameters():
+            torch.nn.init.normal_(p, std=0.05)
+        x = torch.randn((B, L, cfg.hidden_size), device=gpu, generator=torch.Generator(device=gpu).manual_seed(1)).to(torch.bfloat16)
+        cache = CompactAttnCache(B, 1024, gpu, torch.bfloat16)
+        inv = 1.0 / (10000.0 ** (torch.arange(0, 128, 2, dtype=torch.float32, device=gpu) / 128))
+        got, calls = [], []
+        for s in range(0, L, chunk):
+            e = min(s + chunk, L)
+            pos = torch.arange(s, e, device=gpu)
+            ang = torch.cat([pos.float()[:, None] * inv[None]] * 2, -1)
+            bang = torch.cat([pos[::bs].float()[:, None] * inv[None]] * 2, -1)
+            n0 = _lib.launch_count()
+            got.append(attn(x[:, s:e], (ang.cos()[None].to(torch.bfloat16), ang.sin()[None].to(torch.bfloat16)), None,
+                            past_key_value=cache, block_position_embeddings=(bang.cos()[None], bang.sin()[None]))[0])
+            calls.append(_lib.launch_count() - n0)
+        outs[debug] = torch.cat(got, 1)
+        if not debug:
+            assert cache.layers[0].plan is not None  # the one-call route ran
+            # first chunk (dense): append, gate preparation, attention (+ its merge launch); later chunks add the
+            # logits (not for synthetic scores) and the fused rule + table launch
+            assert calls[0] in (3, 4) and all(c in (4, 5, 6) for c in calls[1:]), calls
+            assert int(cache.layers[0].plan.scratch.status.item()) == 0
+        else:
+            assert cache.layers[0].plan is None
+    assert not torch.isnan(outs[False].float()).any()
+    assert torch.equal(outs[False], outs[True])

@@ -65,10 +65,10 @@ def test_struct_sizes_match_c_layout():
         #include <stdio.h>
         #include "compactattn_b200.h"
         int main(void) {
-          printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(ca_gate_prepare_params), sizeof(ca_kv_layout), sizeof(ca_attn_params),
+          printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(ca_gate_prepare_params), sizeof(ca_kv_layout), sizeof(ca_attn_params),
                  sizeof(ca_select_params), sizeof(ca_union_params), sizeof(ca_pool_params),
                  sizeof(ca_project_params), sizeof(ca_gate_score_params), sizeof(ca_flashprefill_score_params),
-                 sizeof(ca_gather_params), sizeof(ca_rope_append_params));
+                 sizeof(ca_gather_params), sizeof(ca_rope_append_params), sizeof(ca_chunk_step_params));
           return 0;
         }""")
     with tempfile.TemporaryDirectory() as d:
@@ -79,7 +79,7 @@ def test_struct_sizes_match_c_layout():
         sizes = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
     mirrors = [_lib.GatePrepareParams, _lib.KvLayout, _lib.AttnParams, _lib.SelectParams, _lib.UnionParams, _lib.PoolParams,
                _lib.ProjectParams, _lib.GateScoreParams, _lib.FlashPrefillScoreParams, _lib.GatherParams,
-               _lib.RopeAppendParams]
+               _lib.RopeAppendParams, _lib.ChunkStepParams]
     assert sizes == [ctypes.sizeof(m) for m in mirrors]
 
 
