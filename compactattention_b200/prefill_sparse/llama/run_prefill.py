@@ -57,23 +57,40 @@ def main():
     ids = torch.randint(0, cfg.vocab_size, (1, args.prompt), generator=g).to(dev)
     # CUDA events around every attention module call
     events = []
+    host_s = [0.0]
+    import time
     for layer in model.layers:
         orig = layer.self_attn.forward
 
         def timed(*a, _orig=orig, **kw):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
+            w0 = time.perf_counter()
             out = _orig(*a, **kw)
+            host_s[0] += time.perf_counter() - w0   # host time to enqueue the module's work (nothing waits inside)
             e1.record()
             events.append((e0, e1))
             return out
 
         layer.self_attn.forward = timed
+    # warm-up outside the timed region: two chunks on a throw-away cache bring up the NCCL communicator
+    # (its first collective takes seconds), cuBLAS workspaces and the library's scratch buffers
+    warm = model.new_cache(1, 2 * args.chunk)
+    model.prefill(ids[:, : 2 * args.chunk], args.chunk, warm)
+    del warm
+    events.clear()
+    host_s[0] = 0.0
     cache = model.new_cache(1, args.prompt)
+    for i in range(args.layers):   # the paged caches are allocated (and zero-filled) before the clock starts
+        cache.layer(i, len(shard.kv_heads), cfg.head_dim)
     torch.cuda.synchronize()
+    if world > 1:
+        torch.distributed.barrier()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
+    w_all = time.perf_counter()
     hidden, cache = model.prefill(ids, args.chunk, cache)
+    host_total_s = time.perf_counter() - w_all      # host time to enqueue the whole prefill
     t1.record()
     torch.cuda.synchronize()
     total_ms = t0.elapsed_time(t1)
@@ -91,6 +108,9 @@ def main():
             "attn_per_chunk_ms": round(vals[1] / n_chunks, 3),
             "attn_last_chunk_ms": round(vals[2], 3),
             "attn_last_chunk_per_layer_us": round(vals[2] / args.layers * 1e3, 1),
+            "host_enqueue_ms": round(host_total_s * 1e3, 1),
+            "host_attn_module_us_per_layer_call": round(host_s[0] / max(len(events), 1) * 1e6, 1),
+            "host_us_per_layer_call": round(host_total_s / max(len(events), 1) * 1e6, 1),
             "finite": bool(torch.isfinite(hidden.float()).all()),
         }))
     if world > 1:
