@@ -218,6 +218,24 @@ class RopeAppendParams(C.Structure):
     ]
 
 
+class OprojParams(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("a_stride_m", C.c_int64),
+        ("w", C.c_void_p), ("w_stride_n", C.c_int64),
+        ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
+        ("dtype", C.c_int32),
+        ("world", C.c_int32), ("rank", C.c_int32),
+        ("stage", C.POINTER(C.c_void_p)),
+        ("tile_counters", C.POINTER(C.c_void_p)),
+        ("done_counters", C.POINTER(C.c_void_p)),
+        ("out", C.POINTER(C.c_void_p)),
+        ("out_stride_m", C.c_int64),
+        ("epoch", C.c_uint32), ("phases", C.c_uint32),
+        ("wait_limit_ns", C.c_uint64),
+        ("status", C.c_void_p),
+    ]
+
+
 class ChunkStepParams(C.Structure):
     _fields_ = [
         ("append", RopeAppendParams),
@@ -257,6 +275,8 @@ _SIGNATURES = {
     "ca_gather_kv": (C.c_int, [C.POINTER(GatherParams), C.c_void_p]),
     "ca_rope_append": (C.c_int, [C.POINTER(RopeAppendParams), C.c_void_p]),
     "ca_chunk_step": (C.c_int, [C.POINTER(ChunkStepParams), C.c_void_p]),
+    "ca_oproj_scratch_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
+    "ca_oproj_allreduce": (C.c_int, [C.POINTER(OprojParams), C.c_void_p]),
 }
 
 _lib = None

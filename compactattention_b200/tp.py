@@ -78,6 +78,91 @@ def reduce_layer_output(partial: torch.Tensor, group=None, async_op: bool = Fals
     return dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
 
 
+class FusedOutputProjection:
+    """Row-parallel output projection whose tensor-parallel sum travels inside the library's kernels
+    (``ca_oproj_allreduce``: a tcgen05 GEMM that stores partial tiles into the owning rank's memory, a
+    reduction that stores finished tiles into every rank's output, a bounded wait) instead of a library GEMM
+    followed by an NCCL all-reduce.  Buffers live in symmetric memory (``torch.distributed._symmetric_memory``),
+    allocated and exchanged once; every call reuses them, so a call's output is valid until the next call.
+
+    All ranks must construct it with the same sizes and call it in the same order.  ``check()`` reads the
+    status word (a device-to-host read) and raises if a wait ran out - e.g. a rank that died."""
+
+    def __init__(self, max_rows: int, out_features: int, device, dtype=torch.bfloat16, group=None, wait_limit_s: float = 2.0):
+        import ctypes as C
+
+        from . import _lib
+        self._lib, self._C = _lib, C
+        self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)
+        self.world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
+        self.max_rows, self.N, self.dtype, self.device = int(max_rows), int(out_features), dtype, torch.device(device)
+        self.epoch = 0
+        self.wait_limit_ns = int(wait_limit_s * 1e9)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        stage_b, cnt_b = C.c_size_t(0), C.c_size_t(0)
+        _lib.check(_lib.load().ca_oproj_scratch_bytes(self.max_rows, self.N, self.world, C.byref(stage_b), C.byref(cnt_b)),
+                   "ca_oproj_scratch_bytes")
+        esize = torch.empty((), dtype=dtype).element_size()
+        if self.world == 1:
+            self.out = torch.empty((self.max_rows, self.N), dtype=dtype, device=device)
+            self._ptrs = {"out": [self.out.data_ptr()], "stage": None, "tiles": None, "done": None}
+            return
+        import torch.distributed._symmetric_memory as symm
+        name = self.group.group_name
+        self.out = symm.empty((self.max_rows, self.N), dtype=dtype, device=self.device)
+        self.stage = symm.empty(max(int(stage_b.value) // esize, 8), dtype=dtype, device=self.device)
+        self.counters = symm.empty(int(cnt_b.value) // 4, dtype=torch.int32, device=self.device)
+        self.counters.zero_()
+        handles = [symm.rendezvous(t, name) for t in (self.out, self.stage, self.counters)]
+        n_tile_counters = int(cnt_b.value) // 4 - 1
+        self._ptrs = {
+            "out": list(handles[0].buffer_ptrs), "stage": list(handles[1].buffer_ptrs),
+            "tiles": list(handles[2].buffer_ptrs), "done": [p + 4 * n_tile_counters for p in handles[2].buffer_ptrs],
+        }
+        self._handles = handles
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)   # every rank's counters are zero before anyone's first call
+
+    def _array(self, ptrs):
+        C = self._C
+        return None if ptrs is None else (C.c_void_p * len(ptrs))(*ptrs)
+
+    def __call__(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        """``x [..., K]`` (this rank's attention output, K contiguous) times ``weight [N, K]`` (this rank's input
+        columns of the projection), summed over the ranks.  Returns a view ``[..., N]`` of the shared output
+        buffer."""
+        from . import ops
+        C = self._C
+        lead = x.shape[:-1]
+        K = x.shape[-1]
+        a = x.reshape(-1, K)
+        M = a.shape[0]
+        if M > self.max_rows:
+            raise ValueError(f"{M} rows exceed the buffers of this projection ({self.max_rows})")
+        if a.stride(1) != 1 or weight.stride(1) != 1 or weight.shape != (self.N, K) or a.dtype != self.dtype or weight.dtype != self.dtype:
+            raise ValueError("x must be [..., K] and weight [N, K], both K-contiguous and of the projection's dtype")
+        self.epoch += 1
+        p = self._lib.OprojParams()
+        p.a, p.a_stride_m, p.w, p.w_stride_n = a.data_ptr(), a.stride(0), weight.data_ptr(), weight.stride(0)
+        p.M, p.N, p.K, p.dtype = M, self.N, K, ops._DTYPES[self.dtype]
+        p.world, p.rank = self.world, self.rank
+        arrays = {k: self._array(v) for k, v in self._ptrs.items()}
+        p.out = C.cast(arrays["out"], C.POINTER(C.c_void_p))
+        if self.world > 1:
+            p.stage = C.cast(arrays["stage"], C.POINTER(C.c_void_p))
+            p.tile_counters = C.cast(arrays["tiles"], C.POINTER(C.c_void_p))
+            p.done_counters = C.cast(arrays["done"], C.POINTER(C.c_void_p))
+        p.out_stride_m, p.epoch, p.wait_limit_ns, p.status = self.N, self.epoch, self.wait_limit_ns, self.status.data_ptr()
+        self._lib.check(self._lib.load().ca_oproj_allreduce(C.byref(p), ops._stream()), "ca_oproj_allreduce")
+        return self.out[:M].view(*lead, self.N)
+
+    def check(self) -> None:
+        """Raises if a device-side wait of an earlier call ran out (reads the status word: synchronises)."""
+        if int(self.status.item()) & self._lib.CA_STATUS_TIMEOUT:
+            raise RuntimeError("the fused output projection timed out waiting for another rank's tiles; its output is invalid")
+
+
 def max_over_ranks(values, device, group=None):
     """Element-wise max of a list of floats over the ranks (multi-GPU timings are max over ranks)."""
     t = torch.tensor(list(values), dtype=torch.float64, device=device)

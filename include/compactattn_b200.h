@@ -470,6 +470,52 @@ typedef struct ca_rope_append_params {
 int ca_rope_append(const ca_rope_append_params* p, ca_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Output projection fused with the tensor-parallel reduction
+ * ---------------------------------------------------------------------------------------- */
+/*
+ * out (on every rank) = sum over ranks r of  a_r [M, K_r] . w_r[N, K_r]^T,  16-bit in and out, fp32 accumulate.
+ * Rank `rank` of `world` passes its own a and w and, for EVERY rank, the peer-mapped device addresses of that
+ * rank's staging buffer, per-tile arrival counters, finished-tile counter and output buffer (symmetric
+ * allocations of the same sizes on all ranks, see ca_oproj_scratch_bytes; counters zero before the first
+ * call).  Three launches: a tcgen05 GEMM whose epilogue stores each 128 x 256 partial tile into the staging
+ * buffer of the rank that owns the tile (tile t -> rank t % world) with plain peer stores and bumps the
+ * owner's arrival counter; a reduction in which every rank sums the partials of its own tiles and stores the
+ * result into every rank's output; a one-thread wait until this rank's output is complete.  Every wait is
+ * bounded by wait_limit_ns (0 = 2 s); on expiry *status gets CA_STATUS_TIMEOUT and the output is invalid.
+ * `epoch` is the number of this call on these buffers (1, 2, ...), the same on every rank: counters only
+ * grow, nothing is reset.  All ranks must issue the same sequence of calls with the same M, N.  world == 1 is
+ * a plain GEMM into out[0].
+ * Replaces the row-parallel o_proj of the reference's tensor-parallel plan followed by its all-reduce
+ * (compact_attn/prefill_sparse/llama/modeling_llama_seerattn.py:111-120; the deferred wait of
+ * modeling_llama_flashprefill_compactattn.py:37-41, 321-322).
+ */
+typedef struct ca_oproj_params {
+  const void* a;      /* [M, K] this rank's attention output, K contiguous */
+  int64_t a_stride_m;
+  const void* w;      /* [N, K] this rank's input columns of the projection weight, K contiguous */
+  int64_t w_stride_n;
+  int32_t M, N, K;    /* N a multiple of 256, K a multiple of 64 */
+  int32_t dtype;      /* CA_DTYPE_BF16 or CA_DTYPE_F16 */
+  int32_t world, rank;
+  void* const* stage;              /* [world] staging buffers (NULL when world == 1) */
+  uint32_t* const* tile_counters;  /* [world] per-owned-tile arrival counters */
+  uint32_t* const* done_counters;  /* [world] finished-tile counters (one uint32 each) */
+  void* const* out;                /* [world] output buffers [M, N] */
+  int64_t out_stride_m;
+  uint32_t epoch;
+  uint32_t phases; /* 0 = all three launches; else a mask: 1 GEMM + push, 2 reduction + broadcast, 4 final wait
+                      (several ranks emulated on one device enqueue phase by phase, so that no kernel waits for
+                      one that has not been launched) */
+  uint64_t wait_limit_ns;
+  int32_t* status; /* optional */
+} ca_oproj_params;
+
+/* Bytes of the symmetric staging buffer and of the counter block (per-owned-tile counters followed by the
+ * finished-tile counter) for outputs of up to M_max rows. */
+int ca_oproj_scratch_bytes(int M_max, int N, int world, size_t* stage_bytes, size_t* counter_bytes);
+int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
  * One chunk of one layer in one call
  * ---------------------------------------------------------------------------------------- */
 /*
