@@ -185,39 +185,53 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (ok) ptx::tc_commit(ptx::smem_u32(&sh->acc_full));
     }
   } else {
-    // epilogue: thread = tile row (TMEM lane); 32 columns at a time -> 64 bytes of the 16-bit partial tile
+    // epilogue: thread = tile row (TMEM lane).  The 16-bit tile is first laid down in shared memory (the ring is
+    // idle by now: every load has landed and every MMA has read its operands), 16-byte pieces XOR-swizzled by the
+    // row so that neither side has bank conflicts; then each warp writes its 32 rows out 512 contiguous bytes at
+    // a time.  A thread-per-row store straight from registers sends 16-byte pieces 512 bytes apart, which over
+    // NVLink cost ~4x the time of the whole GEMM.
     const int quad = warp & 3;
-    const int r = quad * 32 + lane;
     ok = ptx::mbar_wait_bounded(ptx::smem_u32(&sh->acc_full), 0, abort_flag, limit);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       ptx::tc_fence_after();
       const int owner = a.world > 1 ? tile % a.world : 0;
       const int local_tile = a.world > 1 ? tile / a.world : 0;
-      T* dst;
+      T* dst;            // first element of this warp's first row
+      long long ld;      // elements between rows
       if (a.world > 1) {
         dst = reinterpret_cast<T*>(a.stage[owner]) +
-              (static_cast<long long>(a.rank) * a.tiles_per_owner + local_tile) * kTileElems + static_cast<long long>(r) * kBN;
+              (static_cast<long long>(a.rank) * a.tiles_per_owner + local_tile) * kTileElems + static_cast<long long>(quad * 32) * kBN;
+        ld = kBN;
       } else {
-        dst = reinterpret_cast<T*>(a.out_local) + static_cast<long long>(tm * kBM + r) * a.out_stride_m + tn * kBN;
+        dst = reinterpret_cast<T*>(a.out_local) + static_cast<long long>(tm * kBM + quad * 32) * a.out_stride_m + tn * kBN;
+        ld = a.out_stride_m;
       }
-      const bool live = tm * kBM + r < a.M;
+      uint8_t* wtile = smem_aligned + quad * (32 * kBN * 2);   // 32 rows x 512 bytes of this warp
       const uint32_t taddr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
 #pragma unroll 2
       for (int c = 0; c < kBN / 32; ++c) {
         uint32_t v[32];
         ptx::tmem_ld32(taddr + c * 32, v);
         ptx::tc_wait_ld();
-        if (live) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 w;
-            w.x = pack2<T>(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
-            w.y = pack2<T>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-            w.z = pack2<T>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
-            w.w = pack2<T>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
-            *reinterpret_cast<uint4*>(dst + c * 32 + i) = w;
-          }
+        for (int i = 0; i < 32; i += 8) {
+          uint4 w;
+          w.x = pack2<T>(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
+          w.y = pack2<T>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+          w.z = pack2<T>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+          w.w = pack2<T>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+          const int piece = (c * 4 + i / 8) ^ lane;
+          *reinterpret_cast<uint4*>(wtile + lane * (kBN * 2) + piece * 16) = w;
+        }
+      }
+      __syncwarp();
+      const int rows_live = min(32, a.M - (tm * kBM + quad * 32));   // may be <= 0
+#pragma unroll 4
+      for (int rr = 0; rr < 32; ++rr) {
+        if (rr < rows_live) {
+          const uint4 w = *reinterpret_cast<const uint4*>(wtile + rr * (kBN * 2) + ((lane ^ rr) * 16));
+          *reinterpret_cast<uint4*>(dst + rr * ld + lane * 8) = w;
         }
       }
       if (a.world > 1) {
@@ -256,13 +270,18 @@ struct ReduceArgs {
   int32_t* status;
 };
 
-// One CTA per tile this rank owns: sum of the `world` staged partials -> every rank's output.
+constexpr int kReduceSplit = 4;  // CTAs per owned tile (32 rows each): 4x the CTAs of one per tile fill the GPU
+
+// kReduceSplit CTAs per tile this rank owns: sum of the `world` staged partials -> every rank's output.
 template <typename T>
 __global__ void __launch_bounds__(256) oproj_reduce_kernel(const ReduceArgs a) {
+  // Launched programmatically behind the GEMM and deliberately without a grid-dependency wait: everything this
+  // kernel reads is guarded by a tile counter (release by the producer, acquire here), so its CTAs may take
+  // their seats while the GEMM's CTAs are still computing and reduce each tile the moment its partials land.
+  // The GEMM itself is a plain launch, so nothing of an earlier call or of the producer of A is overtaken.
   ptx::grid_launch_dependents();
-  ptx::grid_dependency_wait();
   __shared__ int sh_ok;
-  const int lt = blockIdx.x;
+  const int lt = blockIdx.x / kReduceSplit, part = blockIdx.x % kReduceSplit;
   const int tile = lt * a.world + a.rank;
   if (tile >= a.n_tiles) return;
   if (threadIdx.x == 0) {
@@ -276,7 +295,8 @@ __global__ void __launch_bounds__(256) oproj_reduce_kernel(const ReduceArgs a) {
     const T* base = reinterpret_cast<const T*>(a.stage_local) + static_cast<long long>(lt) * kTileElems;
     const long long src_stride = static_cast<long long>(a.tiles_per_owner) * kTileElems;
     // 8 elements (16 bytes) per thread and step; a row of the tile is 32 such groups
-    for (int e = threadIdx.x; e < kTileElems / 8; e += 256) {
+    constexpr int kPartGroups = kTileElems / 8 / kReduceSplit;
+    for (int e = part * kPartGroups + threadIdx.x; e < (part + 1) * kPartGroups; e += 256) {
       const int r = e / (kBN / 8), c8 = e % (kBN / 8);
       if (tm * kBM + r >= a.M) break;  // rows are visited in order: the rest lies beyond M too
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -300,12 +320,12 @@ __global__ void __launch_bounds__(256) oproj_reduce_kernel(const ReduceArgs a) {
   __syncthreads();
   // the finished tile is in every rank's output: every rank's count of delivered tiles moves on.  (After a
   // timeout nothing is counted: the other ranks' final waits then run out too and report it.)
-  if (threadIdx.x < a.world && ok) red_add_release_sys(a.done_counters[threadIdx.x], 1u);
+  if (threadIdx.x < a.world && ok) red_add_release_sys(a.done_counters[threadIdx.x], 1u);  // kReduceSplit per tile
 }
 
 __global__ void oproj_wait_kernel(const uint32_t* done_local, uint32_t target, unsigned long long limit_ns, int32_t* status) {
-  ptx::grid_launch_dependents();
-  ptx::grid_dependency_wait();
+  // no grid-dependency wait either: the counter is the dependency.  Whatever follows on the stream is a plain
+  // launch, so it still waits for this kernel and the two before it.
   if (threadIdx.x == 0 && !wait_counter(done_local, target, limit_ns) && status) atomicOr(status, CA_STATUS_TIMEOUT);
 }
 
@@ -427,15 +447,16 @@ int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream_) {
   r.status = p->status;
   if (phases & 2u) {
     if (p->dtype == CA_DTYPE_BF16) {
-      launch_kernel(oproj_reduce_kernel<__nv_bfloat16>, dim3(g.tiles_per_owner), dim3(256), 0, stream, r);
+      launch_kernel_as(true, oproj_reduce_kernel<__nv_bfloat16>, dim3(g.tiles_per_owner * kReduceSplit), dim3(256), 0, stream, r);
     } else {
-      launch_kernel(oproj_reduce_kernel<__half>, dim3(g.tiles_per_owner), dim3(256), 0, stream, r);
+      launch_kernel_as(true, oproj_reduce_kernel<__half>, dim3(g.tiles_per_owner * kReduceSplit), dim3(256), 0, stream, r);
     }
     CA_LAUNCH_CHECK("oproj_reduce_kernel");
   }
   if (phases & 4u) {
-    launch_kernel(oproj_wait_kernel, dim3(1), dim3(32), 0, stream, static_cast<const uint32_t*>(p->done_counters[p->rank]),
-                  p->epoch * static_cast<uint32_t>(g.n_tiles), static_cast<unsigned long long>(g.wait_limit_ns), p->status);
+    launch_kernel_as(true, oproj_wait_kernel, dim3(1), dim3(32), 0, stream, static_cast<const uint32_t*>(p->done_counters[p->rank]),
+                     p->epoch * static_cast<uint32_t>(g.n_tiles * kReduceSplit), static_cast<unsigned long long>(g.wait_limit_ns),
+                     p->status);
     CA_LAUNCH_CHECK("oproj_wait_kernel");
   }
   return CA_OK;

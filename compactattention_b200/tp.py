@@ -98,6 +98,7 @@ class FusedOutputProjection:
         self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
         self.max_rows, self.N, self.dtype, self.device = int(max_rows), int(out_features), dtype, torch.device(device)
         self.epoch = 0
+        self.phases = 7   # all three launches; a subset only for tests and timing (see ca_oproj_params.phases)
         self.wait_limit_ns = int(wait_limit_s * 1e9)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         stage_b, cnt_b = C.c_size_t(0), C.c_size_t(0)
@@ -154,6 +155,7 @@ class FusedOutputProjection:
             p.tile_counters = C.cast(arrays["tiles"], C.POINTER(C.c_void_p))
             p.done_counters = C.cast(arrays["done"], C.POINTER(C.c_void_p))
         p.out_stride_m, p.epoch, p.wait_limit_ns, p.status = self.N, self.epoch, self.wait_limit_ns, self.status.data_ptr()
+        p.phases = self.phases
         self._lib.check(self._lib.load().ca_oproj_allreduce(C.byref(p), ops._stream()), "ca_oproj_allreduce")
         return self.out[:M].view(*lead, self.N)
 
