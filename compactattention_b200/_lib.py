@@ -233,6 +233,10 @@ class OprojParams(C.Structure):
         ("epoch", C.c_uint32), ("phases", C.c_uint32),
         ("wait_limit_ns", C.c_uint64),
         ("status", C.c_void_p),
+        ("mode", C.c_int32),
+        ("stage_bytes", C.c_size_t),
+        ("row_epochs", C.POINTER(C.c_uint32)),
+        ("done_tiles_total", C.c_uint32),
     ]
 
 
@@ -277,6 +281,7 @@ _SIGNATURES = {
     "ca_chunk_step": (C.c_int, [C.POINTER(ChunkStepParams), C.c_void_p]),
     "ca_oproj_scratch_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "ca_oproj_allreduce": (C.c_int, [C.POINTER(OprojParams), C.c_void_p]),
+    "ca_oproj_tile_count": (C.c_int, [C.c_int, C.c_int]),
 }
 
 _lib = None

@@ -36,12 +36,16 @@ constexpr int kStageBytes = kABytes + kWBytes;
 constexpr int kThreads = 192;            // warp 0 TMA, warp 1 MMA (+ TMEM alloc), warps 2-5 epilogue
 constexpr int kMaxWorld = 8;
 constexpr int kTileElems = kBM * kBN;
+constexpr int kMaxRowTiles = 128;        // rows per call <= 128 * 128
 
 struct GemmArgs {
   int M, N, K;
   int tiles_n, n_tiles;
   int world, rank, tiles_per_owner;
-  void* stage[kMaxWorld];            // every rank's staging buffer: [src][owned tile][128][256] 16-bit
+  int one_shot;                      // 1: every tile goes to every rank (no broadcast afterwards)
+  int slot_tiles;                    // tiles per source rank in a staging buffer (two-shot: tiles_per_owner; one-shot: n_tiles)
+  long long buf_off_elems;           // one-shot: offset of this call's half of the double-buffered staging area
+  void* stage[kMaxWorld];            // every rank's staging buffer: [src][tile slot][128][256] 16-bit
   uint32_t* tile_counters[kMaxWorld];
   void* out_local;                   // world == 1: the output itself
   long long out_stride_m;
@@ -67,6 +71,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
       "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
 }
+
+// Untiled bulk copy shared -> global (both addresses 16-byte aligned, size a multiple of 16 bytes); the
+// destination may be peer-mapped memory.  Completion is tracked by the issuing thread's bulk groups.
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -185,29 +197,21 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (ok) ptx::tc_commit(ptx::smem_u32(&sh->acc_full));
     }
   } else {
-    // epilogue: thread = tile row (TMEM lane).  The 16-bit tile is first laid down in shared memory (the ring is
-    // idle by now: every load has landed and every MMA has read its operands), 16-byte pieces XOR-swizzled by the
-    // row so that neither side has bank conflicts; then each warp writes its 32 rows out 512 contiguous bytes at
-    // a time.  A thread-per-row store straight from registers sends 16-byte pieces 512 bytes apart, which over
-    // NVLink cost ~4x the time of the whole GEMM.
+    // epilogue: thread = tile row (TMEM lane).  The 16-bit row is laid down in shared memory (the ring is idle
+    // by now: every load has landed and every MMA has read its operands; rows padded by 16 bytes so that the
+    // 16-byte pieces of 8 neighbouring rows fall into different banks) and leaves as one 512-byte bulk copy per
+    // row and destination.  A thread-per-row store straight from registers sends 16-byte pieces 512 bytes
+    // apart, which over NVLink cost ~4x the time of the whole GEMM.
     const int quad = warp & 3;
     ok = ptx::mbar_wait_bounded(ptx::smem_u32(&sh->acc_full), 0, abort_flag, limit);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       ptx::tc_fence_after();
       const int owner = a.world > 1 ? tile % a.world : 0;
-      const int local_tile = a.world > 1 ? tile / a.world : 0;
-      T* dst;            // first element of this warp's first row
-      long long ld;      // elements between rows
-      if (a.world > 1) {
-        dst = reinterpret_cast<T*>(a.stage[owner]) +
-              (static_cast<long long>(a.rank) * a.tiles_per_owner + local_tile) * kTileElems + static_cast<long long>(quad * 32) * kBN;
-        ld = kBN;
-      } else {
-        dst = reinterpret_cast<T*>(a.out_local) + static_cast<long long>(tm * kBM + quad * 32) * a.out_stride_m + tn * kBN;
-        ld = a.out_stride_m;
-      }
-      uint8_t* wtile = smem_aligned + quad * (32 * kBN * 2);   // 32 rows x 512 bytes of this warp
+      const int slot = a.one_shot ? tile : (a.world > 1 ? tile / a.world : 0);   // tile slot (and counter) at the destination
+      const int n_dst = (a.world > 1 && a.one_shot) ? a.world : 1;
+      constexpr int kRowPitch = kBN * 2 + 16;
+      uint8_t* my_row = smem_aligned + (quad * 32 + lane) * kRowPitch;
       const uint32_t taddr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
 #pragma unroll 2
       for (int c = 0; c < kBN / 32; ++c) {
@@ -221,24 +225,34 @@ __global__ void __launch_bounds__(kThreads, 1)
           w.y = pack2<T>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
           w.z = pack2<T>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
           w.w = pack2<T>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
-          const int piece = (c * 4 + i / 8) ^ lane;
-          *reinterpret_cast<uint4*>(wtile + lane * (kBN * 2) + piece * 16) = w;
+          *reinterpret_cast<uint4*>(my_row + (c * 32 + i) * 2) = w;
         }
       }
-      __syncwarp();
-      const int rows_live = min(32, a.M - (tm * kBM + quad * 32));   // may be <= 0
-#pragma unroll 4
-      for (int rr = 0; rr < 32; ++rr) {
-        if (rr < rows_live) {
-          const uint4 w = *reinterpret_cast<const uint4*>(wtile + rr * (kBN * 2) + ((lane ^ rr) * 16));
-          *reinterpret_cast<uint4*>(dst + rr * ld + lane * 8) = w;
+      ptx::fence_proxy_async_smem();   // this thread's row is visible to the bulk-copy engine
+      const int row = tm * kBM + quad * 32 + lane;
+      if (row < a.M) {
+        for (int di = 0; di < n_dst; ++di) {
+          const int d = a.one_shot ? (a.rank + 1 + di) % a.world : owner;   // one-shot: the peers first, this rank last
+          T* dst;
+          if (a.world > 1) {
+            dst = reinterpret_cast<T*>(a.stage[d]) + a.buf_off_elems +
+                  (static_cast<long long>(a.rank) * a.slot_tiles + slot) * kTileElems + static_cast<long long>(quad * 32 + lane) * kBN;
+          } else {
+            dst = reinterpret_cast<T*>(a.out_local) + static_cast<long long>(row) * a.out_stride_m + tn * kBN;
+          }
+          bulk_store(dst, ptx::smem_u32(my_row), kBN * 2);
         }
+        bulk_commit();
+        bulk_wait_all();   // the copies have been performed (not merely read out of shared memory)
       }
       if (a.world > 1) {
-        // the partial tile is out: make it visible system-wide, then tell the owner
+        // the partial tile is out: make it visible system-wide, then tell its reader(s)
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (tid == 64) red_add_release_sys(a.tile_counters[owner] + local_tile, 1u);
+        if (tid >= 64 && tid < 64 + n_dst) {
+          const int d = a.one_shot ? (a.rank + 1 + (tid - 64)) % a.world : owner;
+          red_add_release_sys(a.tile_counters[d] + slot, 1u);
+        }
       }
     }
   }
@@ -260,12 +274,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 struct ReduceArgs {
   int M, N, tiles_n, n_tiles, world, rank, tiles_per_owner;
+  int one_shot, slot_tiles;            // as in GemmArgs
+  long long buf_off_elems;
+  uint32_t row_target[kMaxRowTiles];   // arrivals expected at a tile of row tile tm once this call's partials are in
   const void* stage_local;             // this rank's staging buffer
   const uint32_t* tile_counters_local;
   void* out[kMaxWorld];                // every rank's output [M, N]
   long long out_stride_m;
   uint32_t* done_counters[kMaxWorld];
-  uint32_t epoch;
   unsigned long long wait_limit_ns;
   int32_t* status;
 };
@@ -281,19 +297,20 @@ __global__ void __launch_bounds__(256) oproj_reduce_kernel(const ReduceArgs a) {
   // The GEMM itself is a plain launch, so nothing of an earlier call or of the producer of A is overtaken.
   ptx::grid_launch_dependents();
   __shared__ int sh_ok;
-  const int lt = blockIdx.x / kReduceSplit, part = blockIdx.x % kReduceSplit;
-  const int tile = lt * a.world + a.rank;
+  const int lt = blockIdx.x / kReduceSplit, part = blockIdx.x % kReduceSplit;   // lt: tile slot and counter on this rank
+  const int tile = a.one_shot ? lt : lt * a.world + a.rank;
   if (tile >= a.n_tiles) return;
   if (threadIdx.x == 0) {
-    sh_ok = wait_counter(a.tile_counters_local + lt, a.epoch * static_cast<uint32_t>(a.world), a.wait_limit_ns) ? 1 : 0;
+    sh_ok = wait_counter(a.tile_counters_local + lt, a.row_target[tile / a.tiles_n], a.wait_limit_ns) ? 1 : 0;
     if (!sh_ok && a.status) atomicOr(a.status, CA_STATUS_TIMEOUT);
   }
   __syncthreads();
   const bool ok = sh_ok != 0;
   if (ok) {
     const int tm = tile / a.tiles_n, tn = tile % a.tiles_n;
-    const T* base = reinterpret_cast<const T*>(a.stage_local) + static_cast<long long>(lt) * kTileElems;
-    const long long src_stride = static_cast<long long>(a.tiles_per_owner) * kTileElems;
+    const T* base = reinterpret_cast<const T*>(a.stage_local) + a.buf_off_elems + static_cast<long long>(lt) * kTileElems;
+    const long long src_stride = static_cast<long long>(a.slot_tiles) * kTileElems;
+    const int d0 = a.one_shot ? a.rank : 0, d1 = a.one_shot ? a.rank + 1 : a.world;   // one-shot: only this rank's output
     // 8 elements (16 bytes) per thread and step; a row of the tile is 32 such groups
     constexpr int kPartGroups = kTileElems / 8 / kReduceSplit;
     for (int e = part * kPartGroups + threadIdx.x; e < (part + 1) * kPartGroups; e += 256) {
@@ -313,10 +330,11 @@ __global__ void __launch_bounds__(256) oproj_reduce_kernel(const ReduceArgs a) {
       uint4 o;
       o.x = pack2<T>(acc[0], acc[1]), o.y = pack2<T>(acc[2], acc[3]), o.z = pack2<T>(acc[4], acc[5]), o.w = pack2<T>(acc[6], acc[7]);
       const long long off = static_cast<long long>(tm * kBM + r) * a.out_stride_m + tn * kBN + c8 * 8;
-      for (int d = 0; d < a.world; ++d) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.out[d]) + off) = o;
+      for (int d = d0; d < d1; ++d) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.out[d]) + off) = o;
     }
-    __threadfence_system();
+    if (!a.one_shot) __threadfence_system();
   }
+  if (a.one_shot) return;   // nothing left another rank waits for
   __syncthreads();
   // the finished tile is in every rank's output: every rank's count of delivered tiles moves on.  (After a
   // timeout nothing is counted: the other ranks' final waits then run out too and report it.)
@@ -356,9 +374,16 @@ int ca_oproj_scratch_bytes(int M_max, int N, int world, size_t* stage_bytes, siz
              kMaxWorld);
   const long long n_tiles = static_cast<long long>(ceil_div(M_max, kBM)) * (N / kBN);
   const long long per_owner = (n_tiles + world - 1) / world;
-  *stage_bytes = world > 1 ? static_cast<size_t>(world) * per_owner * kTileElems * 2 : 0;
-  *counter_bytes = (static_cast<size_t>(per_owner) + 1) * sizeof(uint32_t);  // per owned tile, then the finished-tile count
+  // two-shot: [src][owned tile]; one-shot (two ranks only): two halves of [src][tile], used by alternate calls
+  const long long slots = world == 2 ? 2 * n_tiles : per_owner;
+  *stage_bytes = world > 1 ? static_cast<size_t>(world) * slots * kTileElems * 2 : 0;
+  *counter_bytes = (static_cast<size_t>(n_tiles) + 1) * sizeof(uint32_t);  // per tile slot, then the finished-tile count
   return CA_OK;
+}
+
+int ca_oproj_tile_count(int M, int N) {
+  using namespace ca::oproj;
+  return (M > 0 && N > 0) ? ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN) : 0;
 }
 
 int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream_) {
@@ -382,6 +407,9 @@ int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream_) {
     }
   }
   CA_REQUIRE(p->world == 1 || p->epoch > 0, "epoch counts calls from 1");
+  CA_REQUIRE(ceil_div(p->M, kBM) <= kMaxRowTiles, "M (%d) exceeds %d rows per call", p->M, kMaxRowTiles * kBM);
+  CA_REQUIRE(p->mode >= 0 && p->mode <= 2, "mode must be 0 (auto), 1 (two-shot) or 2 (one-shot)");
+  const bool one_shot = p->world > 1 && (p->mode == 2 || (p->mode == 0 && p->world == 2));
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   DeviceInfo dev;
   int rc = get_device_info(&dev);
@@ -399,6 +427,16 @@ int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream_) {
   g.n_tiles = ceil_div(p->M, kBM) * g.tiles_n;
   g.world = p->world, g.rank = p->rank;
   g.tiles_per_owner = ceil_div(g.n_tiles, p->world);
+  g.one_shot = one_shot ? 1 : 0;
+  g.slot_tiles = one_shot ? g.n_tiles : g.tiles_per_owner;
+  g.buf_off_elems = 0;
+  if (p->world > 1) {
+    const size_t need = static_cast<size_t>(p->world) * g.slot_tiles * kTileElems * 2 * (one_shot ? 2 : 1);
+    CA_REQUIRE(p->stage_bytes >= need, "staging buffers of %zu bytes are too small for this call (%zu)", p->stage_bytes, need);
+    // one-shot: alternate calls use alternate halves, so a rank that is one call ahead never overwrites what a
+    // slower rank still reads (it cannot get two calls ahead: its own reduction waits for the slower rank's tiles)
+    if (one_shot && (p->epoch & 1u)) g.buf_off_elems = static_cast<long long>(p->stage_bytes / 4 / 8) * 8;
+  }
   for (int r = 0; r < kMaxWorld; ++r) {
     g.stage[r] = (p->world > 1 && r < p->world) ? p->stage[r] : nullptr;
     g.tile_counters[r] = (p->world > 1 && r < p->world) ? p->tile_counters[r] : nullptr;
@@ -435,6 +473,11 @@ int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream_) {
   ReduceArgs r;
   r.M = p->M, r.N = p->N, r.tiles_n = g.tiles_n, r.n_tiles = g.n_tiles, r.world = p->world, r.rank = p->rank;
   r.tiles_per_owner = g.tiles_per_owner;
+  r.one_shot = g.one_shot, r.slot_tiles = g.slot_tiles, r.buf_off_elems = g.buf_off_elems;
+  for (int tm = 0; tm < kMaxRowTiles; ++tm) {
+    const uint32_t calls = (p->row_epochs && tm < ceil_div(p->M, kBM)) ? p->row_epochs[tm] : p->epoch;
+    r.row_target[tm] = calls * static_cast<uint32_t>(p->world);
+  }
   r.stage_local = p->stage[p->rank];
   r.tile_counters_local = p->tile_counters[p->rank];
   for (int d = 0; d < kMaxWorld; ++d) {
@@ -442,20 +485,21 @@ int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream_) {
     r.done_counters[d] = d < p->world ? p->done_counters[d] : nullptr;
   }
   r.out_stride_m = p->out_stride_m;
-  r.epoch = p->epoch;
   r.wait_limit_ns = g.wait_limit_ns;
   r.status = p->status;
   if (phases & 2u) {
+    const dim3 grid(g.slot_tiles * kReduceSplit);
     if (p->dtype == CA_DTYPE_BF16) {
-      launch_kernel_as(true, oproj_reduce_kernel<__nv_bfloat16>, dim3(g.tiles_per_owner * kReduceSplit), dim3(256), 0, stream, r);
+      launch_kernel_as(true, oproj_reduce_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, r);
     } else {
-      launch_kernel_as(true, oproj_reduce_kernel<__half>, dim3(g.tiles_per_owner * kReduceSplit), dim3(256), 0, stream, r);
+      launch_kernel_as(true, oproj_reduce_kernel<__half>, grid, dim3(256), 0, stream, r);
     }
     CA_LAUNCH_CHECK("oproj_reduce_kernel");
   }
-  if (phases & 4u) {
+  if ((phases & 4u) && !one_shot) {
+    const uint32_t done_tiles = p->done_tiles_total ? p->done_tiles_total : p->epoch * static_cast<uint32_t>(g.n_tiles);
     launch_kernel_as(true, oproj_wait_kernel, dim3(1), dim3(32), 0, stream, static_cast<const uint32_t*>(p->done_counters[p->rank]),
-                     p->epoch * static_cast<uint32_t>(g.n_tiles * kReduceSplit), static_cast<unsigned long long>(g.wait_limit_ns),
+                     done_tiles * static_cast<uint32_t>(kReduceSplit), static_cast<unsigned long long>(g.wait_limit_ns),
                      p->status);
     CA_LAUNCH_CHECK("oproj_wait_kernel");
   }

@@ -88,7 +88,8 @@ class FusedOutputProjection:
     All ranks must construct it with the same sizes and call it in the same order.  ``check()`` reads the
     status word (a device-to-host read) and raises if a wait ran out - e.g. a rank that died."""
 
-    def __init__(self, max_rows: int, out_features: int, device, dtype=torch.bfloat16, group=None, wait_limit_s: float = 2.0):
+    def __init__(self, max_rows: int, out_features: int, device, dtype=torch.bfloat16, group=None, wait_limit_s: float = 2.0,
+                 mode: int = 0):
         import ctypes as C
 
         from . import _lib
@@ -99,6 +100,10 @@ class FusedOutputProjection:
         self.max_rows, self.N, self.dtype, self.device = int(max_rows), int(out_features), dtype, torch.device(device)
         self.epoch = 0
         self.phases = 7   # all three launches; a subset only for tests and timing (see ca_oproj_params.phases)
+        self.mode = int(mode)   # 0: one exchange on two ranks, reduce-scatter + all-gather beyond; 1 / 2 force either
+        self._row_calls = [0] * ((self.max_rows + 127) // 128)   # calls that covered each block of 128 rows
+        self._tiles_total = 0
+        self._stage_bytes = 0
         self.wait_limit_ns = int(wait_limit_s * 1e9)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         stage_b, cnt_b = C.c_size_t(0), C.c_size_t(0)
@@ -115,6 +120,7 @@ class FusedOutputProjection:
         self.stage = symm.empty(max(int(stage_b.value) // esize, 8), dtype=dtype, device=self.device)
         self.counters = symm.empty(int(cnt_b.value) // 4, dtype=torch.int32, device=self.device)
         self.counters.zero_()
+        self._stage_bytes = self.stage.numel() * esize
         handles = [symm.rendezvous(t, name) for t in (self.out, self.stage, self.counters)]
         n_tile_counters = int(cnt_b.value) // 4 - 1
         self._ptrs = {
@@ -144,7 +150,14 @@ class FusedOutputProjection:
         if a.stride(1) != 1 or weight.stride(1) != 1 or weight.shape != (self.N, K) or a.dtype != self.dtype or weight.dtype != self.dtype:
             raise ValueError("x must be [..., K] and weight [N, K], both K-contiguous and of the projection's dtype")
         self.epoch += 1
+        blocks = (M + 127) // 128
+        for tm in range(blocks):
+            self._row_calls[tm] += 1
+        self._tiles_total = (self._tiles_total + self._lib.load().ca_oproj_tile_count(M, self.N)) & 0xFFFFFFFF
+        row_epochs = (C.c_uint32 * blocks)(*[c & 0xFFFFFFFF for c in self._row_calls[:blocks]])
         p = self._lib.OprojParams()
+        p.mode, p.stage_bytes, p.done_tiles_total = self.mode, self._stage_bytes, self._tiles_total
+        p.row_epochs = C.cast(row_epochs, C.POINTER(C.c_uint32))
         p.a, p.a_stride_m, p.w, p.w_stride_n = a.data_ptr(), a.stride(0), weight.data_ptr(), weight.stride(0)
         p.M, p.N, p.K, p.dtype = M, self.N, K, ops._DTYPES[self.dtype]
         p.world, p.rank = self.world, self.rank

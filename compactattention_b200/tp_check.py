@@ -34,16 +34,21 @@ def main() -> None:
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     x = torch.randn((1, M, K), device=dev, generator=g).to(torch.bfloat16)
     w = (torch.randn((N, K), device=dev, generator=g) * 0.02).to(torch.bfloat16)
-    fused = tp.FusedOutputProjection(M, N, dev, torch.bfloat16)
+    # two ranks exchange once (every partial tile to both ranks); the reduce-scatter + all-gather form is timed too
+    routes = {"auto": tp.FusedOutputProjection(M, N, dev, torch.bfloat16)}
+    if world == 2:
+        routes["two_shot"] = tp.FusedOutputProjection(M, N, dev, torch.bfloat16, mode=1)
     # correctness: three calls in a row (buffers reused), against GEMM + all-reduce in fp32
     worst = 0.0
     for _ in range(3):
-        got = fused(x, w).float().clone()
         ref = x.float() @ w.float().T
         dist.all_reduce(ref)
-        worst = max(worst, ((got - ref).abs() / (ref.abs() + 1.0)).max().item())
+        for fused in routes.values():
+            got = fused(x, w).float()
+            worst = max(worst, ((got - ref).abs() / (ref.abs() + 1.0)).max().item())
         x = (x.float() * 0.5 + 0.1).to(torch.bfloat16)
-    fused.check()
+    for fused in routes.values():
+        fused.check()
 
     def timed(fn):
         for _ in range(5):
@@ -64,22 +69,27 @@ def main() -> None:
         dist.all_reduce(y)
         return y
 
-    # The three launches one by one.  Each loop replays the same epochs with one phase enabled: the pushes of
-    # the first loop leave every counter ahead of what the later loops wait for, so those measure the kernels
-    # themselves, not the waiting.
-    phase_us, first_epoch = {}, fused.epoch
-    for name, mask in (("gemm_and_push", 1), ("reduce_and_broadcast", 2), ("final_wait", 4)):
-        fused.epoch, fused.phases = first_epoch, mask
-        phase_us[name] = round(timed(lambda: fused(x, w)), 1)
-    fused.phases = 7
-    fused_us = timed(lambda: fused(x, w))
-    fused.check()
+    # The launches one by one.  Each loop replays the same calls with one phase enabled: the pushes of the first
+    # loop leave every counter ahead of what the later loops wait for, so those measure the kernels themselves,
+    # not the waiting (and, launched back to back without a dependency, they overlap: a rate, not a latency).
+    results = {}
+    for name, fused in routes.items():
+        phase_us = {}
+        start = (fused.epoch, list(fused._row_calls), fused._tiles_total)
+        for pname, mask in (("gemm_and_push", 1), ("reduce", 2), ("final_wait", 4)):
+            fused.epoch, fused._row_calls, fused._tiles_total = start[0], list(start[1]), start[2]
+            fused.phases = mask
+            phase_us[pname] = round(timed(lambda: fused(x, w)), 1)
+        fused.phases = 7
+        total = timed(lambda: fused(x, w))
+        fused.check()
+        results[name] = {"fused_us": round(total, 1), "phase_us": phase_us}
     lib_us = timed(library_route)
     gemm_us = timed(lambda: torch.nn.functional.linear(x, w))
     if rank == 0:
         print(json.dumps({"world": world, "rows": M, "hidden": N, "k_per_rank": K, "max_rel_err_vs_gemm_plus_allreduce": round(worst, 5),
-                          "fused_us": round(fused_us, 1), "library_gemm_plus_nccl_allreduce_us": round(lib_us, 1),
-                          "library_gemm_alone_us": round(gemm_us, 1), "fused_phase_us": phase_us}))
+                          "fused": results, "library_gemm_plus_nccl_allreduce_us": round(lib_us, 1),
+                          "library_gemm_alone_us": round(gemm_us, 1)}))
     dist.destroy_process_group()
 
 

@@ -477,14 +477,17 @@ int ca_rope_append(const ca_rope_append_params* p, ca_stream_t stream);
  * Rank `rank` of `world` passes its own a and w and, for EVERY rank, the peer-mapped device addresses of that
  * rank's staging buffer, per-tile arrival counters, finished-tile counter and output buffer (symmetric
  * allocations of the same sizes on all ranks, see ca_oproj_scratch_bytes; counters zero before the first
- * call).  Three launches: a tcgen05 GEMM whose epilogue stores each 128 x 256 partial tile into the staging
- * buffer of the rank that owns the tile (tile t -> rank t % world) with plain peer stores and bumps the
- * owner's arrival counter; a reduction in which every rank sums the partials of its own tiles and stores the
- * result into every rank's output; a one-thread wait until this rank's output is complete.  Every wait is
- * bounded by wait_limit_ns (0 = 2 s); on expiry *status gets CA_STATUS_TIMEOUT and the output is invalid.
- * `epoch` is the number of this call on these buffers (1, 2, ...), the same on every rank: counters only
- * grow, nothing is reset.  All ranks must issue the same sequence of calls with the same M, N.  world == 1 is
- * a plain GEMM into out[0].
+ * call).  Two-shot (any world): three launches - a tcgen05 GEMM whose epilogue stores each 128 x 256 partial
+ * tile into the staging buffer of the rank that owns the tile (tile t -> rank t % world) with plain peer stores
+ * and bumps the owner's arrival counter; a reduction in which every rank sums the partials of its own tiles and
+ * stores the result into every rank's output; a one-thread wait until this rank's output is complete.  One-shot
+ * (two ranks): the GEMM stores every partial tile into BOTH ranks' staging buffers and each rank reduces all
+ * tiles into its own output - the same bytes over NVLink, one exchange instead of two, no final wait; the
+ * staging buffer is used in halves by alternate calls.  Every wait is bounded by wait_limit_ns (0 = 2 s); on
+ * expiry *status gets CA_STATUS_TIMEOUT and the output is invalid.  `epoch` is the number of this call on these
+ * buffers (1, 2, ...), the same on every rank: counters only grow, nothing is reset.  All ranks must issue the
+ * same sequence of calls with the same M, N and mode; M may change from call to call when row_epochs and
+ * done_tiles_total are kept (see the fields).  world == 1 is a plain GEMM into out[0].
  * Replaces the row-parallel o_proj of the reference's tensor-parallel plan followed by its all-reduce
  * (compact_attn/prefill_sparse/llama/modeling_llama_seerattn.py:111-120; the deferred wait of
  * modeling_llama_flashprefill_compactattn.py:37-41, 321-322).
@@ -508,11 +511,20 @@ typedef struct ca_oproj_params {
                       one that has not been launched) */
   uint64_t wait_limit_ns;
   int32_t* status; /* optional */
+  int32_t mode;    /* 0 = auto (one-shot on two ranks, else two-shot), 1 = two-shot, 2 = one-shot */
+  size_t stage_bytes;          /* size of each staging buffer (checked against what the call needs) */
+  const uint32_t* row_epochs;  /* HOST array [ceil(M/128)], optional: for each block of 128 rows, how many calls on
+                                  these buffers (this one included) had at least that many rows.  NULL = `epoch` for
+                                  every block, i.e. every call so far had at least this call's number of row blocks */
+  uint32_t done_tiles_total;   /* two-shot: sum of ca_oproj_tile_count(M, N) over all calls so far, this one included;
+                                  0 = epoch * this call's tile count (every call the same M) */
 } ca_oproj_params;
 
 /* Bytes of the symmetric staging buffer and of the counter block (per-owned-tile counters followed by the
  * finished-tile counter) for outputs of up to M_max rows. */
 int ca_oproj_scratch_bytes(int M_max, int N, int world, size_t* stage_bytes, size_t* counter_bytes);
+/* Number of 128 x 256 output tiles of an [M, N] result (what done_tiles_total accumulates). */
+int ca_oproj_tile_count(int M, int N);
 int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------

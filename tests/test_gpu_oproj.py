@@ -25,7 +25,7 @@ def arr(ptrs):
     return a, C.cast(a, C.POINTER(C.c_void_p))
 
 
-def call(lib, a, w, rank, world, bufs, epoch, status, limit_ns=0, phases=0):
+def call(lib, a, w, rank, world, bufs, epoch, status, limit_ns=0, phases=0, mode=0, row_epochs=None, done_tiles_total=0):
     from compactattention_b200 import ops
     p = lib.OprojParams()
     p.a, p.a_stride_m, p.w, p.w_stride_n = a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0)
@@ -39,6 +39,10 @@ def call(lib, a, w, rank, world, bufs, epoch, status, limit_ns=0, phases=0):
         keep.append(k)
         setattr(p, name, ptr)
     p.out_stride_m, p.epoch, p.phases, p.wait_limit_ns, p.status = w.shape[0], epoch, phases, limit_ns, status.data_ptr()
+    p.mode, p.stage_bytes, p.done_tiles_total = mode, bufs.get("stage_bytes", 0), done_tiles_total
+    if row_epochs is not None:
+        re_arr = (C.c_uint32 * len(row_epochs))(*row_epochs)
+        p.row_epochs = C.cast(re_arr, C.POINTER(C.c_uint32))
     rc = lib.load().ca_oproj_allreduce(C.byref(p), ops._stream())
     assert rc == 0, lib.load().ca_last_error()
 
@@ -69,12 +73,15 @@ def make_world(lib, world, M_max, N, dtype):
     counters = [torch.zeros(int(cnt_b.value) // 4, dtype=torch.int32, device="cuda") for _ in range(world)]
     n_tc = int(cnt_b.value) // 4 - 1
     bufs = {"out": [t.data_ptr() for t in outs], "stage": [t.data_ptr() for t in stages],
-            "tile_counters": [t.data_ptr() for t in counters], "done_counters": [t.data_ptr() + 4 * n_tc for t in counters]}
+            "tile_counters": [t.data_ptr() for t in counters], "done_counters": [t.data_ptr() + 4 * n_tc for t in counters],
+            "stage_bytes": int(stage_b.value)}
     return outs, stages, counters, bufs
 
 
-@pytest.mark.parametrize("world,M,N,K", [(2, 1024, 4096, 2048), (4, 1024, 4096, 1024), (8, 1000, 4096, 512), (2, 232, 1024, 256)])
-def test_reduction_protocol_with_emulated_ranks(lib, world, M, N, K):
+@pytest.mark.parametrize("world,M,N,K,mode", [(2, 1024, 4096, 2048, 0), (2, 1024, 4096, 2048, 1), (4, 1024, 4096, 1024, 0),
+                                              (8, 1000, 4096, 512, 0), (2, 232, 1024, 256, 0), (2, 232, 1024, 256, 1)])
+def test_reduction_protocol_with_emulated_ranks(lib, world, M, N, K, mode):
+    one_shot = world == 2 and mode != 1   # auto picks the one-shot exchange on two ranks
     dtype = torch.bfloat16
     g = torch.Generator(device="cuda").manual_seed(world * 100 + M)
     outs, stages, counters, bufs = make_world(lib, world, 1024, N, dtype)
@@ -90,8 +97,8 @@ def test_reduction_protocol_with_emulated_ranks(lib, world, M, N, K):
         n0 = L.launch_count()
         for phase in (1, 2, 4):
             for r in range(world):
-                call(lib, xs[r], ws[r], r, world, bufs, epoch, status, phases=phase)
-        assert L.launch_count() - n0 == 3 * world
+                call(lib, xs[r], ws[r], r, world, bufs, epoch, status, phases=phase, mode=mode)
+        assert L.launch_count() - n0 == (2 if one_shot else 3) * world   # one-shot has no final wait
         torch.cuda.synchronize()
         assert int(status.item()) == 0
         parts = [x.float() @ w.float().T for x, w in zip(xs, ws)]
@@ -105,6 +112,35 @@ def test_reduction_protocol_with_emulated_ranks(lib, world, M, N, K):
             assert ((got - want).abs() <= tol).all(), (epoch, r, (got - want).abs().max().item())
         for r in range(1, world):
             assert torch.equal(outs[r][:M], outs[0][:M])  # every rank holds the same bits
+
+
+@pytest.mark.parametrize("world,mode", [(2, 0), (2, 1), (4, 0)])
+def test_row_counts_may_change_between_calls(lib, world, mode):
+    """Chunked prefill ends with a ragged chunk and goes on with single-row decode steps: the per-row-block call
+    counts and the running tile total keep the counters' targets right when M shrinks and grows again."""
+    N, K, dtype = 1024, 256, torch.bfloat16
+    g = torch.Generator(device="cuda").manual_seed(7 + world)
+    outs, stages, counters, bufs = make_world(lib, world, 1024, N, dtype)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    row_calls, tiles_total = [0] * 8, 0
+    for epoch, M in enumerate((1024, 232, 1, 1024, 129), start=1):
+        blocks = (M + 127) // 128
+        for tm in range(blocks):
+            row_calls[tm] += 1
+        tiles_total += lib.load().ca_oproj_tile_count(M, N)
+        xs = [torch.randn((M, K), device="cuda", generator=g).to(dtype) for _ in range(world)]
+        ws = [(torch.randn((N, K), device="cuda", generator=g) * 0.05).to(dtype) for _ in range(world)]
+        for phase in (1, 2, 4):
+            for r in range(world):
+                call(lib, xs[r], ws[r], r, world, bufs, epoch, status, phases=phase, mode=mode, row_epochs=row_calls[:blocks],
+                     done_tiles_total=tiles_total, limit_ns=50_000_000)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0, (epoch, M)
+        parts = [x.float() @ w.float().T for x, w in zip(xs, ws)]
+        want = sum(parts)
+        tol = 2.0 ** -8 * (sum(p.abs() for p in parts) + want.abs()) + 1e-3
+        for r in range(world):
+            assert ((outs[r][:M].float() - want).abs() <= tol).all(), (epoch, M, r)
 
 
 def test_a_wait_that_nothing_satisfies_ends_with_the_status_bit(lib):
