@@ -8,19 +8,30 @@
 //
 //   1. oproj_gemm_kernel   tcgen05 GEMM, one CTA per 128 x 256 output tile: TMA loads of A and W from this
 //      GPU's own memory into a 4-stage ring, 128x256x16 MMAs into a TMEM accumulator, and an epilogue that
-//      stores the 16-bit partial tile straight into the staging buffer of the rank that OWNS the tile
-//      (tile t belongs to rank t % world) - plain st.global on peer-mapped memory - then fences and bumps
-//      that tile's arrival counter on the owner.
-//   2. oproj_reduce_kernel one CTA per owned tile: waits (bounded) until all `world` partials of the tile
-//      have arrived, sums them in fp32, and stores the finished 16-bit tile into EVERY rank's output buffer
-//      (plain peer stores again), then bumps every rank's count of finished tiles.
-//   3. oproj_wait_kernel   one thread: waits (bounded) until this rank's output holds all tiles.
+//      lays the 16-bit partial tile down in shared memory and sends it with bulk copies (512 bytes per row)
+//      into the staging buffer of the rank(s) that reduce the tile - peer-mapped memory - then fences and
+//      bumps that tile's arrival counter there.
+//   2. oproj_reduce_kernel four CTAs per tile: wait (bounded) until all `world` partials of the tile have
+//      arrived, sum them in fp32, store the finished 16-bit tile.  Launched programmatically behind the GEMM
+//      without a grid-dependency wait, so its CTAs are seated while the GEMM still runs.
+//   3. oproj_wait_kernel   (two-shot only) one thread: waits (bounded) until this rank's output holds all tiles.
 //
-// Each rank sends (world-1)/world of the output once as partials and once as results, the traffic of a
-// reduce-scatter plus an all-gather, and the first half overlaps the GEMM tile by tile.  No TMA load ever
-// touches another GPU's memory and nothing uses cluster multicast.  Counters only grow (targets are
-// multiples of a per-call epoch), so nothing has to be reset between calls.  A wait that runs out sets
-// CA_STATUS_TIMEOUT and the kernel returns; the output is then invalid but the context stays usable.
+// Two exchange forms.  Two-shot (any world): tile t is reduced by rank t % world, which then stores the result
+// into EVERY rank's output and bumps every rank's count of finished tiles - the traffic of a reduce-scatter
+// plus an all-gather, (world-1)/world of the output each way.  One-shot (two ranks, the default there): every
+// partial tile goes to both ranks and each rank reduces all tiles into its own output - the same bytes over
+// NVLink on two ranks, but one exchange and one chain of signalling latencies instead of two and no final
+// wait.  Its staging buffer is used in halves by alternate calls: a rank one call ahead writes the other
+// half, and it cannot get two calls ahead because its own reduction waits for the slower rank's tiles.
+//
+// No TMA load ever touches another GPU's memory and nothing uses cluster multicast.  Counters only grow
+// (targets are multiples of per-row-block call counts kept by the host), so nothing has to be reset between
+// calls and M may change from call to call.  A wait that runs out sets CA_STATUS_TIMEOUT and the kernel
+// returns; the output is then invalid but the context stays usable.
+//
+// Measured and rejected: computing the tile as two passes over K (128 columns each) so that the first half
+// travels while the second is computed - the two passes load A twice and 128-column passes need 128 bytes per
+// clock and SM from L2, more than it delivers: the GEMM alone went from 16.4 to 28.2 us (M 1024, K 2048).
 #include "ca_common.cuh"
 
 #include <mutex>

@@ -45,9 +45,14 @@ class ShardedMLP(nn.Module):
         self.gate_proj = nn.Linear(config.hidden_size, inter, bias=False)
         self.up_proj = nn.Linear(config.hidden_size, inter, bias=False)
         self.down_proj = nn.Linear(inter, config.hidden_size, bias=False)
+        self.fused_rows = int(getattr(config, "compactattn_fused_oproj_rows", 0) or 0)
 
     def forward(self, x):
-        out = self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
+        h = F.silu(self.gate_proj(x)) * self.up_proj(x)
+        # the down projection is row-parallel like o_proj: the same fused GEMM + sum over peer memory serves it
+        if self.fused_rows and tp.fused_projection_applies(h, self.down_proj.weight, None, self.fused_rows):
+            return tp.project_and_reduce(h, self.down_proj.weight, self.fused_rows)
+        out = self.down_proj(h)
         tp.reduce_layer_output(out)
         return out
 

@@ -86,6 +86,9 @@ class CompactAttnLlamaConfig:
     seerattn_flashprefill_last_n_block: int = 0
     seerattn_flashprefill_min_budget: int = 0
     seerattn_defer_async_collective_wait: bool = False
+    # Tensor parallel only: o_proj and its sum over the ranks as this library's fused kernels over peer memory
+    # (ca_oproj_allreduce) instead of a library GEMM + NCCL all-reduce; chunks of up to this many rows (0 = off).
+    compactattn_fused_oproj_rows: int = 0
     compactattn_debug: bool = False
 
 
@@ -232,7 +235,12 @@ class _CompactAttnBase(nn.Module):
         return q, k, v
 
     def _finish(self, attn_output, input_shape):
-        out = self.o_proj(attn_output.reshape(*input_shape, -1))
+        x = attn_output.reshape(*input_shape, -1)
+        rows = int(getattr(self.config, "compactattn_fused_oproj_rows", 0) or 0)
+        if rows and tp.fused_projection_applies(x, self.o_proj.weight, self.o_proj.bias, rows):
+            self._pending_reduce = None
+            return tp.project_and_reduce(x, self.o_proj.weight, rows)
+        out = self.o_proj(x)
         work = tp.reduce_layer_output(out, async_op=bool(self.config.seerattn_defer_async_collective_wait))
         self._pending_reduce = work
         return out

@@ -35,6 +35,9 @@ def main():
     ap.add_argument("--dense", action="store_true", help="force dense attention in every chunk (comparator)")
     ap.add_argument("--graph-mlp", action="store_true",
                     help="replay the local part of the residual + norm + MLP half of every layer from a CUDA graph")
+    ap.add_argument("--fused-projections", action="store_true",
+                    help="tensor parallel: o_proj and the MLP's down projection with their sums over the ranks as the "
+                         "library's fused kernels over peer memory instead of library GEMMs + NCCL all-reduces")
     ap.add_argument("--seed", type=int, default=1234 + 4)
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -46,7 +49,8 @@ def main():
         torch.distributed.init_process_group(backend="nccl", device_id=dev)
     cfg = CompactAttnLlamaConfig(num_hidden_layers=args.layers, seerattn_gate_type="Qavg_Kavg", seerattn_gate_force_double=True,
                                  seerattn_sparsity_method=args.rule, seerattn_topk_ratio=(int(round(args.topk * 1000)), 1000),
-                                 seerattn_chunked_prefill_force_dense=args.dense, max_position_embeddings=args.prompt)
+                                 seerattn_chunked_prefill_force_dense=args.dense, max_position_embeddings=args.prompt,
+                                 compactattn_fused_oproj_rows=args.chunk if args.fused_projections else 0)
     shard = tp.HeadShard(world, rank, cfg.num_attention_heads, cfg.num_key_value_heads)
     model = LlamaCompactAttnStack(cfg, args.selector, shard).to(torch.bfloat16).to(dev)
     model.init_weights(seed=args.seed)
@@ -103,7 +107,8 @@ def main():
         print(json.dumps({
             "workload": f"{args.layers}-layer Llama-3.1-8B-shaped stack, prompt {args.prompt}, chunk {args.chunk}, "
                         f"selector {args.selector}/{args.rule} {args.topk:.0%}{' (dense forced)' if args.dense else ''}"
-                        f"{', MLP half from CUDA graphs' if args.graph_mlp else ''}, tp{world}",
+                        f"{', MLP half from CUDA graphs' if args.graph_mlp else ''}"
+                        f"{', fused projections' if args.fused_projections and world > 1 else ''}, tp{world}",
             "prefill_ms": round(vals[0], 2), "chunks": n_chunks,
             "attn_per_chunk_ms": round(vals[1] / n_chunks, 3),
             "attn_last_chunk_ms": round(vals[2], 3),
@@ -112,7 +117,10 @@ def main():
             "host_attn_module_us_per_layer_call": round(host_s[0] / max(len(events), 1) * 1e6, 1),
             "host_us_per_layer_call": round(host_total_s / max(len(events), 1) * 1e6, 1),
             "finite": bool(torch.isfinite(hidden.float()).all()),
+            "hidden_checksum": round(float(hidden.float().abs().mean()), 5),
         }))
+    for proj in tp._SHARED_PROJECTIONS.values():
+        proj.check()   # a device-side wait that ran out would have left invalid outputs
     if world > 1:
         torch.distributed.destroy_process_group()
 

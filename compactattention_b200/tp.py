@@ -178,6 +178,38 @@ class FusedOutputProjection:
             raise RuntimeError("the fused output projection timed out waiting for another rank's tiles; its output is invalid")
 
 
+_SHARED_PROJECTIONS: dict = {}
+
+
+def shared_fused_projection(max_rows: int, out_features: int, device, dtype=torch.bfloat16, group=None) -> FusedOutputProjection:
+    """One ``FusedOutputProjection`` per (sizes, device, dtype, group) for all layers of a stack: every layer's
+    projection reuses the same symmetric buffers, so a layer's output must be consumed (the residual add)
+    before the next layer's projection is enqueued - which stream order gives for free.  All ranks must ask in
+    the same order (the first request allocates and exchanges the buffers, a collective step)."""
+    key = (int(max_rows), int(out_features), str(torch.device(device)), dtype, id(group))
+    proj = _SHARED_PROJECTIONS.get(key)
+    if proj is None:
+        proj = _SHARED_PROJECTIONS[key] = FusedOutputProjection(max_rows, out_features, device, dtype, group)
+    return proj
+
+
+def fused_projection_applies(x: torch.Tensor, weight: torch.Tensor, bias, max_rows: int) -> bool:
+    """Whether ``linear(x, weight)`` + sum over ranks can go through the fused kernels: more than one rank,
+    no bias, 16-bit operands, K a multiple of 64, N a multiple of 256, rows within the buffers."""
+    if not (dist.is_initialized() and dist.get_world_size() > 1) or bias is not None or not x.is_cuda:
+        return False
+    if x.dtype not in (torch.bfloat16, torch.float16) or weight.dtype != x.dtype or weight.stride(1) != 1 or x.stride(-1) != 1:
+        return False
+    rows = x.numel() // x.shape[-1]
+    return 0 < rows <= max_rows and x.shape[-1] % 64 == 0 and weight.shape[0] % 256 == 0
+
+
+def project_and_reduce(x: torch.Tensor, weight: torch.Tensor, max_rows: int) -> torch.Tensor:
+    """``linear(x, weight)`` summed over the ranks through the shared fused projection."""
+    proj = shared_fused_projection(max_rows, weight.shape[0], x.device, x.dtype)
+    return proj(x, weight)
+
+
 def max_over_ranks(values, device, group=None):
     """Element-wise max of a list of floats over the ranks (multi-GPU timings are max over ranks)."""
     t = torch.tensor(list(values), dtype=torch.float64, device=device)
