@@ -57,6 +57,8 @@ def parse_args():
     ap.add_argument("--sustained-seconds", type=float, default=1.0)
     ap.add_argument("--dependent-launch", action="store_true",
                     help="enqueue programmatic dependent launches instead of plain ones (for A/B timing)")
+    ap.add_argument("--two-launch-selection", action="store_true",
+                    help="gate scores and rule + table as two launches (the form before ca_gate_score_select; for A/B timing)")
     return ap.parse_args()
 
 
@@ -341,7 +343,13 @@ def run_native(args):
             ops.attn_compact(L["q"], L["kv"], K, hkv, L["table"].block_idx, L["table"].counts, block_size=BS, out=L["out"],
                              status=L["status"])
 
-        out = [("gate_prepare", prepare), ("gate_scores", sel.score), ("select_union_table", select), ("attention", attention)]
+        def score_select():
+            return sel.score_select(rule, hkv, BS, table=L["table"])
+
+        if args.two_launch_selection:
+            out = [("gate_prepare", prepare), ("gate_scores", sel.score), ("select_union_table", select), ("attention", attention)]
+        else:   # scores, row rule, Block-Union and table in one launch: the logits never leave the SM
+            out = [("gate_prepare", prepare), ("gate_score_select", score_select), ("attention", attention)]
         if world > 1:
             out.append(("all_reduce", lambda: tp.reduce_layer_output(reduce_buf)))
         return out

@@ -251,6 +251,7 @@ class ChunkStepParams(C.Structure):
         ("union_scratch", C.c_void_p),
         ("union_scratch_bytes", C.c_size_t),
         ("attn", AttnParams),
+        ("write_scores", C.c_int32),
     ]
 
 
@@ -282,6 +283,8 @@ _SIGNATURES = {
     "ca_oproj_scratch_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "ca_oproj_allreduce": (C.c_int, [C.POINTER(OprojParams), C.c_void_p]),
     "ca_oproj_tile_count": (C.c_int, [C.c_int, C.c_int]),
+    "ca_gate_score_select": (C.c_int, [C.POINTER(GateScoreParams), C.POINTER(SelectParams), C.POINTER(UnionParams), C.c_void_p,
+                                       C.c_size_t, C.c_int, C.c_void_p]),
 }
 
 _lib = None

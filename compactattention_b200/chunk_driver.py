@@ -74,6 +74,22 @@ class GateSelectorState:
                                       device=self.q_blocks.device)
         return ops.gate_scores(self.q_blocks, kb, kb.shape[1] - nb, scale=gate.scale, out=self.logits)
 
+    def score_select(self, rule: "SelectionRule", num_kv_heads: int, block_size: int, *, table=None, bits=None,
+                     write_scores: bool = False, rows_voting: int = 0) -> ops.BlockTable:
+        """Scores the chunk's Q blocks (from the last ``append``) against every cached block, applies the row
+        rule and builds the Block-Union table: ONE launch for the learned gate's usual shape
+        (``ca_gate_score_select``), the logits staying on chip unless ``write_scores``."""
+        gate, nb = self.gate, self.q_blocks.shape[1]
+        kb = self.cache.blocks()
+        if self.logits is None or self.logits.shape[3] != kb.shape[1] or self.logits.shape[2] != nb:
+            self.logits = torch.empty((self.q_blocks.shape[0], gate.num_q_head, nb, kb.shape[1]), dtype=torch.float32,
+                                      device=self.q_blocks.device)
+        return ops.gate_score_select(self.q_blocks, kb, kb.shape[1] - nb, rule.rule, num_kv_heads=num_kv_heads, scores=self.logits,
+                                     write_scores=write_scores, scale=gate.scale, block_size=block_size,
+                                     keep_recent=rule.keep_recent, softmax=rule.softmax, threshold=rule.threshold, alpha=rule.alpha,
+                                     topk_k=rule.topk_k, topk_ratio=rule.topk_ratio, min_budget=rule.min_budget, sink=rule.sink,
+                                     local=rule.local, rows_voting=rows_voting, bits=bits, out=table)
+
     def append_and_score(self, q_nope: torch.Tensor, k_nope: torch.Tensor, block_rope_q=None, block_rope_k=None) -> torch.Tensor:
         """``append`` then ``score`` (two launches)."""
         self.append(q_nope, k_nope, block_rope_q, block_rope_k)

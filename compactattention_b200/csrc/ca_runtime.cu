@@ -71,9 +71,17 @@ int ca_chunk_step(const ca_chunk_step_params* p, ca_stream_t stream) {
   int rc = CA_OK;
   if (p->append.k != nullptr && (rc = ca_rope_append(&p->append, stream)) != CA_OK) return rc;
   if (p->prepare.q.x != nullptr && (rc = ca_gate_prepare(&p->prepare, stream)) != CA_OK) return rc;
-  if (p->score.q != nullptr && (rc = ca_gate_scores(&p->score, stream)) != CA_OK) return rc;
+  // gate scores feeding a fused rule + table: one launch for the three stages
+  const bool score_select = p->score.q != nullptr && p->union_scratch != nullptr && p->select.score != nullptr &&
+                            p->select.score == p->score.out && p->fp_score.q == nullptr;
+  if (score_select) {
+    if ((rc = ca_gate_score_select(&p->score, &p->select, &p->table, p->union_scratch, p->union_scratch_bytes, p->write_scores,
+                                   stream)) != CA_OK)
+      return rc;
+  }
+  if (!score_select && p->score.q != nullptr && (rc = ca_gate_scores(&p->score, stream)) != CA_OK) return rc;
   if (p->fp_score.q != nullptr && (rc = ca_flashprefill_score(&p->fp_score, stream)) != CA_OK) return rc;
-  if (p->select.score != nullptr) {
+  if (!score_select && p->select.score != nullptr) {
     if (p->union_scratch != nullptr) {
       if ((rc = ca_select_union_table(&p->select, &p->table, p->union_scratch, p->union_scratch_bytes, stream)) != CA_OK) return rc;
     } else {

@@ -59,9 +59,29 @@ struct RowArgs {
   int32_t* pages_per_row;
 };
 
-// Exclusive block-wide prefix sum of one int per thread (kRowThreads threads).
-__device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int* total) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// A team is a warp-aligned group of `nt` threads of a CTA that works on one row and synchronises on its own
+// named barrier: the row kernels run one team per CTA (barrier 0 = the whole CTA), the fused score + rule
+// kernel runs one team per query head of a KV head side by side.
+struct Team {
+  int tid;  // thread index inside the team
+  int nt;   // threads in the team (a multiple of 32, <= kRowThreads)
+  int bar;  // named barrier of the team
+};
+__device__ __forceinline__ void team_sync(const Team& t) { asm volatile("bar.sync %0, %1;" ::"r"(t.bar), "r"(t.nt) : "memory"); }
+
+// Per-team scratch in shared memory.
+struct TeamShared {
+  float red[kRowThreads / 32];
+  int hist[256];
+  int warp_sums[kRowThreads / 32];
+  int cut, total, nvalid;
+  uint32_t prefix;
+  int remaining, last_bin_count;
+};
+
+// Exclusive team-wide prefix sum of one int per thread.
+__device__ __forceinline__ int block_exclusive_scan(const Team& tm, int v, int* warp_sums, int* total) {
+  const int lane = tm.tid & 31, warp = tm.tid >> 5;
   int inc = v;
 #pragma unroll
   for (int d = 1; d < 32; d <<= 1) {
@@ -69,76 +89,76 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int* 
     if (lane >= d) inc += n;
   }
   if (lane == 31) warp_sums[warp] = inc;
-  __syncthreads();
+  team_sync(tm);
   if (warp == 0) {
-    int w = lane < (kRowThreads / 32) ? warp_sums[lane] : 0;
+    int w = lane < (tm.nt / 32) ? warp_sums[lane] : 0;
     int winc = w;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       int n = __shfl_up_sync(0xffffffffu, winc, d);
       if (lane >= d) winc += n;
     }
-    if (lane < (kRowThreads / 32)) warp_sums[lane] = winc - w;
+    if (lane < (tm.nt / 32)) warp_sums[lane] = winc - w;
     if (lane == 31) *total = winc;
   }
-  __syncthreads();
+  team_sync(tm);
   int r = warp_sums[warp] + inc - v;
-  __syncthreads();
+  team_sync(tm);
   return r;
 }
 
-__device__ __forceinline__ float block_reduce_max(float v, float* scratch) {
+__device__ __forceinline__ float block_reduce_max(const Team& tm, float v, float* scratch) {
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
-  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-  __syncthreads();
+  if ((tm.tid & 31) == 0) scratch[tm.tid >> 5] = v;
+  team_sync(tm);
   float r = scratch[0];
-  for (int w = 1; w < kRowThreads / 32; ++w) r = fmaxf(r, scratch[w]);
-  __syncthreads();
+  for (int w = 1; w < tm.nt / 32; ++w) r = fmaxf(r, scratch[w]);
+  team_sync(tm);
   return r;
 }
 
 // Deterministic block sum: fixed tree inside the warp, then warps added in order.
-__device__ __forceinline__ float block_reduce_sum(float v, float* scratch) {
+__device__ __forceinline__ float block_reduce_sum(const Team& tm, float v, float* scratch) {
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-  __syncthreads();
+  if ((tm.tid & 31) == 0) scratch[tm.tid >> 5] = v;
+  team_sync(tm);
   float r = 0.f;
-  for (int w = 0; w < kRowThreads / 32; ++w) r += scratch[w];
-  __syncthreads();
+  for (int w = 0; w < tm.nt / 32; ++w) r += scratch[w];
+  team_sync(tm);
   return r;
 }
 
 // Marks the k largest entries of s[0..n) (ties -> lower index) in keep[] (1 byte per entry).
 // Radix select over the monotone keys, 8 bits per pass, then an ordered pass for the ties.
-__device__ void topk_mark(const float* s, int n, int k, uint8_t* keep, int* hist, int* warp_sums) {
-  __shared__ uint32_t sh_prefix;
-  __shared__ int sh_remaining, sh_total, sh_last_bin_count;
+__device__ void topk_mark(const Team& tm, const float* s, int n, int k, uint8_t* keep, TeamShared* ts) {
+  int* hist = ts->hist;
+  int* warp_sums = ts->warp_sums;
   if (k >= n) {
-    for (int j = threadIdx.x; j < n; j += kRowThreads) keep[j] = 1;
-    __syncthreads();
+    for (int j = tm.tid; j < n; j += tm.nt) keep[j] = 1;
+    team_sync(tm);
     return;
   }
-  if (threadIdx.x == 0) {
-    sh_prefix = 0;
-    sh_remaining = k;
+  if (tm.tid == 0) {
+    ts->prefix = 0;
+    ts->remaining = k;
   }
-  __syncthreads();
+  team_sync(tm);
   for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int i = threadIdx.x; i < 256; i += kRowThreads) hist[i] = 0;
-    __syncthreads();
-    const uint32_t prefix = sh_prefix;
+    for (int i = tm.tid; i < 256; i += tm.nt) hist[i] = 0;
+    team_sync(tm);
+    const uint32_t prefix = ts->prefix;
     const uint32_t mask_hi = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-    for (int j = threadIdx.x; j < n; j += kRowThreads) {
+    for (int j = tm.tid; j < n; j += tm.nt) {
       const uint32_t key = order_key(s[j]);
       if ((key & mask_hi) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
     }
-    __syncthreads();
-    if (threadIdx.x < 32) {
+    team_sync(tm);
+    if (tm.tid < 32) {
       // warp 0 finds the bin that holds the rem-th largest key: lane l owns bins 255-8l .. 248-8l
-      const int lane = threadIdx.x;
-      const int rem = sh_remaining;
+      const int lane = tm.tid;
+      const int rem = ts->remaining;
       int mine = 0;
 #pragma unroll
       for (int u = 0; u < 8; ++u) mine += hist[255 - 8 * lane - u];
@@ -158,39 +178,39 @@ __device__ void topk_mark(const float* s, int n, int k, uint8_t* keep, int* hist
           left -= hist[bin];
           --bin;
         }
-        sh_prefix = prefix | (static_cast<uint32_t>(bin) << shift);
-        sh_remaining = left;  // entries still wanted among those equal to the chosen digit
-        sh_last_bin_count = hist[bin];
+        ts->prefix = prefix | (static_cast<uint32_t>(bin) << shift);
+        ts->remaining = left;  // entries still wanted among those equal to the chosen digit
+        ts->last_bin_count = hist[bin];
       }
     }
-    __syncthreads();
+    team_sync(tm);
   }
-  const uint32_t kth = sh_prefix;
-  const int want_equal = sh_remaining;
-  if (want_equal == sh_last_bin_count) {
+  const uint32_t kth = ts->prefix;
+  const int want_equal = ts->remaining;
+  if (want_equal == ts->last_bin_count) {
     // every key equal to the k-th is wanted: no tie to break
-    for (int j = threadIdx.x; j < n; j += kRowThreads) keep[j] = order_key(s[j]) >= kth;
-    __syncthreads();
+    for (int j = tm.tid; j < n; j += tm.nt) keep[j] = order_key(s[j]) >= kth;
+    team_sync(tm);
     return;
   }
   // ordered pass: keys above kth are kept, keys equal to kth are kept in index order
   int taken = 0;
-  for (int base = 0; base < n; base += kRowThreads) {
-    const int j = base + threadIdx.x;
+  for (int base = 0; base < n; base += tm.nt) {
+    const int j = base + tm.tid;
     const uint32_t key = j < n ? order_key(s[j]) : 0u;
     const int eq = (j < n && key == kth) ? 1 : 0;
-    const int pos = block_exclusive_scan(eq, warp_sums, &sh_total);
+    const int pos = block_exclusive_scan(tm, eq, warp_sums, &ts->total);
     if (j < n) keep[j] = (key > kth) || (eq && (taken + pos) < want_equal);
-    taken += sh_total;
-    __syncthreads();
+    taken += ts->total;
+    team_sync(tm);
   }
 }
 
 // Sorts comp[0..n2) ascending (n2 a power of two), bitonic network in shared memory.
-__device__ void bitonic_sort(unsigned long long* comp, int n2) {
+__device__ void bitonic_sort(const Team& tm, unsigned long long* comp, int n2) {
   for (int size = 2; size <= n2; size <<= 1) {
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      for (int t = threadIdx.x; t < (n2 >> 1); t += kRowThreads) {
+      for (int t = tm.tid; t < (n2 >> 1); t += tm.nt) {
         const int lo = 2 * t - (t & (stride - 1));
         const int hi = lo + stride;
         const bool asc = (lo & size) == 0;
@@ -200,7 +220,7 @@ __device__ void bitonic_sort(unsigned long long* comp, int n2) {
           comp[hi] = x;
         }
       }
-      __syncthreads();
+      team_sync(tm);
     }
   }
 }
@@ -209,12 +229,12 @@ __device__ void bitonic_sort(unsigned long long* comp, int n2) {
 // some query head / Q-block) -> ascending past block ids, -1 padded, count, seqlen, pages.  Columns
 // j >= Kb - keep_recent are forced on first; only past columns (j < Pb) enter the table.  All threads of
 // the CTA call it.
-__device__ void compact_row(uint32_t* words, int W, int Kb, int Pb, int Qb, int keep_recent, int block_size, int page_size,
+__device__ void compact_row(const Team& tm, uint32_t* words, int W, int Kb, int Pb, int Qb, int keep_recent, int block_size, int page_size,
                             int32_t* idx_row, int idx_stride, int row, int32_t* counts, int32_t* cache_seqlens,
                             int32_t* pages_per_row, uint8_t* keep_kv_row, int* warp_sums, int* sh_total) {
   int running = 0;
-  for (int wbase = 0; wbase < W; wbase += kRowThreads) {
-    const int w = wbase + threadIdx.x;
+  for (int wbase = 0; wbase < W; wbase += tm.nt) {
+    const int w = wbase + tm.tid;
     uint32_t word = 0;
     if (w < W) {
       word = words[w];
@@ -230,7 +250,7 @@ __device__ void compact_row(uint32_t* words, int W, int Kb, int Pb, int Qb, int 
       if (j0 + 32 > Pb) word = j0 >= Pb ? 0u : (word & ((1u << (Pb - j0)) - 1u));
     }
     const int pc = __popc(word);
-    const int off = running + block_exclusive_scan(pc, warp_sums, sh_total);
+    const int off = running + block_exclusive_scan(tm, pc, warp_sums, sh_total);
     int o = off;
     while (word) {
       const int t = __ffs(word) - 1;
@@ -239,11 +259,11 @@ __device__ void compact_row(uint32_t* words, int W, int Kb, int Pb, int Qb, int 
       ++o;
     }
     running += *sh_total;
-    __syncthreads();
+    team_sync(tm);
   }
   const int count = running < idx_stride ? running : idx_stride;
-  for (int o = count + threadIdx.x; o < idx_stride; o += kRowThreads) idx_row[o] = -1;
-  if (threadIdx.x == 0) {
+  for (int o = count + tm.tid; o < idx_stride; o += tm.nt) idx_row[o] = -1;
+  if (tm.tid == 0) {
     counts[row] = count;
     const int seqlen = (count + Qb) * block_size;
     if (cache_seqlens) cache_seqlens[row] = seqlen;
@@ -251,41 +271,36 @@ __device__ void compact_row(uint32_t* words, int W, int Kb, int Pb, int Qb, int 
   }
 }
 
-__global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs a) {
-  ptx::grid_launch_dependents();
-  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
-  extern __shared__ unsigned char dyn_smem[];
-  float* s = reinterpret_cast<float*>(dyn_smem);                    // [Kb]
-  uint8_t* keep = reinterpret_cast<uint8_t*>(s + a.Kb);              // [Kb]
-  uint8_t* flag = keep + a.Kb;                                       // [Kb] scratch flags
+// One row (b, h, i) of the rule, by one team: scores -> (softmax) -> rule -> forced blocks -> packed bits, which
+// go to a.bits (if given) and, with a.fuse, are ORed into the KV-head row's union words.  `row_smem` holds
+// s[Kb] f32, keep[Kb], flag[Kb] and, for the cumulative-mass rule, the sort keys.  With `preloaded` the raw
+// scores of the row are already in s[] (the fused score + rule kernel) instead of in a.score.
+__device__ void select_row(const RowArgs& a, const Team& tm, TeamShared* ts, unsigned char* row_smem, int b, int h, int i,
+                           bool preloaded) {
+  float* s = reinterpret_cast<float*>(row_smem);                     // [Kb]
+  uint8_t* keep = reinterpret_cast<uint8_t*>(s + a.Kb);               // [Kb]
+  uint8_t* flag = keep + a.Kb;                                        // [Kb] scratch flags
   unsigned long long* comp =
-      reinterpret_cast<unsigned long long*>(dyn_smem + ((a.Kb * 6 + 15) / 16) * 16);  // cummass only
-  __shared__ float red[kRowThreads / 32];
-  __shared__ int hist[256];
-  __shared__ int warp_sums[kRowThreads / 32];
-  __shared__ int sh_cut;
-
-  const int i = blockIdx.x % a.Qb;
-  const int h = (blockIdx.x / a.Qb) % a.H;
-  const int b = blockIdx.x / (a.Qb * a.H);
+      reinterpret_cast<unsigned long long*>(row_smem + ((a.Kb * 6 + 15) / 16) * 16);  // cummass only
   const int diag = a.Pb + i;  // last causally valid key block of this row
   uint32_t* bits_row = a.bits ? a.bits + ((static_cast<long long>(b) * a.H + h) * a.Qb + i) * a.W : nullptr;
   const int kv_row = a.fuse ? b * (a.H / a.G) + h / a.G : 0;
-
   const bool voting = i < a.rows_voting;
   if (!voting) {
-    if (a.bits) for (int w = threadIdx.x; w < a.W; w += kRowThreads) bits_row[w] = 0u;
-    if (!a.fuse) return;
+    if (a.bits) for (int w = tm.tid; w < a.W; w += tm.nt) bits_row[w] = 0u;
+    return;
   }
-  if (voting) {
+  {
   const long long s_off = b * a.s_b + h * a.s_h + i * a.s_q;
   const long long v_off = a.valid ? (b * a.v_b + h * a.v_h + i * a.v_q) : 0;
 
   // ---- load the row; invalid entries become -inf ----
-  for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) {
+  for (int j = tm.tid; j < a.Kb; j += tm.nt) {
     const bool ok = a.valid ? (a.valid[v_off + j * a.v_k] != 0) : (j <= diag);
     float x;
-    if (a.rule == CA_RULE_MASK) {
+    if (preloaded) {
+      x = s[j];  // left there by the caller (only entries with j <= diag are meaningful)
+    } else if (a.rule == CA_RULE_MASK) {
       x = reinterpret_cast<const uint8_t*>(a.score)[s_off + j * a.s_k] ? 1.f : 0.f;
     } else {
       x = load_score(a.score, s_off + j * a.s_k, a.score_dtype);
@@ -293,78 +308,77 @@ __global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs 
     s[j] = ok ? x : -INFINITY;
     keep[j] = 0;
   }
-  __syncthreads();
+  team_sync(tm);
 
   if (a.softmax) {
     float m = -INFINITY;
-    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) m = fmaxf(m, s[j]);
-    m = block_reduce_max(m, red);
+    for (int j = tm.tid; j < a.Kb; j += tm.nt) m = fmaxf(m, s[j]);
+    m = block_reduce_max(tm, m, ts->red);
     float sum = 0.f;
-    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) {
+    for (int j = tm.tid; j < a.Kb; j += tm.nt) {
       const float e = s[j] == -INFINITY ? 0.f : expf(s[j] - m);
       s[j] = e;
       sum += e;
     }
-    sum = block_reduce_sum(sum, red);
+    sum = block_reduce_sum(tm, sum, ts->red);
     const float inv = sum > 0.f ? 1.0f / sum : 0.f;
-    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) {
+    for (int j = tm.tid; j < a.Kb; j += tm.nt) {
       const bool ok = a.valid ? (a.valid[v_off + j * a.v_k] != 0) : (j <= diag);
       s[j] = ok ? s[j] * inv : -INFINITY;
     }
-    __syncthreads();
+    team_sync(tm);
   }
   if (a.prob_out) {
     float* prow = a.prob_out + ((static_cast<long long>(b) * a.H + h) * a.Qb + i) * a.Kb;
-    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) prow[j] = s[j] == -INFINITY ? 0.f : s[j];
+    for (int j = tm.tid; j < a.Kb; j += tm.nt) prow[j] = s[j] == -INFINITY ? 0.f : s[j];
   }
 
   // ---- the rule ----
   const float thr = a.threshold_ptr ? __ldg(a.threshold_ptr + b * a.threshold_stride) : a.threshold;
   if (a.rule == CA_RULE_THRESHOLD) {
-    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) keep[j] = s[j] > thr;  // -inf never passes
+    for (int j = tm.tid; j < a.Kb; j += tm.nt) keep[j] = s[j] > thr;  // -inf never passes
   } else if (a.rule == CA_RULE_MASK) {
-    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) keep[j] = s[j] > 0.5f;
+    for (int j = tm.tid; j < a.Kb; j += tm.nt) keep[j] = s[j] > 0.5f;
   } else if (a.rule == CA_RULE_ALPHA_ROWMAX) {
     // non-finite or acausal entries count as 0 for the maximum and are never selected by score
     // (the reference zero-fills them before taking the maximum and the top-k)
     float m = 0.f;
-    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) {
+    for (int j = tm.tid; j < a.Kb; j += tm.nt) {
       const float x = s[j];
       const bool fin = (x == x) && fabsf(x) != INFINITY && j <= diag;
       flag[j] = fin;
       s[j] = fin ? x : 0.f;
       m = fmaxf(m, s[j]);
     }
-    m = block_reduce_max(m, red);
+    m = block_reduce_max(tm, m, ts->red);
     if (a.min_budget > 0) {
-      topk_mark(s, a.Kb, a.min_budget < a.Kb ? a.min_budget : a.Kb, keep, hist, warp_sums);
-      __syncthreads();
+      topk_mark(tm, s, a.Kb, a.min_budget < a.Kb ? a.min_budget : a.Kb, keep, ts);
+      team_sync(tm);
     }
-    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) keep[j] = keep[j] || (flag[j] && s[j] >= m * a.alpha);
+    for (int j = tm.tid; j < a.Kb; j += tm.nt) keep[j] = keep[j] || (flag[j] && s[j] >= m * a.alpha);
   } else if (a.rule == CA_RULE_TOPK) {
     // valid entries are a prefix for the block-causal case; in general count them
     int cnt = 0;
-    for (int j = threadIdx.x; j < a.Kb; j += kRowThreads) cnt += a.valid ? (a.valid[v_off + j * a.v_k] != 0) : (j <= diag);
-    __shared__ int sh_nvalid;
-    block_exclusive_scan(cnt, warp_sums, &sh_nvalid);
-    const int n_valid = sh_nvalid;
+    for (int j = tm.tid; j < a.Kb; j += tm.nt) cnt += a.valid ? (a.valid[v_off + j * a.v_k] != 0) : (j <= diag);
+    block_exclusive_scan(tm, cnt, ts->warp_sums, &ts->nvalid);
+    const int n_valid = ts->nvalid;
     int k = a.topk_k > 0 ? a.topk_k
                          : static_cast<int>((static_cast<long long>(a.topk_num) * n_valid + a.topk_den / 2) / a.topk_den);
     if (k < 1) k = 1;
     if (k > n_valid) k = n_valid;
     // invalid entries are -inf and sort last, so taking k <= n_valid never reaches them
-    if (k > 0) topk_mark(s, a.Kb, k, keep, hist, warp_sums);
+    if (k > 0) topk_mark(tm, s, a.Kb, k, keep, ts);
   } else if (a.rule == CA_RULE_CUMMASS) {
     int n2 = 1;
     while (n2 < a.Kb) n2 <<= 1;
-    for (int j = threadIdx.x; j < n2; j += kRowThreads) {
+    for (int j = tm.tid; j < n2; j += tm.nt) {
       // descending by value, ascending by index; invalid (-inf) and padding sort last
       const uint32_t key = j < a.Kb ? order_key(s[j] == -INFINITY ? -1.0f : s[j]) : 0u;
       comp[j] = (static_cast<unsigned long long>(~key) << 32) | static_cast<uint32_t>(j);
     }
-    __syncthreads();
-    bitonic_sort(comp, n2);
-    if (threadIdx.x == 0) {
+    team_sync(tm);
+    bitonic_sort(tm, comp, n2);
+    if (tm.tid == 0) {
       // sequential fp32 prefix sum in sorted order; keep the shortest prefix with mass >= tau
       float acc = 0.f;
       int cut = a.Kb;
@@ -377,20 +391,20 @@ __global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs 
           break;
         }
       }
-      sh_cut = cut;
+      ts->cut = cut;
     }
-    __syncthreads();
-    const int cut = sh_cut;
-    for (int r = threadIdx.x; r < cut; r += kRowThreads) {
+    team_sync(tm);
+    const int cut = ts->cut;
+    for (int r = tm.tid; r < cut; r += tm.nt) {
       const int j = static_cast<int>(comp[r] & 0xffffffffu);
       keep[j] = s[j] != -INFINITY;
     }
   }
-  __syncthreads();
+  team_sync(tm);
 
   // ---- forced blocks, validity, bit packing ----
-  for (int base = 0; base < a.W * 32; base += kRowThreads) {
-    const int j = base + threadIdx.x;
+  for (int base = 0; base < a.W * 32; base += tm.nt) {
+    const int j = base + tm.tid;
     bool k = false;
     if (j < a.Kb) {
       const bool ok = a.valid ? (a.valid[v_off + j * a.v_k] != 0) : (j <= diag);
@@ -399,16 +413,29 @@ __global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs 
       k = (keep[j] || forced) && ok;
     }
     const uint32_t word = __ballot_sync(0xffffffffu, k);
-    if ((threadIdx.x & 31) == 0 && (j >> 5) < a.W) {
+    if ((tm.tid & 31) == 0 && (j >> 5) < a.W) {
       if (bits_row) bits_row[j >> 5] = word;
       if (a.fuse && word) atomicOr(&a.union_words[static_cast<long long>(kv_row) * a.W + (j >> 5)], word);
     }
   }
-  }  // voting
+  }
+}
+
+__global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  __shared__ TeamShared ts;
+  __shared__ int sh_last;
+  const Team tm{static_cast<int>(threadIdx.x), kRowThreads, 0};
+  const int i = blockIdx.x % a.Qb;
+  const int h = (blockIdx.x / a.Qb) % a.H;
+  const int b = blockIdx.x / (a.Qb * a.H);
+  select_row(a, tm, &ts, dyn_smem, b, h, i, false);
   if (!a.fuse) return;
+  const int kv_row = b * (a.H / a.G) + h / a.G;
   // ---- fused Block-Union: the last row CTA of this KV-head row builds the table.  Nobody waits: a CTA
   // publishes its words, takes a ticket and leaves unless the ticket is the last one. ----
-  __shared__ int sh_last;
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -426,9 +453,143 @@ __global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs 
   }
   if (threadIdx.x == 0) a.tickets[kv_row] = 0u;
   __syncthreads();
-  compact_row(words, a.W, a.Kb, a.Pb, a.Qb, a.keep_recent, a.block_size, a.page_size,
+  compact_row(tm, words, a.W, a.Kb, a.Pb, a.Qb, a.keep_recent, a.block_size, a.page_size,
               a.block_idx + static_cast<long long>(kv_row) * a.idx_stride, a.idx_stride, kv_row, a.counts, a.cache_seqlens,
-              a.pages_per_row, nullptr, warp_sums, &sh_cut);
+              a.pages_per_row, nullptr, ts.warp_sums, &ts.cut);
+}
+
+// ------------------------------------------------------------------------------------------
+// Gate scores + row rule + Block-Union + table in ONE launch.
+// One CTA per (batch, KV head, Q-block): G teams of 128 threads, one per query head of the KV head.  All
+// threads first compute the G rows of gate logits against the KV head's key-block cache - a thread owns a key
+// block, fetches its 128 channels with sixteen 128-bit loads issued back to back and accumulates the G dot
+// products in the channel order of gate_scores3_kernel, so the logits equal the stand-alone kernel's bit for
+// bit - straight into the rows' shared memory.  Then every team runs the rule on its row (select_row), ORs its
+// bits into the KV-head row's words, and the CTA takes ONE ticket; the CTA with the last ticket of a KV-head
+// row compacts it.  The 4 MB of logits (128K context) never travel to memory and back, three launches
+// become one, and the key-block cache is read once per Q-block from L2.
+struct GateSelArgs {
+  RowArgs row;  // row.score is unused
+  const void* q;  // [B,Qb,Hq,128] by strides
+  long long q_b, q_blk, q_h;
+  int q_dtype;
+  const void* k;  // [B,Kb,Hkv,128] by strides, 16-bit
+  long long k_b, k_blk, k_h;
+  float scale, masked_value;
+  float* score_out;  // optional [B,Hq,Qb,Kb] contiguous: the logits as gate_scores writes them
+  int row_bytes;     // shared memory per row
+};
+
+constexpr int kFusedTeam = 128;
+
+__device__ __forceinline__ void widen8_16(const uint4& raw, int dtype, float (&v)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (dtype == CA_DTYPE_BF16) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    } else {
+      const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+      v[2 * i] = __low2float(h);
+      v[2 * i + 1] = __high2float(h);
+    }
+  }
+}
+
+template <int KDT, int G>
+__global__ void __launch_bounds__(G* kFusedTeam) gate_select_kernel(const GateSelArgs a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  __shared__ TeamShared ts[G];
+  __shared__ int sh_last;
+  constexpr int T = G * kFusedTeam;
+  const RowArgs& r = a.row;
+  const int tid = threadIdx.x;
+  const int Hkv = r.H / G;
+  const int i = blockIdx.x % r.Qb;
+  const int hk = (blockIdx.x / r.Qb) % Hkv;
+  const int b = blockIdx.x / (r.Qb * Hkv);
+  float* qs = reinterpret_cast<float*>(dyn_smem);  // [G][128]
+  unsigned char* rows = dyn_smem + G * 128 * sizeof(float);
+  for (int e = tid; e < G * 128; e += T) {
+    const int g = e >> 7, c = e & 127;
+    qs[e] = load_score(a.q, b * a.q_b + i * a.q_blk + static_cast<long long>(hk * G + g) * a.q_h + c, a.q_dtype);
+  }
+  __syncthreads();
+  const int diag = r.Pb + i;
+  const int jmax = r.valid ? r.Kb - 1 : diag;  // with an explicit validity mask every column may count
+  for (int j = tid; j <= jmax; j += T) {
+    const uint16_t* kp = reinterpret_cast<const uint16_t*>(a.k) + b * a.k_b + static_cast<long long>(j) * a.k_blk + hk * a.k_h;
+    uint4 raw[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u) raw[u] = __ldg(reinterpret_cast<const uint4*>(kp + u * 8));
+    float acc[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) acc[g] = 0.f;
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      float kv[8];
+      widen8_16(raw[u], KDT, kv);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float4 q0 = *reinterpret_cast<const float4*>(&qs[g * 128 + u * 8]);
+        const float4 q1 = *reinterpret_cast<const float4*>(&qs[g * 128 + u * 8 + 4]);
+        acc[g] = fmaf(q0.x, kv[0], acc[g]);
+        acc[g] = fmaf(q0.y, kv[1], acc[g]);
+        acc[g] = fmaf(q0.z, kv[2], acc[g]);
+        acc[g] = fmaf(q0.w, kv[3], acc[g]);
+        acc[g] = fmaf(q1.x, kv[4], acc[g]);
+        acc[g] = fmaf(q1.y, kv[5], acc[g]);
+        acc[g] = fmaf(q1.z, kv[6], acc[g]);
+        acc[g] = fmaf(q1.w, kv[7], acc[g]);
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float v = j <= diag ? acc[g] * a.scale : a.masked_value;
+      reinterpret_cast<float*>(rows + static_cast<size_t>(g) * a.row_bytes)[j] = v;
+      if (a.score_out) a.score_out[((static_cast<long long>(b) * r.H + hk * G + g) * r.Qb + i) * r.Kb + j] = v;
+    }
+  }
+  if (a.score_out) {
+    for (int e = tid; e < G * (r.Kb - 1 - jmax); e += T) {
+      const int g = e / (r.Kb - 1 - jmax), j = jmax + 1 + e % (r.Kb - 1 - jmax);
+      a.score_out[((static_cast<long long>(b) * r.H + hk * G + g) * r.Qb + i) * r.Kb + j] = a.masked_value;
+    }
+  }
+  __syncthreads();
+  {
+    const int g = tid / kFusedTeam;
+    const Team tm{tid % kFusedTeam, kFusedTeam, 1 + g};
+    select_row(r, tm, &ts[g], rows + static_cast<size_t>(g) * a.row_bytes, b, hk * G + g, i, true);
+  }
+  // ---- Block-Union: one ticket per CTA; the last CTA of the KV-head row builds its table ----
+  const int kv_row = b * Hkv + hk;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned int ticket = atomicAdd(&r.tickets[kv_row], 1u);
+    sh_last = ticket == static_cast<unsigned int>(r.Qb - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!sh_last) return;
+  __threadfence();
+  constexpr int kTail = T < kRowThreads ? T : kRowThreads;
+  if (tid >= kTail) return;
+  const Team tm{tid, kTail, 1};
+  uint32_t* words = reinterpret_cast<uint32_t*>(rows);  // the rows' scratch is free now
+  uint32_t* gw = r.union_words + static_cast<long long>(kv_row) * r.W;
+  for (int w = tid; w < r.W; w += kTail) {
+    words[w] = __ldcg(&gw[w]);
+    gw[w] = 0u;  // left clean for the next call
+  }
+  if (tid == 0) r.tickets[kv_row] = 0u;
+  team_sync(tm);
+  compact_row(tm, words, r.W, r.Kb, r.Pb, r.Qb, r.keep_recent, r.block_size, r.page_size,
+              r.block_idx + static_cast<long long>(kv_row) * r.idx_stride, r.idx_stride, kv_row, r.counts, r.cache_seqlens,
+              r.pages_per_row, nullptr, ts[0].warp_sums, &ts[0].cut);
 }
 
 struct UnionArgs {
@@ -476,7 +637,8 @@ __global__ void __launch_bounds__(kRowThreads) union_table_kernel(const UnionArg
     if (word) atomicOr(&words[w], word);
   }
   __syncthreads();
-  compact_row(words, a.W, a.Kb, a.Pb, a.Qb, a.keep_recent, a.block_size, a.page_size, idx_row, a.idx_stride, row, a.counts,
+  const Team tm{static_cast<int>(threadIdx.x), kRowThreads, 0};
+  compact_row(tm, words, a.W, a.Kb, a.Pb, a.Qb, a.keep_recent, a.block_size, a.page_size, idx_row, a.idx_stride, row, a.counts,
               a.cache_seqlens, a.pages_per_row, a.keep_kv ? a.keep_kv + static_cast<long long>(row) * a.Kb : nullptr, warp_sums,
               &sh_total);
 }
@@ -491,10 +653,11 @@ __global__ void __launch_bounds__(kRowThreads) paged_metadata_kernel(const int32
   __shared__ int warp_sums[kRowThreads / 32];
   __shared__ int sh_total;
   int running = 0;
+  const Team tm{static_cast<int>(threadIdx.x), kRowThreads, 0};
   for (int base = 0; base < R; base += kRowThreads) {
     const int r = base + threadIdx.x;
     const int v = r < R ? pages_per_row[r] : 0;
-    const int off = running + block_exclusive_scan(v, warp_sums, &sh_total);
+    const int off = running + block_exclusive_scan(tm, v, warp_sums, &sh_total);
     if (r < R) page_offsets[r] = off;
     running += sh_total;
     __syncthreads();
@@ -511,6 +674,26 @@ __global__ void __launch_bounds__(kRowThreads) paged_metadata_kernel(const int32
 
 }  // namespace select
 }  // namespace ca
+
+namespace {
+template <int KDT, int G>
+int launch_gate_select(const ca::select::GateSelArgs& a, size_t smem, int ctas, int device, cudaStream_t stream) {
+  using namespace ca;
+  using namespace ca::select;
+  static std::mutex mu;
+  static bool done[64] = {};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done[device]) {
+      CA_CUDA(cudaFuncSetAttribute(gate_select_kernel<KDT, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      done[device] = true;
+    }
+  }
+  launch_kernel(gate_select_kernel<KDT, G>, dim3(ctas), dim3(G * kFusedTeam), smem, stream, a);
+  CA_LAUNCH_CHECK("gate_select_kernel");
+  return CA_OK;
+}
+}  // namespace
 
 extern "C" {
 
@@ -599,8 +782,9 @@ int ca_select_union_scratch_bytes(int B, int Hkv, int Kb, size_t* bytes_out) {
   return CA_OK;
 }
 
-int ca_select_union_table(const ca_select_params* p, const ca_union_params* u, void* scratch, size_t scratch_bytes,
-                          ca_stream_t stream_) {
+// The fused rule + union + table request: validates both halves and fills the row kernel's arguments.
+static int fill_fused_args(const ca_select_params* p, const ca_union_params* u, void* scratch, size_t scratch_bytes,
+                           ca::select::RowArgs* out, size_t* smem_out) {
   using namespace ca;
   using namespace ca::select;
   RowArgs a;
@@ -628,9 +812,69 @@ int ca_select_union_table(const ca_select_params* p, const ca_union_params* u, v
   a.tickets = a.union_words + static_cast<size_t>(u->B) * u->Hkv * a.W;
   a.keep_recent = u->keep_recent, a.block_size = u->block_size, a.page_size = u->page_size, a.idx_stride = u->idx_stride;
   a.block_idx = u->block_idx, a.counts = u->counts, a.cache_seqlens = u->cache_seqlens, a.pages_per_row = u->pages_per_row;
+  *out = a;
+  *smem_out = smem;
+  return CA_OK;
+}
+
+int ca_select_union_table(const ca_select_params* p, const ca_union_params* u, void* scratch, size_t scratch_bytes,
+                          ca_stream_t stream_) {
+  using namespace ca;
+  using namespace ca::select;
+  RowArgs a;
+  size_t smem = 0;
+  int rc = fill_fused_args(p, u, scratch, scratch_bytes, &a, &smem);
+  if (rc != CA_OK) return rc;
   launch_kernel(select_rows_kernel, dim3(p->B * p->H * p->Qb), dim3(kRowThreads), smem, static_cast<cudaStream_t>(stream_), a);
   CA_LAUNCH_CHECK("select_rows_kernel");
   return CA_OK;
+}
+
+
+int ca_gate_score_select(const ca_gate_score_params* g, const ca_select_params* p, const ca_union_params* u, void* scratch,
+                         size_t scratch_bytes, int write_scores, ca_stream_t stream_) {
+  using namespace ca;
+  using namespace ca::select;
+  CA_REQUIRE(g != nullptr && p != nullptr && u != nullptr, "params are null");
+  CA_REQUIRE(g->q && g->k && g->out, "q, k and the score buffer must be non-null");
+  CA_REQUIRE(p->score == g->out && p->score_dtype == CA_DTYPE_F32 && p->score_stride_k == 1 && p->score_stride_q == g->Kb &&
+                 p->score_stride_h == static_cast<int64_t>(g->Qb) * g->Kb && p->score_stride_b == p->score_stride_h * g->Hq,
+             "the selection must read the gate's contiguous fp32 score buffer");
+  CA_REQUIRE(p->B == g->B && p->H == g->Hq && p->Qb == g->Qb && p->Kb == g->Kb && p->Pb == g->Pb, "scores and selection disagree on sizes");
+  RowArgs a;
+  size_t row_smem = 0;
+  int rc = fill_fused_args(p, u, scratch, scratch_bytes, &a, &row_smem);
+  if (rc != CA_OK) return rc;
+  const int G = u->G;
+  const bool k16 = g->k_dtype == CA_DTYPE_BF16 || g->k_dtype == CA_DTYPE_F16;
+  const size_t smem = static_cast<size_t>(G) * 128 * sizeof(float) + static_cast<size_t>(G) * row_smem;
+  const bool fused = g->C == 128 && k16 && g->Hk == u->Hkv && (G == 1 || G == 2 || G == 4) && p->rule != CA_RULE_MASK &&
+                     smem <= 200 * 1024 && g->k_stride_blk % 8 == 0 && g->k_stride_h % 8 == 0 && g->k_stride_b % 8 == 0 &&
+                     reinterpret_cast<uintptr_t>(g->k) % 16 == 0;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!fused) {
+    // shapes the one-launch form does not cover: the two kernels it stands for
+    rc = ca_gate_scores(g, stream_);
+    if (rc != CA_OK) return rc;
+    launch_kernel(select_rows_kernel, dim3(p->B * p->H * p->Qb), dim3(kRowThreads), row_smem, stream, a);
+    CA_LAUNCH_CHECK("select_rows_kernel");
+    return CA_OK;
+  }
+  DeviceInfo dev;
+  rc = get_device_info(&dev);
+  if (rc != CA_OK) return rc;
+  GateSelArgs ga;
+  ga.row = a;
+  ga.q = g->q, ga.q_b = g->q_stride_b, ga.q_blk = g->q_stride_blk, ga.q_h = g->q_stride_h, ga.q_dtype = g->q_dtype;
+  ga.k = g->k, ga.k_b = g->k_stride_b, ga.k_blk = g->k_stride_blk, ga.k_h = g->k_stride_h;
+  ga.scale = g->scale, ga.masked_value = g->masked_value;
+  ga.score_out = write_scores ? g->out : nullptr;
+  ga.row_bytes = static_cast<int>(row_smem);
+  const int ctas = p->B * u->Hkv * p->Qb;
+  const bool bf = g->k_dtype == CA_DTYPE_BF16;
+  if (G == 1) return bf ? launch_gate_select<CA_DTYPE_BF16, 1>(ga, smem, ctas, dev.ordinal, stream) : launch_gate_select<CA_DTYPE_F16, 1>(ga, smem, ctas, dev.ordinal, stream);
+  if (G == 2) return bf ? launch_gate_select<CA_DTYPE_BF16, 2>(ga, smem, ctas, dev.ordinal, stream) : launch_gate_select<CA_DTYPE_F16, 2>(ga, smem, ctas, dev.ordinal, stream);
+  return bf ? launch_gate_select<CA_DTYPE_BF16, 4>(ga, smem, ctas, dev.ordinal, stream) : launch_gate_select<CA_DTYPE_F16, 4>(ga, smem, ctas, dev.ordinal, stream);
 }
 
 int ca_union_table(const ca_union_params* p, ca_stream_t stream_) {

@@ -361,6 +361,7 @@ def select_union_table(
     prob_out: Optional[torch.Tensor] = None,
     out: Optional["BlockTable"] = None,
     scratch: Optional[torch.Tensor] = None,
+    _gate=None,  # (GateScoreParams writing `score`, write_scores): set by gate_score_select
 ) -> "BlockTable":
     """``select_rows`` followed by ``union_table`` in ONE launch (see ``ca_select_union_table``): row rule,
     Q-block union, GQA union and the per-KV-head block table.  ``scratch`` must be zero on first use and
@@ -393,8 +394,12 @@ def select_union_table(
         scratch = union_scratch(dev, B, num_kv_heads, Kb)
     if scratch.dtype != torch.int32 or not scratch.is_contiguous():
         raise ValueError("scratch must be a contiguous int32 tensor (zero on first use)")
-    _lib.check(_lib.load().ca_select_union_table(C.byref(p), C.byref(u), scratch.data_ptr(), scratch.numel() * 4, _stream()),
-               "ca_select_union_table")
+    if _gate is not None:
+        _lib.check(_lib.load().ca_gate_score_select(C.byref(_gate[0]), C.byref(p), C.byref(u), scratch.data_ptr(), scratch.numel() * 4,
+                                                    1 if _gate[1] else 0, _stream()), "ca_gate_score_select")
+    else:
+        _lib.check(_lib.load().ca_select_union_table(C.byref(p), C.byref(u), scratch.data_ptr(), scratch.numel() * 4, _stream()),
+                   "ca_select_union_table")
     del keep
     return out
 
@@ -628,6 +633,12 @@ def gate_scores(
     out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Gate logits [B, Hq, Qb, Kb] float32; entries above the block diagonal get masked_value."""
+    p, out = _gate_score_params(q_blocks, k_blocks, past_blocks, scale, masked_value, out)
+    _lib.check(_lib.load().ca_gate_scores(C.byref(p), _stream()), "ca_gate_scores")
+    return out
+
+
+def _gate_score_params(q_blocks, k_blocks, past_blocks, scale, masked_value, out):
     _require_cuda(q_blocks, k_blocks, out)
     B, Qb, Hq, Cc = q_blocks.shape
     Kb, Hk = k_blocks.shape[1], k_blocks.shape[2]
@@ -645,8 +656,27 @@ def gate_scores(
     p.B, p.Hq, p.Hk, p.Qb, p.Kb, p.Pb, p.C = B, Hq, Hk, Qb, Kb, past_blocks, Cc
     p.scale = float(scale) if scale is not None else Cc ** -0.5
     p.masked_value = masked_value
-    _lib.check(_lib.load().ca_gate_scores(C.byref(p), _stream()), "ca_gate_scores")
-    return out
+    return p, out
+
+
+def gate_score_select(
+    q_blocks: torch.Tensor,  # [B, Qb, Hq, C]
+    k_blocks: torch.Tensor,  # [B, Kb, Hk, C] (a view of the K-block cache)
+    past_blocks: int,
+    rule: str,
+    *,
+    num_kv_heads: int,
+    scores: Optional[torch.Tensor] = None,  # [B, Hq, Qb, Kb] f32 buffer of the logits (allocated when missing)
+    write_scores: bool = False,
+    scale: Optional[float] = None,
+    masked_value: float = float(torch.finfo(torch.float32).min),
+    **select_kwargs,
+) -> "BlockTable":
+    """``gate_scores`` + ``select_union_table`` in ONE launch where the shape allows (see ``ca_gate_score_select``),
+    else as the two launches.  ``scores`` receives the logits only when ``write_scores`` (or when the two-launch
+    form runs).  ``select_kwargs`` are those of ``select_union_table``."""
+    g, scores = _gate_score_params(q_blocks, k_blocks, past_blocks, scale, masked_value, scores)
+    return select_union_table(scores, past_blocks, rule, num_kv_heads=num_kv_heads, _gate=(g, bool(write_scores)), **select_kwargs)
 
 
 def flashprefill_score(

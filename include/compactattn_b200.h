@@ -127,7 +127,12 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream);
  * banned, and which therefore cannot obtain the workspace that lets the kernel cut work units
  * across SMs.)  The partial accumulators live in a buffer built into the library instead:
  * 41.6 MiB of device memory per GPU that loads the library, enough for a device of up to 160 SMs;
- * a larger device is refused with CA_ERR_CAPACITY.  p->workspace and p->workspace_bytes are
+ * a larger device is refused with CA_ERR_CAPACITY.  The buffer is part of the library's device
+ * module: it is reserved on every GPU on which any entry point of the library has run, for every
+ * user of the library whether or not this entry point is ever called, and it is reserved when the
+ * module is loaded on that GPU - so a host that gives the rest of HBM to its own pool must make its
+ * first call into the library on that GPU (any entry point) BEFORE it does so, or the module load
+ * fails for lack of memory.  p->workspace and p->workspace_bytes are
  * ignored; inputs and outputs are still the caller's.  Nothing is allocated or freed by this
  * call.  The first call on a device looks up the buffer's device address (one runtime query, no
  * allocation), so make that first call outside any stream capture.  All calls on a device share
@@ -367,6 +372,23 @@ typedef struct ca_gate_score_params {
 int ca_gate_scores(const ca_gate_score_params* p, ca_stream_t stream);
 
 /*
+ * Gate scores, row rule, Block-Union and block table in ONE launch: the result of ca_gate_scores(score)
+ * followed by ca_select_union_table(sel, un, scratch) with sel->score == score->out (the gate's contiguous fp32
+ * buffer), for the learned gate's usual shape - 128 gate channels, a 16-bit key-block cache with one head per KV
+ * head (score->Hk == un->Hkv), 1, 2 or 4 query heads per KV head, any rule but CA_RULE_MASK.  One CTA per
+ * (batch, KV head, Q-block) computes its query heads' rows of logits into shared memory (bit-identical to
+ * ca_gate_scores), applies the rule to each, ORs the rows into the KV head's union words and takes a ticket; the
+ * last CTA of a KV head compacts the table.  The logits are written to score->out only when write_scores != 0
+ * (tests, callers that log them).  Any other shape runs the two launches it stands for (score->out is then
+ * always written).  Same reference lines as ca_gate_scores and ca_select_union_table; replaces the chain
+ * AttnGate.score_compressed_blocks -> keep-mask builders -> index builders
+ * (compact_attn/prefill_sparse/attn_gate.py:173-204, compact_attn/modules/attention_forward_chunked_dense.py:352-403,
+ * 641-683, compact_attn/csrc/compactattn/cache_fill_kernel.cu:275-385).
+ */
+int ca_gate_score_select(const ca_gate_score_params* score, const ca_select_params* sel, const ca_union_params* un, void* scratch,
+                         size_t scratch_bytes, int write_scores, ca_stream_t stream);
+
+/*
  * Training-free block score.  For q-block i, head h, key block j over the tokens t of the q-block
  * with P + t >= (j+1)*bs - 1:  S = (q_t . mean_k_j) * D^-0.5 * log2(e),  max_raw = max_t S,
  * score_raw = sum_t 2^(S - max_raw)  (-inf where no token qualifies); all [B,Qb,Kb,Hq] f32.
@@ -539,6 +561,9 @@ int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream);
  *   fp_score ca_flashprefill_score   training-free block scores                            [fp_score.q]
  *   select + table  ca_select_union_table (one launch) when union_scratch is given, else
  *            ca_select_rows then ca_union_table                                            [select.score]
+ *            (score + select + table are ONE launch, ca_gate_score_select, when the score stage is present,
+ *            union_scratch is given and select.score == score.out; the logits are then not written
+ *            unless write_scores is set)
  *   attn     ca_attn_compact                                                               [attn.q]
  * It stands where the reference runs its per-layer Python between the KV-cache update and o_proj:
  * _compute_chunked_gate_from_cache, the keep-mask / index builders and the indexed attention call
@@ -557,6 +582,7 @@ typedef struct ca_chunk_step_params {
   void* union_scratch;
   size_t union_scratch_bytes;
   ca_attn_params attn;
+  int32_t write_scores; /* keep the gate logits in score.out even when the fused score + select launch runs */
 } ca_chunk_step_params;
 
 int ca_chunk_step(const ca_chunk_step_params* p, ca_stream_t stream);

@@ -236,3 +236,51 @@ def test_fused_select_union_contract_errors(ops):
     small = torch.zeros(4, dtype=torch.int32, device="cuda")
     with pytest.raises(RuntimeError, match="scratch holds"):
         ops.select_union_table(score, 60, "topk", num_kv_heads=2, topk_k=4, scratch=small)
+
+
+@pytest.mark.parametrize("rule,kw", [
+    ("topk", dict(topk_ratio=(1, 5), sink=1, local=2)),
+    ("threshold", dict(softmax=True, threshold=2e-3, keep_recent=2)),
+    ("alpha_rowmax", dict(alpha=0.3, sink=2, local=4, rows_voting=3, min_budget=3)),
+    ("cummass", dict(softmax=True, threshold=0.8, sink=1, local=1)),
+])
+@pytest.mark.parametrize("B,Hkv,G,Qb,Kb,C,kdt", [
+    (1, 8, 4, 16, 2048, 128, torch.bfloat16),   # the headline shape: one launch
+    (2, 2, 2, 3, 37, 128, torch.float16),       # one launch, two heads per KV head, ragged word count
+    (1, 3, 1, 1, 5, 128, torch.bfloat16),       # one launch, one head per KV head, a single Q-block
+    (1, 1, 4, 16, 600, 128, torch.bfloat16),    # a tensor-parallel rank with one KV head
+    (1, 2, 8, 2, 70, 128, torch.bfloat16),      # eight heads per KV head: the two-launch form behind the same call
+    (1, 2, 4, 2, 70, 64, torch.float32),        # 64 channels, fp32 cache: two launches
+])
+def test_gate_score_select_equals_scores_then_selection(ops, rule, kw, B, Hkv, G, Qb, Kb, C, kdt):
+    """Gate logits + row rule + Block-Union + table behind one call against ca_gate_scores followed by
+    ca_select_union_table: the logits (when asked for) and every table output bit for bit, on three calls in a
+    row (scratch left clean), and the logits buffer untouched when they are not asked for."""
+    Pb, Hq = Kb - Qb, Hkv * G
+    kw = dict(kw)
+    keep_recent = kw.pop("keep_recent", 0)
+    if "rows_voting" in kw:
+        kw["rows_voting"] = min(kw["rows_voting"], Qb)
+    g = torch.Generator().manual_seed(Kb * 11 + Qb + G)
+    import compactattention_b200._lib as L
+    for call in range(3):
+        qb = torch.randn((B, Qb, Hq, C), generator=g).cuda()
+        kb = torch.randn((B, Kb, Hkv, C), generator=g).to(kdt).cuda()
+        logits = ops.gate_scores(qb, kb, Pb)
+        want = ops.select_union_table(logits, Pb, rule, num_kv_heads=Hkv, block_size=64, keep_recent=keep_recent, **kw)
+        write = call != 1
+        got_scores = torch.full_like(logits, 7.0)
+        n0 = L.launch_count()
+        got = ops.gate_score_select(qb, kb, Pb, rule, num_kv_heads=Hkv, scores=got_scores, write_scores=write, block_size=64,
+                                    keep_recent=keep_recent, **kw)
+        launches = L.launch_count() - n0
+        one_launch = C == 128 and kdt != torch.float32 and G in (1, 2, 4)
+        assert launches == (1 if one_launch else 2)
+        for name in ("block_idx", "counts", "cache_seqlens", "pages_per_row"):
+            assert torch.equal(getattr(got, name), getattr(want, name)), (name, call)
+        if write or not one_launch:
+            assert torch.equal(got_scores, logits), call
+        else:
+            assert bool((got_scores == 7.0).all())  # the logits stayed on chip
+    scratch = ops.union_scratch(torch.device("cuda", torch.cuda.current_device()), B, Hkv, Kb)
+    assert int(scratch.abs().sum().item()) == 0
