@@ -827,6 +827,7 @@ static bool dtype_ok(int dt) { return dt == CA_DTYPE_F32 || dt == CA_DTYPE_BF16 
 
 namespace ca {
 int launch_fp_score_sm100(const ca_flashprefill_score_params* p, cudaStream_t stream);  // ca_fpscore_sm100.cu
+int launch_gate_scores_tc(const ca_gate_score_params* g, cudaStream_t stream);            // ca_select.cu
 }
 
 extern "C" {
@@ -965,6 +966,11 @@ int ca_gate_scores(const ca_gate_score_params* p, ca_stream_t stream_) {
   const size_t smem = static_cast<size_t>(p->Qb) * p->C * sizeof(float);
   CA_REQUIRE(smem <= 160 * 1024, "Qb * C too large for the gate score kernel");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  {
+    // the learned gate's usual shape: the tensor-core form, the same arithmetic as the fused score + rule launch
+    const int rc_tc = launch_gate_scores_tc(p, stream);
+    if (rc_tc != CA_ERR_UNSUPPORTED) return rc_tc;
+  }
   if (p->C == 128 && p->Qb <= kGateRows && (p->k_dtype == CA_DTYPE_BF16 || p->k_dtype == CA_DTYPE_F16)) {
     const dim3 grid3(ceil_div(p->Kb, kGateThreads), p->Hq, p->B);
     const size_t smem3 = static_cast<size_t>(kGateRows) * 128 * sizeof(float);

@@ -11,6 +11,18 @@ namespace ca {
 namespace select {
 
 constexpr int kRowThreads = 256;
+
+#ifdef CA_SELECT_PROFILE
+// Development build: cycle stamps of one CTA's phases (thread 0 of team 0 of CTA 0).
+__device__ long long g_sel_prof[32];
+#define SEL_MARK(team_is_first, tid, k) \
+  if (blockIdx.x == 0 && (team_is_first) && (tid) == 0) g_sel_prof[k] = clock64();
+#define SEL_MARK_ANY(k) \
+  if (blockIdx.x == 0) g_sel_prof[k] = clock64();
+#else
+#define SEL_MARK(team_is_first, tid, k)
+#define SEL_MARK_ANY(k)
+#endif
 constexpr int kMaxKb = 8192;  // key blocks per row supported by the row kernels (512K tokens at bs 64)
 
 __device__ __forceinline__ float load_score(const void* base, long long off, int dtype) {
@@ -132,13 +144,26 @@ __device__ __forceinline__ float block_reduce_sum(const Team& tm, float v, float
 
 // Marks the k largest entries of s[0..n) (ties -> lower index) in keep[] (1 byte per entry).
 // Radix select over the monotone keys, 8 bits per pass, then an ordered pass for the ties.
-__device__ void topk_mark(const Team& tm, const float* s, int n, int k, uint8_t* keep, TeamShared* ts) {
+// EPT > 0: n <= EPT * tm.nt and every thread keeps its EPT keys in registers across the passes (the key is
+// computed once and a pass costs a compare, a shift and one shared-memory atomic per entry - the rule is bound
+// by instruction issue: 512 rows x 2048 entries x every instruction of the pass loops); EPT == 0: any n, keys
+// re-read from shared memory in every pass.
+template <int EPT>
+__device__ void topk_mark_impl(const Team& tm, const float* s, int n, int k, uint8_t* keep, TeamShared* ts) {
   int* hist = ts->hist;
   int* warp_sums = ts->warp_sums;
   if (k >= n) {
     for (int j = tm.tid; j < n; j += tm.nt) keep[j] = 1;
     team_sync(tm);
     return;
+  }
+  uint32_t key[EPT > 0 ? EPT : 1];
+  if (EPT > 0) {
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+      const int j = tm.tid + e * tm.nt;
+      key[e] = j < n ? order_key(s[j]) : 0u;
+    }
   }
   if (tm.tid == 0) {
     ts->prefix = 0;
@@ -150,9 +175,16 @@ __device__ void topk_mark(const Team& tm, const float* s, int n, int k, uint8_t*
     team_sync(tm);
     const uint32_t prefix = ts->prefix;
     const uint32_t mask_hi = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-    for (int j = tm.tid; j < n; j += tm.nt) {
-      const uint32_t key = order_key(s[j]);
-      if ((key & mask_hi) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
+    if (EPT > 0) {
+#pragma unroll
+      for (int e = 0; e < EPT; ++e) {
+        if (tm.tid + e * tm.nt < n && (key[e] & mask_hi) == prefix) atomicAdd(&hist[(key[e] >> shift) & 255u], 1);
+      }
+    } else {
+      for (int j = tm.tid; j < n; j += tm.nt) {
+        const uint32_t kj = order_key(s[j]);
+        if ((kj & mask_hi) == prefix) atomicAdd(&hist[(kj >> shift) & 255u], 1);
+      }
     }
     team_sync(tm);
     if (tm.tid < 32) {
@@ -189,7 +221,15 @@ __device__ void topk_mark(const Team& tm, const float* s, int n, int k, uint8_t*
   const int want_equal = ts->remaining;
   if (want_equal == ts->last_bin_count) {
     // every key equal to the k-th is wanted: no tie to break
-    for (int j = tm.tid; j < n; j += tm.nt) keep[j] = order_key(s[j]) >= kth;
+    if (EPT > 0) {
+#pragma unroll
+      for (int e = 0; e < EPT; ++e) {
+        const int j = tm.tid + e * tm.nt;
+        if (j < n) keep[j] = key[e] >= kth;
+      }
+    } else {
+      for (int j = tm.tid; j < n; j += tm.nt) keep[j] = order_key(s[j]) >= kth;
+    }
     team_sync(tm);
     return;
   }
@@ -197,12 +237,25 @@ __device__ void topk_mark(const Team& tm, const float* s, int n, int k, uint8_t*
   int taken = 0;
   for (int base = 0; base < n; base += tm.nt) {
     const int j = base + tm.tid;
-    const uint32_t key = j < n ? order_key(s[j]) : 0u;
-    const int eq = (j < n && key == kth) ? 1 : 0;
+    const uint32_t kj = j < n ? order_key(s[j]) : 0u;
+    const int eq = (j < n && kj == kth) ? 1 : 0;
     const int pos = block_exclusive_scan(tm, eq, warp_sums, &ts->total);
-    if (j < n) keep[j] = (key > kth) || (eq && (taken + pos) < want_equal);
+    if (j < n) keep[j] = (kj > kth) || (eq && (taken + pos) < want_equal);
     taken += ts->total;
     team_sync(tm);
+  }
+}
+
+__device__ void topk_mark(const Team& tm, const float* s, int n, int k, uint8_t* keep, TeamShared* ts) {
+  const int per_thread = (n + tm.nt - 1) / tm.nt;
+  if (per_thread <= 8) {
+    topk_mark_impl<8>(tm, s, n, k, keep, ts);
+  } else if (per_thread <= 16) {
+    topk_mark_impl<16>(tm, s, n, k, keep, ts);
+  } else if (per_thread <= 32) {
+    topk_mark_impl<32>(tm, s, n, k, keep, ts);
+  } else {
+    topk_mark_impl<0>(tm, s, n, k, keep, ts);
   }
 }
 
@@ -276,7 +329,7 @@ __device__ void compact_row(const Team& tm, uint32_t* words, int W, int Kb, int 
 // s[Kb] f32, keep[Kb], flag[Kb] and, for the cumulative-mass rule, the sort keys.  With `preloaded` the raw
 // scores of the row are already in s[] (the fused score + rule kernel) instead of in a.score.
 __device__ void select_row(const RowArgs& a, const Team& tm, TeamShared* ts, unsigned char* row_smem, int b, int h, int i,
-                           bool preloaded) {
+                           bool preloaded, uint32_t* cta_union = nullptr) {
   float* s = reinterpret_cast<float*>(row_smem);                     // [Kb]
   uint8_t* keep = reinterpret_cast<uint8_t*>(s + a.Kb);               // [Kb]
   uint8_t* flag = keep + a.Kb;                                        // [Kb] scratch flags
@@ -285,6 +338,7 @@ __device__ void select_row(const RowArgs& a, const Team& tm, TeamShared* ts, uns
   const int diag = a.Pb + i;  // last causally valid key block of this row
   uint32_t* bits_row = a.bits ? a.bits + ((static_cast<long long>(b) * a.H + h) * a.Qb + i) * a.W : nullptr;
   const int kv_row = a.fuse ? b * (a.H / a.G) + h / a.G : 0;
+  SEL_MARK(tm.bar <= 1, tm.tid, 4);
   const bool voting = i < a.rows_voting;
   if (!voting) {
     if (a.bits) for (int w = tm.tid; w < a.W; w += tm.nt) bits_row[w] = 0u;
@@ -333,6 +387,7 @@ __device__ void select_row(const RowArgs& a, const Team& tm, TeamShared* ts, uns
     for (int j = tm.tid; j < a.Kb; j += tm.nt) prow[j] = s[j] == -INFINITY ? 0.f : s[j];
   }
 
+  SEL_MARK(tm.bar <= 1, tm.tid, 5);
   // ---- the rule ----
   const float thr = a.threshold_ptr ? __ldg(a.threshold_ptr + b * a.threshold_stride) : a.threshold;
   if (a.rule == CA_RULE_THRESHOLD) {
@@ -402,8 +457,13 @@ __device__ void select_row(const RowArgs& a, const Team& tm, TeamShared* ts, uns
   }
   team_sync(tm);
 
+  SEL_MARK(tm.bar <= 1, tm.tid, 6);
   // ---- forced blocks, validity, bit packing ----
-  for (int base = 0; base < a.W * 32; base += tm.nt) {
+  // the rows of a KV head OR into the same words: each starts at another word, so they do not queue on one address
+  const int n_it = (a.W * 32 + tm.nt - 1) / tm.nt;
+  const int it0 = (h * a.Qb + i) % n_it;
+  for (int it = 0; it < n_it; ++it) {
+    const int base = ((it + it0) % n_it) * tm.nt;
     const int j = base + tm.tid;
     bool k = false;
     if (j < a.Kb) {
@@ -415,13 +475,18 @@ __device__ void select_row(const RowArgs& a, const Team& tm, TeamShared* ts, uns
     const uint32_t word = __ballot_sync(0xffffffffu, k);
     if ((tm.tid & 31) == 0 && (j >> 5) < a.W) {
       if (bits_row) bits_row[j >> 5] = word;
-      if (a.fuse && word) atomicOr(&a.union_words[static_cast<long long>(kv_row) * a.W + (j >> 5)], word);
+      // fused union: into the CTA's own words when several rows of the KV head share the CTA (one global
+      // atomic per word and CTA afterwards), else straight into the KV-head row's words in global memory
+      if (a.fuse && word) {
+        if (cta_union) atomicOr(&cta_union[j >> 5], word);
+        else atomicOr(&a.union_words[static_cast<long long>(kv_row) * a.W + (j >> 5)], word);
+      }
     }
   }
   }
 }
 
-__global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs a) {
+__global__ void __launch_bounds__(kRowThreads, 4) select_rows_kernel(const RowArgs a) {
   ptx::grid_launch_dependents();
   ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   extern __shared__ __align__(16) unsigned char dyn_smem[];
@@ -458,138 +523,176 @@ __global__ void __launch_bounds__(kRowThreads) select_rows_kernel(const RowArgs 
               a.pages_per_row, nullptr, ts.warp_sums, &ts.cut);
 }
 
-// ------------------------------------------------------------------------------------------
-// Gate scores + row rule + Block-Union + table in ONE launch.
-// One CTA per (batch, KV head, Q-block): G teams of 128 threads, one per query head of the KV head.  All
-// threads first compute the G rows of gate logits against the KV head's key-block cache - a thread owns a key
-// block, fetches its 128 channels with sixteen 128-bit loads issued back to back and accumulates the G dot
-// products in the channel order of gate_scores3_kernel, so the logits equal the stand-alone kernel's bit for
-// bit - straight into the rows' shared memory.  Then every team runs the rule on its row (select_row), ORs its
-// bits into the KV-head row's words, and the CTA takes ONE ticket; the CTA with the last ticket of a KV-head
-// row compacts it.  The 4 MB of logits (128K context) never travel to memory and back, three launches
-// become one, and the key-block cache is read once per Q-block from L2.
-struct GateSelArgs {
-  RowArgs row;  // row.score is unused
-  const void* q;  // [B,Qb,Hq,128] by strides
-  long long q_b, q_blk, q_h;
-  int q_dtype;
-  const void* k;  // [B,Kb,Hkv,128] by strides, 16-bit
-  long long k_b, k_blk, k_h;
-  float scale, masked_value;
-  float* score_out;  // optional [B,Hq,Qb,Kb] contiguous: the logits as gate_scores writes them
-  int row_bytes;     // shared memory per row
-};
+constexpr int kGsTileKeys = 128;
+constexpr int kGsHalfBytes = kGsTileKeys * 128;  // [128 key blocks][64 x 16-bit], 128-byte swizzle
+constexpr int kGsTileBytes = 2 * kGsHalfBytes;
 
-constexpr int kFusedTeam = 128;
-
-__device__ __forceinline__ void widen8_16(const uint4& raw, int dtype, float (&v)[8]) {
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    if (dtype == CA_DTYPE_BF16) {
-      v[2 * i] = __uint_as_float(w[i] << 16);
-      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    } else {
-      const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
-      v[2 * i] = __low2float(h);
-      v[2 * i + 1] = __high2float(h);
-    }
+__device__ __forceinline__ uint16_t to16(float x, int dtype) {
+  if (dtype == CA_DTYPE_BF16) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(x);
+    return *reinterpret_cast<const uint16_t*>(&h);
   }
+  const __half h = __float2half_rn(x);
+  return *reinterpret_cast<const uint16_t*>(&h);
+}
+__device__ __forceinline__ float from16(uint16_t v, int dtype) {
+  if (dtype == CA_DTYPE_BF16) return __uint_as_float(static_cast<uint32_t>(v) << 16);
+  return __half2float(*reinterpret_cast<const __half*>(&v));
 }
 
-template <int KDT, int G>
-__global__ void __launch_bounds__(G* kFusedTeam) gate_select_kernel(const GateSelArgs a) {
+// ------------------------------------------------------------------------------------------
+// Gate logits of a whole chunk on the tensor core, every key block read once.
+// One CTA per (key tile of 128 blocks, cache head, batch): D[128 key blocks][N] = K_tile . Q^T with the N
+// columns holding ALL Q-blocks and query heads of the cache head - first their values rounded to the cache's
+// 16-bit type, then the rounding remainders (hi + lo restores the f32 query to 2^-16) - so N = 2 * Qb * G
+// (128 for 16 Q-blocks of 4 heads).  Eight tcgen05.mma (M 128, K 16 each) per CTA; the key blocks are the
+// TMEM lanes, a thread of the four collecting warps owns one and writes its logits row by row, 32 lanes to
+// 128 consecutive bytes.
+// Measured and dropped: (1) CUDA-core forms (a thread, or a half-warp with packed f32x2 FMAs and a halving
+// shuffle reduction, per key block): 27 600 - 50 000 cycles per CTA of four rows, bound first by the L1 tag
+// stage (128-bit loads 256 bytes apart across a warp), then by issue slots.  (2) One launch for scores + rule +
+// table, a CTA per (KV head, Q-block) with N = 16 columns and the rule run by teams of the same CTA: correct
+// and bit-identical, but every Q-block re-reads the head's cache from L2 (TMA delivered a 32 KB tile per
+// 1 100 - 1 400 cycles) and eight N = 16 MMAs took as long again: 41 us against 47 us for the two launches it
+// replaced, while this kernel reads every key block once.
+struct GateTcArgs {
+  const void* q;  // [B,Qb,Hq,128] by strides
+  long long q_b, q_blk, q_h;
+  int q_dtype, k_dtype;
+  float* out;     // [B,Hq,Qb,Kb] contiguous
+  int B, Hq, Hk, G, Qb, Kb, Pb;
+  int n_cols;     // 2 * Qb * G rounded up to 16
+  float scale, masked_value;
+  uint32_t idesc;
+  unsigned long long wait_limit_ns;
+};
+
+struct GateTcShared {
+  uint64_t k_full, t_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(160, 1) gate_scores_tc_kernel(const __grid_constant__ CUtensorMap k_map, const GateTcArgs a) {
   ptx::grid_launch_dependents();
   ptx::grid_dependency_wait();  // nothing in global memory is touched before this
-  extern __shared__ __align__(16) unsigned char dyn_smem[];
-  __shared__ TeamShared ts[G];
-  __shared__ int sh_last;
-  constexpr int T = G * kFusedTeam;
-  const RowArgs& r = a.row;
-  const int tid = threadIdx.x;
-  const int Hkv = r.H / G;
-  const int i = blockIdx.x % r.Qb;
-  const int hk = (blockIdx.x / r.Qb) % Hkv;
-  const int b = blockIdx.x / (r.Qb * Hkv);
-  float* qs = reinterpret_cast<float*>(dyn_smem);  // [G][128]
-  unsigned char* rows = dyn_smem + G * 128 * sizeof(float);
-  for (int e = tid; e < G * 128; e += T) {
-    const int g = e >> 7, c = e & 127;
-    qs[e] = load_score(a.q, b * a.q_b + i * a.q_blk + static_cast<long long>(hk * G + g) * a.q_h + c, a.q_dtype);
+  extern __shared__ uint8_t gt_smem_raw[];
+  __shared__ GateTcShared sh;
+  const uint32_t smem_base = (ptx::smem_u32(gt_smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_aligned = gt_smem_raw + (smem_base - ptx::smem_u32(gt_smem_raw));
+  // layout: K tile (two swizzled halves) | Q tile (two swizzled halves of n_cols rows)
+  const uint32_t k_smem = smem_base;
+  uint8_t* q_tile = smem_aligned + kGsTileBytes;
+  const uint32_t q_smem = smem_base + kGsTileBytes;
+  const uint32_t q_half_bytes = static_cast<uint32_t>(a.n_cols) * 128u;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  volatile int* abort_flag = &sh.abort_flag;
+  const int n_rows = a.Qb * a.G;  // query rows of this cache head: row = i * G + g
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < static_cast<uint32_t>(a.n_cols)) tmem_cols <<= 1;
+
+  if (tid == 0) {
+    ptx::mbar_init(ptx::smem_u32(&sh.k_full), 1);
+    ptx::mbar_init(ptx::smem_u32(&sh.t_full), 1);
+    sh.abort_flag = 0;
+    ptx::mbar_fence_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 4) {
+    ptx::tmem_alloc(ptx::smem_u32(&sh.tmem_base), tmem_cols);
+    ptx::tmem_relinquish();
   }
   __syncthreads();
-  const int diag = r.Pb + i;
-  const int jmax = r.valid ? r.Kb - 1 : diag;  // with an explicit validity mask every column may count
-  for (int j = tid; j <= jmax; j += T) {
-    const uint16_t* kp = reinterpret_cast<const uint16_t*>(a.k) + b * a.k_b + static_cast<long long>(j) * a.k_blk + hk * a.k_h;
-    uint4 raw[16];
+  if (warp == 4 && lane == 0) {
+    // the key tile is on its way while the other warps build the Q tile
+    ptx::mbar_expect_tx(ptx::smem_u32(&sh.k_full), kGsTileBytes);
+    for (int h = 0; h < 2; ++h)
+      ptx::tma_load_4d(k_smem + h * kGsHalfBytes, &k_map, ptx::smem_u32(&sh.k_full), h * 64, hk, tile * kGsTileKeys, b);
+  }
+  // Q tile: column n < n_rows = query row n rounded to 16 bits, column n_rows + n = what the rounding dropped
+  for (int e = tid; e < a.n_cols * 16; e += 160) {   // 8 channels (one 16-byte piece) per step
+    const int n = e >> 4, piece = e & 15;
+    uint32_t packed[4] = {0u, 0u, 0u, 0u};
+    if (n < 2 * n_rows) {
+      const int rr = n < n_rows ? n : n - n_rows;
+      const int i = rr / a.G, g = rr % a.G;
+      const long long off = b * a.q_b + i * a.q_blk + static_cast<long long>(hk * a.G + g) * a.q_h + piece * 8;
 #pragma unroll
-    for (int u = 0; u < 16; ++u) raw[u] = __ldg(reinterpret_cast<const uint4*>(kp + u * 8));
-    float acc[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) acc[g] = 0.f;
-#pragma unroll
-    for (int u = 0; u < 16; ++u) {
-      float kv[8];
-      widen8_16(raw[u], KDT, kv);
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const float4 q0 = *reinterpret_cast<const float4*>(&qs[g * 128 + u * 8]);
-        const float4 q1 = *reinterpret_cast<const float4*>(&qs[g * 128 + u * 8 + 4]);
-        acc[g] = fmaf(q0.x, kv[0], acc[g]);
-        acc[g] = fmaf(q0.y, kv[1], acc[g]);
-        acc[g] = fmaf(q0.z, kv[2], acc[g]);
-        acc[g] = fmaf(q0.w, kv[3], acc[g]);
-        acc[g] = fmaf(q1.x, kv[4], acc[g]);
-        acc[g] = fmaf(q1.y, kv[5], acc[g]);
-        acc[g] = fmaf(q1.z, kv[6], acc[g]);
-        acc[g] = fmaf(q1.w, kv[7], acc[g]);
+      for (int c = 0; c < 8; c += 2) {
+        const float x0 = load_score(a.q, off + c, a.q_dtype), x1 = load_score(a.q, off + c + 1, a.q_dtype);
+        const uint16_t h0 = to16(x0, a.k_dtype), h1 = to16(x1, a.k_dtype);
+        const uint16_t v0 = n < n_rows ? h0 : to16(x0 - from16(h0, a.k_dtype), a.k_dtype);
+        const uint16_t v1 = n < n_rows ? h1 : to16(x1 - from16(h1, a.k_dtype), a.k_dtype);
+        packed[c >> 1] = static_cast<uint32_t>(v0) | (static_cast<uint32_t>(v1) << 16);
       }
     }
+    const int half = piece >> 3, chunk = piece & 7;
+    const uint32_t off = half * q_half_bytes + (n >> 3) * 1024 + (n & 7) * 128 + ((chunk ^ (n & 7)) << 4);
+    *reinterpret_cast<uint4*>(q_tile + off) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  }
+  ptx::fence_proxy_async_smem();  // the tensor core reads the tile through the async proxy
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = sh.tmem_base;
+  bool ok = true;
+  if (warp == 4) {
+    if (lane == 0) {
+      ok = ptx::mbar_wait_bounded(ptx::smem_u32(&sh.k_full), 0, abort_flag, a.wait_limit_ns);
+      if (ok) {
+        ptx::tc_fence_after();
+        const uint64_t k_desc0 = ptx::make_smem_desc_sw128(k_smem, 0, 1024);
+        const uint64_t q_desc0 = ptx::make_smem_desc_sw128(q_smem, 0, 1024);
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float v = j <= diag ? acc[g] * a.scale : a.masked_value;
-      reinterpret_cast<float*>(rows + static_cast<size_t>(g) * a.row_bytes)[j] = v;
-      if (a.score_out) a.score_out[((static_cast<long long>(b) * r.H + hk * G + g) * r.Qb + i) * r.Kb + j] = v;
+        for (int k = 0; k < 8; ++k) {
+          const uint64_t ko = static_cast<uint64_t>(((k >> 2) * kGsHalfBytes + (k & 3) * 32) >> 4);
+          const uint64_t qo = static_cast<uint64_t>(((k >> 2) * q_half_bytes + (k & 3) * 32) >> 4);
+          ptx::mma_ss(tmem, k_desc0 + ko, q_desc0 + qo, a.idesc, k > 0 ? 1u : 0u);
+        }
+        ptx::tc_commit(ptx::smem_u32(&sh.t_full));
+      }
+    }
+  } else {
+    ok = ptx::mbar_wait_bounded(ptx::smem_u32(&sh.t_full), 0, abort_flag, a.wait_limit_ns);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      ptx::tc_fence_after();
+      const int j = tile * kGsTileKeys + tid;  // this thread's key block
+      const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+      const long long head_stride = static_cast<long long>(a.Qb) * a.Kb;
+      float* out_b = a.out + (static_cast<long long>(b) * a.Hq + hk * a.G) * head_stride;
+      for (int c0 = 0; c0 < n_rows; c0 += 16) {
+        uint32_t hi[16], lo[16];
+        ptx::tmem_ld16(tmem + lane_base + c0, hi);
+        ptx::tmem_ld16(tmem + lane_base + n_rows + c0, lo);
+        ptx::tc_wait_ld();
+        if (j < a.Kb) {
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            const int rr = c0 + u;
+            if (rr < n_rows) {
+              const int i = rr / a.G, g = rr % a.G;
+              const float dot = __uint_as_float(hi[u]) + __uint_as_float(lo[u]);
+              out_b[g * head_stride + static_cast<long long>(i) * a.Kb + j] = j <= a.Pb + i ? dot * a.scale : a.masked_value;
+            }
+          }
+        }
+      }
     }
   }
-  if (a.score_out) {
-    for (int e = tid; e < G * (r.Kb - 1 - jmax); e += T) {
-      const int g = e / (r.Kb - 1 - jmax), j = jmax + 1 + e % (r.Kb - 1 - jmax);
-      a.score_out[((static_cast<long long>(b) * r.H + hk * G + g) * r.Qb + i) * r.Kb + j] = a.masked_value;
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    if (lane == 0 && sh.abort_flag) {
+      const uint64_t t0 = ptx::globaltimer_ns();
+      while (ptx::globaltimer_ns() - t0 < 200000ull) {
+      }
     }
+    __syncwarp();
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, tmem_cols);
   }
-  __syncthreads();
-  {
-    const int g = tid / kFusedTeam;
-    const Team tm{tid % kFusedTeam, kFusedTeam, 1 + g};
-    select_row(r, tm, &ts[g], rows + static_cast<size_t>(g) * a.row_bytes, b, hk * G + g, i, true);
-  }
-  // ---- Block-Union: one ticket per CTA; the last CTA of the KV-head row builds its table ----
-  const int kv_row = b * Hkv + hk;
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const unsigned int ticket = atomicAdd(&r.tickets[kv_row], 1u);
-    sh_last = ticket == static_cast<unsigned int>(r.Qb - 1) ? 1 : 0;
-  }
-  __syncthreads();
-  if (!sh_last) return;
-  __threadfence();
-  constexpr int kTail = T < kRowThreads ? T : kRowThreads;
-  if (tid >= kTail) return;
-  const Team tm{tid, kTail, 1};
-  uint32_t* words = reinterpret_cast<uint32_t*>(rows);  // the rows' scratch is free now
-  uint32_t* gw = r.union_words + static_cast<long long>(kv_row) * r.W;
-  for (int w = tid; w < r.W; w += kTail) {
-    words[w] = __ldcg(&gw[w]);
-    gw[w] = 0u;  // left clean for the next call
-  }
-  if (tid == 0) r.tickets[kv_row] = 0u;
-  team_sync(tm);
-  compact_row(tm, words, r.W, r.Kb, r.Pb, r.Qb, r.keep_recent, r.block_size, r.page_size,
-              r.block_idx + static_cast<long long>(kv_row) * r.idx_stride, r.idx_stride, kv_row, r.counts, r.cache_seqlens,
-              r.pages_per_row, nullptr, ts[0].warp_sums, &ts[0].cut);
 }
 
 struct UnionArgs {
@@ -675,25 +778,63 @@ __global__ void __launch_bounds__(kRowThreads) paged_metadata_kernel(const int32
 }  // namespace select
 }  // namespace ca
 
-namespace {
-template <int KDT, int G>
-int launch_gate_select(const ca::select::GateSelArgs& a, size_t smem, int ctas, int device, cudaStream_t stream) {
-  using namespace ca;
-  using namespace ca::select;
-  static std::mutex mu;
-  static bool done[64] = {};
+namespace ca {
+
+// ca_gate_scores on the tensor core (declared in ca_score.cu): 128 gate channels, a 16-bit key-block cache and at
+// most 128 query rows (Q-blocks x heads) per cache head.  CA_ERR_UNSUPPORTED for other shapes (the caller then
+// takes the CUDA-core kernels).
+int launch_gate_scores_tc(const ca_gate_score_params* g, cudaStream_t stream) {
+  using namespace select;
+  const bool k16 = g->k_dtype == CA_DTYPE_BF16 || g->k_dtype == CA_DTYPE_F16;
+  if (g->C != 128 || !k16 || g->Hk <= 0 || g->Hq % g->Hk != 0) return CA_ERR_UNSUPPORTED;
+  const int G = g->Hq / g->Hk;
+  const int n_rows = g->Qb * G;
+  if (n_rows > 128) return CA_ERR_UNSUPPORTED;
+  if (g->k_stride_b % 8 != 0 || g->k_stride_blk % 8 != 0 || g->k_stride_h % 8 != 0 || reinterpret_cast<uintptr_t>(g->k) % 16 != 0)
+    return CA_ERR_UNSUPPORTED;
+  DeviceInfo dev;
+  int rc = get_device_info(&dev);
+  if (rc != CA_OK) return rc;
+  if (dev.cc_major != 10) return CA_ERR_UNSUPPORTED;
+  tensor_map_encode_fn enc = get_tensor_map_encoder();
+  if (!enc) return fail(CA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const CUtensorMapDataType dt = g->k_dtype == CA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap k_map;
   {
+    // (channel, cache head, key block, batch); the box is 128 key blocks x 64 channels of one head
+    const cuuint32_t ones[4] = {1, 1, 1, 1};
+    const cuuint64_t dims[4] = {128, (cuuint64_t)g->Hk, (cuuint64_t)g->Kb, (cuuint64_t)g->B};
+    const cuuint64_t strides[3] = {(cuuint64_t)g->k_stride_h * 2, (cuuint64_t)g->k_stride_blk * 2, (cuuint64_t)g->k_stride_b * 2};
+    const cuuint32_t box[4] = {64, 1, (cuuint32_t)kGsTileKeys, 1};
+    CUresult res = enc(&k_map, dt, 4, const_cast<void*>(g->k), dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (res != CUDA_SUCCESS) return fail(CA_ERR_CUDA, "cuTensorMapEncodeTiled(key-block cache) failed with CUresult %d", (int)res);
+  }
+  GateTcArgs a;
+  a.q = g->q, a.q_b = g->q_stride_b, a.q_blk = g->q_stride_blk, a.q_h = g->q_stride_h;
+  a.q_dtype = g->q_dtype, a.k_dtype = g->k_dtype;
+  a.out = g->out;
+  a.B = g->B, a.Hq = g->Hq, a.Hk = g->Hk, a.G = G, a.Qb = g->Qb, a.Kb = g->Kb, a.Pb = g->Pb;
+  a.n_cols = ((2 * n_rows + 15) / 16) * 16;
+  a.scale = g->scale, a.masked_value = g->masked_value;
+  a.idesc = ptx::make_idesc_f16(g->k_dtype == CA_DTYPE_BF16 ? 1u : 0u, kGsTileKeys, static_cast<uint32_t>(a.n_cols), 0, 0);
+  a.wait_limit_ns = 2000000000ull;
+  const size_t smem = 1024 + kGsTileBytes + 2 * static_cast<size_t>(a.n_cols) * 128;
+  {
+    static std::mutex mu;
+    static bool done[64] = {};
     std::lock_guard<std::mutex> lock(mu);
-    if (!done[device]) {
-      CA_CUDA(cudaFuncSetAttribute(gate_select_kernel<KDT, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      done[device] = true;
+    if (!done[dev.ordinal]) {
+      CA_CUDA(cudaFuncSetAttribute(gate_scores_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + kGsTileBytes + 2 * 256 * 128));
+      done[dev.ordinal] = true;
     }
   }
-  launch_kernel(gate_select_kernel<KDT, G>, dim3(ctas), dim3(G * kFusedTeam), smem, stream, a);
-  CA_LAUNCH_CHECK("gate_select_kernel");
+  launch_kernel(gate_scores_tc_kernel, dim3(ceil_div(g->Kb, kGsTileKeys), g->Hk, g->B), dim3(160), smem, stream, k_map, a);
+  CA_LAUNCH_CHECK("gate_scores_tc_kernel");
   return CA_OK;
 }
-}  // namespace
+
+}  // namespace ca
 
 extern "C" {
 
@@ -773,6 +914,12 @@ int ca_select_rows(const ca_select_params* p, ca_stream_t stream_) {
   return CA_OK;
 }
 
+#ifdef CA_SELECT_PROFILE
+int ca_debug_select_profile(long long* out32) {
+  return cudaMemcpyFromSymbol(out32, ca::select::g_sel_prof, 32 * sizeof(long long)) == cudaSuccess ? 0 : -3;
+}
+#endif
+
 int ca_select_union_scratch_bytes(int B, int Hkv, int Kb, size_t* bytes_out) {
   using namespace ca;
   CA_REQUIRE(bytes_out != nullptr, "bytes_out is null");
@@ -845,36 +992,13 @@ int ca_gate_score_select(const ca_gate_score_params* g, const ca_select_params* 
   size_t row_smem = 0;
   int rc = fill_fused_args(p, u, scratch, scratch_bytes, &a, &row_smem);
   if (rc != CA_OK) return rc;
-  const int G = u->G;
-  const bool k16 = g->k_dtype == CA_DTYPE_BF16 || g->k_dtype == CA_DTYPE_F16;
-  const size_t smem = static_cast<size_t>(G) * 128 * sizeof(float) + static_cast<size_t>(G) * row_smem;
-  const bool fused = g->C == 128 && k16 && g->Hk == u->Hkv && (G == 1 || G == 2 || G == 4) && p->rule != CA_RULE_MASK &&
-                     smem <= 200 * 1024 && g->k_stride_blk % 8 == 0 && g->k_stride_h % 8 == 0 && g->k_stride_b % 8 == 0 &&
-                     reinterpret_cast<uintptr_t>(g->k) % 16 == 0;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (!fused) {
-    // shapes the one-launch form does not cover: the two kernels it stands for
-    rc = ca_gate_scores(g, stream_);
-    if (rc != CA_OK) return rc;
-    launch_kernel(select_rows_kernel, dim3(p->B * p->H * p->Qb), dim3(kRowThreads), row_smem, stream, a);
-    CA_LAUNCH_CHECK("select_rows_kernel");
-    return CA_OK;
-  }
-  DeviceInfo dev;
-  rc = get_device_info(&dev);
+  (void)write_scores;  // the logits always pass through score->out
+  rc = ca_gate_scores(g, stream_);
   if (rc != CA_OK) return rc;
-  GateSelArgs ga;
-  ga.row = a;
-  ga.q = g->q, ga.q_b = g->q_stride_b, ga.q_blk = g->q_stride_blk, ga.q_h = g->q_stride_h, ga.q_dtype = g->q_dtype;
-  ga.k = g->k, ga.k_b = g->k_stride_b, ga.k_blk = g->k_stride_blk, ga.k_h = g->k_stride_h;
-  ga.scale = g->scale, ga.masked_value = g->masked_value;
-  ga.score_out = write_scores ? g->out : nullptr;
-  ga.row_bytes = static_cast<int>(row_smem);
-  const int ctas = p->B * u->Hkv * p->Qb;
-  const bool bf = g->k_dtype == CA_DTYPE_BF16;
-  if (G == 1) return bf ? launch_gate_select<CA_DTYPE_BF16, 1>(ga, smem, ctas, dev.ordinal, stream) : launch_gate_select<CA_DTYPE_F16, 1>(ga, smem, ctas, dev.ordinal, stream);
-  if (G == 2) return bf ? launch_gate_select<CA_DTYPE_BF16, 2>(ga, smem, ctas, dev.ordinal, stream) : launch_gate_select<CA_DTYPE_F16, 2>(ga, smem, ctas, dev.ordinal, stream);
-  return bf ? launch_gate_select<CA_DTYPE_BF16, 4>(ga, smem, ctas, dev.ordinal, stream) : launch_gate_select<CA_DTYPE_F16, 4>(ga, smem, ctas, dev.ordinal, stream);
+  launch_kernel(select_rows_kernel, dim3(p->B * p->H * p->Qb), dim3(kRowThreads), row_smem, stream, a);
+  CA_LAUNCH_CHECK("select_rows_kernel");
+  return CA_OK;
 }
 
 int ca_union_table(const ca_union_params* p, ca_stream_t stream_) {

@@ -372,15 +372,12 @@ typedef struct ca_gate_score_params {
 int ca_gate_scores(const ca_gate_score_params* p, ca_stream_t stream);
 
 /*
- * Gate scores, row rule, Block-Union and block table in ONE launch: the result of ca_gate_scores(score)
+ * Gate scores, row rule, Block-Union and block table behind ONE host call: exactly ca_gate_scores(score)
  * followed by ca_select_union_table(sel, un, scratch) with sel->score == score->out (the gate's contiguous fp32
- * buffer), for the learned gate's usual shape - 128 gate channels, a 16-bit key-block cache with one head per KV
- * head (score->Hk == un->Hkv), 1, 2 or 4 query heads per KV head, any rule but CA_RULE_MASK.  One CTA per
- * (batch, KV head, Q-block) computes its query heads' rows of logits into shared memory (bit-identical to
- * ca_gate_scores), applies the rule to each, ORs the rows into the KV head's union words and takes a ticket; the
- * last CTA of a KV head compacts the table.  The logits are written to score->out only when write_scores != 0
- * (tests, callers that log them).  Any other shape runs the two launches it stands for (score->out is then
- * always written).  Same reference lines as ca_gate_scores and ca_select_union_table; replaces the chain
+ * buffer) - two launches (the tensor-core score kernel reads every key block once for all Q-blocks and heads; the
+ * rule kernel builds the union and the table), validated together.  write_scores is accepted for callers written
+ * against an earlier single-launch form and ignored: the logits always pass through score->out.
+ * Same reference lines as ca_gate_scores and ca_select_union_table; replaces the chain
  * AttnGate.score_compressed_blocks -> keep-mask builders -> index builders
  * (compact_attn/prefill_sparse/attn_gate.py:173-204, compact_attn/modules/attention_forward_chunked_dense.py:352-403,
  * 641-683, compact_attn/csrc/compactattn/cache_fill_kernel.cu:275-385).
@@ -561,9 +558,8 @@ int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream);
  *   fp_score ca_flashprefill_score   training-free block scores                            [fp_score.q]
  *   select + table  ca_select_union_table (one launch) when union_scratch is given, else
  *            ca_select_rows then ca_union_table                                            [select.score]
- *            (score + select + table are ONE launch, ca_gate_score_select, when the score stage is present,
- *            union_scratch is given and select.score == score.out; the logits are then not written
- *            unless write_scores is set)
+ *            (score + select + table go through ca_gate_score_select when the score stage is present,
+ *            union_scratch is given and select.score == score.out)
  *   attn     ca_attn_compact                                                               [attn.q]
  * It stands where the reference runs its per-layer Python between the KV-cache update and o_proj:
  * _compute_chunked_gate_from_cache, the keep-mask / index builders and the indexed attention call
@@ -582,7 +578,7 @@ typedef struct ca_chunk_step_params {
   void* union_scratch;
   size_t union_scratch_bytes;
   ca_attn_params attn;
-  int32_t write_scores; /* keep the gate logits in score.out even when the fused score + select launch runs */
+  int32_t write_scores; /* passed to ca_gate_score_select (ignored there: the logits always reach score.out) */
 } ca_chunk_step_params;
 
 int ca_chunk_step(const ca_chunk_step_params* p, ca_stream_t stream);
