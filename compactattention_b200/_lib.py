@@ -269,7 +269,7 @@ _SIGNATURES = {
     "ca_attn_compact_static_scratch": (C.c_int, [C.POINTER(AttnParams), C.c_void_p]),
     "ca_select_rows": (C.c_int, [C.POINTER(SelectParams), C.c_void_p]),
     "ca_union_table": (C.c_int, [C.POINTER(UnionParams), C.c_void_p]),
-    "ca_select_union_scratch_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_size_t)]),
+    "ca_select_union_scratch_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_size_t)]),
     "ca_select_union_table": (C.c_int, [C.POINTER(SelectParams), C.POINTER(UnionParams), C.c_void_p, C.c_size_t, C.c_void_p]),
     "ca_paged_metadata": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "ca_pool_blocks": (C.c_int, [C.POINTER(PoolParams), C.c_void_p]),

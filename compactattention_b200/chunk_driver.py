@@ -154,8 +154,8 @@ class StepScratch:
                                     torch.empty((batch, kv_heads), dtype=torch.int32, device=device),
                                     torch.empty((batch, kv_heads), dtype=torch.int32, device=device),
                                     torch.empty((batch, kv_heads), dtype=torch.int32, device=device))
-        self.union = ops.union_scratch(torch.device(device) if not isinstance(device, torch.device) else device, batch, kv_heads,
-                                       max_blocks)
+        self.union = ops.union_scratch(torch.device(device) if not isinstance(device, torch.device) else device, batch, heads,
+                                       kv_heads, q_blocks, max_blocks)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
 

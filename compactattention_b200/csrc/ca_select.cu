@@ -17,11 +17,11 @@ constexpr int kRowThreads = 256;
 __device__ long long g_sel_prof[32];
 #define SEL_MARK(team_is_first, tid, k) \
   if (blockIdx.x == 0 && (team_is_first) && (tid) == 0) g_sel_prof[k] = clock64();
-#define SEL_MARK_ANY(k) \
-  if (blockIdx.x == 0) g_sel_prof[k] = clock64();
+#define SEL_MARK_ANY0(k) \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) g_sel_prof[k] = clock64();
 #else
 #define SEL_MARK(team_is_first, tid, k)
-#define SEL_MARK_ANY(k)
+#define SEL_MARK_ANY0(k)
 #endif
 constexpr int kMaxKb = 8192;  // key blocks per row supported by the row kernels (512K tokens at bs 64)
 
@@ -57,13 +57,13 @@ struct RowArgs {
   int min_budget;  // ALPHA_ROWMAX: also keep the top min_budget entries
   int sink, local; // forced blocks: j < sink, and 0 <= (Pb+i) - j < local
   int rows_voting; // rows i >= rows_voting produce no bits (FlashPrefill last_n_block)
-  // Fused Block-Union (optional, fuse != 0): every row CTA ORs its words into the KV-head row's word
-  // array in global memory and takes a ticket; the CTA that takes the last ticket of a KV-head row
-  // compacts that row into the block table and leaves the words and the ticket zeroed for the next call.
+  // Fused Block-Union (optional, fuse != 0): every row CTA stores its words (`bits`, the caller's or a scratch
+  // area: plain stores - OR-ing them into one word array with atomics made 64 CTAs queue on every address)
+  // and takes a ticket; the CTA that takes the last ticket of a KV-head row ORs that row's G * Qb word rows,
+  // compacts them into the block table and leaves the ticket zeroed for the next call.
   int fuse;
   int G;                 // query heads per KV head (H = Hkv * G)
-  uint32_t* union_words; // [B*Hkv, W], zero on entry
-  uint32_t* tickets;     // [B*Hkv], zero on entry
+  uint32_t* tickets;     // [B*Hkv], zero on entry, left zero
   int keep_recent, block_size, page_size, idx_stride;
   int32_t* block_idx;
   int32_t* counts;
@@ -329,7 +329,7 @@ __device__ void compact_row(const Team& tm, uint32_t* words, int W, int Kb, int 
 // s[Kb] f32, keep[Kb], flag[Kb] and, for the cumulative-mass rule, the sort keys.  With `preloaded` the raw
 // scores of the row are already in s[] (the fused score + rule kernel) instead of in a.score.
 __device__ void select_row(const RowArgs& a, const Team& tm, TeamShared* ts, unsigned char* row_smem, int b, int h, int i,
-                           bool preloaded, uint32_t* cta_union = nullptr) {
+                           bool preloaded) {
   float* s = reinterpret_cast<float*>(row_smem);                     // [Kb]
   uint8_t* keep = reinterpret_cast<uint8_t*>(s + a.Kb);               // [Kb]
   uint8_t* flag = keep + a.Kb;                                        // [Kb] scratch flags
@@ -348,19 +348,33 @@ __device__ void select_row(const RowArgs& a, const Team& tm, TeamShared* ts, uns
   const long long s_off = b * a.s_b + h * a.s_h + i * a.s_q;
   const long long v_off = a.valid ? (b * a.v_b + h * a.v_h + i * a.v_q) : 0;
 
-  // ---- load the row; invalid entries become -inf ----
-  for (int j = tm.tid; j < a.Kb; j += tm.nt) {
-    const bool ok = a.valid ? (a.valid[v_off + j * a.v_k] != 0) : (j <= diag);
-    float x;
-    if (preloaded) {
-      x = s[j];  // left there by the caller (only entries with j <= diag are meaningful)
-    } else if (a.rule == CA_RULE_MASK) {
-      x = reinterpret_cast<const uint8_t*>(a.score)[s_off + j * a.s_k] ? 1.f : 0.f;
-    } else {
-      x = load_score(a.score, s_off + j * a.s_k, a.score_dtype);
+  // ---- load the row; invalid entries become -inf.  Eight entries per thread and round, every load issued
+  // before the first store (the loop used to pay one memory latency per entry) ----
+  for (int base = 0; base < a.Kb; base += tm.nt * 8) {
+    float x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int j = base + u * tm.nt + tm.tid;
+      x[u] = 0.f;
+      if (j < a.Kb) {
+        if (preloaded) {
+          x[u] = s[j];  // left there by the caller (only entries with j <= diag are meaningful)
+        } else if (a.rule == CA_RULE_MASK) {
+          x[u] = reinterpret_cast<const uint8_t*>(a.score)[s_off + j * a.s_k] ? 1.f : 0.f;
+        } else {
+          x[u] = load_score(a.score, s_off + j * a.s_k, a.score_dtype);
+        }
+      }
     }
-    s[j] = ok ? x : -INFINITY;
-    keep[j] = 0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int j = base + u * tm.nt + tm.tid;
+      if (j < a.Kb) {
+        const bool ok = a.valid ? (a.valid[v_off + j * a.v_k] != 0) : (j <= diag);
+        s[j] = ok ? x[u] : -INFINITY;
+        keep[j] = 0;
+      }
+    }
   }
   team_sync(tm);
 
@@ -412,11 +426,14 @@ __device__ void select_row(const RowArgs& a, const Team& tm, TeamShared* ts, uns
     }
     for (int j = tm.tid; j < a.Kb; j += tm.nt) keep[j] = keep[j] || (flag[j] && s[j] >= m * a.alpha);
   } else if (a.rule == CA_RULE_TOPK) {
-    // valid entries are a prefix for the block-causal case; in general count them
-    int cnt = 0;
-    for (int j = tm.tid; j < a.Kb; j += tm.nt) cnt += a.valid ? (a.valid[v_off + j * a.v_k] != 0) : (j <= diag);
-    block_exclusive_scan(tm, cnt, ts->warp_sums, &ts->nvalid);
-    const int n_valid = ts->nvalid;
+    // valid entries are a prefix for the block-causal case; with an explicit mask they are counted
+    int n_valid = diag + 1 < a.Kb ? diag + 1 : a.Kb;
+    if (a.valid) {
+      int cnt = 0;
+      for (int j = tm.tid; j < a.Kb; j += tm.nt) cnt += a.valid[v_off + j * a.v_k] != 0;
+      block_exclusive_scan(tm, cnt, ts->warp_sums, &ts->nvalid);
+      n_valid = ts->nvalid;
+    }
     int k = a.topk_k > 0 ? a.topk_k
                          : static_cast<int>((static_cast<long long>(a.topk_num) * n_valid + a.topk_den / 2) / a.topk_den);
     if (k < 1) k = 1;
@@ -459,11 +476,7 @@ __device__ void select_row(const RowArgs& a, const Team& tm, TeamShared* ts, uns
 
   SEL_MARK(tm.bar <= 1, tm.tid, 6);
   // ---- forced blocks, validity, bit packing ----
-  // the rows of a KV head OR into the same words: each starts at another word, so they do not queue on one address
-  const int n_it = (a.W * 32 + tm.nt - 1) / tm.nt;
-  const int it0 = (h * a.Qb + i) % n_it;
-  for (int it = 0; it < n_it; ++it) {
-    const int base = ((it + it0) % n_it) * tm.nt;
+  for (int base = 0; base < a.W * 32; base += tm.nt) {
     const int j = base + tm.tid;
     bool k = false;
     if (j < a.Kb) {
@@ -475,12 +488,6 @@ __device__ void select_row(const RowArgs& a, const Team& tm, TeamShared* ts, uns
     const uint32_t word = __ballot_sync(0xffffffffu, k);
     if ((tm.tid & 31) == 0 && (j >> 5) < a.W) {
       if (bits_row) bits_row[j >> 5] = word;
-      // fused union: into the CTA's own words when several rows of the KV head share the CTA (one global
-      // atomic per word and CTA afterwards), else straight into the KV-head row's words in global memory
-      if (a.fuse && word) {
-        if (cta_union) atomicOr(&cta_union[j >> 5], word);
-        else atomicOr(&a.union_words[static_cast<long long>(kv_row) * a.W + (j >> 5)], word);
-      }
     }
   }
   }
@@ -496,7 +503,9 @@ __global__ void __launch_bounds__(kRowThreads, 4) select_rows_kernel(const RowAr
   const int i = blockIdx.x % a.Qb;
   const int h = (blockIdx.x / a.Qb) % a.H;
   const int b = blockIdx.x / (a.Qb * a.H);
+  SEL_MARK(true, tm.tid, 0);
   select_row(a, tm, &ts, dyn_smem, b, h, i, false);
+  SEL_MARK(true, tm.tid, 7);
   if (!a.fuse) return;
   const int kv_row = b * (a.H / a.G) + h / a.G;
   // ---- fused Block-Union: the last row CTA of this KV-head row builds the table.  Nobody waits: a CTA
@@ -508,15 +517,33 @@ __global__ void __launch_bounds__(kRowThreads, 4) select_rows_kernel(const RowAr
     sh_last = ticket == static_cast<unsigned int>(a.G * a.Qb - 1) ? 1 : 0;
   }
   __syncthreads();
+  SEL_MARK(true, tm.tid, 9);
   if (!sh_last) return;
   __threadfence();
   uint32_t* words = reinterpret_cast<uint32_t*>(dyn_smem);  // the row's score scratch is free now
-  uint32_t* gw = a.union_words + static_cast<long long>(kv_row) * a.W;
-  for (int w = threadIdx.x; w < a.W; w += kRowThreads) {
-    words[w] = __ldcg(&gw[w]);
-    gw[w] = 0u;  // left clean for the next call
+  for (int w = threadIdx.x; w < a.W; w += kRowThreads) words[w] = 0u;
+  if (threadIdx.x == 0) a.tickets[kv_row] = 0u;  // left clean for the next call
+  __syncthreads();
+  {
+    // OR of the KV head's G * Qb word rows (contiguous: heads h0..h0+G-1, every Q-block), read past L1
+    const uint32_t* src = a.bits + ((static_cast<long long>(b) * a.H + (h / a.G) * a.G) * a.Qb) * a.W;
+    const int n_words = a.G * a.Qb * a.W;
+    if (a.W % 4 == 0) {
+      for (int e = threadIdx.x * 4; e < n_words; e += kRowThreads * 4) {
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + e));
+        const int w = e % a.W;
+        if (v.x) atomicOr(&words[w], v.x);
+        if (v.y) atomicOr(&words[w + 1], v.y);
+        if (v.z) atomicOr(&words[w + 2], v.z);
+        if (v.w) atomicOr(&words[w + 3], v.w);
+      }
+    } else {
+      for (int e = threadIdx.x; e < n_words; e += kRowThreads) {
+        const uint32_t v = __ldcg(src + e);
+        if (v) atomicOr(&words[e % a.W], v);
+      }
+    }
   }
-  if (threadIdx.x == 0) a.tickets[kv_row] = 0u;
   __syncthreads();
   compact_row(tm, words, a.W, a.Kb, a.Pb, a.Qb, a.keep_recent, a.block_size, a.page_size,
               a.block_idx + static_cast<long long>(kv_row) * a.idx_stride, a.idx_stride, kv_row, a.counts, a.cache_seqlens,
@@ -541,27 +568,29 @@ __device__ __forceinline__ float from16(uint16_t v, int dtype) {
 }
 
 // ------------------------------------------------------------------------------------------
-// Gate logits of a whole chunk on the tensor core, every key block read once.
-// One CTA per (key tile of 128 blocks, cache head, batch): D[128 key blocks][N] = K_tile . Q^T with the N
-// columns holding ALL Q-blocks and query heads of the cache head - first their values rounded to the cache's
-// 16-bit type, then the rounding remainders (hi + lo restores the f32 query to 2^-16) - so N = 2 * Qb * G
-// (128 for 16 Q-blocks of 4 heads).  Eight tcgen05.mma (M 128, K 16 each) per CTA; the key blocks are the
-// TMEM lanes, a thread of the four collecting warps owns one and writes its logits row by row, 32 lanes to
-// 128 consecutive bytes.
+// Gate logits of a whole chunk on the tensor core.
+// One CTA per (key tile of 128 blocks, group of 16 query rows, cache head, batch), a query row being a
+// (Q-block, query head) pair of the cache head: D[128 key blocks][32] = K_tile . Q^T, the 32 columns holding
+// the 16 rows rounded to the cache's 16-bit type and then their rounding remainders (hi + lo restores the f32
+// query to 2^-16).  Eight tcgen05.mma (M 128, N 32, K 16) per CTA; the key blocks are the TMEM lanes, a thread
+// of the four collecting warps owns one and writes its 16 logits row by row, 32 lanes to 128 consecutive bytes.
+// A key tile is fetched once per row group (4 times at 16 Q-blocks x 4 heads: 16 MB from L2 in all).
 // Measured and dropped: (1) CUDA-core forms (a thread, or a half-warp with packed f32x2 FMAs and a halving
 // shuffle reduction, per key block): 27 600 - 50 000 cycles per CTA of four rows, bound first by the L1 tag
 // stage (128-bit loads 256 bytes apart across a warp), then by issue slots.  (2) One launch for scores + rule +
 // table, a CTA per (KV head, Q-block) with N = 16 columns and the rule run by teams of the same CTA: correct
-// and bit-identical, but every Q-block re-reads the head's cache from L2 (TMA delivered a 32 KB tile per
+// and bit-identical, but every Q-block re-read the head's cache from L2 (TMA delivered a 32 KB tile per
 // 1 100 - 1 400 cycles) and eight N = 16 MMAs took as long again: 41 us against 47 us for the two launches it
-// replaced, while this kernel reads every key block once.
+// replaced.  (3) All rows of a cache head as the columns of one CTA (N = 128, 128 CTAs of 5 warps): 18 000
+// instructions per CTA for the query tile and the 64 stores per thread at 8 % occupancy, 15.6 us.
 struct GateTcArgs {
   const void* q;  // [B,Qb,Hq,128] by strides
   long long q_b, q_blk, q_h;
-  int q_dtype, k_dtype;
+  int q_dtype;
   float* out;     // [B,Hq,Qb,Kb] contiguous
   int B, Hq, Hk, G, Qb, Kb, Pb;
-  int n_cols;     // 2 * Qb * G rounded up to 16
+  int n_rows;     // Qb * G query rows per cache head
+  int n_groups;   // ceil(n_rows / 16)
   float scale, masked_value;
   uint32_t idesc;
   unsigned long long wait_limit_ns;
@@ -573,24 +602,43 @@ struct GateTcShared {
   int abort_flag;
 };
 
-__global__ void __launch_bounds__(160, 1) gate_scores_tc_kernel(const __grid_constant__ CUtensorMap k_map, const GateTcArgs a) {
+constexpr int kGtRows = 16;                 // query rows per CTA
+constexpr int kGtCols = 2 * kGtRows;        // MMA N: hi and lo
+constexpr int kGtQHalfBytes = kGtCols * 128;
+constexpr int kGtThreads = 160;             // 4 collecting warps + the TMA / MMA warp
+
+template <int KDT>
+__device__ __forceinline__ uint32_t pack16x2(float x0, float x1) {
+  if (KDT == CA_DTYPE_BF16) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  const __half2 h = __floats2half2_rn(x0, x1);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <int KDT>
+__device__ __forceinline__ float2 unpack16x2(uint32_t v) {
+  if (KDT == CA_DTYPE_BF16) return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+  return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+
+template <int KDT>
+__global__ void __launch_bounds__(kGtThreads) gate_scores_tc_kernel(const __grid_constant__ CUtensorMap k_map, const GateTcArgs a) {
   ptx::grid_launch_dependents();
   ptx::grid_dependency_wait();  // nothing in global memory is touched before this
   extern __shared__ uint8_t gt_smem_raw[];
   __shared__ GateTcShared sh;
   const uint32_t smem_base = (ptx::smem_u32(gt_smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = gt_smem_raw + (smem_base - ptx::smem_u32(gt_smem_raw));
-  // layout: K tile (two swizzled halves) | Q tile (two swizzled halves of n_cols rows)
+  // layout: K tile (two swizzled halves) | Q tile (two swizzled halves of 32 rows)
   const uint32_t k_smem = smem_base;
   uint8_t* q_tile = smem_aligned + kGsTileBytes;
   const uint32_t q_smem = smem_base + kGsTileBytes;
-  const uint32_t q_half_bytes = static_cast<uint32_t>(a.n_cols) * 128u;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int tile = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int tile = blockIdx.x / a.n_groups, group = blockIdx.x % a.n_groups;
+  const int hk = blockIdx.y, b = blockIdx.z;
+  const int row0 = group * kGtRows;  // first query row (i * G + g) of this CTA
   volatile int* abort_flag = &sh.abort_flag;
-  const int n_rows = a.Qb * a.G;  // query rows of this cache head: row = i * G + g
-  uint32_t tmem_cols = 32;
-  while (tmem_cols < static_cast<uint32_t>(a.n_cols)) tmem_cols <<= 1;
 
   if (tid == 0) {
     ptx::mbar_init(ptx::smem_u32(&sh.k_full), 1);
@@ -600,37 +648,62 @@ __global__ void __launch_bounds__(160, 1) gate_scores_tc_kernel(const __grid_con
     ptx::fence_proxy_async_smem();
   }
   if (warp == 4) {
-    ptx::tmem_alloc(ptx::smem_u32(&sh.tmem_base), tmem_cols);
+    ptx::tmem_alloc(ptx::smem_u32(&sh.tmem_base), kGtCols);
     ptx::tmem_relinquish();
   }
   __syncthreads();
+  SEL_MARK_ANY0(16);
   if (warp == 4 && lane == 0) {
     // the key tile is on its way while the other warps build the Q tile
     ptx::mbar_expect_tx(ptx::smem_u32(&sh.k_full), kGsTileBytes);
     for (int h = 0; h < 2; ++h)
       ptx::tma_load_4d(k_smem + h * kGsHalfBytes, &k_map, ptx::smem_u32(&sh.k_full), h * 64, hk, tile * kGsTileKeys, b);
   }
-  // Q tile: column n < n_rows = query row n rounded to 16 bits, column n_rows + n = what the rounding dropped
-  for (int e = tid; e < a.n_cols * 16; e += 160) {   // 8 channels (one 16-byte piece) per step
-    const int n = e >> 4, piece = e & 15;
-    uint32_t packed[4] = {0u, 0u, 0u, 0u};
-    if (n < 2 * n_rows) {
-      const int rr = n < n_rows ? n : n - n_rows;
-      const int i = rr / a.G, g = rr % a.G;
-      const long long off = b * a.q_b + i * a.q_blk + static_cast<long long>(hk * a.G + g) * a.q_h + piece * 8;
+  // Q tile: column n < 16 = query row row0 + n rounded to 16 bits, column 16 + n = what the rounding dropped.
+  // An item is 8 channels of one query row: 256 items, at most two per thread, loads first.
+  {
+    float v[2][8];
 #pragma unroll
-      for (int c = 0; c < 8; c += 2) {
-        const float x0 = load_score(a.q, off + c, a.q_dtype), x1 = load_score(a.q, off + c + 1, a.q_dtype);
-        const uint16_t h0 = to16(x0, a.k_dtype), h1 = to16(x1, a.k_dtype);
-        const uint16_t v0 = n < n_rows ? h0 : to16(x0 - from16(h0, a.k_dtype), a.k_dtype);
-        const uint16_t v1 = n < n_rows ? h1 : to16(x1 - from16(h1, a.k_dtype), a.k_dtype);
-        packed[c >> 1] = static_cast<uint32_t>(v0) | (static_cast<uint32_t>(v1) << 16);
+    for (int u = 0; u < 2; ++u) {
+      const int e = tid + u * kGtThreads;
+      const int rr = row0 + (e >> 4), piece = e & 15;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) v[u][c] = 0.f;
+      if (e < kGtRows * 16 && rr < a.n_rows) {
+        const int i = rr / a.G, g = rr - i * a.G;
+        const long long off = b * a.q_b + i * a.q_blk + static_cast<long long>(hk * a.G + g) * a.q_h + piece * 8;
+        if (a.q_dtype == CA_DTYPE_F32) {
+          const float4 x0 = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.q) + off));
+          const float4 x1 = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.q) + off + 4));
+          v[u][0] = x0.x, v[u][1] = x0.y, v[u][2] = x0.z, v[u][3] = x0.w, v[u][4] = x1.x, v[u][5] = x1.y, v[u][6] = x1.z, v[u][7] = x1.w;
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) v[u][c] = load_score(a.q, off + c, a.q_dtype);
+        }
       }
     }
-    const int half = piece >> 3, chunk = piece & 7;
-    const uint32_t off = half * q_half_bytes + (n >> 3) * 1024 + (n & 7) * 128 + ((chunk ^ (n & 7)) << 4);
-    *reinterpret_cast<uint4*>(q_tile + off) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int e = tid + u * kGtThreads;
+      if (e < kGtRows * 16) {
+        const int n = e >> 4, piece = e & 15;
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          hi[c] = pack16x2<KDT>(v[u][2 * c], v[u][2 * c + 1]);
+          const float2 back = unpack16x2<KDT>(hi[c]);
+          lo[c] = pack16x2<KDT>(v[u][2 * c] - back.x, v[u][2 * c + 1] - back.y);
+        }
+        const int half = piece >> 3, chunk = piece & 7;
+        const int nl = kGtRows + n;
+        *reinterpret_cast<uint4*>(q_tile + half * kGtQHalfBytes + (n >> 3) * 1024 + (n & 7) * 128 + ((chunk ^ (n & 7)) << 4)) =
+            make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(q_tile + half * kGtQHalfBytes + (nl >> 3) * 1024 + (nl & 7) * 128 + ((chunk ^ (nl & 7)) << 4)) =
+            make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      }
+    }
   }
+  SEL_MARK_ANY0(17);
   ptx::fence_proxy_async_smem();  // the tensor core reads the tile through the async proxy
   ptx::tc_fence_before();
   __syncthreads();
@@ -646,8 +719,9 @@ __global__ void __launch_bounds__(160, 1) gate_scores_tc_kernel(const __grid_con
         const uint64_t q_desc0 = ptx::make_smem_desc_sw128(q_smem, 0, 1024);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
+          // A: key blocks (K-major), B: query rows (K-major); channel half k>>2, 32-byte step inside the swizzled row
           const uint64_t ko = static_cast<uint64_t>(((k >> 2) * kGsHalfBytes + (k & 3) * 32) >> 4);
-          const uint64_t qo = static_cast<uint64_t>(((k >> 2) * q_half_bytes + (k & 3) * 32) >> 4);
+          const uint64_t qo = static_cast<uint64_t>(((k >> 2) * kGtQHalfBytes + (k & 3) * 32) >> 4);
           ptx::mma_ss(tmem, k_desc0 + ko, q_desc0 + qo, a.idesc, k > 0 ? 1u : 0u);
         }
         ptx::tc_commit(ptx::smem_u32(&sh.t_full));
@@ -656,42 +730,47 @@ __global__ void __launch_bounds__(160, 1) gate_scores_tc_kernel(const __grid_con
   } else {
     ok = ptx::mbar_wait_bounded(ptx::smem_u32(&sh.t_full), 0, abort_flag, a.wait_limit_ns);
     ok = __all_sync(0xffffffffu, ok);
+    SEL_MARK_ANY0(18);
     if (ok) {
       ptx::tc_fence_after();
       const int j = tile * kGsTileKeys + tid;  // this thread's key block
-      const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-      const long long head_stride = static_cast<long long>(a.Qb) * a.Kb;
-      float* out_b = a.out + (static_cast<long long>(b) * a.Hq + hk * a.G) * head_stride;
-      for (int c0 = 0; c0 < n_rows; c0 += 16) {
-        uint32_t hi[16], lo[16];
-        ptx::tmem_ld16(tmem + lane_base + c0, hi);
-        ptx::tmem_ld16(tmem + lane_base + n_rows + c0, lo);
-        ptx::tc_wait_ld();
-        if (j < a.Kb) {
+      uint32_t acc[32];
+      ptx::tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16), acc);
+      ptx::tc_wait_ld();
+      if (j < a.Kb) {
+        const long long head_stride = static_cast<long long>(a.Qb) * a.Kb;
+        int i = row0 / a.G, g = row0 - i * a.G;
+        float* dst = a.out + (static_cast<long long>(b) * a.Hq + hk * a.G + g) * head_stride + static_cast<long long>(i) * a.Kb + j;
 #pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            const int rr = c0 + u;
-            if (rr < n_rows) {
-              const int i = rr / a.G, g = rr % a.G;
-              const float dot = __uint_as_float(hi[u]) + __uint_as_float(lo[u]);
-              out_b[g * head_stride + static_cast<long long>(i) * a.Kb + j] = j <= a.Pb + i ? dot * a.scale : a.masked_value;
+        for (int u = 0; u < kGtRows; ++u) {
+          if (row0 + u < a.n_rows) {
+            const float dot = __uint_as_float(acc[u]) + __uint_as_float(acc[kGtRows + u]);
+            *dst = j <= a.Pb + i ? dot * a.scale : a.masked_value;
+            // next row: next head of the same Q-block, or head 0 of the next Q-block
+            if (++g == a.G) {
+              g = 0, ++i;
+              dst += a.Kb - static_cast<long long>(a.G - 1) * head_stride;
+            } else {
+              dst += head_stride;
             }
           }
         }
       }
     }
   }
+  SEL_MARK_ANY0(19);
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 4) {
     if (lane == 0 && sh.abort_flag) {
+      // after an expired wait: give the copy and the MMAs that may still be in flight 200 us to land
       const uint64_t t0 = ptx::globaltimer_ns();
       while (ptx::globaltimer_ns() - t0 < 200000ull) {
       }
     }
     __syncwarp();
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem, tmem_cols);
+    ptx::tmem_dealloc(tmem, kGtCols);
   }
 }
 
@@ -789,7 +868,6 @@ int launch_gate_scores_tc(const ca_gate_score_params* g, cudaStream_t stream) {
   if (g->C != 128 || !k16 || g->Hk <= 0 || g->Hq % g->Hk != 0) return CA_ERR_UNSUPPORTED;
   const int G = g->Hq / g->Hk;
   const int n_rows = g->Qb * G;
-  if (n_rows > 128) return CA_ERR_UNSUPPORTED;
   if (g->k_stride_b % 8 != 0 || g->k_stride_blk % 8 != 0 || g->k_stride_h % 8 != 0 || reinterpret_cast<uintptr_t>(g->k) % 16 != 0)
     return CA_ERR_UNSUPPORTED;
   DeviceInfo dev;
@@ -812,24 +890,23 @@ int launch_gate_scores_tc(const ca_gate_score_params* g, cudaStream_t stream) {
   }
   GateTcArgs a;
   a.q = g->q, a.q_b = g->q_stride_b, a.q_blk = g->q_stride_blk, a.q_h = g->q_stride_h;
-  a.q_dtype = g->q_dtype, a.k_dtype = g->k_dtype;
+  a.q_dtype = g->q_dtype;
   a.out = g->out;
   a.B = g->B, a.Hq = g->Hq, a.Hk = g->Hk, a.G = G, a.Qb = g->Qb, a.Kb = g->Kb, a.Pb = g->Pb;
-  a.n_cols = ((2 * n_rows + 15) / 16) * 16;
+  a.n_rows = n_rows;
+  a.n_groups = ceil_div(n_rows, kGtRows);
   a.scale = g->scale, a.masked_value = g->masked_value;
-  a.idesc = ptx::make_idesc_f16(g->k_dtype == CA_DTYPE_BF16 ? 1u : 0u, kGsTileKeys, static_cast<uint32_t>(a.n_cols), 0, 0);
+  a.idesc = ptx::make_idesc_f16(g->k_dtype == CA_DTYPE_BF16 ? 1u : 0u, kGsTileKeys, kGtCols, 0, 0);
   a.wait_limit_ns = 2000000000ull;
-  const size_t smem = 1024 + kGsTileBytes + 2 * static_cast<size_t>(a.n_cols) * 128;
-  {
-    static std::mutex mu;
-    static bool done[64] = {};
-    std::lock_guard<std::mutex> lock(mu);
-    if (!done[dev.ordinal]) {
-      CA_CUDA(cudaFuncSetAttribute(gate_scores_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + kGsTileBytes + 2 * 256 * 128));
-      done[dev.ordinal] = true;
-    }
+  const size_t smem = 1024 + kGsTileBytes + 2 * kGtQHalfBytes;
+  const long long ctas_x = static_cast<long long>(ceil_div(g->Kb, kGsTileKeys)) * a.n_groups;
+  if (ctas_x > 0x7fffffffLL) return CA_ERR_UNSUPPORTED;
+  const dim3 grid(static_cast<unsigned>(ctas_x), g->Hk, g->B);
+  if (g->k_dtype == CA_DTYPE_BF16) {
+    launch_kernel(gate_scores_tc_kernel<CA_DTYPE_BF16>, grid, dim3(kGtThreads), smem, stream, k_map, a);
+  } else {
+    launch_kernel(gate_scores_tc_kernel<CA_DTYPE_F16>, grid, dim3(kGtThreads), smem, stream, k_map, a);
   }
-  launch_kernel(gate_scores_tc_kernel, dim3(ceil_div(g->Kb, kGsTileKeys), g->Hk, g->B), dim3(160), smem, stream, k_map, a);
   CA_LAUNCH_CHECK("gate_scores_tc_kernel");
   return CA_OK;
 }
@@ -874,7 +951,7 @@ static int fill_row_args(const ca_select_params* p, ca::select::RowArgs* out, si
   a.sink = p->sink, a.local = p->local;
   a.rows_voting = p->rows_voting > 0 ? p->rows_voting : p->Qb;
   a.fuse = 0, a.G = 1;
-  a.union_words = nullptr, a.tickets = nullptr;
+  a.tickets = nullptr;
   a.keep_recent = 0, a.block_size = 0, a.page_size = 0, a.idx_stride = 0;
   a.block_idx = nullptr, a.counts = nullptr, a.cache_seqlens = nullptr, a.pages_per_row = nullptr;
   size_t smem = ((static_cast<size_t>(p->Kb) * 6 + 15) / 16) * 16;
@@ -920,12 +997,13 @@ int ca_debug_select_profile(long long* out32) {
 }
 #endif
 
-int ca_select_union_scratch_bytes(int B, int Hkv, int Kb, size_t* bytes_out) {
+int ca_select_union_scratch_bytes(int B, int H, int Hkv, int Qb, int Kb, size_t* bytes_out) {
   using namespace ca;
   CA_REQUIRE(bytes_out != nullptr, "bytes_out is null");
-  CA_REQUIRE(B > 0 && Hkv > 0 && Kb > 0, "B, Hkv, Kb must be positive");
-  const size_t rows = static_cast<size_t>(B) * Hkv;
-  *bytes_out = (rows * ((Kb + 31) / 32) + rows) * sizeof(uint32_t);
+  CA_REQUIRE(B > 0 && H > 0 && Hkv > 0 && Qb > 0 && Kb > 0, "B, H, Hkv, Qb, Kb must be positive");
+  // tickets (one word per KV-head row, rounded to 16 bytes), then the rows' packed bits for callers that do not keep them
+  const size_t tickets = ((static_cast<size_t>(B) * Hkv + 3) / 4) * 4;
+  *bytes_out = (tickets + static_cast<size_t>(B) * H * Qb * ((Kb + 31) / 32)) * sizeof(uint32_t);
   return CA_OK;
 }
 
@@ -951,12 +1029,14 @@ static int fill_fused_args(const ca_select_params* p, const ca_union_params* u, 
   CA_REQUIRE(u->keep_kv == nullptr && u->bits == nullptr && u->mask == nullptr,
              "the fused form takes its input from the selection; keep_kv is not produced");
   size_t need = 0;
-  ca_select_union_scratch_bytes(u->B, u->Hkv, u->Kb, &need);
-  CA_REQUIRE(scratch != nullptr && reinterpret_cast<uintptr_t>(scratch) % 4 == 0, "scratch must be a 4-byte aligned device pointer");
+  ca_select_union_scratch_bytes(u->B, p->H, u->Hkv, p->Qb, u->Kb, &need);
+  const size_t ticket_words = ((static_cast<size_t>(u->B) * u->Hkv + 3) / 4) * 4;
+  if (p->bits != nullptr) need = ticket_words * sizeof(uint32_t);  // the caller's bits serve as the rows' word store
+  CA_REQUIRE(scratch != nullptr && reinterpret_cast<uintptr_t>(scratch) % 16 == 0, "scratch must be a 16-byte aligned device pointer");
   if (scratch_bytes < need) return fail(CA_ERR_CAPACITY, "scratch holds %zu bytes, %zu are needed", scratch_bytes, need);
   a.fuse = 1, a.G = u->G;
-  a.union_words = static_cast<uint32_t*>(scratch);
-  a.tickets = a.union_words + static_cast<size_t>(u->B) * u->Hkv * a.W;
+  a.tickets = static_cast<uint32_t*>(scratch);
+  if (a.bits == nullptr) a.bits = a.tickets + ticket_words;
   a.keep_recent = u->keep_recent, a.block_size = u->block_size, a.page_size = u->page_size, a.idx_stride = u->idx_stride;
   a.block_idx = u->block_idx, a.counts = u->counts, a.cache_seqlens = u->cache_seqlens, a.pages_per_row = u->pages_per_row;
   *out = a;

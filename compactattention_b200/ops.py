@@ -324,13 +324,14 @@ def select_rows(
 _UNION_SCRATCH: dict = {}
 
 
-def union_scratch(device: torch.device, batch: int, num_kv_heads: int, kv_blocks: int) -> torch.Tensor:
-    """Zeroed scratch of the fused selection + table launch (the per-KV-head union words and tickets).  The
-    kernel leaves it zeroed, so one buffer per (device, stream) serves every call on that stream; it only
-    grows."""
-    key = (device.index, _stream())
+def union_scratch(device: torch.device, batch: int, heads: int, num_kv_heads: int, q_blocks: int, kv_blocks: int) -> torch.Tensor:
+    """Scratch of the fused selection + table launch: a ticket per KV-head row (zero on entry, left zero by the
+    kernel) followed by room for the rows' packed bits.  One buffer per (device, stream) serves every call on
+    that stream and ticket count (the ticket words must never have held anything else); it only grows."""
+    key = (device.index, _stream(), batch * num_kv_heads)
     need = C.c_size_t(0)
-    _lib.check(_lib.load().ca_select_union_scratch_bytes(batch, num_kv_heads, kv_blocks, C.byref(need)), "ca_select_union_scratch_bytes")
+    _lib.check(_lib.load().ca_select_union_scratch_bytes(batch, heads, num_kv_heads, q_blocks, kv_blocks, C.byref(need)),
+               "ca_select_union_scratch_bytes")
     buf = _UNION_SCRATCH.get(key)
     if buf is None or buf.numel() * 4 < need.value:
         buf = torch.zeros((int(need.value) + 3) // 4, dtype=torch.int32, device=device)
@@ -391,7 +392,7 @@ def select_union_table(
     u.cache_seqlens = out.cache_seqlens.data_ptr()
     u.pages_per_row = out.pages_per_row.data_ptr()
     if scratch is None:
-        scratch = union_scratch(dev, B, num_kv_heads, Kb)
+        scratch = union_scratch(dev, B, H, num_kv_heads, Qb, Kb)
     if scratch.dtype != torch.int32 or not scratch.is_contiguous():
         raise ValueError("scratch must be a contiguous int32 tensor (zero on first use)")
     if _gate is not None:

@@ -233,21 +233,22 @@ typedef struct ca_union_params {
 int ca_union_table(const ca_union_params* p, ca_stream_t stream);
 
 /*
- * ca_select_rows and ca_union_table in ONE launch: every row CTA of the selection ORs its packed bits
- * into its KV-head row of a small word array and takes a ticket; the CTA that takes the last ticket
- * of a KV-head row (nobody waits for anybody) compacts that row into the block table.  It replaces the
- * same reference functions as the two calls it fuses, in particular the pair
+ * ca_select_rows and ca_union_table in ONE launch: every row CTA of the selection stores its packed bits
+ * (into sel->bits, or into the scratch when sel->bits is NULL) and takes a ticket; the CTA that takes the last
+ * ticket of a KV-head row (nobody waits for anybody) ORs that row's G * Qb bit rows and compacts them into the
+ * block table.  It replaces the same reference functions as the two calls it fuses, in particular the pair
  * build_keep_past_fast_kernel / build_keep_curr_fast_kernel followed by
  * build_past_indices_and_metadata_from_keep_block_kernel
  * (compact_attn/csrc/compactattn/cache_fill_kernel.cu:275-385) and the fused Triton
  * _flashprefill_kv_union_from_scores_kernel (compact_attn/modules/flashprefill_prefill.py:307-376).
- * sel->bits may be NULL (the per-row bits are then not written).  un gives the table outputs and
- * Hkv, G (sel->H = Hkv*G), Qin = sel->Qb, Kb, Pb, keep_recent, block_size, page_size; its bits, mask
- * and keep_kv must be NULL.  scratch: ca_select_union_scratch_bytes() bytes of device memory that is
- * ZERO on the first call; the kernel leaves it zero, so one buffer serves every later call on the same
- * stream (calls that may overlap on the device need a buffer each).
+ * un gives the table outputs and Hkv, G (sel->H = Hkv*G), Qin = sel->Qb, Kb, Pb, keep_recent, block_size,
+ * page_size; its bits, mask and keep_kv must be NULL.  scratch: ca_select_union_scratch_bytes() bytes of
+ * 16-byte aligned device memory whose first ceil4(B*Hkv) words (the tickets) are ZERO on the first call; the
+ * kernel leaves them zero, so one buffer serves every later call on the same stream (calls that may overlap on
+ * the device need a buffer each).  The rest of the scratch holds the rows' bits when sel->bits is NULL and
+ * needs no initialisation.
  */
-int ca_select_union_scratch_bytes(int B, int Hkv, int Kb, size_t* bytes_out);
+int ca_select_union_scratch_bytes(int B, int H, int Hkv, int Qb, int Kb, size_t* bytes_out);
 int ca_select_union_table(const ca_select_params* sel, const ca_union_params* un, void* scratch, size_t scratch_bytes,
                           ca_stream_t stream);
 

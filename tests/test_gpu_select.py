@@ -223,8 +223,8 @@ def test_fused_select_union_table_equals_the_two_launches(ops, rule, kw, B, Hkv,
         keep_block[..., Kb - keep_recent:] = True
     idx, counts = co.block_union_table(keep_block, Qb * 64, Kb * 64, 64, G)
     assert torch.equal(got.block_idx.cpu(), idx) and torch.equal(got.counts.cpu(), counts)
-    scratch = ops.union_scratch(torch.device("cuda", torch.cuda.current_device()), B, Hkv, Kb)
-    assert int(scratch.abs().sum().item()) == 0  # left clean
+    scratch = ops.union_scratch(torch.device("cuda", torch.cuda.current_device()), B, H, Hkv, Qb, Kb)
+    assert int(scratch[: B * Hkv].abs().sum().item()) == 0  # the tickets are left clean
 
 
 def test_fused_select_union_contract_errors(ops):
@@ -279,5 +279,5 @@ def test_gate_score_select_equals_scores_then_selection(ops, rule, kw, B, Hkv, G
         for name in ("block_idx", "counts", "cache_seqlens", "pages_per_row"):
             assert torch.equal(getattr(got, name), getattr(want, name)), (name, call)
         assert torch.equal(got_scores, logits), call
-    scratch = ops.union_scratch(torch.device("cuda", torch.cuda.current_device()), B, Hkv, Kb)
-    assert int(scratch.abs().sum().item()) == 0
+    scratch = ops.union_scratch(torch.device("cuda", torch.cuda.current_device()), B, Hq, Hkv, Qb, Kb)
+    assert int(scratch[: B * Hkv].abs().sum().item()) == 0
