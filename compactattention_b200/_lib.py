@@ -283,6 +283,7 @@ _SIGNATURES = {
     "ca_oproj_scratch_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "ca_oproj_allreduce": (C.c_int, [C.POINTER(OprojParams), C.c_void_p]),
     "ca_oproj_tile_count": (C.c_int, [C.c_int, C.c_int]),
+    "ca_selftest_bounded_wait": (C.c_int, [C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "ca_gate_score_select": (C.c_int, [C.POINTER(GateScoreParams), C.POINTER(SelectParams), C.POINTER(UnionParams), C.c_void_p,
                                        C.c_size_t, C.c_int, C.c_void_p]),
 }

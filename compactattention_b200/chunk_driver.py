@@ -327,11 +327,13 @@ def capture_step(fn, warmup: int = 2) -> "torch.cuda.CUDAGraph":
     selector scores -> row rule -> Block-Union table -> attention at one chunk position — into a CUDA
     graph and returns it; ``graph.replay()`` then enqueues the whole step with one host call.
 
-    The entry points need nothing special for this: they allocate nothing, never synchronise, and
-    their per-device attributes and the attention workspace of the capturing stream are set up by
-    the warm-up calls, which run on a side stream before the capture as torch requires.  A step is
-    only replayable while its shapes hold (the chunk position is baked into the launch parameters),
-    which is the case for a layer stack at one chunk position and for a benchmark loop.
+    The entry points allocate nothing and never synchronise; what the tensor-level wrappers cache per stream
+    (the attention workspace that lets the kernel cut work units, the union scratch of the fused selection) and
+    the library's per-device kernel attributes are set up by the warm-up calls.  Warm-up and capture run on
+    the SAME side stream, so the capture finds those buffers in the cache instead of allocating them inside
+    the graph; their addresses are baked into the graph, and they stay alive in the wrappers' caches.  A step
+    is only replayable while its shapes hold (the chunk position is baked into the launch parameters), which
+    is the case for a layer stack at one chunk position and for a benchmark loop.
     """
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -340,7 +342,7 @@ def capture_step(fn, warmup: int = 2) -> "torch.cuda.CUDAGraph":
             fn()
     torch.cuda.current_stream().wait_stream(side)
     graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
+    with torch.cuda.graph(graph, stream=side):
         fn()
     return graph
 

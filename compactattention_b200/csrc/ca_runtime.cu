@@ -57,9 +57,40 @@ int get_device_info(DeviceInfo* out) {
   return CA_OK;
 }
 
+// One CTA waits, with the bounded wait every tcgen05 / TMA kernel of the library uses, on a barrier nothing
+// ever arrives on: the wait must end after `limit_ns` with the abort flag set, and the kernel must return.
+__global__ void selftest_bounded_wait_kernel(unsigned long long limit_ns, int32_t* status, unsigned long long* waited_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    ptx::mbar_init(ptx::smem_u32(&bar), 1);
+    ptx::mbar_fence_init();
+  }
+  __syncthreads();
+  const uint64_t t0 = ptx::globaltimer_ns();
+  // every thread waits like the roles of a kernel do; the first to pass the limit raises the flag, the others see it
+  const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar), 0, &abort_flag, limit_ns);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (waited_ns) *waited_ns = ptx::globaltimer_ns() - t0;
+    if (!ok && abort_flag && status) atomicOr(status, CA_STATUS_TIMEOUT);
+  }
+}
+
 }  // namespace ca
 
 extern "C" {
+
+int ca_selftest_bounded_wait(uint64_t limit_ns, int32_t* status, uint64_t* waited_ns, ca_stream_t stream) {
+  using namespace ca;
+  CA_REQUIRE(status != nullptr, "status must be non-null");
+  CA_REQUIRE(limit_ns > 0 && limit_ns <= 1000000000ull, "limit_ns must lie in (0, 1 s]");
+  launch_kernel(selftest_bounded_wait_kernel, dim3(1), dim3(128), 0, static_cast<cudaStream_t>(stream),
+                static_cast<unsigned long long>(limit_ns), status, reinterpret_cast<unsigned long long*>(waited_ns));
+  CA_LAUNCH_CHECK("selftest_bounded_wait_kernel");
+  return CA_OK;
+}
 
 const char* ca_last_error(void) { return ca::last_error_buffer(); }
 

@@ -78,6 +78,39 @@ def reduce_layer_output(partial: torch.Tensor, group=None, async_op: bool = Fals
     return dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
 
 
+class ProjectionCallLedger:
+    """What the counters of ``ca_oproj_allreduce`` expect after each call on one set of buffers: the call number
+    (``epoch``), per block of 128 rows the number of calls that covered it (``row_epochs``), and the running
+    number of output tiles (``done_tiles_total``).  Every rank keeps the same ledger because every rank issues
+    the same calls; counters only grow, so a call with fewer rows (a ragged last chunk, a decode step) leaves
+    the targets of the uncovered row blocks where they were."""
+
+    TILE_ROWS, TILE_COLS = 128, 256
+
+    def __init__(self, max_rows: int, out_features: int):
+        self.max_rows, self.out_features = int(max_rows), int(out_features)
+        self.epoch = 0
+        self.row_calls = [0] * ((self.max_rows + self.TILE_ROWS - 1) // self.TILE_ROWS)
+        self.tiles_total = 0
+
+    def next_call(self, rows: int):
+        """Advances the ledger by one call of ``rows`` rows; returns ``(epoch, row_epochs, done_tiles_total)``."""
+        if not 0 < rows <= self.max_rows:
+            raise ValueError(f"{rows} rows exceed the buffers of this projection ({self.max_rows})")
+        self.epoch += 1
+        blocks = (rows + self.TILE_ROWS - 1) // self.TILE_ROWS
+        for tm in range(blocks):
+            self.row_calls[tm] += 1
+        self.tiles_total = (self.tiles_total + blocks * ((self.out_features + self.TILE_COLS - 1) // self.TILE_COLS)) & 0xFFFFFFFF
+        return self.epoch, [c & 0xFFFFFFFF for c in self.row_calls[:blocks]], self.tiles_total
+
+    def snapshot(self):
+        return self.epoch, list(self.row_calls), self.tiles_total
+
+    def restore(self, snap) -> None:
+        self.epoch, self.row_calls, self.tiles_total = snap[0], list(snap[1]), snap[2]
+
+
 class FusedOutputProjection:
     """Row-parallel output projection whose tensor-parallel sum travels inside the library's kernels
     (``ca_oproj_allreduce``: a tcgen05 GEMM that stores partial tiles into the owning rank's memory, a
@@ -98,11 +131,9 @@ class FusedOutputProjection:
         self.world = dist.get_world_size(self.group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
         self.max_rows, self.N, self.dtype, self.device = int(max_rows), int(out_features), dtype, torch.device(device)
-        self.epoch = 0
+        self.ledger = ProjectionCallLedger(self.max_rows, self.N)
         self.phases = 7   # all three launches; a subset only for tests and timing (see ca_oproj_params.phases)
         self.mode = int(mode)   # 0: one exchange on two ranks, reduce-scatter + all-gather beyond; 1 / 2 force either
-        self._row_calls = [0] * ((self.max_rows + 127) // 128)   # calls that covered each block of 128 rows
-        self._tiles_total = 0
         self._stage_bytes = 0
         self.wait_limit_ns = int(wait_limit_s * 1e9)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
@@ -145,18 +176,12 @@ class FusedOutputProjection:
         K = x.shape[-1]
         a = x.reshape(-1, K)
         M = a.shape[0]
-        if M > self.max_rows:
-            raise ValueError(f"{M} rows exceed the buffers of this projection ({self.max_rows})")
         if a.stride(1) != 1 or weight.stride(1) != 1 or weight.shape != (self.N, K) or a.dtype != self.dtype or weight.dtype != self.dtype:
             raise ValueError("x must be [..., K] and weight [N, K], both K-contiguous and of the projection's dtype")
-        self.epoch += 1
-        blocks = (M + 127) // 128
-        for tm in range(blocks):
-            self._row_calls[tm] += 1
-        self._tiles_total = (self._tiles_total + self._lib.load().ca_oproj_tile_count(M, self.N)) & 0xFFFFFFFF
-        row_epochs = (C.c_uint32 * blocks)(*[c & 0xFFFFFFFF for c in self._row_calls[:blocks]])
+        epoch, row_calls, tiles_total = self.ledger.next_call(M)
+        row_epochs = (C.c_uint32 * len(row_calls))(*row_calls)
         p = self._lib.OprojParams()
-        p.mode, p.stage_bytes, p.done_tiles_total = self.mode, self._stage_bytes, self._tiles_total
+        p.mode, p.stage_bytes, p.done_tiles_total = self.mode, self._stage_bytes, tiles_total
         p.row_epochs = C.cast(row_epochs, C.POINTER(C.c_uint32))
         p.a, p.a_stride_m, p.w, p.w_stride_n = a.data_ptr(), a.stride(0), weight.data_ptr(), weight.stride(0)
         p.M, p.N, p.K, p.dtype = M, self.N, K, ops._DTYPES[self.dtype]
@@ -167,7 +192,7 @@ class FusedOutputProjection:
             p.stage = C.cast(arrays["stage"], C.POINTER(C.c_void_p))
             p.tile_counters = C.cast(arrays["tiles"], C.POINTER(C.c_void_p))
             p.done_counters = C.cast(arrays["done"], C.POINTER(C.c_void_p))
-        p.out_stride_m, p.epoch, p.wait_limit_ns, p.status = self.N, self.epoch, self.wait_limit_ns, self.status.data_ptr()
+        p.out_stride_m, p.epoch, p.wait_limit_ns, p.status = self.N, epoch, self.wait_limit_ns, self.status.data_ptr()
         p.phases = self.phases
         self._lib.check(self._lib.load().ca_oproj_allreduce(C.byref(p), ops._stream()), "ca_oproj_allreduce")
         return self.out[:M].view(*lead, self.N)

@@ -75,9 +75,9 @@ def main() -> None:
     results = {}
     for name, fused in routes.items():
         phase_us = {}
-        start = (fused.epoch, list(fused._row_calls), fused._tiles_total)
+        start = fused.ledger.snapshot()
         for pname, mask in (("gemm_and_push", 1), ("reduce", 2), ("final_wait", 4)):
-            fused.epoch, fused._row_calls, fused._tiles_total = start[0], list(start[1]), start[2]
+            fused.ledger.restore(start)
             fused.phases = mask
             phase_us[pname] = round(timed(lambda: fused(x, w)), 1)
         fused.phases = 7

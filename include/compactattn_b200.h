@@ -547,6 +547,16 @@ int ca_oproj_scratch_bytes(int M_max, int N, int world, size_t* stage_bytes, siz
 int ca_oproj_tile_count(int M, int N);
 int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream);
 
+/*
+ * Self-test of the bounded device-side wait (no counterpart in the reference).  Every kernel of the library
+ * that waits on an mbarrier (TMA arrivals, tensor-core commits, hand-offs between warp roles) does so through
+ * one routine that gives up after a time limit, raises the CTA's abort flag and lets the kernel drain and return
+ * with CA_STATUS_TIMEOUT instead of hanging.  This entry point runs that routine on a barrier nothing arrives on:
+ * one small CTA waits limit_ns (at most 1 s), then ORs CA_STATUS_TIMEOUT into *status and stores the time it
+ * waited (nanoseconds of the GPU's global timer) into *waited_ns (optional).  The context stays usable.
+ */
+int ca_selftest_bounded_wait(uint64_t limit_ns, int32_t* status, uint64_t* waited_ns, ca_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * One chunk of one layer in one call
  * ---------------------------------------------------------------------------------------- */

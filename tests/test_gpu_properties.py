@@ -230,3 +230,26 @@ def test_step_replays_from_a_cuda_graph(ops):
             assert torch.equal(a, b)
         score.copy_(torch.randn(score.shape, generator=g))   # new scores, same buffers: the graph follows
         q.copy_(torch.randn(q.shape, generator=g).to(torch.bfloat16))
+
+
+def test_a_bounded_wait_runs_out_and_the_context_stays_usable(ops):
+    """The wait routine behind every mbarrier wait of the tcgen05 / TMA kernels, on a barrier nothing arrives on:
+    it must give up after the limit (not before, not much later), report CA_STATUS_TIMEOUT, and leave the
+    context able to run the attention kernel afterwards."""
+    from compactattention_b200 import _lib
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    waited = torch.zeros(1, dtype=torch.int64, device="cuda")
+    limit_ns = 3_000_000   # 3 ms
+    rc = _lib.load().ca_selftest_bounded_wait(limit_ns, status.data_ptr(), waited.data_ptr(), ops._stream())
+    assert rc == 0, _lib.load().ca_last_error()
+    torch.cuda.synchronize()
+    assert int(status.item()) & _lib.CA_STATUS_TIMEOUT
+    assert limit_ns <= int(waited.item()) < 20 * limit_ns
+    assert _lib.load().ca_selftest_bounded_wait(0, status.data_ptr(), None, ops._stream()) == -1   # limits are bounded themselves
+    # the context is intact: a small attention call still runs and reports no timeout
+    q = torch.randn((1, 128, 4, 128), device="cuda").to(torch.bfloat16)
+    k = torch.randn((1, 256, 2, 128), device="cuda").to(torch.bfloat16)
+    st2 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.attn_compact(q, ops.KvCacheView.from_seq_first(k, k.clone()), 256, 2, None, None, status=st2)
+    torch.cuda.synchronize()
+    assert int(st2.item()) == 0 and torch.isfinite(out.float()).all()

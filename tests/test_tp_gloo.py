@@ -103,3 +103,56 @@ def test_rank_failure_before_collective_times_out_not_hangs():
     assert "injected failure" in res.get("error1", "")
     # rank 0 entered the all-reduce alone and got an error from the process-group time-out
     assert "error0" in res, res
+
+
+def _ledger_worker(rank, world, port, result_dict):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    try:
+        from compactattention_b200 import _lib
+        ledger = tp.ProjectionCallLedger(1024, 4096)
+        states = []
+        for rows in (1024, 232, 1, 1024, 129):   # full chunks, a ragged last chunk, a decode step
+            epoch, row_epochs, tiles = ledger.next_call(rows)
+            assert tiles == sum(_lib.load().ca_oproj_tile_count(r, 4096) for r in (1024, 232, 1, 1024, 129)[:epoch])
+            states.append([epoch, tiles] + row_epochs + [0] * (8 - len(row_epochs)))
+        mine = torch.tensor(states, dtype=torch.int64)
+        gathered = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        # CPU tensors never take the fused kernels: the library GEMM + all-reduce route stays in charge
+        g = torch.Generator().manual_seed(3)
+        x_all = torch.randn((world, 4, 64), generator=g)
+        w_all = torch.randn((world, 256, 64), generator=g)
+        assert not tp.fused_projection_applies(x_all[rank], w_all[rank], None, 1024)
+        y = torch.nn.functional.linear(x_all[rank], w_all[rank])
+        tp.reduce_layer_output(y)
+        if rank == 0:
+            result_dict["same_ledgers"] = all(torch.equal(gathered[0], t) for t in gathered)
+            result_dict["last_state"] = states[-1]
+            result_dict["sum_ok"] = bool(torch.allclose(y, sum(x_all[r] @ w_all[r].T for r in range(world)), atol=1e-4))
+    except Exception as exc:
+        result_dict[f"error{rank}"] = f"{type(exc).__name__}: {exc}"
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_projection_ledgers_agree_across_ranks_and_cpu_tensors_take_the_library_route():
+    """The counters of the fused output projection only grow; their targets come from a ledger every rank keeps
+    by itself.  Two gloo ranks issue the same calls (row counts that shrink and grow) and must hold identical
+    ledgers; a block of 128 rows that a short call did not cover keeps its old target."""
+    port = _free_port()
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_ledger_worker, args=(2, port, results), nprocs=2, join=True)
+        res = dict(results)
+    assert not [k for k in res if k.startswith("error")], res
+    assert res["same_ledgers"] and res["sum_ok"]
+    # after 1024, 232, 1, 1024, 129 rows: call 5; row block 0 covered 5 times, block 1 four times (not by the
+    # decode step), blocks 2..7 twice
+    assert res["last_state"][0] == 5 and res["last_state"][2:4] == [5, 4]
+    ledger = tp.ProjectionCallLedger(256, 512)
+    with pytest.raises(ValueError):
+        ledger.next_call(257)
