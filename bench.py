@@ -282,7 +282,9 @@ def run_native(args):
     cfg = CompactAttnLlamaConfig(hidden_size=hidden_size, num_attention_heads=HQ, num_key_value_heads=HKV, head_dim=D,
                                  seerattn_gate_type="Qavg_Kavg", seerattn_gate_force_double=True, seerattn_gate_block_size=BS,
                                  seerattn_sparsity_method="topk", seerattn_topk_ratio=(num, den),
-                                 seerattn_compactattn_keep_recent_blocks=2, max_position_embeddings=K, attention_bias=True)
+                                 seerattn_compactattn_keep_recent_blocks=2, max_position_embeddings=K, attention_bias=True,
+                                 # e2e at N > 1: o_proj and its sum over the ranks through the fused kernels
+                                 compactattn_fused_oproj_rows=Q if world in FUSED_PROJECTION_WORLDS else 0)
     inv = 1.0 / (500000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
     ang = torch.arange(K - Q, K, dtype=torch.float32).view(-1, 1) * inv.view(1, -1)
     ang = torch.cat([ang, ang], dim=-1)
@@ -857,6 +859,10 @@ def run_reference(args):
         "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+# world sizes at which the fused output projection measured faster than a library GEMM + NCCL all-reduce
+FUSED_PROJECTION_WORLDS = (2,)
 
 
 def main():
