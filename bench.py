@@ -57,6 +57,8 @@ def parse_args():
     ap.add_argument("--sustained-seconds", type=float, default=1.0)
     ap.add_argument("--dependent-launch", action="store_true",
                     help="enqueue programmatic dependent launches instead of plain ones (for A/B timing)")
+    ap.add_argument("--nccl-all-reduce", action="store_true",
+                    help="N > 1: NCCL for the layer-output all-reduce of the step even where the library's own exchange is the default")
     ap.add_argument("--two-launch-selection", action="store_true",
                     help="gate scores and rule + table as two launches (the form before ca_gate_score_select; for A/B timing)")
     return ap.parse_args()
@@ -326,6 +328,9 @@ def run_native(args):
         st.kv.append(layers[-1]["k_chunk"], layers[-1]["v_chunk"], position=K - Q)
         del t
     reduce_buf = torch.zeros((1, Q, HQ * D), dtype=torch.bfloat16, device=dev) if world > 1 else None
+    own_exchange = None
+    if world in OWN_ALL_REDUCE_WORLDS and not args.nccl_all_reduce:
+        own_exchange = tp.shared_fused_projection(Q, HQ * D, dev, torch.bfloat16)   # the module's e2e path shares it
     rope_chunk = (cos[:, Pb:], sin[:, Pb:])
 
     # ---- one step = one pass of the path for one chunk, as a list of stages (one launch each, the
@@ -353,7 +358,10 @@ def run_native(args):
         else:   # scores, row rule, Block-Union and table in one launch: the logits never leave the SM
             out = [("gate_prepare", prepare), ("gate_score_select", score_select), ("attention", attention)]
         if world > 1:
-            out.append(("all_reduce", lambda: tp.reduce_layer_output(reduce_buf)))
+            if own_exchange is not None:   # the library's own all-reduce over peer memory (ca_oproj_allreduce without the GEMM)
+                out.append(("all_reduce", lambda: own_exchange.all_reduce(reduce_buf)))
+            else:
+                out.append(("all_reduce", lambda: tp.reduce_layer_output(reduce_buf)))
         return out
 
     def step(L, attn_events=None):
@@ -597,6 +605,9 @@ def run_native(args):
             "kv_len": K, "chunk": Q, "density_target": args.density,
             "selected_past_blocks_per_kv_head": round(sel_blocks / hkv, 1), "past_blocks": Pb,
             "parallelism": f"tp{world} (KV-head sharded)" if world > 1 else "single GPU",
+            "layer_output_all_reduce": (None if world == 1 else
+                                        ("library exchange over peer memory (ca_oproj_allreduce without the GEMM)"
+                                         if own_exchange is not None else "NCCL")),
             "l2": f"steps rotate over {len(layers)} layer states ({len(layers) * 2 * K * hkv * D * 2 / 2**30:.1f} GiB of KV), more than L2",
             "launches_per_step": launches / args.steps,
             "programmatic_dependent_launch": args.dependent_launch,
@@ -863,6 +874,8 @@ def run_reference(args):
 
 # world sizes at which the fused output projection measured faster than a library GEMM + NCCL all-reduce
 FUSED_PROJECTION_WORLDS = (2,)
+# world sizes at which the library's own exchange measured faster than NCCL's all-reduce of the layer output
+OWN_ALL_REDUCE_WORLDS = (2,)
 
 
 def main():

@@ -283,6 +283,49 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (tid == 0 && sh->abort_flag && a.status) atomicOr(a.status, CA_STATUS_TIMEOUT);
 }
 
+// The exchange without the GEMM: `src` already holds this rank's partial [M, N] (a_stride_m elements between
+// rows) and is pushed tile by tile exactly as the GEMM's epilogue would push it.  One CTA per 128 x 256 tile,
+// 256 threads, 16 bytes per thread and step (a warp covers one 512-byte tile row), all loads of a pass issued
+// before its stores.
+template <typename T>
+__global__ void __launch_bounds__(256) oproj_push_kernel(const T* __restrict__ src, long long src_stride_m, const GemmArgs a) {
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();  // nothing in global memory is touched before this
+  const int tile = blockIdx.x;
+  const int tm = tile / a.tiles_n, tn = tile % a.tiles_n;
+  const int owner = tile % a.world;
+  const int slot = a.one_shot ? tile : tile / a.world;
+  const int n_dst = a.one_shot ? a.world : 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rows_live = min(kBM, a.M - tm * kBM);
+  const T* tile_src = src + static_cast<long long>(tm * kBM) * src_stride_m + tn * kBN + lane * 8;
+  for (int r0 = warp; r0 < rows_live; r0 += 8 * 8) {   // 8 warps, 8 rows each per pass
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int r = r0 + u * 8;
+      v[u] = r < rows_live ? *reinterpret_cast<const uint4*>(tile_src + static_cast<long long>(r) * src_stride_m) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    for (int di = 0; di < n_dst; ++di) {
+      const int d = a.one_shot ? (a.rank + 1 + di) % a.world : owner;   // the peers first, this rank last
+      T* dst = reinterpret_cast<T*>(a.stage[d]) + a.buf_off_elems + (static_cast<long long>(a.rank) * a.slot_tiles + slot) * kTileElems +
+               lane * 8;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int r = r0 + u * 8;
+        if (r < rows_live) *reinterpret_cast<uint4*>(dst + static_cast<long long>(r) * kBN) = v[u];
+      }
+    }
+  }
+  // the partial tile is out: make it visible system-wide, then tell its reader(s)
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < n_dst) {
+    const int d = a.one_shot ? (a.rank + 1 + threadIdx.x) % a.world : owner;
+    red_add_release_sys(a.tile_counters[d] + slot, 1u);
+  }
+}
+
 struct ReduceArgs {
   int M, N, tiles_n, n_tiles, world, rank, tiles_per_owner;
   int one_shot, slot_tiles;            // as in GemmArgs
@@ -401,13 +444,17 @@ int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream_) {
   using namespace ca;
   using namespace ca::oproj;
   CA_REQUIRE(p != nullptr, "params is null");
-  CA_REQUIRE(p->a && p->w, "a and w must be non-null");
+  CA_REQUIRE(p->a, "a must be non-null");
+  const bool reduce_only = p->w == nullptr;  // a is the partial [M, N] itself
+  CA_REQUIRE(!reduce_only || p->world > 1, "without w there is nothing to do on one rank");
   CA_REQUIRE(p->dtype == CA_DTYPE_BF16 || p->dtype == CA_DTYPE_F16, "dtype must be bf16 or f16");
-  CA_REQUIRE(p->M > 0 && p->N > 0 && p->K > 0, "M, N, K must be positive");
+  CA_REQUIRE(p->M > 0 && p->N > 0 && (reduce_only || p->K > 0), "M, N, K must be positive");
   CA_REQUIRE(p->N % kBN == 0, "N (%d) must be a multiple of %d", p->N, kBN);
-  CA_REQUIRE(p->K % kBK == 0, "K (%d) must be a multiple of %d", p->K, kBK);
-  CA_REQUIRE(p->a_stride_m % 8 == 0 && p->w_stride_n % 8 == 0 && p->out_stride_m % 8 == 0, "strides must be multiples of 8 elements");
+  CA_REQUIRE(reduce_only || p->K % kBK == 0, "K (%d) must be a multiple of %d", p->K, kBK);
+  CA_REQUIRE(p->a_stride_m % 8 == 0 && (reduce_only || p->w_stride_n % 8 == 0) && p->out_stride_m % 8 == 0,
+             "strides must be multiples of 8 elements");
   CA_REQUIRE((reinterpret_cast<uintptr_t>(p->a) | reinterpret_cast<uintptr_t>(p->w)) % 16 == 0, "a and w must be 16-byte aligned");
+  CA_REQUIRE(!reduce_only || p->a_stride_m >= p->N, "without w, a is the partial [M, N]: its row stride must cover N");
   CA_REQUIRE(p->world >= 1 && p->world <= kMaxWorld && p->rank >= 0 && p->rank < p->world, "world (1..%d) / rank out of range", kMaxWorld);
   CA_REQUIRE(p->out != nullptr, "out pointer list is null");
   for (int r = 0; r < p->world; ++r) {
@@ -428,10 +475,12 @@ int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream_) {
   if (dev.cc_major != 10) return fail(CA_ERR_UNSUPPORTED, "this library targets sm_100a; device is sm_%d%d", dev.cc_major, dev.cc_minor);
   const CUtensorMapDataType dt = p->dtype == CA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUtensorMap a_map, w_map;
-  rc = encode_2d(&a_map, dt, p->a, p->K, p->M, static_cast<uint64_t>(p->a_stride_m) * 2, kBK, kBM, "a");
-  if (rc != CA_OK) return rc;
-  rc = encode_2d(&w_map, dt, p->w, p->K, p->N, static_cast<uint64_t>(p->w_stride_n) * 2, kBK, kBN, "w");
-  if (rc != CA_OK) return rc;
+  if (!reduce_only) {
+    rc = encode_2d(&a_map, dt, p->a, p->K, p->M, static_cast<uint64_t>(p->a_stride_m) * 2, kBK, kBM, "a");
+    if (rc != CA_OK) return rc;
+    rc = encode_2d(&w_map, dt, p->w, p->K, p->N, static_cast<uint64_t>(p->w_stride_n) * 2, kBK, kBN, "w");
+    if (rc != CA_OK) return rc;
+  }
   GemmArgs g;
   g.M = p->M, g.N = p->N, g.K = p->K;
   g.tiles_n = p->N / kBN;
@@ -472,7 +521,12 @@ int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream_) {
     }
   }
   const uint32_t phases = p->phases ? p->phases : 7u;
-  if (phases & 1u) {
+  if ((phases & 1u) && reduce_only) {
+    // both 16-bit types move as bits
+    launch_kernel(oproj_push_kernel<uint16_t>, dim3(g.n_tiles), dim3(256), 0, stream, static_cast<const uint16_t*>(p->a),
+                  static_cast<long long>(p->a_stride_m), g);
+    CA_LAUNCH_CHECK("oproj_push_kernel");
+  } else if (phases & 1u) {
     if (p->dtype == CA_DTYPE_BF16) {
       launch_kernel(oproj_gemm_kernel<__nv_bfloat16>, dim3(g.n_tiles), dim3(kThreads), kSmemBytes, stream, a_map, w_map, g);
     } else {

@@ -6,8 +6,8 @@ its inputs exceed L2, so DRAM counters mean something and a capture ends by itse
     python -m compactattention_b200.kernel_case gather  [--kv-len 131072] [--density 0.2]
     python -m compactattention_b200.kernel_case append  [--chunk 8192]
     python -m compactattention_b200.kernel_case fpscore [--kv-len 131072]
-    python -m compactattention_b200.kernel_case select  [--kv-len 131072]      # select_rows + union_table
-    python -m compactattention_b200.kernel_case gate    [--kv-len 131072]      # gate_prepare + gate_scores
+    python -m compactattention_b200.kernel_case select  [--kv-len 131072]      # select_rows + union_table (stand-alone)
+    python -m compactattention_b200.kernel_case gate    [--kv-len 131072]      # gate_prepare + gate_scores_tc + select_rows with the fused union
 
 Shapes: 32 query / 8 KV heads, d = 128, block 64, chunk 1024 (unless ``--chunk``), bf16.  Prints the
 average time per launch from CUDA events (never quote it from a run under a profiler).
@@ -110,12 +110,17 @@ def main() -> None:
         st.cache.blocks_view().normal_(generator=g)   # stands in for the blocks of earlier chunks
         q, k = rnd(1, Q, HQ, D), rnd(1, Q, HKV, D)
 
+        from .chunk_driver import SelectionRule
+        rule = SelectionRule(rule="topk", softmax=False, topk_ratio=(1, 5), sink=1, local=2)
+
         def run():
             st.cache.length = pb   # the chunk's blocks are (re)appended after the past blocks
-            st.append_and_score(q, k, None, None)
+            st.append(q, k, None, None)
+            st.score_select(rule, HKV, BS)   # tensor-core scores, then rule + Block-Union + table
 
         us = _time(run, args.launches)
-        print(f"gate_prepare_kernel + gate_scores kernel: {K // BS} key blocks, {us:.1f} us per pair")
+        print(f"gate_prepare_kernel + gate_scores_tc_kernel + select_rows_kernel (fused union): {K // BS} key blocks, "
+              f"{us:.1f} us per chain")
 
 
 if __name__ == "__main__":

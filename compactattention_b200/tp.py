@@ -197,6 +197,35 @@ class FusedOutputProjection:
         self._lib.check(self._lib.load().ca_oproj_allreduce(C.byref(p), ops._stream()), "ca_oproj_allreduce")
         return self.out[:M].view(*lead, self.N)
 
+    def all_reduce(self, partial: torch.Tensor) -> torch.Tensor:
+        """Sum over the ranks of ``partial [..., N]`` (this rank's already projected output) through the same
+        exchange, without the GEMM: the library's own all-reduce over peer memory.  Returns a view of the shared
+        output buffer, valid until the next call."""
+        from . import ops
+        C = self._C
+        lead = partial.shape[:-1]
+        a = partial.reshape(-1, partial.shape[-1])
+        M = a.shape[0]
+        if a.shape[1] != self.N or a.stride(1) != 1 or a.dtype != self.dtype or self.world == 1:
+            raise ValueError("partial must be [..., N] of the projection's dtype, N contiguous, on more than one rank")
+        epoch, row_calls, tiles_total = self.ledger.next_call(M)
+        row_epochs = (C.c_uint32 * len(row_calls))(*row_calls)
+        p = self._lib.OprojParams()
+        p.mode, p.stage_bytes, p.done_tiles_total = self.mode, self._stage_bytes, tiles_total
+        p.row_epochs = C.cast(row_epochs, C.POINTER(C.c_uint32))
+        p.a, p.a_stride_m, p.w, p.w_stride_n = a.data_ptr(), a.stride(0), None, 0
+        p.M, p.N, p.K, p.dtype = M, self.N, 0, ops._DTYPES[self.dtype]
+        p.world, p.rank = self.world, self.rank
+        arrays = {k: self._array(v) for k, v in self._ptrs.items()}
+        p.out = C.cast(arrays["out"], C.POINTER(C.c_void_p))
+        p.stage = C.cast(arrays["stage"], C.POINTER(C.c_void_p))
+        p.tile_counters = C.cast(arrays["tiles"], C.POINTER(C.c_void_p))
+        p.done_counters = C.cast(arrays["done"], C.POINTER(C.c_void_p))
+        p.out_stride_m, p.epoch, p.wait_limit_ns, p.status = self.N, epoch, self.wait_limit_ns, self.status.data_ptr()
+        p.phases = self.phases
+        self._lib.check(self._lib.load().ca_oproj_allreduce(C.byref(p), ops._stream()), "ca_oproj_allreduce")
+        return self.out[:M].view(*lead, self.N)
+
     def check(self) -> None:
         """Raises if a device-side wait of an earlier call ran out (reads the status word: synchronises)."""
         if int(self.status.item()) & self._lib.CA_STATUS_TIMEOUT:

@@ -84,12 +84,25 @@ def main() -> None:
         total = timed(lambda: fused(x, w))
         fused.check()
         results[name] = {"fused_us": round(total, 1), "phase_us": phase_us}
+    # the exchange alone (no GEMM) against NCCL's all-reduce of the same [rows, hidden] tensor
+    y_part = torch.nn.functional.linear(x, w)
+    fused0 = routes["auto"]
+    got = fused0.all_reduce(y_part).float().clone()
+    ref = y_part.float().clone()
+    dist.all_reduce(ref)
+    ar_err = ((got - ref).abs() / (ref.abs() + 1.0)).max().item()
+    own_ar_us = timed(lambda: fused0.all_reduce(y_part))
+    fused0.check()
+    y_nccl = y_part.clone()
+    nccl_ar_us = timed(lambda: dist.all_reduce(y_nccl))
     lib_us = timed(library_route)
     gemm_us = timed(lambda: torch.nn.functional.linear(x, w))
     if rank == 0:
         print(json.dumps({"world": world, "rows": M, "hidden": N, "k_per_rank": K, "max_rel_err_vs_gemm_plus_allreduce": round(worst, 5),
                           "fused": results, "library_gemm_plus_nccl_allreduce_us": round(lib_us, 1),
-                          "library_gemm_alone_us": round(gemm_us, 1)}))
+                          "library_gemm_alone_us": round(gemm_us, 1),
+                          "all_reduce_alone": {"own_exchange_us": round(own_ar_us, 1), "nccl_us": round(nccl_ar_us, 1),
+                                               "max_rel_err": round(ar_err, 5)}}))
     dist.destroy_process_group()
 
 

@@ -515,7 +515,9 @@ int ca_rope_append(const ca_rope_append_params* p, ca_stream_t stream);
 typedef struct ca_oproj_params {
   const void* a;      /* [M, K] this rank's attention output, K contiguous */
   int64_t a_stride_m;
-  const void* w;      /* [N, K] this rank's input columns of the projection weight, K contiguous */
+  const void* w;      /* [N, K] this rank's input columns of the projection weight, K contiguous; NULL = no GEMM:
+                         a is then this rank's partial [M, N] itself (a_stride_m >= N, K ignored) and the call is
+                         the sum over the ranks alone, an all-reduce through the same exchange (world > 1) */
   int64_t w_stride_n;
   int32_t M, N, K;    /* N a multiple of 256, K a multiple of 64 */
   int32_t dtype;      /* CA_DTYPE_BF16 or CA_DTYPE_F16 */

@@ -28,8 +28,12 @@ def arr(ptrs):
 def call(lib, a, w, rank, world, bufs, epoch, status, limit_ns=0, phases=0, mode=0, row_epochs=None, done_tiles_total=0):
     from compactattention_b200 import ops
     p = lib.OprojParams()
-    p.a, p.a_stride_m, p.w, p.w_stride_n = a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0)
-    p.M, p.N, p.K, p.dtype = a.shape[0], w.shape[0], a.shape[1], ops._DTYPES[a.dtype]
+    if w is None:   # a is the partial [M, N] itself: the exchange without the GEMM
+        p.a, p.a_stride_m, p.w, p.w_stride_n = a.data_ptr(), a.stride(0), None, 0
+        p.M, p.N, p.K, p.dtype = a.shape[0], a.shape[1], 0, ops._DTYPES[a.dtype]
+    else:
+        p.a, p.a_stride_m, p.w, p.w_stride_n = a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0)
+        p.M, p.N, p.K, p.dtype = a.shape[0], w.shape[0], a.shape[1], ops._DTYPES[a.dtype]
     p.world, p.rank = world, rank
     keep = []
     for name in ("out", "stage", "tile_counters", "done_counters"):
@@ -38,7 +42,7 @@ def call(lib, a, w, rank, world, bufs, epoch, status, limit_ns=0, phases=0, mode
         k, ptr = arr(bufs[name])
         keep.append(k)
         setattr(p, name, ptr)
-    p.out_stride_m, p.epoch, p.phases, p.wait_limit_ns, p.status = w.shape[0], epoch, phases, limit_ns, status.data_ptr()
+    p.out_stride_m, p.epoch, p.phases, p.wait_limit_ns, p.status = p.N, epoch, phases, limit_ns, status.data_ptr()
     p.mode, p.stage_bytes, p.done_tiles_total = mode, bufs.get("stage_bytes", 0), done_tiles_total
     if row_epochs is not None:
         re_arr = (C.c_uint32 * len(row_epochs))(*row_epochs)
@@ -141,6 +145,28 @@ def test_row_counts_may_change_between_calls(lib, world, mode):
         tol = 2.0 ** -8 * (sum(p.abs() for p in parts) + want.abs()) + 1e-3
         for r in range(world):
             assert ((outs[r][:M].float() - want).abs() <= tol).all(), (epoch, M, r)
+
+
+@pytest.mark.parametrize("world,M,N,mode", [(2, 1024, 4096, 0), (2, 1000, 512, 1), (4, 1024, 4096, 0), (8, 130, 1024, 0)])
+def test_all_reduce_of_existing_partials(lib, world, M, N, mode):
+    """w == NULL: the ranks' [M, N] partials are summed through the same exchange without the GEMM - the library's
+    own all-reduce.  Emulated ranks on one device; the result must be the fp32 sum rounded once, on every rank."""
+    dtype = torch.bfloat16
+    g = torch.Generator(device="cuda").manual_seed(world + M)
+    outs, stages, counters, bufs = make_world(lib, world, 1024, N, dtype)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for epoch in (1, 2):
+        parts = [torch.randn((M, N), device="cuda", generator=g).to(dtype) for _ in range(world)]
+        for o in outs:
+            o.fill_(float("nan"))
+        for phase in (1, 2, 4):
+            for r in range(world):
+                call(lib, parts[r], None, r, world, bufs, epoch, status, phases=phase, mode=mode)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        want = sum(p.float() for p in parts).to(dtype)   # exact partials, one rounding of the fp32 sum
+        for r in range(world):
+            assert torch.equal(outs[r][:M], want), (epoch, r)
 
 
 def test_a_wait_that_nothing_satisfies_ends_with_the_status_bit(lib):
