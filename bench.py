@@ -57,6 +57,11 @@ def parse_args():
     ap.add_argument("--sustained-seconds", type=float, default=1.0)
     ap.add_argument("--dependent-launch", action="store_true",
                     help="enqueue programmatic dependent launches instead of plain ones (for A/B timing)")
+    ap.add_argument("--no-call-lists", action="store_true",
+                    help="fill the parameter blocks of every library call afresh in every step (the tensor-level wrappers) "
+                         "instead of re-issuing the calls recorded once per layer state")
+    ap.add_argument("--own-all-reduce", action="store_true",
+                    help="N > 1: the library's own exchange for the layer-output all-reduce even where NCCL is the default")
     ap.add_argument("--nccl-all-reduce", action="store_true",
                     help="N > 1: NCCL for the layer-output all-reduce of the step even where the library's own exchange is the default")
     ap.add_argument("--two-launch-selection", action="store_true",
@@ -329,7 +334,7 @@ def run_native(args):
         del t
     reduce_buf = torch.zeros((1, Q, HQ * D), dtype=torch.bfloat16, device=dev) if world > 1 else None
     own_exchange = None
-    if world in OWN_ALL_REDUCE_WORLDS and not args.nccl_all_reduce:
+    if (world in OWN_ALL_REDUCE_WORLDS or (args.own_all_reduce and world > 1)) and not args.nccl_all_reduce:
         own_exchange = tp.shared_fused_projection(Q, HQ * D, dev, torch.bfloat16)   # the module's e2e path shares it
     rope_chunk = (cos[:, Pb:], sin[:, Pb:])
 
@@ -365,15 +370,32 @@ def run_native(args):
         return out
 
     def step(L, attn_events=None):
-        for name, fn in stages(L):
+        """One step.  The library calls of a stage are re-issued from the call list recorded for this layer state
+        (same entry points, same parameter blocks: a host that keeps its parameter blocks between chunks, as
+        `GateLayerStep` does); the collective is issued afresh."""
+        recorded = L.get("calls")
+        for name, fn in (recorded if recorded is not None else stages(L)):
+            run = fn.run if isinstance(fn, _lib.CallList) else fn
             if name == "attention" and attn_events is not None:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-                fn()
+                run()
                 e1.record()
                 attn_events.append((e0, e1))
             else:
+                run()
+
+    def record_calls(L):
+        """Runs every stage of `L` once and keeps its library calls; the collective stays a Python call."""
+        kept = []
+        for name, fn in stages(L):
+            if name == "all_reduce":
+                kept.append((name, fn))
+                continue
+            with _lib.record() as calls:
                 fn()
+            kept.append((name, calls))
+        L["calls"] = kept
 
     def barrier():
         if world > 1:
@@ -384,6 +406,9 @@ def run_native(args):
     def max_ranks(vals):
         return tp.max_over_ranks(vals, dev)
 
+    if not args.no_call_lists:
+        for L in layers:
+            record_calls(L)
     for i in range(max(args.warmup, 3)):
         step(layers[i % len(layers)])
     barrier()
@@ -611,6 +636,8 @@ def run_native(args):
             "l2": f"steps rotate over {len(layers)} layer states ({len(layers) * 2 * K * hkv * D * 2 / 2**30:.1f} GiB of KV), more than L2",
             "launches_per_step": launches / args.steps,
             "programmatic_dependent_launch": args.dependent_launch,
+            "host_side": ("library calls re-issued from parameter blocks kept per layer state" if not args.no_call_lists
+                          else "parameter blocks filled afresh every step by the tensor-level wrappers"),
             "step_us": {k: round(v, 1) for k, v in step_stats.items()},
             "attention_us": {k: round(v, 1) for k, v in attn_stats.items()},
             "stage_us": stage_us,
@@ -873,9 +900,9 @@ def run_reference(args):
 
 
 # world sizes at which the fused output projection measured faster than a library GEMM + NCCL all-reduce
-FUSED_PROJECTION_WORLDS = (2,)
+FUSED_PROJECTION_WORLDS = (2, 8)
 # world sizes at which the library's own exchange measured faster than NCCL's all-reduce of the layer output
-OWN_ALL_REDUCE_WORLDS = (2,)
+OWN_ALL_REDUCE_WORLDS = (2, 4, 8)
 
 
 def main():

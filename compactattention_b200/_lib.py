@@ -295,7 +295,71 @@ class MissingLibraryError(RuntimeError):
     pass
 
 
-def load() -> C.CDLL:
+class CallList:
+    """Library calls recorded once (see ``record``) and re-issued as they were: the same entry points with the
+    same parameter blocks, pointers and stream.  What a host keeps between chunks when shapes and buffers do
+    not change (a benchmark loop, a layer at a fixed chunk position): replaying costs one foreign call per
+    entry, not the Python that filled the structs.  The blocks hold raw device pointers: the tensors they came
+    from must stay alive, and calls whose parameters change per call (epochs, positions) must not be replayed."""
+
+    def __init__(self):
+        self.calls = []
+
+    def run(self) -> None:
+        for name, fn, args in self.calls:
+            rc = fn(*args)
+            if rc != CA_OK:
+                check(rc, name)
+
+
+# Entry points that enqueue work take the stream as their last argument; only these are recorded - except the
+# ones whose parameters must change from call to call (the exchange's epochs).
+_NEVER_RECORDED = {"ca_oproj_allreduce", "ca_selftest_bounded_wait"}
+_recording: "CallList | None" = None
+
+
+class _Recording:
+    def __enter__(self) -> CallList:
+        global _recording
+        if _recording is not None:
+            raise RuntimeError("library calls are already being recorded")
+        _recording = CallList()
+        return _recording
+
+    def __exit__(self, *exc) -> None:
+        global _recording
+        _recording = None
+
+
+def record() -> _Recording:
+    """``with record() as calls:`` runs the body normally and also keeps every enqueuing library call it makes
+    in ``calls`` (a ``CallList``)."""
+    return _Recording()
+
+
+class _Library:
+    """The loaded library.  Attribute access gives the foreign functions; while ``record()`` is active the
+    enqueuing ones are also appended to the recording."""
+
+    def __init__(self, cdll: C.CDLL):
+        self._cdll = cdll
+        self._wrapped = {}
+
+    def __getattr__(self, name):
+        fn = getattr(self._cdll, name)   # AttributeError for names the library does not export
+        if name not in _SIGNATURES or _SIGNATURES[name][1][-1:] != [C.c_void_p] or name in _NEVER_RECORDED:
+            return fn
+        w = self._wrapped.get(name)
+        if w is None:
+            def w(*args, _fn=fn, _name=name):
+                if _recording is not None:
+                    _recording.calls.append((_name, _fn, args))
+                return _fn(*args)
+            self._wrapped[name] = w
+        return w
+
+
+def load() -> "_Library":
     """Load the shared library once. Fails loudly: nothing in this package computes without it."""
     global _lib
     if _lib is not None:
@@ -311,8 +375,8 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)  # AttributeError here means header and library disagree
         fn.restype = restype
         fn.argtypes = argtypes
-    _lib = lib
-    return lib
+    _lib = _Library(lib)
+    return _lib
 
 
 def exported_names() -> list[str]:

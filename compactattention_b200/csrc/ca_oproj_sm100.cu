@@ -329,6 +329,7 @@ __global__ void __launch_bounds__(256) oproj_push_kernel(const T* __restrict__ s
 struct ReduceArgs {
   int M, N, tiles_n, n_tiles, world, rank, tiles_per_owner;
   int one_shot, slot_tiles;            // as in GemmArgs
+  int split;                           // CTAs per tile: 4, 8, 16 or 32
   long long buf_off_elems;
   uint32_t row_target[kMaxRowTiles];   // arrivals expected at a tile of row tile tm once this call's partials are in
   const void* stage_local;             // this rank's staging buffer
@@ -340,10 +341,13 @@ struct ReduceArgs {
   int32_t* status;
 };
 
-constexpr int kReduceSplit = 4;  // CTAs per owned tile (32 rows each): 4x the CTAs of one per tile fill the GPU
+constexpr int kMaxReduceSplit = 32;  // a tile's 128 rows go to 4, 8, 16 or 32 CTAs: enough CTAs to fill the GPU when a
+                                     // rank owns few tiles; a finished part counts kMaxReduceSplit / split, so a
+                                     // finished tile always adds kMaxReduceSplit to the ranks' done counters
 
-// kReduceSplit CTAs per tile this rank owns: sum of the `world` staged partials -> every rank's output.
-template <typename T>
+// `split` CTAs per tile this rank reduces: sum of the `world` staged partials -> every rank's output.
+// W: compile-time bound of the rank count (2, 4 or 8) - the loads of all partials are unrolled to it.
+template <typename T, int W>
 __global__ void __launch_bounds__(256) oproj_reduce_kernel(const ReduceArgs a) {
   // Launched programmatically behind the GEMM and deliberately without a grid-dependency wait: everything this
   // kernel reads is guarded by a tile counter (release by the producer, acquire here), so its CTAs may take
@@ -351,7 +355,7 @@ __global__ void __launch_bounds__(256) oproj_reduce_kernel(const ReduceArgs a) {
   // The GEMM itself is a plain launch, so nothing of an earlier call or of the producer of A is overtaken.
   ptx::grid_launch_dependents();
   __shared__ int sh_ok;
-  const int lt = blockIdx.x / kReduceSplit, part = blockIdx.x % kReduceSplit;   // lt: tile slot and counter on this rank
+  const int lt = blockIdx.x / a.split, part = blockIdx.x % a.split;   // lt: tile slot and counter on this rank
   const int tile = a.one_shot ? lt : lt * a.world + a.rank;
   if (tile >= a.n_tiles) return;
   if (threadIdx.x == 0) {
@@ -366,19 +370,28 @@ __global__ void __launch_bounds__(256) oproj_reduce_kernel(const ReduceArgs a) {
     const long long src_stride = static_cast<long long>(a.slot_tiles) * kTileElems;
     const int d0 = a.one_shot ? a.rank : 0, d1 = a.one_shot ? a.rank + 1 : a.world;   // one-shot: only this rank's output
     // 8 elements (16 bytes) per thread and step; a row of the tile is 32 such groups
-    constexpr int kPartGroups = kTileElems / 8 / kReduceSplit;
-    for (int e = part * kPartGroups + threadIdx.x; e < (part + 1) * kPartGroups; e += 256) {
+    const int part_groups = kTileElems / 8 / a.split;
+    for (int e = part * part_groups + threadIdx.x; e < (part + 1) * part_groups; e += 256) {
       const int r = e / (kBN / 8), c8 = e % (kBN / 8);
       if (tm * kBM + r >= a.M) break;  // rows are visited in order: the rest lies beyond M too
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int s = 0; s < a.world; ++s) {
-        // L2 loads: the partials arrived from other GPUs, a line cached in L1 by an earlier call would be stale
-        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(base + s * src_stride + static_cast<long long>(e) * 8));
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      // L2 loads (the partials arrived from other GPUs; a line cached in L1 by an earlier call would be stale), all
+      // of them in flight before the first addition
+      uint4 raw[W];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = unpack2<T>(w[i]);
-          acc[2 * i] += f.x, acc[2 * i + 1] += f.y;
+      for (int s = 0; s < W; ++s) {
+        raw[s] = s < a.world ? __ldcg(reinterpret_cast<const uint4*>(base + s * src_stride + static_cast<long long>(e) * 8))
+                             : make_uint4(0u, 0u, 0u, 0u);
+      }
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s = 0; s < W; ++s) {
+        if (s < a.world) {
+          const uint32_t w[4] = {raw[s].x, raw[s].y, raw[s].z, raw[s].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = unpack2<T>(w[i]);
+            acc[2 * i] += f.x, acc[2 * i + 1] += f.y;
+          }
         }
       }
       uint4 o;
@@ -392,7 +405,7 @@ __global__ void __launch_bounds__(256) oproj_reduce_kernel(const ReduceArgs a) {
   __syncthreads();
   // the finished tile is in every rank's output: every rank's count of delivered tiles moves on.  (After a
   // timeout nothing is counted: the other ranks' final waits then run out too and report it.)
-  if (threadIdx.x < a.world && ok) red_add_release_sys(a.done_counters[threadIdx.x], 1u);  // kReduceSplit per tile
+  if (threadIdx.x < a.world && ok) red_add_release_sys(a.done_counters[threadIdx.x], static_cast<uint32_t>(kMaxReduceSplit / a.split));
 }
 
 __global__ void oproj_wait_kernel(const uint32_t* done_local, uint32_t target, unsigned long long limit_ns, int32_t* status) {
@@ -539,6 +552,8 @@ int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream_) {
   r.M = p->M, r.N = p->N, r.tiles_n = g.tiles_n, r.n_tiles = g.n_tiles, r.world = p->world, r.rank = p->rank;
   r.tiles_per_owner = g.tiles_per_owner;
   r.one_shot = g.one_shot, r.slot_tiles = g.slot_tiles, r.buf_off_elems = g.buf_off_elems;
+  r.split = 4;
+  while (r.split < kMaxReduceSplit && g.slot_tiles * r.split < 2 * dev.sm_count) r.split *= 2;
   for (int tm = 0; tm < kMaxRowTiles; ++tm) {
     const uint32_t calls = (p->row_epochs && tm < ceil_div(p->M, kBM)) ? p->row_epochs[tm] : p->epoch;
     r.row_target[tm] = calls * static_cast<uint32_t>(p->world);
@@ -553,18 +568,24 @@ int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream_) {
   r.wait_limit_ns = g.wait_limit_ns;
   r.status = p->status;
   if (phases & 2u) {
-    const dim3 grid(g.slot_tiles * kReduceSplit);
-    if (p->dtype == CA_DTYPE_BF16) {
-      launch_kernel_as(true, oproj_reduce_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, r);
+    const dim3 grid(g.slot_tiles * r.split);
+    const bool bf = p->dtype == CA_DTYPE_BF16;
+    if (p->world <= 2) {
+      if (bf) launch_kernel_as(true, oproj_reduce_kernel<__nv_bfloat16, 2>, grid, dim3(256), 0, stream, r);
+      else launch_kernel_as(true, oproj_reduce_kernel<__half, 2>, grid, dim3(256), 0, stream, r);
+    } else if (p->world <= 4) {
+      if (bf) launch_kernel_as(true, oproj_reduce_kernel<__nv_bfloat16, 4>, grid, dim3(256), 0, stream, r);
+      else launch_kernel_as(true, oproj_reduce_kernel<__half, 4>, grid, dim3(256), 0, stream, r);
     } else {
-      launch_kernel_as(true, oproj_reduce_kernel<__half>, grid, dim3(256), 0, stream, r);
+      if (bf) launch_kernel_as(true, oproj_reduce_kernel<__nv_bfloat16, 8>, grid, dim3(256), 0, stream, r);
+      else launch_kernel_as(true, oproj_reduce_kernel<__half, 8>, grid, dim3(256), 0, stream, r);
     }
     CA_LAUNCH_CHECK("oproj_reduce_kernel");
   }
   if ((phases & 4u) && !one_shot) {
     const uint32_t done_tiles = p->done_tiles_total ? p->done_tiles_total : p->epoch * static_cast<uint32_t>(g.n_tiles);
     launch_kernel_as(true, oproj_wait_kernel, dim3(1), dim3(32), 0, stream, static_cast<const uint32_t*>(p->done_counters[p->rank]),
-                     done_tiles * static_cast<uint32_t>(kReduceSplit), static_cast<unsigned long long>(g.wait_limit_ns),
+                     done_tiles * static_cast<uint32_t>(kMaxReduceSplit), static_cast<unsigned long long>(g.wait_limit_ns),
                      p->status);
     CA_LAUNCH_CHECK("oproj_wait_kernel");
   }

@@ -123,3 +123,22 @@ def test_reference_arm_prints_the_contract_line():
     assert line["metric"].startswith("per-chunk attn latency") and line["value"] > 0
     assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"] == {"value": line["value"], "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+
+
+def test_recorded_calls_are_reissued_as_they_were(lib):
+    """`_lib.record()` keeps the enqueuing calls of its body; `CallList.run()` re-issues them and raises on a
+    failing return code.  (Null parameter blocks: the calls fail validation before touching a device.)"""
+    from compactattention_b200 import _lib
+
+    u = _lib.UnionParams()
+    with _lib.record() as calls:
+        assert lib.ca_union_table(ctypes.byref(u), None) == -1
+        assert lib.ca_abi_version() == 2          # not an enqueuing call: not recorded
+    assert [c[0] for c in calls.calls] == ["ca_union_table"]
+    with pytest.raises(RuntimeError, match="ca_union_table"):
+        calls.run()
+    assert lib.ca_union_table(ctypes.byref(u), None) == -1 and len(calls.calls) == 1   # nothing is recorded outside the block
+    with pytest.raises(RuntimeError):
+        with _lib.record():
+            with _lib.record():
+                pass
