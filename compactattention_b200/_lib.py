@@ -236,6 +236,7 @@ class OprojParams(C.Structure):
         ("mode", C.c_int32),
         ("stage_bytes", C.c_size_t),
         ("row_epochs", C.POINTER(C.c_uint32)),
+        ("stage_mc", C.c_void_p), ("out_mc", C.c_void_p),
         ("done_tiles_total", C.c_uint32),
     ]
 

@@ -133,7 +133,9 @@ class FusedOutputProjection:
         self.max_rows, self.N, self.dtype, self.device = int(max_rows), int(out_features), dtype, torch.device(device)
         self.ledger = ProjectionCallLedger(self.max_rows, self.N)
         self.phases = 7   # all three launches; a subset only for tests and timing (see ca_oproj_params.phases)
-        self.mode = int(mode)   # 0: one exchange on two ranks, reduce-scatter + all-gather beyond; 1 / 2 force either
+        self.mode = int(mode)   # 0: one exchange on two ranks, reduce-scatter + all-gather over peer stores beyond;
+                                # 1 / 2 force either; 3: through the NVLink switch (multimem), where it offers multicast
+        self._mc = None
         self._stage_bytes = 0
         self.wait_limit_ns = int(wait_limit_s * 1e9)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
@@ -159,6 +161,11 @@ class FusedOutputProjection:
             "tiles": list(handles[2].buffer_ptrs), "done": [p + 4 * n_tile_counters for p in handles[2].buffer_ptrs],
         }
         self._handles = handles
+        # NVLink-switch multicast addresses of the outputs and the staging buffers (0 where the fabric has none):
+        # mode 3 lets the switch do the additions (multimem.ld_reduce / multimem.st)
+        out_mc = int(getattr(handles[0], "multicast_ptr", 0) or 0)
+        stage_mc = int(getattr(handles[1], "multicast_ptr", 0) or 0)
+        self._mc = (stage_mc, out_mc) if (out_mc and stage_mc) else None
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)   # every rank's counters are zero before anyone's first call
 
@@ -183,6 +190,8 @@ class FusedOutputProjection:
         p = self._lib.OprojParams()
         p.mode, p.stage_bytes, p.done_tiles_total = self.mode, self._stage_bytes, tiles_total
         p.row_epochs = C.cast(row_epochs, C.POINTER(C.c_uint32))
+        if self._mc is not None:
+            p.stage_mc, p.out_mc = self._mc
         p.a, p.a_stride_m, p.w, p.w_stride_n = a.data_ptr(), a.stride(0), weight.data_ptr(), weight.stride(0)
         p.M, p.N, p.K, p.dtype = M, self.N, K, ops._DTYPES[self.dtype]
         p.world, p.rank = self.world, self.rank
@@ -213,6 +222,8 @@ class FusedOutputProjection:
         p = self._lib.OprojParams()
         p.mode, p.stage_bytes, p.done_tiles_total = self.mode, self._stage_bytes, tiles_total
         p.row_epochs = C.cast(row_epochs, C.POINTER(C.c_uint32))
+        if self._mc is not None:
+            p.stage_mc, p.out_mc = self._mc
         p.a, p.a_stride_m, p.w, p.w_stride_n = a.data_ptr(), a.stride(0), None, 0
         p.M, p.N, p.K, p.dtype = M, self.N, 0, ops._DTYPES[self.dtype]
         p.world, p.rank = self.world, self.rank

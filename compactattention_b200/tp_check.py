@@ -25,6 +25,7 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=1024)
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--switch", action="store_true", help="also time the form that reduces through the NVLink switch (multimem)")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -34,10 +35,12 @@ def main() -> None:
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     x = torch.randn((1, M, K), device=dev, generator=g).to(torch.bfloat16)
     w = (torch.randn((N, K), device=dev, generator=g) * 0.02).to(torch.bfloat16)
-    # two ranks exchange once (every partial tile to both ranks); the reduce-scatter + all-gather form is timed too
+    # the default form (two ranks: one exchange; more: through the NVLink switch where it offers multicast) and the
+    # reduce-scatter + all-gather form over plain peer stores
     routes = {"auto": tp.FusedOutputProjection(M, N, dev, torch.bfloat16)}
-    if world == 2:
-        routes["two_shot"] = tp.FusedOutputProjection(M, N, dev, torch.bfloat16, mode=1)
+    routes["two_shot"] = tp.FusedOutputProjection(M, N, dev, torch.bfloat16, mode=1)   # reduce-scatter + all-gather over peer stores
+    if world > 2 and args.switch and routes["auto"]._mc is not None:
+        routes["switch"] = tp.FusedOutputProjection(M, N, dev, torch.bfloat16, mode=3)        # additions done by the NVLink switch
     # correctness: three calls in a row (buffers reused), against GEMM + all-reduce in fp32
     worst = 0.0
     for _ in range(3):
@@ -93,6 +96,8 @@ def main() -> None:
     ar_err = ((got - ref).abs() / (ref.abs() + 1.0)).max().item()
     own_ar_us = timed(lambda: fused0.all_reduce(y_part))
     fused0.check()
+    two_shot_ar_us = timed(lambda: routes["two_shot"].all_reduce(y_part))
+    routes["two_shot"].check()
     y_nccl = y_part.clone()
     nccl_ar_us = timed(lambda: dist.all_reduce(y_nccl))
     lib_us = timed(library_route)
@@ -101,7 +106,8 @@ def main() -> None:
         print(json.dumps({"world": world, "rows": M, "hidden": N, "k_per_rank": K, "max_rel_err_vs_gemm_plus_allreduce": round(worst, 5),
                           "fused": results, "library_gemm_plus_nccl_allreduce_us": round(lib_us, 1),
                           "library_gemm_alone_us": round(gemm_us, 1),
-                          "all_reduce_alone": {"own_exchange_us": round(own_ar_us, 1), "nccl_us": round(nccl_ar_us, 1),
+                          "auto_form": "one exchange" if world == 2 else "reduce-scatter + all-gather",
+                          "all_reduce_alone": {"own_exchange_us": round(own_ar_us, 1), "own_two_shot_us": round(two_shot_ar_us, 1), "nccl_us": round(nccl_ar_us, 1),
                                                "max_rel_err": round(ar_err, 5)}}))
     dist.destroy_process_group()
 

@@ -533,11 +533,15 @@ typedef struct ca_oproj_params {
                       one that has not been launched) */
   uint64_t wait_limit_ns;
   int32_t* status; /* optional */
-  int32_t mode;    /* 0 = auto (one-shot on two ranks, else two-shot), 1 = two-shot, 2 = one-shot */
+  int32_t mode;    /* 0 = auto (one-shot on two ranks, two-shot beyond), 1 = two-shot, 2 = one-shot,
+                      3 = through the switch (needs stage_mc and out_mc; measured slower than two-shot at 4 GPUs) */
   size_t stage_bytes;          /* size of each staging buffer (checked against what the call needs) */
   const uint32_t* row_epochs;  /* HOST array [ceil(M/128)], optional: for each block of 128 rows, how many calls on
                                   these buffers (this one included) had at least that many rows.  NULL = `epoch` for
                                   every block, i.e. every call so far had at least this call's number of row blocks */
+  void* stage_mc;              /* optional: the NVLink-switch multicast address bound to all ranks' staging buffers ... */
+  void* out_mc;                /* ... and to all ranks' output buffers.  Mode 3 reduces through the switch: every rank keeps its partial tile in its own staging buffer, the tile's owner
+                                  reads the sum with multimem.ld_reduce and stores it to every rank with multimem.st */
   uint32_t done_tiles_total;   /* two-shot: sum of ca_oproj_tile_count(M, N) over all calls so far, this one included;
                                   0 = epoch * this call's tile count (every call the same M) */
 } ca_oproj_params;
