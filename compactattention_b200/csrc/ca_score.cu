@@ -901,7 +901,7 @@ int ca_gate_prepare(const ca_gate_prepare_params* p, ca_stream_t stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 #define CA_PREP_CASE(XD, WD)                                                            \
   if (p->q.x_dtype == XD && wdt == WD) {                                                \
-    launch_kernel(gate_prepare_kernel<XD, WD>, dim3(grid), dim3(kPrepThreads), smem, stream, a);               \
+    launch_kernel_as(true, gate_prepare_kernel<XD, WD>, dim3(grid), dim3(kPrepThreads), smem, stream, a);     \
   } else
   CA_PREP_CASE(CA_DTYPE_BF16, CA_DTYPE_BF16)
   CA_PREP_CASE(CA_DTYPE_BF16, CA_DTYPE_F32)

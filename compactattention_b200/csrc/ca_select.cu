@@ -903,9 +903,9 @@ int launch_gate_scores_tc(const ca_gate_score_params* g, cudaStream_t stream) {
   if (ctas_x > 0x7fffffffLL) return CA_ERR_UNSUPPORTED;
   const dim3 grid(static_cast<unsigned>(ctas_x), g->Hk, g->B);
   if (g->k_dtype == CA_DTYPE_BF16) {
-    launch_kernel(gate_scores_tc_kernel<CA_DTYPE_BF16>, grid, dim3(kGtThreads), smem, stream, k_map, a);
+    launch_kernel_as(true, gate_scores_tc_kernel<CA_DTYPE_BF16>, grid, dim3(kGtThreads), smem, stream, k_map, a);
   } else {
-    launch_kernel(gate_scores_tc_kernel<CA_DTYPE_F16>, grid, dim3(kGtThreads), smem, stream, k_map, a);
+    launch_kernel_as(true, gate_scores_tc_kernel<CA_DTYPE_F16>, grid, dim3(kGtThreads), smem, stream, k_map, a);
   }
   CA_LAUNCH_CHECK("gate_scores_tc_kernel");
   return CA_OK;
@@ -1052,7 +1052,7 @@ int ca_select_union_table(const ca_select_params* p, const ca_union_params* u, v
   size_t smem = 0;
   int rc = fill_fused_args(p, u, scratch, scratch_bytes, &a, &smem);
   if (rc != CA_OK) return rc;
-  launch_kernel(select_rows_kernel, dim3(p->B * p->H * p->Qb), dim3(kRowThreads), smem, static_cast<cudaStream_t>(stream_), a);
+  launch_kernel_as(true, select_rows_kernel, dim3(p->B * p->H * p->Qb), dim3(kRowThreads), smem, static_cast<cudaStream_t>(stream_), a);
   CA_LAUNCH_CHECK("select_rows_kernel");
   return CA_OK;
 }
@@ -1076,7 +1076,7 @@ int ca_gate_score_select(const ca_gate_score_params* g, const ca_select_params* 
   (void)write_scores;  // the logits always pass through score->out
   rc = ca_gate_scores(g, stream_);
   if (rc != CA_OK) return rc;
-  launch_kernel(select_rows_kernel, dim3(p->B * p->H * p->Qb), dim3(kRowThreads), row_smem, stream, a);
+  launch_kernel_as(true, select_rows_kernel, dim3(p->B * p->H * p->Qb), dim3(kRowThreads), row_smem, stream, a);
   CA_LAUNCH_CHECK("select_rows_kernel");
   return CA_OK;
 }
