@@ -369,11 +369,11 @@ def run_native(args):
                 out.append(("all_reduce", lambda: tp.reduce_layer_output(reduce_buf)))
         return out
 
-    def step(L, attn_events=None):
+    def step(L, attn_events=None, fresh=False):
         """One step.  The library calls of a stage are re-issued from the call list recorded for this layer state
         (same entry points, same parameter blocks: a host that keeps its parameter blocks between chunks, as
         `GateLayerStep` does); the collective is issued afresh."""
-        recorded = L.get("calls")
+        recorded = None if fresh else L.get("calls")   # the kept blocks carry the stream they were recorded on
         for name, fn in (recorded if recorded is not None else stages(L)):
             run = fn.run if isinstance(fn, _lib.CallList) else fn
             if name == "attention" and attn_events is not None:
@@ -590,7 +590,7 @@ def run_native(args):
     if world == 1 and not args.no_graph:
         try:
             from compactattention_b200.chunk_driver import capture_step
-            graphs = [capture_step(lambda L=L: step(L)) for L in layers]
+            graphs = [capture_step(lambda L=L: step(L, fresh=True)) for L in layers]
             for i in range(4):
                 graphs[i % len(graphs)].replay()
             g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -358,8 +358,7 @@ constexpr int kMaxReduceSplit = 32;  // a tile's 128 rows go to 4, 8, 16 or 32 C
                                      // finished tile always adds kMaxReduceSplit to the ranks' done counters
 
 // `split` CTAs per tile this rank reduces: sum of the `world` staged partials -> every rank's output.
-// W: compile-time bound of the rank count (2, 4 or 8) - the loads of all partials are unrolled to it.
-template <typename T, int W>
+template <typename T>
 __global__ void __launch_bounds__(256) oproj_reduce_kernel(const ReduceArgs a) {
   // Launched programmatically behind the GEMM and deliberately without a grid-dependency wait: everything this
   // kernel reads is guarded by a tile counter (release by the producer, acquire here), so its CTAs may take
@@ -386,24 +385,17 @@ __global__ void __launch_bounds__(256) oproj_reduce_kernel(const ReduceArgs a) {
     for (int e = part * part_groups + threadIdx.x; e < (part + 1) * part_groups; e += 256) {
       const int r = e / (kBN / 8), c8 = e % (kBN / 8);
       if (tm * kBM + r >= a.M) break;  // rows are visited in order: the rest lies beyond M too
-      // L2 loads (the partials arrived from other GPUs; a line cached in L1 by an earlier call would be stale), all
-      // of them in flight before the first addition
-      uint4 raw[W];
-#pragma unroll
-      for (int s = 0; s < W; ++s) {
-        raw[s] = s < a.world ? __ldcg(reinterpret_cast<const uint4*>(base + s * src_stride + static_cast<long long>(e) * 8))
-                             : make_uint4(0u, 0u, 0u, 0u);
-      }
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < a.world; ++s) {
+        // L2 loads: the partials arrived from other GPUs, a line cached in L1 by an earlier call would be stale.
+        // (Unrolling the loop to the rank count so that all loads are in flight together, and splitting a tile
+        // over 16 CTAs instead of 4 when a rank owns few tiles, both measured slower at 8 GPUs: 22 against 17 us.)
+        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(base + s * src_stride + static_cast<long long>(e) * 8));
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-      for (int s = 0; s < W; ++s) {
-        if (s < a.world) {
-          const uint32_t w[4] = {raw[s].x, raw[s].y, raw[s].z, raw[s].w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 f = unpack2<T>(w[i]);
-            acc[2 * i] += f.x, acc[2 * i + 1] += f.y;
-          }
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = unpack2<T>(w[i]);
+          acc[2 * i] += f.x, acc[2 * i + 1] += f.y;
         }
       }
       uint4 o;
@@ -621,8 +613,7 @@ int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream_) {
   r.M = p->M, r.N = p->N, r.tiles_n = g.tiles_n, r.n_tiles = g.n_tiles, r.world = p->world, r.rank = p->rank;
   r.tiles_per_owner = g.tiles_per_owner;
   r.one_shot = g.one_shot, r.slot_tiles = g.slot_tiles, r.buf_off_elems = g.buf_off_elems;
-  r.split = 4;
-  while (r.split < kMaxReduceSplit && g.slot_tiles * r.split < 2 * dev.sm_count) r.split *= 2;
+  r.split = 4;   // 4, 8, 16 and 32 all work (a finished part counts kMaxReduceSplit / split); 4 measured best
   for (int tm = 0; tm < kMaxRowTiles; ++tm) {
     const uint32_t calls = (p->row_epochs && tm < ceil_div(p->M, kBM)) ? p->row_epochs[tm] : p->epoch;
     r.row_target[tm] = calls * static_cast<uint32_t>(p->world);
@@ -642,15 +633,9 @@ int ca_oproj_allreduce(const ca_oproj_params* p, ca_stream_t stream_) {
     if (via_switch) {
       if (bf) launch_kernel_as(true, oproj_reduce_switch_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, r, static_cast<const void*>(p->stage_mc), p->out_mc);
       else launch_kernel_as(true, oproj_reduce_switch_kernel<__half>, grid, dim3(256), 0, stream, r, static_cast<const void*>(p->stage_mc), p->out_mc);
-    } else if (p->world <= 2) {
-      if (bf) launch_kernel_as(true, oproj_reduce_kernel<__nv_bfloat16, 2>, grid, dim3(256), 0, stream, r);
-      else launch_kernel_as(true, oproj_reduce_kernel<__half, 2>, grid, dim3(256), 0, stream, r);
-    } else if (p->world <= 4) {
-      if (bf) launch_kernel_as(true, oproj_reduce_kernel<__nv_bfloat16, 4>, grid, dim3(256), 0, stream, r);
-      else launch_kernel_as(true, oproj_reduce_kernel<__half, 4>, grid, dim3(256), 0, stream, r);
     } else {
-      if (bf) launch_kernel_as(true, oproj_reduce_kernel<__nv_bfloat16, 8>, grid, dim3(256), 0, stream, r);
-      else launch_kernel_as(true, oproj_reduce_kernel<__half, 8>, grid, dim3(256), 0, stream, r);
+      if (bf) launch_kernel_as(true, oproj_reduce_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, r);
+      else launch_kernel_as(true, oproj_reduce_kernel<__half>, grid, dim3(256), 0, stream, r);
     }
     CA_LAUNCH_CHECK("oproj_reduce_kernel");
   }
