@@ -216,6 +216,9 @@ __device__ void topk_mark_impl(const Team& tm, const float* s, int n, int k, uin
       }
     }
     team_sync(tm);
+    // every key that shares the prefix found so far is wanted: the lower digits cannot change the answer (with
+    // 2048 distinct scores the chosen bin holds a single key after two or three of the four passes)
+    if (ts->remaining == ts->last_bin_count) break;
   }
   const uint32_t kth = ts->prefix;
   const int want_equal = ts->remaining;
