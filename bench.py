@@ -116,18 +116,22 @@ class ClockSampler:
 
     def _poll_nvml(self):
         nv, h = self.nvml, self.handle
+        power, n = 0.0, 0
         while not self.stop_flag:
             try:
                 sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                stamp = time.perf_counter()   # the clock is what the regions are judged by: stamped right after its read
                 try:
                     reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
                 except Exception:
                     reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                power = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
-                self.samples.append((sm, reasons, power, time.perf_counter()))
+                if n % 8 == 0:               # the power query is the slow one: every eighth sample
+                    power = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                n += 1
+                self.samples.append((sm, reasons, power, stamp))
             except Exception:
                 break
-            time.sleep(0.0005)
+            time.sleep(0.0002)
 
     def start(self):
         self.started = True
@@ -458,6 +462,12 @@ def run_native(args):
     ref_gpu = {}
     if not args.no_dense and rank == 0:
         ref_gpu = time_reference_gpu_routes(layers[0], K, Q, hq, hkv, dev)
+    # ---- the path's other selectors at the same shape (informational; the headline is the learned gate with top-k):
+    # the learned gate with the reference's default rule (softmax + threshold), and the training-free selector
+    # (mean-K block score at block 128 + alpha * row-max rule with sink and window), selector launches only ----
+    other_selectors = {}
+    if not args.no_dense and rank == 0:
+        other_selectors = time_other_selectors(layers[0], K, Q, hq, hkv, dev)
     if world > 1:
         barrier()
 
@@ -646,6 +656,7 @@ def run_native(args):
             "dense_same_shape_us": None if dense_us is None else round(dense_us, 1),
             "speedup_vs_dense": None if dense_us is None else round(dense_us / value_us, 2),
             "reference_gpu_routes_us": ref_gpu,
+            "other_selectors_us": other_selectors,
             "attention_effective_tflops": round(achieved, 1),
             "e2e_call": "LlamaSeerAttentionChunkedDense.forward (top-k method): hidden states from pinned host memory, "
                         "q/k/v projections, RoPE + paged append, gate, rule, table, attention, o_proj"
@@ -675,6 +686,63 @@ def load_attention_capture():
         return None
     d = json.loads(path.read_text())
     return {"dram_bytes": float(d["dram_bytes"]), "algorithmic_bytes": float(d["algorithmic_bytes"])}
+
+
+def time_other_selectors(L, K, Q, hq, hkv, dev, reps=10):
+    """Selector launches of the two routes the benchmark's headline does not take, on the same shape: device time
+    per chunk (CUDA events over `reps` chunks behind a device spin, so the host's enqueue rate is not timed).
+      gate_softmax_threshold   gate scores -> softmax + threshold 5e-4 + keep_recent 2 -> union + table
+                               (compact_attn/modules/attention_forward_chunked_dense.py:352-403, the reference's default)
+      flashprefill_block128    mean-K block score + normalisation (block 128) -> alpha 0.06 * row-max, sink 2,
+                               window 4 -> union + table (compact_attn/modules/flashprefill_prefill.py:307-376, 596-666)
+    """
+    import torch
+    from compactattention_b200 import ops
+    out = {}
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(int(2e6))
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return round(e0.elapsed_time(e1) / reps * 1e3, 1)
+
+    try:
+        sel = L["sel"]
+        kb = sel.cache.blocks()
+        Kb, Qb = kb.shape[1], sel.q_blocks.shape[1]
+        logits = torch.empty((1, hq, Qb, Kb), dtype=torch.float32, device=dev)
+        out["gate_softmax_threshold"] = {
+            "scores_rule_table": timed(lambda: ops.gate_score_select(sel.q_blocks, kb, Kb - Qb, "threshold", num_kv_heads=hkv, scores=logits,
+                                                                     scale=sel.gate.scale, block_size=64, softmax=True, threshold=5e-4,
+                                                                     keep_recent=2))}
+    except Exception as exc:  # informational: never fails the benchmark
+        out["gate_softmax_threshold"] = {"error": repr(exc)[:200]}
+    try:
+        bs = 128
+        g = torch.Generator(device=dev).manual_seed(11)
+        mean_k = torch.randn((1, K // bs, hkv, 128), device=dev, generator=g).to(torch.bfloat16)
+        q = L["q"]
+        state = {}
+
+        def score():
+            state["raw"], state["mx"], state["norm"] = ops.flashprefill_score(q, mean_k, K, bs)
+
+        def rule_table():
+            s = state["norm"].permute(0, 3, 1, 2)   # [B, Hq, Qb, Kb] view of [B, Qb, Kb, Hq]
+            ops.select_union_table(s, (K - Q) // bs, "alpha_rowmax", num_kv_heads=hkv, block_size=bs, alpha=0.06, sink=2, local=4)
+
+        score()
+        out["flashprefill_block128"] = {"score_and_normalise": timed(score), "rule_table": timed(rule_table)}
+    except Exception as exc:
+        out["flashprefill_block128"] = {"error": repr(exc)[:200]}
+    return out
 
 
 def time_reference_gpu_routes(L, K, Q, hq, hkv, dev, reps=3):
