@@ -1151,9 +1151,11 @@ int ca_attn_compact(const ca_attn_params* p, ca_stream_t stream_) {
     }
   }
   if (p->dtype == CA_DTYPE_BF16) {
-    launch_kernel(attn_compact_kernel<__nv_bfloat16>, dim3(grid), dim3(kThreads), kSmemBytes, stream, q_map, k_map, v_map, a);
+    // a programmatic dependent launch: barrier set-up, TMEM allocation and descriptor prefetch overlap the tail of
+    // the table builder; the kernel waits (griddepcontrol.wait) before it reads anything from global memory
+    launch_kernel_as(true, attn_compact_kernel<__nv_bfloat16>, dim3(grid), dim3(kThreads), kSmemBytes, stream, q_map, k_map, v_map, a);
   } else {
-    launch_kernel(attn_compact_kernel<__half>, dim3(grid), dim3(kThreads), kSmemBytes, stream, q_map, k_map, v_map, a);
+    launch_kernel_as(true, attn_compact_kernel<__half>, dim3(grid), dim3(kThreads), kSmemBytes, stream, q_map, k_map, v_map, a);
   }
   CA_LAUNCH_CHECK("attn_compact_kernel");
   if (a.split) {
