@@ -104,7 +104,8 @@ def test_programmatic_launch_toggle_is_host_state_only():
 def test_measurement_drivers_import_without_a_gpu():
     """The drivers quoted in profiles/ must at least import and parse their arguments on a CPU box."""
     import importlib
-    for name in ("sweep", "kernel_case", "cycle_accounting", "chunk_driver", "prefill_sparse.llama.run_prefill"):
+    for name in ("sweep", "kernel_case", "cycle_accounting", "select_accounting", "tp_check", "chunk_driver",
+                 "prefill_sparse.llama.run_prefill"):
         importlib.import_module(f"compactattention_b200.{name}")
 
 
