@@ -6,12 +6,15 @@ a 1024-token chunk appended at the end of a 128K-token paged KV cache (64-token 
 permuted page ids), block size 64.  Selection = learned-gate-style selector with random-init weights
 (pooled Q and pooled K, 128 -> 128 projections per head, block RoPE) and per-row block top-k at 20 %
 density plus sink and local blocks.  A step is one pass of the path for one chunk:
-pool Q/K blocks, project + RoPE + append to the gate's K-block cache (one launch), gate logits, top-k rows +
-Block-Union table (one launch), block-table attention.  Data is synthetic (seeded N(0,1)); steps rotate over
+pool Q/K blocks, project + RoPE + append to the gate's K-block cache (one launch), gate logits on the tensor
+core (one launch), top-k rows + Block-Union table (one launch), block-table attention (the kernel and, when it
+cuts work units over the SMs, its merge kernel).  The steps of the timed loop re-issue the library calls from
+parameter blocks kept per layer state.  Data is synthetic (seeded N(0,1)); steps rotate over
 several independent layer states so consecutive steps read different HBM (total > L2).
 
 At N > 1 the KV heads are sharded over the ranks (tensor parallel): every rank selects and attends
-its own heads, then the layer output partial sums are all-reduced over NCCL; total work is fixed
+its own heads, then the layer output partial sums are summed over the ranks - by the library's own exchange over
+peer memory (`ca_oproj_allreduce` without the GEMM) or, with `--nccl-all-reduce`, by NCCL; total work is fixed
 ("strong" scaling) and the value is the max-over-ranks latency.
 
 `--impl reference` times the CPU restatement of the reference's path (oracle port, torch on all host
@@ -342,7 +345,7 @@ def run_native(args):
         own_exchange = tp.shared_fused_projection(Q, HQ * D, dev, torch.bfloat16)   # the module's e2e path shares it
     rope_chunk = (cos[:, Pb:], sin[:, Pb:])
 
-    # ---- one step = one pass of the path for one chunk, as a list of stages (one launch each, the
+    # ---- one step = one pass of the path for one chunk, as a list of stages (one or two launches each, the
     # attention stage two when it cuts work units) so the same code runs timed as a whole and stage by stage
     def stages(L):
         sel = L["sel"]
@@ -364,7 +367,7 @@ def run_native(args):
 
         if args.two_launch_selection:
             out = [("gate_prepare", prepare), ("gate_scores", sel.score), ("select_union_table", select), ("attention", attention)]
-        else:   # scores, row rule, Block-Union and table in one launch: the logits never leave the SM
+        else:   # scores, row rule, Block-Union and table behind one library call (two launches)
             out = [("gate_prepare", prepare), ("gate_score_select", score_select), ("attention", attention)]
         if world > 1:
             if own_exchange is not None:   # the library's own all-reduce over peer memory (ca_oproj_allreduce without the GEMM)

@@ -77,8 +77,8 @@ class GateSelectorState:
     def score_select(self, rule: "SelectionRule", num_kv_heads: int, block_size: int, *, table=None, bits=None,
                      write_scores: bool = False, rows_voting: int = 0) -> ops.BlockTable:
         """Scores the chunk's Q blocks (from the last ``append``) against every cached block, applies the row
-        rule and builds the Block-Union table: ONE launch for the learned gate's usual shape
-        (``ca_gate_score_select``), the logits staying on chip unless ``write_scores``."""
+        rule and builds the Block-Union table: one library call (``ca_gate_score_select``), two launches - the
+        tensor-core score kernel and the rule + union + table kernel."""
         gate, nb = self.gate, self.q_blocks.shape[1]
         kb = self.cache.blocks()
         if self.logits is None or self.logits.shape[3] != kb.shape[1] or self.logits.shape[2] != nb:

@@ -673,9 +673,10 @@ def gate_score_select(
     masked_value: float = float(torch.finfo(torch.float32).min),
     **select_kwargs,
 ) -> "BlockTable":
-    """``gate_scores`` + ``select_union_table`` in ONE launch where the shape allows (see ``ca_gate_score_select``),
-    else as the two launches.  ``scores`` receives the logits only when ``write_scores`` (or when the two-launch
-    form runs).  ``select_kwargs`` are those of ``select_union_table``."""
+    """``gate_scores`` + ``select_union_table`` behind ONE library call (``ca_gate_score_select``): the tensor-core
+    score kernel, then the rule + Block-Union + table kernel.  ``scores`` always receives the logits
+    (``write_scores`` is kept for callers of an earlier single-launch form and ignored).  ``select_kwargs`` are
+    those of ``select_union_table``."""
     g, scores = _gate_score_params(q_blocks, k_blocks, past_blocks, scale, masked_value, scores)
     return select_union_table(scores, past_blocks, rule, num_kv_heads=num_kv_heads, _gate=(g, bool(write_scores)), **select_kwargs)
 
