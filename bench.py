@@ -340,9 +340,19 @@ def run_native(args):
         st.kv.append(layers[-1]["k_chunk"], layers[-1]["v_chunk"], position=K - Q)
         del t
     reduce_buf = torch.zeros((1, Q, HQ * D), dtype=torch.bfloat16, device=dev) if world > 1 else None
-    own_exchange = None
+    own_exchange, own_exchange_note = None, None
     if (world in OWN_ALL_REDUCE_WORLDS or (args.own_all_reduce and world > 1)) and not args.nccl_all_reduce:
-        own_exchange = tp.shared_fused_projection(Q, HQ * D, dev, torch.bfloat16)   # the module's e2e path shares it
+        # Symmetric (peer-mapped) buffers are a collective allocation: every rank either gets them or none does.
+        try:
+            own_exchange = tp.shared_fused_projection(Q, HQ * D, dev, torch.bfloat16)   # the module's e2e path shares it
+            ok = 1.0
+        except Exception as exc:   # no peer access / no symmetric memory on this box: NCCL carries the collective
+            own_exchange_note = f"symmetric memory unavailable ({type(exc).__name__}): NCCL used"
+            ok = 0.0
+        if tp.max_over_ranks([1.0 - ok], dev)[0] > 0.0:
+            own_exchange = None
+            own_exchange_note = own_exchange_note or "symmetric memory unavailable on another rank: NCCL used"
+            cfg.compactattn_fused_oproj_rows = 0
     rope_chunk = (cos[:, Pb:], sin[:, Pb:])
 
     # ---- one step = one pass of the path for one chunk, as a list of stages (one or two launches each, the
@@ -645,7 +655,7 @@ def run_native(args):
             "parallelism": f"tp{world} (KV-head sharded)" if world > 1 else "single GPU",
             "layer_output_all_reduce": (None if world == 1 else
                                         ("library exchange over peer memory (ca_oproj_allreduce without the GEMM)"
-                                         if own_exchange is not None else "NCCL")),
+                                         if own_exchange is not None else (own_exchange_note or "NCCL"))),
             "l2": f"steps rotate over {len(layers)} layer states ({len(layers) * 2 * K * hkv * D * 2 / 2**30:.1f} GiB of KV), more than L2",
             "launches_per_step": launches / args.steps,
             "programmatic_dependent_launch": args.dependent_launch,
