@@ -182,6 +182,8 @@ class ClockSampler:
                    "power_w_max": round(max((x[2] for x in load), default=0.0), 1),
                    "power_w_median": round(statistics.median([x[2] for x in load]), 1) if load else None,
                    "source": "nvml (in-process, while the timed loops ran)", "reasons": reasons}
+            out["note"] = ("sm_mhz is the median over both timed loops and is dominated by the seconds-long sustained loop at the "
+                           "board's power cap; `value` comes from the short region whose median is sm_mhz_timed_region")
             if timed:
                 out["sm_mhz_timed_region"] = statistics.median(float(x[0]) for x in timed)
             if sus:
