@@ -478,19 +478,27 @@ __device__ void select_row(const RowArgs& a, const Team& tm, TeamShared* ts, uns
   team_sync(tm);
 
   SEL_MARK(tm.bar <= 1, tm.tid, 6);
-  // ---- forced blocks, validity, bit packing ----
-  for (int base = 0; base < a.W * 32; base += tm.nt) {
-    const int j = base + tm.tid;
-    bool k = false;
-    if (j < a.Kb) {
-      const bool ok = a.valid ? (a.valid[v_off + j * a.v_k] != 0) : (j <= diag);
-      const int d = diag - j;
-      const bool forced = d >= 0 && (j < a.sink || d < a.local);
-      k = (keep[j] || forced) && ok;
+  // ---- forced blocks, validity, bit packing: a thread packs eight consecutive entries into a byte, four
+  // neighbouring lanes put their bytes together into a word (one pass over the row instead of a ballot per
+  // 32 entries and iteration: the iterations' shared-memory reads and ballots ran one after the other) ----
+  for (int base = 0; base < a.W * 32; base += tm.nt * 8) {
+    const int j0 = base + tm.tid * 8;
+    uint32_t byte = 0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int j = j0 + u;
+      if (j < a.Kb) {
+        const bool ok = a.valid ? (a.valid[v_off + j * a.v_k] != 0) : (j <= diag);
+        const int d = diag - j;
+        const bool forced = d >= 0 && (j < a.sink || d < a.local);
+        if ((keep[j] || forced) && ok) byte |= 1u << u;
+      }
     }
-    const uint32_t word = __ballot_sync(0xffffffffu, k);
-    if ((tm.tid & 31) == 0 && (j >> 5) < a.W) {
-      if (bits_row) bits_row[j >> 5] = word;
+    uint32_t word = byte << (8 * (tm.tid & 3));
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    if ((tm.tid & 3) == 0 && (j0 >> 5) < a.W) {
+      if (bits_row) bits_row[j0 >> 5] = word;
     }
   }
   }
