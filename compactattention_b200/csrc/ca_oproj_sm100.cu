@@ -496,8 +496,8 @@ int ca_oproj_scratch_bytes(int M_max, int N, int world, size_t* stage_bytes, siz
              kMaxWorld);
   const long long n_tiles = static_cast<long long>(ceil_div(M_max, kBM)) * (N / kBN);
   const long long per_owner = (n_tiles + world - 1) / world;
-  // two-shot: [src][owned tile]; one-shot (two ranks only): two halves of [src][tile], used by alternate calls
-  const long long slots = world == 2 ? 2 * n_tiles : per_owner;
+  // two-shot: [src][owned tile]; one-shot (sized for up to four ranks): two halves of [src][tile], used by alternate calls
+  const long long slots = world <= 4 ? 2 * n_tiles : per_owner;   // up to four ranks may ask for the one-exchange form
   *stage_bytes = world > 1 ? static_cast<size_t>(world) * slots * kTileElems * 2 : 0;
   *counter_bytes = (static_cast<size_t>(n_tiles) + 1) * sizeof(uint32_t);  // per tile slot, then the finished-tile count
   return CA_OK;

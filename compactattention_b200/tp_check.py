@@ -39,6 +39,8 @@ def main() -> None:
     # reduce-scatter + all-gather form over plain peer stores
     routes = {"auto": tp.FusedOutputProjection(M, N, dev, torch.bfloat16)}
     routes["two_shot"] = tp.FusedOutputProjection(M, N, dev, torch.bfloat16, mode=1)   # reduce-scatter + all-gather over peer stores
+    if 2 < world <= 4:
+        routes["one_shot"] = tp.FusedOutputProjection(M, N, dev, torch.bfloat16, mode=2)      # every partial tile to every rank
     if world > 2 and args.switch and routes["auto"]._mc is not None:
         routes["switch"] = tp.FusedOutputProjection(M, N, dev, torch.bfloat16, mode=3)        # additions done by the NVLink switch
     # correctness: three calls in a row (buffers reused), against GEMM + all-reduce in fp32
@@ -98,6 +100,10 @@ def main() -> None:
     fused0.check()
     two_shot_ar_us = timed(lambda: routes["two_shot"].all_reduce(y_part))
     routes["two_shot"].check()
+    one_shot_ar_us = None
+    if "one_shot" in routes:
+        one_shot_ar_us = round(timed(lambda: routes["one_shot"].all_reduce(y_part)), 1)
+        routes["one_shot"].check()
     y_nccl = y_part.clone()
     nccl_ar_us = timed(lambda: dist.all_reduce(y_nccl))
     lib_us = timed(library_route)
@@ -107,7 +113,7 @@ def main() -> None:
                           "fused": results, "library_gemm_plus_nccl_allreduce_us": round(lib_us, 1),
                           "library_gemm_alone_us": round(gemm_us, 1),
                           "auto_form": "one exchange" if world == 2 else "reduce-scatter + all-gather",
-                          "all_reduce_alone": {"own_exchange_us": round(own_ar_us, 1), "own_two_shot_us": round(two_shot_ar_us, 1), "nccl_us": round(nccl_ar_us, 1),
+                          "all_reduce_alone": {"own_exchange_us": round(own_ar_us, 1), "own_two_shot_us": round(two_shot_ar_us, 1), "own_one_shot_us": one_shot_ar_us, "nccl_us": round(nccl_ar_us, 1),
                                                "max_rel_err": round(ar_err, 5)}}))
     dist.destroy_process_group()
 
