@@ -708,8 +708,8 @@ def time_other_selectors(L, K, Q, hq, hkv, dev, reps=10):
     per chunk (CUDA events over `reps` chunks behind a device spin, so the host's enqueue rate is not timed).
       gate_softmax_threshold   gate scores -> softmax + threshold 5e-4 + keep_recent 2 -> union + table
                                (compact_attn/modules/attention_forward_chunked_dense.py:352-403, the reference's default)
-      flashprefill_block128    mean-K block score + normalisation (block 128) -> alpha 0.06 * row-max, sink 2,
-                               window 4 -> union + table (compact_attn/modules/flashprefill_prefill.py:307-376, 596-666)
+      flashprefill_block128    mean-K block score (block 128; its normalisation is folded into the rule's row load) ->
+                               alpha 0.06 * row-max, sink 2, window 4 -> union + table (compact_attn/modules/flashprefill_prefill.py:307-376, 596-666)
     """
     import torch
     from compactattention_b200 import ops
@@ -746,15 +746,16 @@ def time_other_selectors(L, K, Q, hq, hkv, dev, reps=10):
         q = L["q"]
         state = {}
 
-        def score():
-            state["raw"], state["mx"], state["norm"] = ops.flashprefill_score(q, mean_k, K, bs)
+        def score():   # score_raw and max_raw; the rule forms score_raw * 2^(max_raw - row max) itself: no normalisation launch
+            state["raw"], state["mx"], _ = ops.flashprefill_score(q, mean_k, K, bs, normalize=False)
 
         def rule_table():
-            s = state["norm"].permute(0, 3, 1, 2)   # [B, Hq, Qb, Kb] view of [B, Qb, Kb, Hq]
-            ops.select_union_table(s, (K - Q) // bs, "alpha_rowmax", num_kv_heads=hkv, block_size=bs, alpha=0.06, sink=2, local=4)
+            s = state["raw"].permute(0, 3, 1, 2)   # [B, Hq, Qb, Kb] view of [B, Qb, Kb, Hq]
+            ops.select_union_table(s, (K - Q) // bs, "alpha_rowmax", num_kv_heads=hkv, block_size=bs, alpha=0.06, sink=2, local=4,
+                                   score_max=state["mx"].permute(0, 3, 1, 2))
 
         score()
-        out["flashprefill_block128"] = {"score_and_normalise": timed(score), "rule_table": timed(rule_table)}
+        out["flashprefill_block128"] = {"score": timed(score), "rule_table": timed(rule_table)}
     except Exception as exc:
         out["flashprefill_block128"] = {"error": repr(exc)[:200]}
     return out

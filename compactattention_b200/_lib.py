@@ -74,6 +74,7 @@ class SelectParams(C.Structure):
         ("rows_voting", C.c_int32),
         ("threshold_ptr", C.c_void_p),
         ("threshold_stride_b", C.c_int64),
+        ("score_max", C.c_void_p),
     ]
 
 

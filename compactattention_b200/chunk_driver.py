@@ -103,13 +103,17 @@ class MeanKSelectorState:
         self.block_size = block_size
         self.mean_k = torch.empty((batch, max_blocks, num_kv_heads, head_dim), dtype=dtype, device=device)
         self.length = 0
+        self.score_max = None   # exponents of the last ``append_and_score`` (same shape and strides as its return)
 
     def append_and_score(self, q: torch.Tensor, k_chunk: torch.Tensor, kv_len: int) -> torch.Tensor:
         nb = -(-k_chunk.shape[1] // self.block_size)
         ops.pool_blocks(k_chunk, self.block_size, ("avg",), out=self.mean_k, out_block_offset=self.length)
         self.length += nb
-        _, _, norm = ops.flashprefill_score(q, self.mean_k[:, : self.length], kv_len, self.block_size)
-        return norm.permute(0, 3, 1, 2)  # [B, Hq, Qb, Kb] view
+        # score_raw and max_raw: the rule forms score_raw * 2^(max_raw - row max) itself (``score_max``), which is
+        # all the alpha * row-max and top-k rules need of the normalisation
+        raw, mx, _ = ops.flashprefill_score(q, self.mean_k[:, : self.length], kv_len, self.block_size, normalize=False)
+        self.score_max = mx.permute(0, 3, 1, 2)
+        return raw.permute(0, 3, 1, 2)  # [B, Hq, Qb, Kb] view
 
 
 def select_and_attend(
@@ -125,6 +129,7 @@ def select_and_attend(
     table: Optional[ops.BlockTable] = None,
     bits: Optional[torch.Tensor] = None,
     status: Optional[torch.Tensor] = None,
+    score_max: Optional[torch.Tensor] = None,
 ):
     """Row rule + Block-Union table (one launch) -> compact attention.  Returns (out, table).  ``bits`` is
     only written when given (a caller that wants the per-row selection)."""
@@ -135,7 +140,7 @@ def select_and_attend(
     table = ops.select_union_table(score, Kb - Qb, rule.rule, num_kv_heads=num_kv_heads, block_size=block_size,
                                    keep_recent=rule.keep_recent, softmax=rule.softmax, threshold=rule.threshold, alpha=rule.alpha,
                                    topk_k=rule.topk_k, topk_ratio=rule.topk_ratio, min_budget=rule.min_budget, sink=rule.sink,
-                                   local=rule.local, rows_voting=rows_voting, bits=bits, out=table)
+                                   local=rule.local, rows_voting=rows_voting, bits=bits, out=table, score_max=score_max)
     out = ops.attn_compact(q, kv, kv_len, num_kv_heads, table.block_idx, table.counts, block_size=block_size,
                            softmax_scale=softmax_scale, out=out, status=status)
     return out, table

@@ -41,6 +41,7 @@ struct RowArgs {
   const void* score;  // [B,H,Qb,Kb] by strides; dtype f32/bf16/f16, or uint8 when rule == MASK
   long long s_b, s_h, s_q, s_k;
   int score_dtype;
+  const float* score_max;  // optional f32, score's strides: the rule sees score[j] * 2^(score_max[j] - row max of score_max)
   const uint8_t* valid;  // optional bool [B,1|H,Qb,Kb] by strides; NULL = block-causal j <= Pb + i
   long long v_b, v_h, v_q, v_k;
   uint32_t* bits;  // [B,H,Qb,W]
@@ -353,6 +354,12 @@ __device__ void select_row(const RowArgs& a, const Team& tm, TeamShared* ts, uns
 
   // ---- load the row; invalid entries become -inf.  Eight entries per thread and round, every load issued
   // before the first store (the loop used to pay one memory latency per entry) ----
+  float exp_max = -INFINITY;  // with score_max: the row's largest exponent
+  if (a.score_max) {
+    float m = -INFINITY;
+    for (int j = tm.tid; j < a.Kb; j += tm.nt) m = fmaxf(m, __ldg(a.score_max + s_off + j * a.s_k));
+    exp_max = block_reduce_max(tm, m, ts->red);
+  }
   for (int base = 0; base < a.Kb; base += tm.nt * 8) {
     float x[8];
 #pragma unroll
@@ -366,6 +373,10 @@ __device__ void select_row(const RowArgs& a, const Team& tm, TeamShared* ts, uns
           x[u] = reinterpret_cast<const uint8_t*>(a.score)[s_off + j * a.s_k] ? 1.f : 0.f;
         } else {
           x[u] = load_score(a.score, s_off + j * a.s_k, a.score_dtype);
+          if (a.score_max) {
+            const float e = __ldg(a.score_max + s_off + j * a.s_k);
+            x[u] = e == -INFINITY ? 0.f : x[u] * exp2f(e - exp_max);
+          }
         }
       }
     }
@@ -941,10 +952,13 @@ static int fill_row_args(const ca_select_params* p, ca::select::RowArgs* out, si
                  p->score_dtype == CA_DTYPE_F16,
              "score dtype must be f32, bf16 or f16");
   if (p->rule == CA_RULE_TOPK) CA_REQUIRE(p->topk_k > 0 || (p->topk_num >= 0 && p->topk_den > 0), "top-k needs k or num/den");
+  CA_REQUIRE(p->score_max == nullptr || (p->score_dtype == CA_DTYPE_F32 && p->softmax == 0 && p->rule != CA_RULE_MASK),
+             "score_max needs f32 scores, no softmax and a rule on scores");
   RowArgs a;
   a.score = p->score;
   a.s_b = p->score_stride_b, a.s_h = p->score_stride_h, a.s_q = p->score_stride_q, a.s_k = p->score_stride_k;
   a.score_dtype = p->score_dtype;
+  a.score_max = p->score_max;
   a.valid = static_cast<const uint8_t*>(p->valid);
   a.v_b = p->valid_stride_b, a.v_h = p->valid_stride_h, a.v_q = p->valid_stride_q, a.v_k = p->valid_stride_k;
   a.bits = static_cast<uint32_t*>(p->bits);

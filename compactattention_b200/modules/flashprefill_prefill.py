@@ -78,16 +78,19 @@ def flashprefill_compactattn_prefill_full_kv(
             key_states, block_size, ("avg",), out_dtype=key_states.dtype)
         if mean_k.shape[1] != kv_blocks:
             raise ValueError(f"mean_k_cache has {mean_k.shape[1]} blocks, expected {kv_blocks}")
-        _, _, norm = ops.flashprefill_score(query_states, mean_k, kv_len, block_size)
-        return norm
+        # The alpha * row-max rule (and its top-k minimum budget) does not depend on the row's normalising sum: the
+        # rule kernel takes score_raw and max_raw and forms score_raw * 2^(max_raw - row max) itself, so the
+        # normalisation launch and its [B, Qb, Kb, Hq] output are skipped.
+        raw, mx, _ = ops.flashprefill_score(query_states, mean_k, kv_len, block_size, normalize=False)
+        return raw, mx
 
-    score, select_ms = _timed(_score, measure_timing)
+    (score, score_max), select_ms = _timed(_score, measure_timing)
     tail = min(max(int(last_n_block), 0), q_blocks - 1) if q_blocks > 1 else 0
 
     def _rule():
         return ops.select_rows(score.permute(0, 3, 1, 2), past_blocks, "alpha_rowmax", alpha=float(alpha),
                                sink=int(attention_sink), local=int(window_size), min_budget=int(min_budget),
-                               rows_voting=max(q_blocks - tail, 1))
+                               rows_voting=max(q_blocks - tail, 1), score_max=score_max.permute(0, 3, 1, 2))
 
     bits, union_ms = _timed(_rule, measure_timing)
     out, compact_stats = chunked_prefill_column_dense_attention_from_keep_block(

@@ -247,7 +247,7 @@ def words_for(kv_blocks: int) -> int:
 
 
 def _select_params(score, past_blocks, rule, valid, softmax, threshold, alpha, topk_k, topk_ratio, min_budget, sink, local,
-                   rows_voting, bits, prob_out, bits_required=True):
+                   rows_voting, bits, prob_out, bits_required=True, score_max=None):
     """Fills ``ca_select_params`` from torch arguments; returns (params, bits, tensors to keep alive)."""
     _require_cuda(score, valid, bits, prob_out)
     B, H, Qb, Kb = score.shape
@@ -292,7 +292,13 @@ def _select_params(score, past_blocks, rule, valid, softmax, threshold, alpha, t
     p.topk_k = int(topk_k)
     p.topk_num, p.topk_den = (topk_ratio if topk_ratio is not None else (0, 1))
     p.min_budget, p.sink, p.local, p.rows_voting = int(min_budget), int(sink), int(local), int(rows_voting)
-    return p, bits, (valid, keep_thr)
+    if score_max is not None:
+        # per-entry exponents with the score's shape and strides: the rule sees score * 2^(score_max - row max)
+        if score_max.dtype != torch.float32 or score.dtype != torch.float32 or score_max.shape != score.shape or \
+                score_max.stride() != score.stride() or not score_max.is_cuda:
+            raise ValueError("score_max must be a float32 CUDA tensor with the score's shape and strides (and the score float32)")
+        p.score_max = score_max.data_ptr()
+    return p, bits, (valid, keep_thr, score_max)
 
 
 def select_rows(
@@ -312,10 +318,11 @@ def select_rows(
     rows_voting: int = 0,
     bits: Optional[torch.Tensor] = None,
     prob_out: Optional[torch.Tensor] = None,
+    score_max: Optional[torch.Tensor] = None,  # f32, the score's shape and strides: the rule sees score * 2^(score_max - row max)
 ) -> torch.Tensor:
     """Per-row selection rule -> packed keep bits int32 [B, H, Qb, ceil(Kb/32)]."""
     p, bits, keep = _select_params(score, past_blocks, rule, valid, softmax, threshold, alpha, topk_k, topk_ratio, min_budget,
-                                   sink, local, rows_voting, bits, prob_out)
+                                   sink, local, rows_voting, bits, prob_out, score_max=score_max)
     _lib.check(_lib.load().ca_select_rows(C.byref(p), _stream()), "ca_select_rows")
     del keep
     return bits
@@ -362,6 +369,7 @@ def select_union_table(
     prob_out: Optional[torch.Tensor] = None,
     out: Optional["BlockTable"] = None,
     scratch: Optional[torch.Tensor] = None,
+    score_max: Optional[torch.Tensor] = None,  # as in select_rows
     _gate=None,  # (GateScoreParams writing `score`, write_scores): set by gate_score_select
 ) -> "BlockTable":
     """``select_rows`` followed by ``union_table`` in ONE launch (see ``ca_select_union_table``): row rule,
@@ -373,7 +381,7 @@ def select_union_table(
     if Kb - past_blocks != Qb:
         raise ValueError("the score must cover the chunk's own key blocks: Kb - past_blocks must equal Qb")
     p, bits, keep = _select_params(score, past_blocks, rule, valid, softmax, threshold, alpha, topk_k, topk_ratio, min_budget,
-                                   sink, local, rows_voting, bits, prob_out, bits_required=False)
+                                   sink, local, rows_voting, bits, prob_out, bits_required=False, score_max=score_max)
     dev = score.device
     if out is None:
         cap = max(past_blocks, 1)

@@ -198,6 +198,13 @@ typedef struct ca_select_params {
    * reading it on the device keeps the call free of a device-to-host synchronisation. */
   const float* threshold_ptr;
   int64_t threshold_stride_b;
+  /* Optional per-entry exponents (f32, the same strides as score): when given, the rule sees
+   * score[j] * 2^(score_max[j] - max_j score_max[j]) (0 where score_max[j] is -inf) - the numerator of the
+   * training-free selector's normalisation (ca_flashprefill_score's score_raw and max_raw) without its division
+   * by the row sum, which the alpha * row-max and top-k rules do not depend on
+   * (compact_attn/flashprefill_vendor/flashprefill_native_forward.py:365-374 followed by
+   * compact_attn/modules/flashprefill_prefill.py:596-666).  score must then be f32 and softmax 0. */
+  const float* score_max;
 } ca_select_params;
 
 int ca_select_rows(const ca_select_params* p, ca_stream_t stream);

@@ -207,3 +207,28 @@ def test_flashprefill_score_random(ops, Q, K, Hq, Hkv, bs, dtype):
     assert fp_row_err(norm.cpu(), o_norm) < REL
     if Q % bs == 0 and K % bs == 0:
         check_alpha_rule_on_gpu_scores(ops, norm, Q, K, bs, Hq // Hkv)
+
+
+@pytest.mark.parametrize("rule,kw", [("alpha_rowmax", dict(alpha=0.06, sink=2, local=4)),
+                                     ("alpha_rowmax", dict(alpha=0.3, min_budget=5, sink=1, local=1)),
+                                     ("topk", dict(topk_ratio=(1, 5), sink=1, local=2))])
+@pytest.mark.parametrize("bs,Q,K", [(128, 1024, 32768), (64, 512, 8192)])
+def test_rules_on_raw_scores_and_exponents_equal_rules_on_normalised_scores(ops, rule, kw, bs, Q, K):
+    """The training-free selector's normalisation divides a row by its sum; the alpha * row-max and top-k rules
+    do not depend on that, so the rule kernel may take score_raw and max_raw (``score_max``) and skip the
+    normalisation launch.  Same keep bits as the rule on the normalised scores, and the same table."""
+    g = torch.Generator().manual_seed(K + bs)
+    Hq, Hkv = 8, 2
+    q = torch.randn((1, Q, Hq, 128), generator=g).to(torch.bfloat16).cuda()
+    mean_k = torch.randn((1, K // bs, Hkv, 128), generator=g).to(torch.bfloat16).cuda()
+    raw, mx, norm = ops.flashprefill_score(q, mean_k, K, bs)
+    Pb = (K - Q) // bs
+    want = ops.select_rows(norm.permute(0, 3, 1, 2), Pb, rule, **kw)
+    got = ops.select_rows(raw.permute(0, 3, 1, 2), Pb, rule, score_max=mx.permute(0, 3, 1, 2), **kw)
+    assert torch.equal(got, want)
+    t_want = ops.select_union_table(norm.permute(0, 3, 1, 2), Pb, rule, num_kv_heads=Hkv, block_size=bs, **kw)
+    t_got = ops.select_union_table(raw.permute(0, 3, 1, 2), Pb, rule, num_kv_heads=Hkv, block_size=bs,
+                                   score_max=mx.permute(0, 3, 1, 2), **kw)
+    assert torch.equal(t_got.block_idx, t_want.block_idx) and torch.equal(t_got.counts, t_want.counts)
+    with pytest.raises(ValueError, match="score_max"):
+        ops.select_rows(raw.permute(0, 3, 1, 2), Pb, rule, score_max=mx, **kw)   # strides differ from the score's
