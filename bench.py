@@ -486,32 +486,6 @@ def run_native(args):
     if world > 1:
         barrier()
 
-    # ---- sustained phase: the same loop repeated until >= 1 s has elapsed (the board reaches its
-    # power cap and the SM clock settles), clocks sampled throughout ----
-    sustained = None
-    if not args.no_sustained:
-        s_attn, n_sus = [], 0
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        sampler.mark("sustained_begin")
-        w0 = time.perf_counter()
-        s0.record()
-        while True:
-            for i in range(args.steps):
-                step(layers[i % len(layers)], s_attn)
-            n_sus += args.steps
-            torch.cuda.current_stream().synchronize()
-            go = 1.0 if time.perf_counter() - w0 < args.sustained_seconds else 0.0
-            if max_ranks([go])[0] == 0.0 or n_sus >= 100000:  # every rank leaves the loop in the same round
-                break
-        s1.record()
-        barrier()
-        sampler.mark("sustained_end")
-        sus_ms, sus_attn = max_ranks([s0.elapsed_time(s1) / n_sus, statistics.mean(a.elapsed_time(b) for a, b in s_attn[-200:])])
-        sustained = {"steps": n_sus, "step_us": round(sus_ms * 1e3, 1), "attention_us": round(sus_attn * 1e3, 1)}
-    clocks = sampler.stop() if rank == 0 else None
-    status = max(int(L["status"].item()) for L in layers)
-
     # ---- per-stage split: events between the launches of a step (a separate loop; the events cost a
     # little, so its sum is not the value) ----
     names = [n for n, _ in stages(layers[0])]
@@ -539,6 +513,32 @@ def run_native(args):
     dict(stages(layers[0]))["attention"]()
     launches_attention = _lib.launch_count() - launches_attention
     stage_us["attention_launches"] = launches_attention  # 2: the merge of cut work units ran inside the attention stage
+
+    # ---- sustained phase: the same loop repeated until >= 1 s has elapsed (the board reaches its
+    # power cap and the SM clock settles), clocks sampled throughout ----
+    sustained = None
+    if not args.no_sustained:
+        s_attn, n_sus = [], 0
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        sampler.mark("sustained_begin")
+        w0 = time.perf_counter()
+        s0.record()
+        while True:
+            for i in range(args.steps):
+                step(layers[i % len(layers)], s_attn)
+            n_sus += args.steps
+            torch.cuda.current_stream().synchronize()
+            go = 1.0 if time.perf_counter() - w0 < args.sustained_seconds else 0.0
+            if max_ranks([go])[0] == 0.0 or n_sus >= 100000:  # every rank leaves the loop in the same round
+                break
+        s1.record()
+        barrier()
+        sampler.mark("sustained_end")
+        sus_ms, sus_attn = max_ranks([s0.elapsed_time(s1) / n_sus, statistics.mean(a.elapsed_time(b) for a, b in s_attn[-200:])])
+        sustained = {"steps": n_sus, "step_us": round(sus_ms * 1e3, 1), "attention_us": round(sus_attn * 1e3, 1)}
+    clocks = sampler.stop() if rank == 0 else None
+    status = max(int(L["status"].item()) for L in layers)
 
     # ---- algorithmic work of one attention launch (this rank) ----
     G = hq // hkv
